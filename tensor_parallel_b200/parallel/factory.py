@@ -70,4 +70,12 @@ def tensor_parallel(
         return TensorParallelPreTrainedModel(module, **common)
     from tensor_parallel_b200.parallel.runtime import TensorParallel
 
+    model_config = getattr(module, "config", None)
+    if tensor_parallel_config is None and getattr(model_config, "model_type", None) is not None:
+        # self-contained models (tensor_parallel_b200.models) carry a config with a known model_type
+        from tensor_parallel_b200.parallel.families import PREDEFINED_CONFIGS
+        from tensor_parallel_b200.parallel.runtime import check_device_ids
+
+        if model_config.model_type in PREDEFINED_CONFIGS:
+            common["tensor_parallel_config"] = PREDEFINED_CONFIGS[model_config.model_type](model_config, check_device_ids(device_ids))
     return TensorParallel(module, **common)

@@ -41,6 +41,34 @@ def check_device_ids(device_ids: Optional[Sequence]) -> tuple:
     return tuple(canonicalize_device(d) for d in device_ids)
 
 
+def _is_stateful_cache(obj) -> bool:
+    return hasattr(obj, "update") and hasattr(obj, "get_seq_length") and not isinstance(obj, (torch.Tensor, nn.Module, dict))
+
+
+_MIRRORED_CACHE_CALLS = ("reorder_cache", "batch_select_indices", "batch_repeat_interleave", "crop", "reset")
+
+
+def _attach_cache_siblings(cache, world_size: int, keep_rank: int, devices):
+    import copy
+
+    siblings = [cache if r == keep_rank else copy.deepcopy(cache) for r in range(world_size)]
+    cache.__dict__["_tp_siblings"] = siblings
+    for method_name in _MIRRORED_CACHE_CALLS:
+        original = getattr(cache, method_name, None)
+        if original is None:
+            continue
+
+        def mirrored(*args, __name=method_name, __original=original, **kwargs):
+            for r, sibling in enumerate(siblings):
+                if sibling is cache:
+                    continue
+                local = [a.to(devices[r]) if isinstance(a, torch.Tensor) else a for a in args]
+                getattr(sibling, __name)(*local, **kwargs)
+            return __original(*args, **kwargs)
+
+        cache.__dict__[method_name] = mirrored
+
+
 class _RankWorker(threading.Thread):
     """Long-lived thread bound to one rank; executes closures handed over through a queue."""
 
@@ -261,10 +289,30 @@ class TensorParallel(nn.Module):
         template = (args, kwargs)
         leaves = list(nested_flatten(template))
         per_rank = []
-        for device in self.devices:
-            moved = [leaf.to(device, non_blocking=True) if isinstance(leaf, torch.Tensor) else leaf for leaf in leaves]
+        for rank, device in enumerate(self.devices):
+            moved = []
+            for leaf in leaves:
+                if isinstance(leaf, torch.Tensor):
+                    leaf = leaf.to(device, non_blocking=True)
+                elif _is_stateful_cache(leaf):
+                    leaf = self._cache_for_rank(leaf, rank)
+                moved.append(leaf)
             per_rank.append(nested_pack(moved, template))
         return zip(*per_rank)
+
+    def _cache_for_rank(self, cache, rank: int):
+        """Stateful KV-cache objects (``transformers.Cache``) are updated in place by the model, so
+        every rank needs its own instance: the output rank keeps the caller's object, the other
+        ranks get empty siblings that live as long as the caller's object and mirror its
+        batch-reordering calls (beam search)."""
+        if rank == self.output_device_index:
+            siblings = cache.__dict__.get("_tp_siblings")
+            if siblings is None:
+                _attach_cache_siblings(cache, len(self.devices), self.output_device_index, self.devices)
+            return cache
+        if cache.__dict__.get("_tp_siblings") is None:
+            _attach_cache_siblings(cache, len(self.devices), self.output_device_index, self.devices)
+        return cache.__dict__["_tp_siblings"][rank]
 
     def _materialize(self):
         if self.need_delayed_init:

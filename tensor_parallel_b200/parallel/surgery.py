@@ -185,7 +185,7 @@ def fill_state_(shard: nn.Module, originals: Dict[str, torch.Tensor], config: Co
                 break
         # .clone() so that the shard owns compact storage rather than a view of the full tensor
         holder.data = source.detach().clone().to(holder.device)
-    if unused:
+    if unused and rank == 0:
         logger.warning("state_rules patterns that matched nothing: %s", sorted(p.pattern for p in unused))
     return sliced
 

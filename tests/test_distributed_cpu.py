@@ -1,0 +1,95 @@
+"""One-process-per-rank mode on CPU (gloo, world size 2 and 3): logits, loss and gradients
+against the unsplit model, with ZeRO-3 on, plus the state-dict key layout.  The reference has
+no test for its distributed branch."""
+import os
+import socket
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, case, result_dir):
+    sys.path.insert(0, REPO)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import tensor_parallel_b200 as tp
+        from tensor_parallel_b200.models.llama import LlamaConfig, LlamaForCausalLM
+        from tensor_parallel_b200.models.t5 import T5Config, T5ForConditionalGeneration
+
+        torch.manual_seed(0)
+        if case == "llama":
+            model = LlamaForCausalLM(LlamaConfig(vocab_size=80, hidden_size=32, intermediate_size=86, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2))
+            batch = dict(input_ids=torch.randint(0, 80, (2, 9)))
+            batch["labels"] = batch["input_ids"]
+        elif case == "t5":
+            model = T5ForConditionalGeneration(T5Config(vocab_size=80, d_model=32, d_kv=8, d_ff=48, num_layers=2, num_heads=4, feed_forward_proj="gated-gelu", tie_word_embeddings=False))
+            batch = dict(input_ids=torch.randint(0, 80, (2, 9)), labels=torch.randint(0, 80, (2, 4)))
+        else:  # automatic config: every linear gathers its output (exercises the all-gather adjoint)
+            model = torch.nn.Sequential(torch.nn.Embedding(80, 16), torch.nn.LayerNorm(16), torch.nn.Linear(16, 32), torch.nn.ReLU(), torch.nn.Linear(32, 6))
+            batch = None
+        if batch is not None:
+            ref = model(**batch)
+            ref.loss.backward()
+        else:
+            ids = torch.randint(0, 80, (5, 7))
+            ref_out = model(ids)
+            ref_out.square().sum().backward()
+        ref_grads = {n: p.grad.clone() for n, p in model.named_parameters()}
+        model.zero_grad()
+
+        wrapped = tp.tensor_parallel(model, ["cpu"], sharded=True)  # distributed because a process group exists
+        assert isinstance(wrapped, tp.DistributedTensorParallel)
+        if batch is not None:
+            out = wrapped(**batch)
+            torch.testing.assert_close(out.logits, ref.logits, atol=3e-5, rtol=1e-5)
+            torch.testing.assert_close(out.loss, ref.loss, atol=1e-5, rtol=1e-5)
+            out.loss.backward()
+        else:
+            out = wrapped(ids)
+            torch.testing.assert_close(out, ref_out, atol=1e-5, rtol=1e-5)
+            out.square().sum().backward()
+
+        cfg = wrapped.tensor_parallel_config
+        for shard_name, p in wrapped.module_shards[0].named_parameters():
+            original = shard_name.replace("tp_wrapped_module.", "")
+            for pattern, action in cfg.state_rules.items():
+                if pattern.search(original):
+                    expected = ref_grads[original] if isinstance(action, tp.Scale) else action(ref_grads[original], rank)
+                    torch.testing.assert_close(p.grad, expected, atol=3e-5, rtol=1e-4, msg=f"{shard_name}@{rank}")
+                    break
+        mgr = wrapped.sharding_manager
+        flats = [torch.zeros_like(mgr.flat_shards[0].grad) for _ in range(world)]
+        dist.all_gather(flats, mgr.flat_shards[0].grad)
+        for shard_name, grad in zip(mgr.sharded_param_names, mgr._combine(torch.stack(flats))):
+            torch.testing.assert_close(grad, ref_grads[shard_name.replace("tp_wrapped_module.", "")], atol=3e-5, rtol=1e-4, msg=shard_name)
+
+        keys = list(wrapped.state_dict().keys())
+        assert all(f".{rank}." in k or k.endswith(f".{rank}") for k in keys), keys[:4]
+        wrapped.load_state_dict(wrapped.state_dict())
+        with tp.save_tensor_parallel(wrapped):
+            merged = wrapped.state_dict()
+        want = model.state_dict()
+        assert set(merged) == set(want)
+        for k, v in want.items():
+            torch.testing.assert_close(merged[k], v, msg=k)
+        open(os.path.join(result_dir, f"ok{rank}"), "w").close()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("case,world", [("llama", 2), ("t5", 2), ("auto", 3)])
+def test_distributed_gloo(case, world, tmp_path):
+    mp.spawn(_worker, args=(world, _free_port(), case, str(tmp_path)), nprocs=world, join=True)
+    assert sorted(os.listdir(tmp_path)) == [f"ok{r}" for r in range(world)]
