@@ -1,0 +1,519 @@
+// Attention kernels for a head-sharded KV cache.
+//   tpb_qkv_rope_append : rotary embedding on q / k of new tokens + write k, v into the pre-allocated
+//                         cache [batch, kv_heads, max_seq, head_dim] (position taken from a device scalar,
+//                         so a captured decode step can be replayed for every token)
+//   tpb_attn_decode     : one query token per sequence against the cache; split over the key range
+//                         (flash-decoding) so that small batches still cover all SMs, fp32 online softmax
+//   tpb_attn_prefill    : tiled flash-style attention for many query tokens (causal or not, MHA / GQA / MQA,
+//                         arbitrary q / k / v strides), fp32 online softmax, optional log-sum-exp output
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+#include "tpb_api.h"
+
+namespace tpb {
+
+typedef __nv_bfloat16 bf16;
+
+// ------------------------------------------------------------------------------------------------
+// rope + cache append
+// ------------------------------------------------------------------------------------------------
+__global__ void qkv_rope_append_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v,
+                                       bf16* __restrict__ q_out, bf16* __restrict__ kcache, bf16* __restrict__ vcache,
+                                       const int* __restrict__ base_pos, int batch, int seq, int q_heads, int kv_heads,
+                                       int head_dim, int rotary_dim, float log2_theta, int interleaved, int max_seq,
+                                       long long q_ld, long long k_ld, long long v_ld) {
+  const int half = rotary_dim >> 1;
+  const int pairs = head_dim >> 1;  // work unit = 2 elements
+  const int heads = q_heads + 2 * kv_heads;
+  const long long total = (long long)batch * seq * heads * pairs;
+  const int pos0 = base_pos ? base_pos[0] : 0;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int p = int(i % pairs);
+    const int h = int((i / pairs) % heads);
+    const long long t = i / ((long long)pairs * heads);
+    const int b = int(t / seq), s = int(t % seq);
+    const int pos = pos0 + s;
+    if (pos >= max_seq) continue;
+    if (h >= q_heads + kv_heads) {  // v: plain copy of elements (2p, 2p+1)
+      const int hv = h - q_heads - kv_heads;
+      const bf16* src = v + t * v_ld + (long long)hv * head_dim + 2 * p;
+      bf16* dst = vcache + (((long long)b * kv_heads + hv) * max_seq + pos) * head_dim + 2 * p;
+      *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(src);
+      continue;
+    }
+    const bool is_q = h < q_heads;
+    const int hh = is_q ? h : h - q_heads;
+    const bf16* src = (is_q ? q + t * q_ld : k + t * k_ld) + (long long)hh * head_dim;
+    bf16* dst = is_q ? q_out + (t * q_heads + hh) * head_dim
+                     : kcache + (((long long)b * kv_heads + hh) * max_seq + pos) * head_dim;
+    if (p < half) {
+      const int ia = interleaved ? 2 * p : p;
+      const int ib = interleaved ? 2 * p + 1 : p + half;
+      const float inv_freq = exp2f(-log2_theta * (2.f * float(p) / float(rotary_dim)));
+      float sn, cs;
+      sincosf(float(pos) * inv_freq, &sn, &cs);
+      const float a = __bfloat162float(src[ia]), c = __bfloat162float(src[ib]);
+      dst[ia] = __float2bfloat16(a * cs - c * sn);
+      dst[ib] = __float2bfloat16(c * cs + a * sn);
+    } else {
+      // elements beyond the rotary span: pairs [half, pairs) map to elements rotary_dim + 2*(p-half) (+1)
+      const int e = rotary_dim + 2 * (p - half);
+      dst[e] = src[e];
+      dst[e + 1] = src[e + 1];
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// decode attention
+// ------------------------------------------------------------------------------------------------
+constexpr int DEC_WARPS = 8;
+constexpr int DEC_THREADS = DEC_WARPS * 32;
+
+template <int D, int G>
+__global__ void __launch_bounds__(DEC_THREADS)
+attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
+                   bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
+                   const int* __restrict__ len_ptr, int len_add, int q_heads, int kv_heads, int g_total, int g_offset,
+                   int max_seq, int splits, float scale_log2e) {
+  constexpr int EPL = D / 8;  // elements per lane (8 lanes cooperate on one key)
+  const int bh = blockIdx.x;  // b * kv_heads + kvh
+  const int b = bh / kv_heads, kvh = bh % kv_heads;
+  const int split = blockIdx.y;
+  const int len = (len_ptr ? len_ptr[0] : 0) + len_add;
+  const int chunk = (len + splits - 1) / splits;
+  const int k0 = split * chunk, k1 = min(len, k0 + chunk);
+
+  __shared__ float q_s[G][D];
+  __shared__ float red_o[DEC_WARPS][G][D];
+  __shared__ float red_m[DEC_WARPS][G], red_l[DEC_WARPS][G];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sub = lane >> 3;   // which of the 4 keys of this warp iteration
+  const int part = lane & 7;   // which D/8 slice
+  for (int i = threadIdx.x; i < G * D; i += DEC_THREADS) {
+    const int g = i / D, d = i % D;
+    const int qh = kvh * g_total + g_offset + g;
+    q_s[g][d] = __bfloat162float(q[((long long)b * q_heads + qh) * D + d]) * scale_log2e;
+  }
+  __syncthreads();
+
+  float m[G], l[G], acc[G][EPL];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    m[g] = -INFINITY;
+    l[g] = 0.f;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) acc[g][e] = 0.f;
+  }
+  const bf16* kbase = kcache + (long long)bh * max_seq * D + part * EPL;
+  const bf16* vbase = vcache + (long long)bh * max_seq * D + part * EPL;
+
+  // the trip count is uniform across the warp (the shuffles below need all 32 lanes); lanes whose key
+  // falls beyond the range load nothing and skip the update
+  for (int key_base = k0 + warp * 4; key_base < k1; key_base += DEC_WARPS * 4) {
+    const int key = key_base + sub;
+    const bool valid = key < k1;
+    float kf[EPL], vf[EPL];
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) { kf[e] = 0.f; vf[e] = 0.f; }
+    if (valid) {
+      const uint4* kp = reinterpret_cast<const uint4*>(kbase + (long long)key * D);
+      const uint4* vp = reinterpret_cast<const uint4*>(vbase + (long long)key * D);
+#pragma unroll
+      for (int c = 0; c < EPL / 8; ++c) {
+        const uint4 ku = __ldg(kp + c), vu = __ldg(vp + c);
+        const uint32_t kw[4] = {ku.x, ku.y, ku.z, ku.w}, vw[4] = {vu.x, vu.y, vu.z, vu.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          kf[c * 8 + 2 * j] = __uint_as_float(kw[j] << 16);
+          kf[c * 8 + 2 * j + 1] = __uint_as_float(kw[j] & 0xFFFF0000u);
+          vf[c * 8 + 2 * j] = __uint_as_float(vw[j] << 16);
+          vf[c * 8 + 2 * j + 1] = __uint_as_float(vw[j] & 0xFFFF0000u);
+        }
+      }
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float s = 0.f;
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) s += kf[e] * q_s[g][part * EPL + e];
+      s += __shfl_xor_sync(0xffffffffu, s, 1);
+      s += __shfl_xor_sync(0xffffffffu, s, 2);
+      s += __shfl_xor_sync(0xffffffffu, s, 4);
+      if (valid) {
+        const float m_new = fmaxf(m[g], s);
+        const float corr = exp2f(m[g] - m_new);
+        const float pexp = exp2f(s - m_new);
+        l[g] = l[g] * corr + pexp;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) acc[g][e] = acc[g][e] * corr + pexp * vf[e];
+        m[g] = m_new;
+      }
+    }
+  }
+
+  // merge the 4 key sub-groups of a warp (lanes differing in bits 3,4), then the warps
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+#pragma unroll
+    for (int off = 8; off <= 16; off <<= 1) {
+      const float m_o = __shfl_xor_sync(0xffffffffu, m[g], off);
+      const float l_o = __shfl_xor_sync(0xffffffffu, l[g], off);
+      const float m_new = fmaxf(m[g], m_o);
+      const float c_me = m[g] == -INFINITY ? 0.f : exp2f(m[g] - m_new);
+      const float c_o = m_o == -INFINITY ? 0.f : exp2f(m_o - m_new);
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) {
+        const float a_o = __shfl_xor_sync(0xffffffffu, acc[g][e], off);
+        acc[g][e] = acc[g][e] * c_me + a_o * c_o;
+      }
+      l[g] = l[g] * c_me + l_o * c_o;
+      m[g] = m_new;
+    }
+    if (sub == 0) {
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) red_o[warp][g][part * EPL + e] = acc[g][e];
+      if (part == 0) { red_m[warp][g] = m[g]; red_l[warp][g] = l[g]; }
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < G * D; i += DEC_THREADS) {
+    const int g = i / D, d = i % D;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) mm = fmaxf(mm, red_m[w][g]);
+    float ll = 0.f, oo = 0.f;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) {
+      const float c = red_m[w][g] == -INFINITY ? 0.f : exp2f(red_m[w][g] - mm);
+      ll += red_l[w][g] * c;
+      oo += red_o[w][g][d] * c;
+    }
+    const int qh = kvh * g_total + g_offset + g;
+    const long long row = (long long)b * q_heads + qh;
+    if (splits == 1) {
+      out[row * D + d] = __float2bfloat16(ll > 0.f ? oo / ll : 0.f);
+    } else {
+      part_o[(row * splits + split) * D + d] = oo;
+      if (d == 0) { part_ml[(row * splits + split) * 2] = mm; part_ml[(row * splits + split) * 2 + 1] = ll; }
+    }
+  }
+}
+
+template <int D>
+__global__ void attn_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                           bf16* __restrict__ out, int splits) {
+  const long long row = blockIdx.x;
+  const int d = threadIdx.x;
+  float mm = -INFINITY;
+  for (int s = 0; s < splits; ++s) mm = fmaxf(mm, part_ml[(row * splits + s) * 2]);
+  float ll = 0.f, oo = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float ms = part_ml[(row * splits + s) * 2];
+    const float c = ms == -INFINITY ? 0.f : exp2f(ms - mm);
+    ll += part_ml[(row * splits + s) * 2 + 1] * c;
+    oo += part_o[(row * splits + s) * D + d] * c;
+  }
+  out[row * D + d] = __float2bfloat16(ll > 0.f ? oo / ll : 0.f);
+}
+
+// ------------------------------------------------------------------------------------------------
+// prefill attention (legacy mma.sync tensor path; 64 query rows x 64 keys per step, 4 warps)
+// ------------------------------------------------------------------------------------------------
+constexpr int PF_M = 64, PF_N = 64, PF_THREADS = 128;
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+  const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+  const int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(gmem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
+  const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem) {
+  const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// smem tile [rows][D] bf16, 16-byte chunks XOR-swizzled by (row & 7)
+template <int D>
+__device__ __forceinline__ bf16* tile_ptr(bf16* base, int row, int chunk) {
+  return base + row * D + ((chunk ^ (row & 7)) << 3);
+}
+
+template <int D>
+__device__ __forceinline__ void load_tile(bf16* smem, const bf16* gmem, long long row_stride, int row0, int rows_valid) {
+  constexpr int CH = D / 8;
+  for (int i = threadIdx.x; i < PF_N * CH; i += PF_THREADS) {
+    const int r = i / CH, c = i % CH;
+    const bool ok = row0 + r < rows_valid;
+    const bf16* src = gmem + (long long)(ok ? row0 + r : 0) * row_stride + c * 8;
+    cp_async16(tile_ptr<D>(smem, r, c), src, ok);
+  }
+}
+
+template <int D>
+__global__ void __launch_bounds__(PF_THREADS)
+attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v,
+                    bf16* __restrict__ out, float* __restrict__ lse, int sq, int sk, int q_heads, int kv_heads,
+                    long long q_sb, long long q_ss, long long q_sh, long long k_sb, long long k_ss, long long k_sh,
+                    long long v_sb, long long v_ss, long long v_sh, long long o_sb, long long o_ss, long long o_sh,
+                    int causal, float scale_log2e) {
+  extern __shared__ __align__(128) uint8_t pf_smem[];
+  bf16* q_s = reinterpret_cast<bf16*>(pf_smem);
+  bf16* k_s = q_s + PF_M * D;
+  bf16* v_s = k_s + PF_N * D;
+
+  const int mblk = (gridDim.x - 1 - blockIdx.x);  // heavy (late) causal blocks first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int kvh = h / (q_heads / kv_heads);
+  const int q0 = mblk * PF_M;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t4 = lane & 3;
+  const int shift = sk - sq;  // query i may see keys j <= i + shift when causal
+
+  const bf16* qg = q + b * q_sb + (long long)h * q_sh;
+  const bf16* kg = k + b * k_sb + (long long)kvh * k_sh;
+  const bf16* vg = v + b * v_sb + (long long)kvh * v_sh;
+
+  int kv_end = sk;
+  if (causal) kv_end = min(sk, q0 + PF_M + shift);
+  const int n_iters = kv_end > 0 ? (kv_end + PF_N - 1) / PF_N : 0;
+
+  load_tile<D>(q_s, qg, q_ss, q0, sq);
+  if (n_iters > 0) load_tile<D>(k_s, kg, k_ss, 0, sk);
+  cp_async_commit();
+
+  uint32_t qf[D / 16][4];
+  float o_acc[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o_acc[i][j] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+  for (int it = 0; it < n_iters; ++it) {
+    const int kv0 = it * PF_N;
+    cp_async_wait_all();
+    __syncthreads();  // K(it) (and Q) landed; every warp is done with V(it-1)
+    load_tile<D>(v_s, vg, v_ss, kv0, sk);
+    cp_async_commit();
+    if (it == 0) {
+      const int id = lane >> 3, r = lane & 7;
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks)
+        ldmatrix_x4(qf[ks], tile_ptr<D>(q_s, warp * 16 + (id & 1) * 8 + r, ks * 2 + (id >> 1)));
+    }
+    // S = Q K^T  (16 x 64 per warp)
+    float s_acc[PF_N / 8][4];
+#pragma unroll
+    for (int i = 0; i < PF_N / 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) s_acc[i][j] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+#pragma unroll
+      for (int np = 0; np < PF_N / 16; ++np) {
+        uint32_t kb[4];
+        const int id = lane >> 3, r = lane & 7;
+        ldmatrix_x4(kb, tile_ptr<D>(k_s, np * 16 + (id >> 1) * 8 + r, ks * 2 + (id & 1)));
+        mma_bf16_16816(s_acc[2 * np], qf[ks], kb[0], kb[1]);
+        mma_bf16_16816(s_acc[2 * np + 1], qf[ks], kb[2], kb[3]);
+      }
+    }
+    // mask + online softmax (rows g and g+8 of this warp's 16 rows)
+    const int qi0 = q0 + warp * 16 + g;
+    float m_new[2] = {m_run[0], m_run[1]};
+#pragma unroll
+    for (int nt = 0; nt < PF_N / 8; ++nt) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int key = kv0 + nt * 8 + 2 * t4 + (j & 1);
+        const int qi = qi0 + (j >> 1) * 8;
+        const bool dead = key >= sk || (causal && key > qi + shift);
+        const float sv = dead ? -INFINITY : s_acc[nt][j] * scale_log2e;
+        s_acc[nt][j] = sv;
+        m_new[j >> 1] = fmaxf(m_new[j >> 1], sv);
+      }
+    }
+#pragma unroll
+    for (int r2 = 0; r2 < 2; ++r2) {
+      m_new[r2] = fmaxf(m_new[r2], __shfl_xor_sync(0xffffffffu, m_new[r2], 1));
+      m_new[r2] = fmaxf(m_new[r2], __shfl_xor_sync(0xffffffffu, m_new[r2], 2));
+    }
+    float corr[2], base[2], row_sum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int r2 = 0; r2 < 2; ++r2) {
+      base[r2] = m_new[r2] == -INFINITY ? 0.f : m_new[r2];
+      corr[r2] = m_run[r2] == -INFINITY ? 0.f : exp2f(m_run[r2] - base[r2]);
+      m_run[r2] = m_new[r2];
+    }
+    uint32_t pf[PF_N / 16][4];
+#pragma unroll
+    for (int nt = 0; nt < PF_N / 8; ++nt) {
+      const float p0 = exp2f(s_acc[nt][0] - base[0]), p1 = exp2f(s_acc[nt][1] - base[0]);
+      const float p2 = exp2f(s_acc[nt][2] - base[1]), p3 = exp2f(s_acc[nt][3] - base[1]);
+      row_sum[0] += p0 + p1;
+      row_sum[1] += p2 + p3;
+      __nv_bfloat162 lo = __floats2bfloat162_rn(p0, p1), hi = __floats2bfloat162_rn(p2, p3);
+      pf[nt >> 1][(nt & 1) * 2] = *reinterpret_cast<uint32_t*>(&lo);
+      pf[nt >> 1][(nt & 1) * 2 + 1] = *reinterpret_cast<uint32_t*>(&hi);
+    }
+#pragma unroll
+    for (int r2 = 0; r2 < 2; ++r2) l_run[r2] = l_run[r2] * corr[r2] + row_sum[r2];
+#pragma unroll
+    for (int dt = 0; dt < D / 8; ++dt) {
+      o_acc[dt][0] *= corr[0]; o_acc[dt][1] *= corr[0];
+      o_acc[dt][2] *= corr[1]; o_acc[dt][3] *= corr[1];
+    }
+    cp_async_wait_all();
+    __syncthreads();  // V(it) landed; every warp is done with K(it)
+    if (it + 1 < n_iters) {
+      load_tile<D>(k_s, kg, k_ss, kv0 + PF_N, sk);
+      cp_async_commit();
+    }
+    // O += P V
+#pragma unroll
+    for (int ks = 0; ks < PF_N / 16; ++ks) {
+#pragma unroll
+      for (int dp = 0; dp < D / 16; ++dp) {
+        uint32_t vb[4];
+        const int id = lane >> 3, r = lane & 7;
+        ldmatrix_x4_trans(vb, tile_ptr<D>(v_s, ks * 16 + (id & 1) * 8 + r, dp * 2 + (id >> 1)));
+        mma_bf16_16816(o_acc[2 * dp], pf[ks], vb[0], vb[1]);
+        mma_bf16_16816(o_acc[2 * dp + 1], pf[ks], vb[2], vb[3]);
+      }
+    }
+  }
+  cp_async_wait_all();
+
+  // finalize: row sums live in quads
+#pragma unroll
+  for (int r2 = 0; r2 < 2; ++r2) {
+    l_run[r2] += __shfl_xor_sync(0xffffffffu, l_run[r2], 1);
+    l_run[r2] += __shfl_xor_sync(0xffffffffu, l_run[r2], 2);
+  }
+#pragma unroll
+  for (int r2 = 0; r2 < 2; ++r2) {
+    const int qi = q0 + warp * 16 + g + r2 * 8;
+    if (qi >= sq) continue;
+    const float inv = l_run[r2] > 0.f ? 1.f / l_run[r2] : 0.f;
+    bf16* orow = out + b * o_sb + (long long)qi * o_ss + (long long)h * o_sh;
+#pragma unroll
+    for (int dt = 0; dt < D / 8; ++dt) {
+      __nv_bfloat162 o2 = __floats2bfloat162_rn(o_acc[dt][r2 * 2] * inv, o_acc[dt][r2 * 2 + 1] * inv);
+      *reinterpret_cast<__nv_bfloat162*>(orow + dt * 8 + 2 * t4) = o2;
+    }
+    if (lse && t4 == 0)
+      lse[((long long)b * q_heads + h) * sq + qi] =
+          l_run[r2] > 0.f ? (m_run[r2] * 0.6931471805599453f + logf(l_run[r2])) : -INFINITY;
+  }
+}
+
+}  // namespace tpb
+
+using namespace tpb;
+
+extern "C" int tpb_qkv_rope_append(const void* q, const void* k, const void* v, void* q_out, void* kcache, void* vcache,
+                                   const int* base_pos, int batch, int seq, int q_heads, int kv_heads, int head_dim,
+                                   int rotary_dim, float theta, int interleaved, int max_seq, long long q_ld,
+                                   long long k_ld, long long v_ld, void* stream_) {
+  if (!q || !k || !v || !q_out || !kcache || !vcache || batch <= 0 || seq <= 0) return TPB_ERR_ARG;
+  if ((head_dim & 1) || (rotary_dim & 1) || rotary_dim > head_dim || (q_ld & 1) || (k_ld & 1) || (v_ld & 1)) return TPB_ERR_ALIGN;
+  cudaStream_t s = static_cast<cudaStream_t>(stream_);
+  const long long work = (long long)batch * seq * (q_heads + 2 * kv_heads) * (head_dim / 2);
+  long long grid = (work + 255) / 256;
+  if (grid > 148 * 16) grid = 148 * 16;
+  qkv_rope_append_kernel<<<int(grid), 256, 0, s>>>((const bf16*)q, (const bf16*)k, (const bf16*)v, (bf16*)q_out, (bf16*)kcache,
+                                                   (bf16*)vcache, base_pos, batch, seq, q_heads, kv_heads, head_dim, rotary_dim,
+                                                   log2f(theta), interleaved, max_seq, q_ld, k_ld, v_ld);
+  return cudaGetLastError() == cudaSuccess ? TPB_OK : TPB_ERR_CUDA;
+}
+
+// workspace: part_o fp32 [batch*q_heads*splits*head_dim], part_ml fp32 [batch*q_heads*splits*2]
+extern "C" int tpb_attn_decode(const void* q, const void* kcache, const void* vcache, void* out, float* part_o,
+                               float* part_ml, const int* len_ptr, int len_add, int batch, int q_heads, int kv_heads,
+                               int head_dim, int max_seq, int splits, float scale, void* stream_) {
+  if (!q || !kcache || !vcache || !out || batch <= 0 || splits < 1 || q_heads % kv_heads) return TPB_ERR_ARG;
+  if (splits > 1 && (!part_o || !part_ml)) return TPB_ERR_ARG;
+  if (head_dim != 64 && head_dim != 128) return TPB_ERR_SIZE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream_);
+  const int g_total = q_heads / kv_heads;
+  const float sl2 = scale * 1.4426950408889634f;
+  dim3 grid(batch * kv_heads, splits);
+  int done = 0;
+  while (done < g_total) {
+    const int left = g_total - done;
+    const int gmax = head_dim == 128 ? 4 : 8;
+    int gnow = 1;
+    while (gnow * 2 <= left && gnow * 2 <= gmax) gnow *= 2;
+#define DEC(D, G)                                                                                                      \
+  attn_decode_kernel<D, G><<<grid, DEC_THREADS, 0, s>>>((const bf16*)q, (const bf16*)kcache, (const bf16*)vcache, (bf16*)out, \
+                                                        part_o, part_ml, len_ptr, len_add, q_heads, kv_heads, g_total, done, \
+                                                        max_seq, splits, sl2)
+    if (head_dim == 128) {
+      if (gnow == 1) DEC(128, 1); else if (gnow == 2) DEC(128, 2); else DEC(128, 4);
+    } else {
+      if (gnow == 1) DEC(64, 1); else if (gnow == 2) DEC(64, 2); else if (gnow == 4) DEC(64, 4); else DEC(64, 8);
+    }
+#undef DEC
+    done += gnow;
+  }
+  if (splits > 1) {
+    if (head_dim == 128)
+      attn_decode_combine_kernel<128><<<batch * q_heads, 128, 0, s>>>(part_o, part_ml, (bf16*)out, splits);
+    else
+      attn_decode_combine_kernel<64><<<batch * q_heads, 64, 0, s>>>(part_o, part_ml, (bf16*)out, splits);
+  }
+  return cudaGetLastError() == cudaSuccess ? TPB_OK : TPB_ERR_CUDA;
+}
+
+// Strides are in elements; head_dim must be contiguous (stride 1) in q, k, v and out.
+extern "C" int tpb_attn_prefill(const void* q, const void* k, const void* v, void* out, float* lse, int batch, int sq,
+                                int sk, int q_heads, int kv_heads, int head_dim, long long q_sb, long long q_ss,
+                                long long q_sh, long long k_sb, long long k_ss, long long k_sh, long long v_sb,
+                                long long v_ss, long long v_sh, long long o_sb, long long o_ss, long long o_sh,
+                                int causal, float scale, void* stream_) {
+  if (!q || !k || !v || !out || batch <= 0 || sq <= 0 || sk <= 0 || q_heads % kv_heads) return TPB_ERR_ARG;
+  if (head_dim != 64 && head_dim != 128) return TPB_ERR_SIZE;
+  if ((q_ss & 7) || (q_sh & 7) || (q_sb & 7) || (k_ss & 7) || (k_sh & 7) || (k_sb & 7) || (v_ss & 7) || (v_sh & 7) ||
+      (v_sb & 7) || (o_ss & 1) || (o_sh & 1) || (o_sb & 1) || ((uintptr_t)q & 15) || ((uintptr_t)k & 15) || ((uintptr_t)v & 15))
+    return TPB_ERR_ALIGN;
+  cudaStream_t s = static_cast<cudaStream_t>(stream_);
+  dim3 grid((sq + PF_M - 1) / PF_M, q_heads, batch);
+  const float sl2 = scale * 1.4426950408889634f;
+  const size_t smem = size_t(PF_M + 2 * PF_N) * head_dim * 2;
+  if (head_dim == 128) {
+    static bool cfg[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !cfg[dev]) {
+      cudaFuncSetAttribute(attn_prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+      cfg[dev] = true;
+    }
+    attn_prefill_kernel<128><<<grid, PF_THREADS, smem, s>>>((const bf16*)q, (const bf16*)k, (const bf16*)v, (bf16*)out, lse, sq, sk,
+                                                            q_heads, kv_heads, q_sb, q_ss, q_sh, k_sb, k_ss, k_sh, v_sb, v_ss, v_sh,
+                                                            o_sb, o_ss, o_sh, causal, sl2);
+  } else {
+    attn_prefill_kernel<64><<<grid, PF_THREADS, smem, s>>>((const bf16*)q, (const bf16*)k, (const bf16*)v, (bf16*)out, lse, sq, sk,
+                                                           q_heads, kv_heads, q_sb, q_ss, q_sh, k_sb, k_ss, k_sh, v_sb, v_ss, v_sh,
+                                                           o_sb, o_ss, o_sh, causal, sl2);
+  }
+  return cudaGetLastError() == cudaSuccess ? TPB_OK : TPB_ERR_CUDA;
+}

@@ -1,0 +1,249 @@
+// Symmetric-memory runtime and stand-alone device-side collectives over NVLink peer memory.
+//
+// Memory model: every rank owns one cudaMalloc'ed "symmetric" region of identical layout; all ranks map
+// all regions (cudaDeviceEnablePeerAccess inside one process, CUDA IPC handles across processes), so a
+// kernel can load from and store to any peer's region with ordinary global accesses.
+//
+// Synchronisation: per-(block, rank) 32-bit signal words inside the regions, written by peers with
+// st.release.sys and polled with ld.acquire.sys under a wall-clock bound.  Signal values are epochs that
+// only grow; each block keeps its own epoch in local device memory, so nothing is reset between calls
+// and a captured CUDA graph can be replayed.  Each collective is bracketed by a start barrier ("every
+// peer's block b has entered this call", so inputs written by earlier kernels are complete and last
+// call's outputs have been consumed) and an end barrier ("every peer's block b has finished its
+// pushes / reads"), matched by block index across ranks.
+//
+// Collectives (bf16 or fp32 payload, fp32 accumulation, fixed summation order -> identical bits on all ranks):
+//   all-reduce   one-shot : every rank reads all peers' inputs and reduces everything locally
+//                two-shot : rank r reduces slice r from all peers and pushes it to every rank's output
+//   all-gather            : rank r pushes its slice to offset r of every rank's output
+//   reduce-scatter        : rank r reduces slice r from all peers into its local output
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <string.h>
+
+#include "ptx_sm100.cuh"
+#include "tpb_api.h"
+
+namespace tpb {
+
+constexpr int COMM_MAX_BLOCKS = 64;
+constexpr int COMM_THREADS = 512;
+
+struct CommParams {
+  int world, rank;
+  const void* in[TPB_MAX_WORLD];   // every rank's input buffer
+  void* out[TPB_MAX_WORLD];        // every rank's output buffer
+  uint32_t* sig[TPB_MAX_WORLD];    // every rank's signal array: [2][COMM_MAX_BLOCKS][TPB_MAX_WORLD]
+  uint32_t* epochs;                // local: [COMM_MAX_BLOCKS]
+  uint32_t* status;                // local status word
+  long long n;                     // elements (all-reduce: total; all-gather / reduce-scatter: per-rank slice)
+  uint64_t wait_ns;
+};
+
+__device__ __forceinline__ bool block_barrier(const CommParams& p, int phase, uint32_t epoch) {
+  // thread r < world: tell peer r that block blockIdx.x of this rank reached `phase`, then wait for peer r
+  __shared__ uint32_t ok_s;
+  if (threadIdx.x == 0) ok_s = 1;
+  __syncthreads();
+  if (threadIdx.x < p.world) {
+    const int peer = threadIdx.x;
+    uint32_t* theirs = p.sig[peer] + (size_t(phase) * COMM_MAX_BLOCKS + blockIdx.x) * TPB_MAX_WORLD + p.rank;
+    st_release_sys(theirs, epoch);
+    const uint32_t* mine = p.sig[p.rank] + (size_t(phase) * COMM_MAX_BLOCKS + blockIdx.x) * TPB_MAX_WORLD + peer;
+    if (!wait_flag_ge(mine, epoch, p.wait_ns)) {
+      atomicMax(p.status, STATUS_TIMEOUT_FLAG);
+      ok_s = 0;
+    }
+  }
+  __syncthreads();
+  return ok_s != 0;
+}
+
+template <typename T> struct Pack {};  // 16-byte packets
+template <> struct Pack<__nv_bfloat16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void unpack(const uint4& u, float (&f)[8]) {
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { f[2 * i] = __uint_as_float(w[i] << 16); f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u); }
+  }
+  static __device__ __forceinline__ uint4 pack(const float (&f)[8]) {
+    uint4 u;
+    u.x = pack_bf16x2(f[0], f[1]); u.y = pack_bf16x2(f[2], f[3]); u.z = pack_bf16x2(f[4], f[5]); u.w = pack_bf16x2(f[6], f[7]);
+    return u;
+  }
+};
+template <> struct Pack<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void unpack(const uint4& u, float (&f)[8]) {
+    f[0] = __uint_as_float(u.x); f[1] = __uint_as_float(u.y); f[2] = __uint_as_float(u.z); f[3] = __uint_as_float(u.w);
+  }
+  static __device__ __forceinline__ uint4 pack(const float (&f)[8]) {
+    return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
+  }
+};
+
+__device__ __forceinline__ uint4 ld_peer(const void* base, long long packet) {
+  // volatile-style load that must not be served from a stale L1 line
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(static_cast<const uint4*>(base) + packet)
+               : "memory");
+  return v;
+}
+
+template <typename T>
+__device__ __forceinline__ uint4 reduce_packet(const CommParams& p, long long packet) {
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int r = 0; r < TPB_MAX_WORLD; ++r) {
+    if (r < p.world) {
+      float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      Pack<T>::unpack(ld_peer(p.in[r], packet), f);
+#pragma unroll
+      for (int i = 0; i < Pack<T>::N; ++i) acc[i] += f[i];
+    }
+  }
+  return Pack<T>::pack(acc);
+}
+
+// mode: 0 all-reduce one-shot, 1 all-reduce two-shot, 2 all-gather, 3 reduce-scatter
+template <typename T, int MODE>
+__global__ void __launch_bounds__(COMM_THREADS) collective_kernel(const CommParams p) {
+  const uint32_t epoch = p.epochs[blockIdx.x] + 1;
+  __syncthreads();
+  if (threadIdx.x == 0) p.epochs[blockIdx.x] = epoch;
+  bool ok = block_barrier(p, 0, epoch);
+  constexpr int N = Pack<T>::N;
+  const long long tid = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  if (ok) {
+    if (MODE == 0) {
+      const long long packets = p.n / N;
+      for (long long i = tid; i < packets; i += stride) static_cast<uint4*>(p.out[p.rank])[i] = reduce_packet<T>(p, i);
+    } else if (MODE == 1) {
+      const long long packets = p.n / N;
+      const long long per = (packets + p.world - 1) / p.world;
+      const long long lo = per * p.rank, hi = min(packets, lo + per);
+      for (long long i = lo + tid; i < hi; i += stride) {
+        const uint4 v = reduce_packet<T>(p, i);
+#pragma unroll
+        for (int r = 0; r < TPB_MAX_WORLD; ++r)
+          if (r < p.world) static_cast<uint4*>(p.out[r])[i] = v;
+      }
+    } else if (MODE == 2) {
+      const long long packets = p.n / N;
+      for (long long i = tid; i < packets; i += stride) {
+        const uint4 v = static_cast<const uint4*>(p.in[p.rank])[i];
+#pragma unroll
+        for (int r = 0; r < TPB_MAX_WORLD; ++r)
+          if (r < p.world) static_cast<uint4*>(p.out[r])[p.rank * packets + i] = v;
+      }
+    } else {
+      const long long packets = p.n / N;
+      for (long long i = tid; i < packets; i += stride)
+        static_cast<uint4*>(p.out[p.rank])[i] = reduce_packet<T>(p, p.rank * packets + i);
+    }
+    __threadfence_system();
+  }
+  block_barrier(p, 1, epoch);
+}
+
+__global__ void wait_flag_test_kernel(const uint32_t* flag, uint32_t target, uint32_t* status, uint64_t wait_ns) {
+  if (!wait_flag_ge(flag, target, wait_ns)) atomicMax(status, STATUS_TIMEOUT_FLAG);
+}
+
+}  // namespace tpb
+
+using namespace tpb;
+
+extern "C" int tpb_device_count(int* n) { return cudaGetDeviceCount(n) == cudaSuccess ? TPB_OK : TPB_ERR_CUDA; }
+
+extern "C" int tpb_malloc(void** ptr, size_t bytes) {
+  if (!ptr) return TPB_ERR_ARG;
+  if (cudaMalloc(ptr, bytes) != cudaSuccess) return TPB_ERR_CUDA;
+  return cudaMemset(*ptr, 0, bytes) == cudaSuccess ? TPB_OK : TPB_ERR_CUDA;
+}
+extern "C" int tpb_free(void* ptr) { return cudaFree(ptr) == cudaSuccess ? TPB_OK : TPB_ERR_CUDA; }
+
+extern "C" int tpb_enable_peer_access(int peer_device) {
+  int dev = 0, can = 0;
+  cudaGetDevice(&dev);
+  if (dev == peer_device) return TPB_OK;
+  if (cudaDeviceCanAccessPeer(&can, dev, peer_device) != cudaSuccess || !can) return TPB_ERR_CUDA;
+  cudaError_t e = cudaDeviceEnablePeerAccess(peer_device, 0);
+  if (e == cudaErrorPeerAccessAlreadyEnabled) { cudaGetLastError(); return TPB_OK; }
+  return e == cudaSuccess ? TPB_OK : TPB_ERR_CUDA;
+}
+
+extern "C" int tpb_ipc_get_handle(void* dev_ptr, void* handle64) {
+  cudaIpcMemHandle_t h;
+  if (cudaIpcGetMemHandle(&h, dev_ptr) != cudaSuccess) return TPB_ERR_CUDA;
+  static_assert(sizeof(h) == 64, "IPC handle size");
+  memcpy(handle64, &h, 64);
+  return TPB_OK;
+}
+extern "C" int tpb_ipc_open_handle(const void* handle64, void** out_ptr) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  return cudaIpcOpenMemHandle(out_ptr, h, cudaIpcMemLazyEnablePeerAccess) == cudaSuccess ? TPB_OK : TPB_ERR_CUDA;
+}
+extern "C" int tpb_ipc_close_handle(void* ptr) { return cudaIpcCloseMemHandle(ptr) == cudaSuccess ? TPB_OK : TPB_ERR_CUDA; }
+
+extern "C" int tpb_last_cuda_error(char* buf, int len) {
+  const char* s = cudaGetErrorString(cudaGetLastError());
+  strncpy(buf, s, len - 1);
+  buf[len - 1] = 0;
+  return TPB_OK;
+}
+
+// kind: 0 all-reduce (algorithm chosen by size), 2 all-gather, 3 reduce-scatter.  dtype: 0 bf16, 1 fp32.
+// `n` = total elements for all-reduce, per-rank slice elements otherwise.  Buffers must be 16-byte aligned
+// and n * sizeof(T) a multiple of 16.
+extern "C" int tpb_collective(int kind, int dtype, int world, int rank, void* const* in, void* const* out,
+                              void* const* sig, void* epochs, void* status, long long n, int force_algo,
+                              double wait_seconds, void* stream_) {
+  if (world < 1 || world > TPB_MAX_WORLD || rank < 0 || rank >= world || !in || !out || !sig || !epochs || !status || n <= 0)
+    return TPB_ERR_ARG;
+  const int per_packet = dtype == 0 ? 8 : 4;
+  if (n % per_packet) return TPB_ERR_ALIGN;
+  CommParams p;
+  memset(&p, 0, sizeof(p));
+  p.world = world;
+  p.rank = rank;
+  for (int r = 0; r < world; ++r) { p.in[r] = in[r]; p.out[r] = out[r]; p.sig[r] = static_cast<uint32_t*>(sig[r]); }
+  p.epochs = static_cast<uint32_t*>(epochs);
+  p.status = static_cast<uint32_t*>(status);
+  p.n = n;
+  p.wait_ns = wait_seconds > 0 ? uint64_t(wait_seconds * 1e9) : TPB_WAIT_LIMIT_NS;
+  cudaStream_t s = static_cast<cudaStream_t>(stream_);
+  const long long bytes = n * (dtype == 0 ? 2 : 4);
+  int mode = kind;
+  if (kind == 0) mode = force_algo >= 0 ? force_algo : (bytes <= 512 * 1024 ? 0 : 1);
+  const long long packets = n / per_packet;
+  long long work = mode == 1 ? (packets + world - 1) / world : packets;
+  int blocks = int((work + COMM_THREADS - 1) / COMM_THREADS);
+  if (blocks < 1) blocks = 1;
+  if (blocks > COMM_MAX_BLOCKS) blocks = COMM_MAX_BLOCKS;
+#define RUN(T, M) collective_kernel<T, M><<<blocks, COMM_THREADS, 0, s>>>(p)
+  if (dtype == 0) {
+    switch (mode) { case 0: RUN(__nv_bfloat16, 0); break; case 1: RUN(__nv_bfloat16, 1); break;
+                    case 2: RUN(__nv_bfloat16, 2); break; case 3: RUN(__nv_bfloat16, 3); break; default: return TPB_ERR_ARG; }
+  } else {
+    switch (mode) { case 0: RUN(float, 0); break; case 1: RUN(float, 1); break;
+                    case 2: RUN(float, 2); break; case 3: RUN(float, 3); break; default: return TPB_ERR_ARG; }
+  }
+#undef RUN
+  return cudaGetLastError() == cudaSuccess ? TPB_OK : TPB_ERR_CUDA;
+}
+
+// Launches a one-thread kernel that waits (bounded by wait_seconds) for *flag >= target and records a
+// timeout in *status.  Used to exercise the give-up path: the kernel always terminates.
+extern "C" int tpb_wait_flag_test(const void* flag, unsigned target, void* status, double wait_seconds, void* stream_) {
+  if (!flag || !status) return TPB_ERR_ARG;
+  wait_flag_test_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream_)>>>(static_cast<const uint32_t*>(flag), target,
+                                                                        static_cast<uint32_t*>(status), uint64_t(wait_seconds * 1e9));
+  return cudaGetLastError() == cudaSuccess ? TPB_OK : TPB_ERR_CUDA;
+}

@@ -1,0 +1,597 @@
+// bf16 GEMM for sm_100a on tcgen05 tensor cores, optionally fused with a split-K reduction and a
+// cross-GPU all-reduce over peer memory.
+//
+//   acc[m, n] = sum_k A[m, k] * B[n, k]            (both operands K-major, i.e. "x @ W^T")
+//
+// A rows fill the 128 TMEM lanes of a tile (UMMA M = 128), B rows fill BN accumulator columns.
+// The host decides which logical operand plays A: for a large token count the activations are A
+// ("normal"), for decode-sized token counts the weight matrix is A and the few tokens are B
+// ("swapped"), so the tensor core still sees full 128-row tiles and weights stream through TMA once.
+// In both cases results are stored as out[token, feature].
+//
+// Structure of one CTA (192 threads), persistent over work items (m_tile, n_tile, k_split):
+//   warp 0   : TMA producer  - cp.async.bulk.tensor loads of A/B k-blocks into a smem ring (no multicast)
+//   warp 1   : MMA issuer    - one elected lane issues tcgen05.mma (K = 16 per instruction) into TMEM;
+//                              tcgen05.commit releases smem stages and publishes finished accumulators
+//   warps 2-5: epilogue      - tcgen05.ld the accumulator (two TMEM buffers, so the next tile's MMAs
+//                              overlap this tile's epilogue), then either
+//                                (direct)  add bias / residual, convert to bf16, store; or
+//                                (reduce)  store the fp32 partial tile into slot [rank * k_splits + split]
+//                                          of EVERY rank's workspace with plain peer stores, then bump
+//                                          that tile's arrival counter on every rank (release, system scope).
+//   Reduce mode, second phase (all warps): for each output tile this CTA owns, wait (bounded) until
+//   world * k_splits partials have arrived, sum them in a fixed order (bit-identical on all ranks),
+//   add bias / residual and store bf16.  All of a CTA's pushes precede its first wait, and the grid is
+//   never larger than what is co-resident, so ranks cannot deadlock each other.
+//
+// Every wait is bounded; on expiry the CTA records a status code in params.status and drains.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "ptx_sm100.cuh"
+#include "tpb_api.h"
+
+namespace tpb {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int MAX_STAGES = 12;
+constexpr int NUM_THREADS = 192;
+constexpr int EPI_THREADS = 128;
+constexpr int MAX_WORLD = 8;
+
+struct GemmParams {
+  int m_extent;   // rows of A (lanes side)
+  int n_extent;   // rows of B (columns side)
+  int k_extent;
+  int m_tiles, n_tiles, k_blocks, k_splits, kb_per_split;
+  int stages;
+  int swapped;        // 0: A rows are tokens, B rows are features; 1: A rows are features, B rows are tokens
+  int ld_out;         // elements between consecutive tokens in out / residual / partial slots
+  __nv_bfloat16* out;
+  const __nv_bfloat16* bias;      // [features] or null
+  const __nv_bfloat16* residual;  // [tokens, ld_out] or null
+  int act;                        // 0 none, 1 relu, 2 gelu(erf), 3 gelu(tanh), 4 silu  (direct epilogue only)
+  // reduce mode (k_splits > 1 or world > 1)
+  int reduce;
+  int world, rank;
+  float* slots[MAX_WORLD];        // per destination rank: [world * k_splits][tokens_pad][ld_out] fp32
+  uint32_t* arrivals[MAX_WORLD];  // per destination rank: [tiles] arrival counters
+  uint32_t* expected;             // local: [tiles] counter value reached after the previous call
+  size_t slot_stride;             // elements between consecutive slots
+  uint32_t* status;               // local status word (0 = ok)
+};
+
+__device__ __forceinline__ float apply_act(float x, int act) {
+  switch (act) {
+    case 1: return fmaxf(x, 0.f);
+    case 2: return 0.5f * x * (1.f + erff(x * 0.70710678118654752f));
+    case 3: {
+      float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+      return 0.5f * x * (1.f + tanhf(u));
+    }
+    case 4: return x / (1.f + __expf(-x));
+    default: return x;
+  }
+}
+
+template <int BN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                         const GemmParams p) {
+  constexpr uint32_t A_BYTES = BM * BK * 2;
+  constexpr uint32_t B_BYTES = BN * BK * 2;
+  constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr uint32_t TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;  // power of two for BN in {16,...,256}
+  constexpr uint32_t IDESC = make_idesc_bf16(BM, BN);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + size_t(p.stages) * STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + MAX_STAGES;
+  uint64_t* acc_full = empty_bar + MAX_STAGES;   // [2]
+  uint64_t* acc_empty = acc_full + 2;            // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+  volatile uint32_t* epi_ok = tmem_slot + 2;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], EPI_THREADS / 32);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tiles = p.m_tiles * p.n_tiles;
+  const int work_items = tiles * p.k_splits;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (elect_one()) {
+      uint32_t it = 0;
+      for (int w = blockIdx.x; w < work_items && !*abort_flag; w += gridDim.x) {
+        const int split = w / tiles;
+        const int tile = w - split * tiles;
+        const int mt = tile % p.m_tiles;
+        const int nt = tile / p.m_tiles;
+        const int kb0 = split * p.kb_per_split;
+        const int kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % p.stages;
+          const uint32_t ph = (it / p.stages) & 1;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1)) {
+            atomicMax(p.status, STATUS_TIMEOUT_MBAR);
+            *abort_flag = 1;
+            break;
+          }
+          uint8_t* a_dst = smem + size_t(s) * STAGE_BYTES;
+          mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+          tma_load_2d(a_dst, &tmap_a, &full_bar[s], kb * BK, mt * BM);
+          tma_load_2d(a_dst + A_BYTES, &tmap_b, &full_bar[s], kb * BK, nt * BN);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (elect_one()) {
+      uint32_t it = 0;
+      uint32_t local = 0;
+      for (int w = blockIdx.x; w < work_items && !*abort_flag; w += gridDim.x, ++local) {
+        const int split = w / tiles;
+        const int kb0 = split * p.kb_per_split;
+        const int kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
+        const int acc = local & 1;
+        const uint32_t acc_ph = (local >> 1) & 1;
+        if (!mbar_wait(&acc_empty[acc], acc_ph ^ 1)) {
+          atomicMax(p.status, STATUS_TIMEOUT_MBAR);
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % p.stages;
+          const uint32_t ph = (it / p.stages) & 1;
+          if (!mbar_wait(&full_bar[s], ph)) {
+            atomicMax(p.status, STATUS_TIMEOUT_MBAR);
+            *abort_flag = 1;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + size_t(s) * STAGE_BYTES);
+          const uint32_t b_addr = a_addr + A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            const uint64_t adesc = make_desc_kmajor_sw128(a_addr + kk * UMMA_K * 2);
+            const uint64_t bdesc = make_desc_kmajor_sw128(b_addr + kk * UMMA_K * 2);
+            umma_bf16(d_tmem, adesc, bdesc, IDESC, (kb > kb0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[s]);  // frees the smem stage when these MMAs retire
+        }
+        umma_commit(&acc_full[acc]);  // accumulator complete
+      }
+    }
+  } else {
+    // ---------------- epilogue warps ----------------
+    const int quarter = warp & 3;  // TMEM lane quarter this warp may access
+    const int row = quarter * 32 + lane;
+    uint32_t local = 0;
+    for (int w = blockIdx.x; w < work_items; w += gridDim.x, ++local) {
+      const int split = w / tiles;
+      const int tile = w - split * tiles;
+      const int mt = tile % p.m_tiles;
+      const int nt = tile / p.m_tiles;
+      const int acc = local & 1;
+      const uint32_t acc_ph = (local >> 1) & 1;
+      // one thread waits, the group agrees on the outcome (so that nobody is left at a named barrier)
+      if (threadIdx.x == 64) {
+        bool ok = !*abort_flag && mbar_wait(&acc_full[acc], acc_ph);
+        if (!ok) {
+          atomicMax(p.status, STATUS_TIMEOUT_MBAR);
+          *abort_flag = 1;
+        }
+        *epi_ok = ok ? 1u : 0u;
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
+      if (!*epi_ok) break;
+      tc_fence_after();
+      const int m = mt * BM + row;
+      const bool m_ok = m < p.m_extent;
+      const uint32_t t_lane = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
+
+      float* my_slots[MAX_WORLD];
+      if (p.reduce) {
+#pragma unroll
+        for (int d = 0; d < MAX_WORLD; ++d)
+          my_slots[d] = d < p.world ? p.slots[d] + size_t(p.rank * p.k_splits + split) * p.slot_stride : nullptr;
+      }
+
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        uint32_t r[16];
+        tmem_ld_x16(t_lane + c0, r);
+        tmem_ld_wait();
+        const int n0 = nt * BN + c0;
+        if (!p.reduce) {
+          if (!p.swapped) {
+            // thread = token m, registers = 16 consecutive features
+            if (m_ok && n0 < p.n_extent) {
+              float v[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+              const size_t base = size_t(m) * p.ld_out + n0;
+              if (n0 + 16 <= p.n_extent && (p.ld_out & 7) == 0) {
+                if (p.bias) {
+                  const uint4* bp = reinterpret_cast<const uint4*>(p.bias + n0);
+                  uint4 b0 = bp[0], b1 = bp[1];
+                  const uint32_t bw[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) {
+                    v[2 * j] += bf16_bits_to_float(bw[j] & 0xFFFF);
+                    v[2 * j + 1] += bf16_bits_to_float(bw[j] >> 16);
+                  }
+                }
+                if (p.act) {
+#pragma unroll
+                  for (int j = 0; j < 16; ++j) v[j] = apply_act(v[j], p.act);
+                }
+                if (p.residual) {
+                  const uint4* rp = reinterpret_cast<const uint4*>(p.residual + base);
+                  uint4 r0 = rp[0], r1 = rp[1];
+                  const uint32_t rw[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) {
+                    v[2 * j] += bf16_bits_to_float(rw[j] & 0xFFFF);
+                    v[2 * j + 1] += bf16_bits_to_float(rw[j] >> 16);
+                  }
+                }
+                uint4 o0, o1;
+                o0.x = pack_bf16x2(v[0], v[1]);   o0.y = pack_bf16x2(v[2], v[3]);
+                o0.z = pack_bf16x2(v[4], v[5]);   o0.w = pack_bf16x2(v[6], v[7]);
+                o1.x = pack_bf16x2(v[8], v[9]);   o1.y = pack_bf16x2(v[10], v[11]);
+                o1.z = pack_bf16x2(v[12], v[13]); o1.w = pack_bf16x2(v[14], v[15]);
+                uint4* op = reinterpret_cast<uint4*>(p.out + base);
+                op[0] = o0;
+                op[1] = o1;
+              } else {
+                for (int j = 0; j < 16 && n0 + j < p.n_extent; ++j) {
+                  float x = v[j] + (p.bias ? __bfloat162float(p.bias[n0 + j]) : 0.f);
+                  x = apply_act(x, p.act);
+                  if (p.residual) x += __bfloat162float(p.residual[base + j]);
+                  p.out[base + j] = __float2bfloat16(x);
+                }
+              }
+            }
+          } else {
+            // thread = feature m, registers = 16 consecutive tokens
+            if (m_ok) {
+              const float b = p.bias ? __bfloat162float(p.bias[m]) : 0.f;
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const int t = n0 + j;
+                if (t < p.n_extent) {
+                  float x = apply_act(__uint_as_float(r[j]) + b, p.act);
+                  const size_t idx = size_t(t) * p.ld_out + m;
+                  if (p.residual) x += __bfloat162float(p.residual[idx]);
+                  p.out[idx] = __float2bfloat16(x);
+                }
+              }
+            }
+          }
+        } else {
+          // push the fp32 partial to every rank's slot
+          if (!p.swapped) {
+            if (m_ok && n0 < p.n_extent) {
+              const size_t base = size_t(m) * p.ld_out + n0;
+              if (n0 + 16 <= p.n_extent && (p.ld_out & 3) == 0) {
+#pragma unroll
+                for (int d = 0; d < MAX_WORLD; ++d) {
+                  if (d < p.world) {
+                    uint4* dst = reinterpret_cast<uint4*>(my_slots[d] + base);
+                    dst[0] = make_uint4(r[0], r[1], r[2], r[3]);
+                    dst[1] = make_uint4(r[4], r[5], r[6], r[7]);
+                    dst[2] = make_uint4(r[8], r[9], r[10], r[11]);
+                    dst[3] = make_uint4(r[12], r[13], r[14], r[15]);
+                  }
+                }
+              } else {
+                for (int d = 0; d < p.world; ++d)
+                  for (int j = 0; j < 16 && n0 + j < p.n_extent; ++j) my_slots[d][base + j] = __uint_as_float(r[j]);
+              }
+            }
+          } else {
+            if (m_ok) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const int t = n0 + j;
+                if (t < p.n_extent) {
+                  const size_t idx = size_t(t) * p.ld_out + m;
+#pragma unroll
+                  for (int d = 0; d < MAX_WORLD; ++d)
+                    if (d < p.world) my_slots[d][idx] = __uint_as_float(r[j]);
+                }
+              }
+            }
+          }
+        }
+      }
+      // accumulator buffer may be overwritten by the MMA warp from here on
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+
+      if (p.reduce) {
+        // make this tile's partial visible system-wide, then count one arrival on every rank
+        __threadfence_system();
+        asm volatile("bar.sync 2, %0;" ::"n"(EPI_THREADS) : "memory");
+        if (threadIdx.x == 64) {
+          for (int d = 0; d < p.world; ++d) red_add_release_sys(p.arrivals[d] + tile, 1u);
+        }
+      }
+    }
+  }
+
+  // ---------------- reduce phase ----------------
+  __syncthreads();
+  if (p.reduce) {
+    const uint32_t contributions = uint32_t(p.world * p.k_splits);
+    const int n_slots = p.world * p.k_splits;
+    const float* base_slot = p.slots[p.rank];
+    // token / feature extents of one tile in out[token, feature] coordinates
+    const int tok_tile = p.swapped ? BN : BM;
+    const int feat_tile = p.swapped ? BM : BN;
+    const int tokens = p.swapped ? p.n_extent : p.m_extent;
+    const int features = p.swapped ? p.m_extent : p.n_extent;
+    __shared__ uint32_t wait_ok;
+    for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+      const int mt = tile % p.m_tiles;
+      const int nt = tile / p.m_tiles;
+      if (threadIdx.x == 0) {
+        const uint32_t target = p.expected[tile] + contributions;
+        bool ok = !*abort_flag && wait_flag_ge(p.arrivals[p.rank] + tile, target);
+        if (!ok) atomicMax(p.status, STATUS_TIMEOUT_FLAG);
+        p.expected[tile] = target;
+        wait_ok = ok ? 1u : 0u;
+      }
+      __syncthreads();
+      if (wait_ok) {
+        const int tok0 = (p.swapped ? nt : mt) * tok_tile;
+        const int feat0 = (p.swapped ? mt : nt) * feat_tile;
+        const int tok_n = min(tok_tile, tokens - tok0);
+        const int feat_n = min(feat_tile, features - feat0);
+        const int feat_vec = (feat_n + 3) >> 2;
+        const bool vec_ok = (p.ld_out & 3) == 0 && (feat_n & 3) == 0;
+        for (int e = threadIdx.x; e < tok_n * feat_vec; e += NUM_THREADS) {
+          const int t = tok0 + e / feat_vec;
+          const int f = feat0 + (e % feat_vec) * 4;
+          const size_t idx = size_t(t) * p.ld_out + f;
+          float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (vec_ok) {
+            for (int k = 0; k < n_slots; ++k) {
+              const float4 v = __ldcg(reinterpret_cast<const float4*>(base_slot + size_t(k) * p.slot_stride + idx));
+              s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+            }
+          } else {
+            float* sp = &s.x;
+            for (int k = 0; k < n_slots; ++k)
+              for (int j = 0; j < 4 && f + j < feat0 + feat_n; ++j) sp[j] += __ldcg(base_slot + size_t(k) * p.slot_stride + idx + j);
+          }
+          float o[4] = {s.x, s.y, s.z, s.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (f + j < feat0 + feat_n) {
+              float x = o[j] + (p.bias ? __bfloat162float(p.bias[f + j]) : 0.f);
+              x = apply_act(x, p.act);
+              if (p.residual) x += __bfloat162float(p.residual[idx + j]);
+              p.out[idx + j] = __float2bfloat16(x);
+            }
+          }
+        }
+      }
+      __syncthreads();
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// 2-D bf16 row-major [rows, cols] (cols contiguous, row pitch ld elements), box = [box_rows, 64 cols], 128B swizzle.
+static int make_tmap_2d(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return TPB_ERR_DRIVER;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {BK, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? TPB_OK : TPB_ERR_TMAP;
+}
+
+template <int BN>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, int grid, cudaStream_t stream) {
+  constexpr size_t stage_bytes = size_t(BM * BK * 2 + BN * BK * 2);
+  int stages = int((200 * 1024) / stage_bytes);
+  if (stages > MAX_STAGES) stages = MAX_STAGES;
+  if (stages > p.kb_per_split + 1 && p.m_tiles * p.n_tiles * p.k_splits <= grid) stages = max(2, p.kb_per_split + 1);
+  p.stages = stages;
+  size_t smem = stages * stage_bytes + 1024 /*align*/ + (2 * MAX_STAGES + 4) * 8 + 16;
+  // opt in to large dynamic shared memory (per device); static + dynamic must stay within 227 KB
+  static size_t configured[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && configured[dev] < smem) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    if (e != cudaSuccess) return TPB_ERR_CUDA;
+    configured[dev] = smem;
+  }
+  gemm_bf16_tcgen05_kernel<BN><<<grid, NUM_THREADS, smem, stream>>>(ta, tb, p);
+  return cudaGetLastError() == cudaSuccess ? TPB_OK : TPB_ERR_CUDA;
+}
+
+static int g_sm_count[16] = {0};
+static int sm_count() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 16) return 148;
+  if (!g_sm_count[dev]) cudaDeviceGetAttribute(&g_sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
+  return g_sm_count[dev] ? g_sm_count[dev] : 148;
+}
+
+}  // namespace tpb
+
+using namespace tpb;
+
+// Plan of a linear layer out[tokens, features] = x[tokens, K] @ w[features, K]^T.
+extern "C" int tpb_gemm_plan(int tokens, int features, int k, int world, int force_splits, tpb_gemm_plan_t* plan) {
+  if (!plan || tokens <= 0 || features <= 0 || k <= 0) return TPB_ERR_ARG;
+  const int sms = sm_count();
+  plan->swapped = tokens <= 64 ? 1 : 0;
+  int bn;
+  if (plan->swapped) {
+    bn = tokens <= 16 ? 16 : (tokens <= 32 ? 32 : 64);
+    plan->m_tiles = (features + BM - 1) / BM;
+    plan->n_tiles = (tokens + bn - 1) / bn;
+  } else {
+    bn = features >= 256 ? 256 : (features > 64 ? 128 : 64);
+    // prefer 128-wide tiles when 256-wide ones would leave most SMs idle
+    if (bn == 256 && ((tokens + BM - 1) / BM) * ((features + 255) / 256) < sms) bn = 128;
+    plan->m_tiles = (tokens + BM - 1) / BM;
+    plan->n_tiles = (features + bn - 1) / bn;
+  }
+  plan->bn = bn;
+  plan->k_blocks = (k + BK - 1) / BK;
+  int splits = 1;
+  const int tiles = plan->m_tiles * plan->n_tiles;
+  if (force_splits > 0) {
+    splits = force_splits;
+  } else if (tiles < sms && plan->k_blocks >= 8) {
+    splits = sms / tiles;
+    const int max_by_k = plan->k_blocks / 4;  // at least 4 k-blocks per split
+    if (splits > max_by_k) splits = max_by_k;
+    if (splits > 16) splits = 16;
+    if (splits < 1) splits = 1;
+  }
+  int per = (plan->k_blocks + splits - 1) / splits;
+  splits = (plan->k_blocks + per - 1) / per;  // no empty split
+  plan->k_splits = splits;
+  plan->kb_per_split = per;
+  plan->reduce = (splits > 1 || world > 1) ? 1 : 0;
+  const int work = tiles * splits;
+  plan->grid = work < sms ? work : sms;
+  plan->tokens_pad = plan->swapped ? plan->n_tiles * bn : plan->m_tiles * BM;
+  plan->slot_elems = size_t(tokens) * size_t(features);
+  plan->tiles = tiles;
+  return TPB_OK;
+}
+
+extern "C" int tpb_gemm_bf16(const void* x, const void* w, void* out, const void* bias, const void* residual, int tokens,
+                             int features, int k, int ldx, int ldw, int ld_out, int act, const tpb_gemm_plan_t* plan,
+                             const tpb_reduce_ctx_t* rc, void* stream_) {
+  if (!x || !w || !out || !plan) return TPB_ERR_ARG;
+  if ((ldx & 7) || (ldw & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return TPB_ERR_ALIGN;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.swapped = plan->swapped;
+  p.m_extent = plan->swapped ? features : tokens;
+  p.n_extent = plan->swapped ? tokens : features;
+  p.k_extent = k;
+  p.m_tiles = plan->m_tiles;
+  p.n_tiles = plan->n_tiles;
+  p.k_blocks = plan->k_blocks;
+  p.k_splits = plan->k_splits;
+  p.kb_per_split = plan->kb_per_split;
+  p.ld_out = ld_out;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.residual = static_cast<const __nv_bfloat16*>(residual);
+  p.act = act;
+  p.reduce = plan->reduce;
+  p.world = 1;
+  p.rank = 0;
+  if (plan->reduce) {
+    if (!rc || rc->world < 1 || rc->world > MAX_WORLD) return TPB_ERR_ARG;
+    if (size_t(tokens) * size_t(ld_out) > rc->slot_stride) return TPB_ERR_WORKSPACE;
+    if (size_t(rc->world) * plan->k_splits > size_t(rc->max_slots) || plan->tiles > rc->max_tiles) return TPB_ERR_WORKSPACE;
+    p.world = rc->world;
+    p.rank = rc->rank;
+    for (int d = 0; d < rc->world; ++d) {
+      p.slots[d] = static_cast<float*>(rc->slots[d]);
+      p.arrivals[d] = static_cast<uint32_t*>(rc->arrivals[d]);
+    }
+    p.expected = static_cast<uint32_t*>(rc->expected);
+    p.slot_stride = rc->slot_stride;
+    p.status = static_cast<uint32_t*>(rc->status);
+  } else {
+    if (!rc || !rc->status) return TPB_ERR_ARG;
+    p.status = static_cast<uint32_t*>(rc->status);
+  }
+
+  const void* a_ptr = plan->swapped ? w : x;
+  const void* b_ptr = plan->swapped ? x : w;
+  const int a_rows = p.m_extent, b_rows = p.n_extent;
+  const int lda = plan->swapped ? ldw : ldx, ldb = plan->swapped ? ldx : ldw;
+  CUtensorMap ta, tb;
+  int rcode = make_tmap_2d(&ta, a_ptr, a_rows, k, lda, BM);
+  if (rcode != TPB_OK) return rcode;
+  rcode = make_tmap_2d(&tb, b_ptr, b_rows, k, ldb, plan->bn);
+  if (rcode != TPB_OK) return rcode;
+
+  switch (plan->bn) {
+    case 16: return launch_gemm<16>(ta, tb, p, plan->grid, stream);
+    case 32: return launch_gemm<32>(ta, tb, p, plan->grid, stream);
+    case 64: return launch_gemm<64>(ta, tb, p, plan->grid, stream);
+    case 128: return launch_gemm<128>(ta, tb, p, plan->grid, stream);
+    case 256: return launch_gemm<256>(ta, tb, p, plan->grid, stream);
+    default: return TPB_ERR_ARG;
+  }
+}

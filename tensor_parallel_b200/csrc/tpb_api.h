@@ -1,0 +1,56 @@
+// C ABI of libtpb200: every entry point is extern "C", takes raw device pointers plus a CUDA stream
+// handle, launches asynchronously on that stream and returns one of the TPB_* codes below.
+#pragma once
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  TPB_OK = 0,
+  TPB_ERR_ARG = 1,        // null pointer / non-positive size / unsupported value
+  TPB_ERR_ALIGN = 2,      // pointer or leading dimension violates an alignment rule (TMA needs 16 bytes)
+  TPB_ERR_CUDA = 3,       // a CUDA runtime call failed (see cudaGetLastError)
+  TPB_ERR_DRIVER = 4,     // a driver entry point is unavailable
+  TPB_ERR_TMAP = 5,       // cuTensorMapEncodeTiled rejected the descriptor
+  TPB_ERR_WORKSPACE = 6,  // reduction workspace too small for this shape
+  TPB_ERR_SIZE = 7,       // size beyond a compiled-in maximum
+};
+
+#define TPB_MAX_WORLD 8
+
+typedef struct {
+  int swapped;  // 1: weight rows fill the 128 tensor-core rows (few tokens), 0: tokens do
+  int bn;       // accumulator columns per tile
+  int m_tiles, n_tiles, k_blocks, k_splits, kb_per_split;
+  int reduce;   // partial tiles go through the slot workspace (split-K and / or several ranks)
+  int grid;
+  int tokens_pad;
+  int tiles;
+  size_t slot_elems;  // fp32 elements one slot must hold
+} tpb_gemm_plan_t;
+
+// Workspace of the fused split-K / all-reduce epilogue.  All pointers are device pointers valid on the
+// launching GPU; slots[d] / arrivals[d] point into rank d's memory (peer-mapped for d != rank).
+typedef struct {
+  int world, rank;
+  void* slots[TPB_MAX_WORLD];     // fp32 [max_slots][slot_stride]
+  void* arrivals[TPB_MAX_WORLD];  // uint32 [max_tiles]
+  void* expected;                 // local uint32 [max_tiles]
+  void* status;                   // local uint32 status word
+  size_t slot_stride;             // elements per slot
+  int max_slots, max_tiles;
+} tpb_reduce_ctx_t;
+
+int tpb_gemm_plan(int tokens, int features, int k, int world, int force_splits, tpb_gemm_plan_t* plan);
+
+// out[tokens, features] = act(x[tokens, k] @ w[features, k]^T + bias) + residual   (bf16, fp32 accumulate)
+int tpb_gemm_bf16(const void* x, const void* w, void* out, const void* bias, const void* residual, int tokens,
+                  int features, int k, int ldx, int ldw, int ld_out, int act, const tpb_gemm_plan_t* plan,
+                  const tpb_reduce_ctx_t* rc, void* stream);
+
+#ifdef __cplusplus
+}
+#endif

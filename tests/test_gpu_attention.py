@@ -1,0 +1,91 @@
+"""Attention kernels against the fp32 reference ``attention_ref`` (same masking convention)."""
+import pytest
+import torch
+
+from tensor_parallel_b200.ops import functional as OF
+
+pytestmark = pytest.mark.gpu
+
+
+def _native():
+    from tensor_parallel_b200.ops import native
+
+    return native
+
+
+CASES = [
+    # batch, sq, sk, hq, hkv, d, causal
+    (2, 128, 128, 4, 4, 128, True),
+    (1, 200, 200, 8, 2, 64, True),     # GQA, ragged
+    (2, 77, 77, 4, 4, 64, False),      # bidirectional (encoder)
+    (1, 64, 300, 4, 1, 128, True),     # chunked prefill on top of a cache (MQA)
+    (1, 5, 133, 2, 2, 64, False),      # cross attention shape
+    (1, 1024, 1024, 2, 2, 128, True),
+]
+
+
+@pytest.mark.parametrize("b,sq,sk,hq,hkv,d,causal", CASES)
+def test_prefill_attention(b, sq, sk, hq, hkv, d, causal):
+    nat = _native()
+    torch.manual_seed(0)
+    q = torch.randn(b, sq, hq, d, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(b, sk, hkv, d, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(b, sk, hkv, d, device="cuda", dtype=torch.bfloat16)
+    out, lse = nat.attention_forward(q, k, v, causal, None, want_lse=True)
+    ref = OF.attention_ref(q.float(), k.float(), v.float(), causal)
+    torch.testing.assert_close(out.float(), ref, atol=2e-2, rtol=2e-2)
+    assert torch.isfinite(lse).all()
+
+
+def test_prefill_attention_reads_cache_layout():
+    """k / v handed over as transposed views of a [B, H, S, D] cache (strides, no copy)."""
+    nat = _native()
+    torch.manual_seed(1)
+    b, s, h, d = 2, 96, 4, 128
+    q = torch.randn(b, s, h, d, device="cuda", dtype=torch.bfloat16)
+    kc = torch.randn(b, h, 256, d, device="cuda", dtype=torch.bfloat16)
+    vc = torch.randn(b, h, 256, d, device="cuda", dtype=torch.bfloat16)
+    k, v = kc[:, :, :s].transpose(1, 2), vc[:, :, :s].transpose(1, 2)
+    out, _ = nat.attention_forward(q, k, v, True, None)
+    torch.testing.assert_close(out.float(), OF.attention_ref(q.float(), k.float(), v.float(), True), atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("hq,hkv,d", [(8, 8, 128), (8, 2, 128), (16, 1, 64), (32, 32, 128), (6, 2, 64)])
+@pytest.mark.parametrize("splits", [1, 4])
+def test_decode_attention_with_cache_append(hq, hkv, d, splits):
+    nat = _native()
+    torch.manual_seed(2)
+    b, ctx, smax = 3, 201, 256
+    kc = torch.zeros(b, hkv, smax, d, device="cuda", dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    kc[:, :, :ctx] = torch.randn(b, hkv, ctx, d, device="cuda")
+    vc[:, :, :ctx] = torch.randn(b, hkv, ctx, d, device="cuda")
+    qkv = torch.randn(b, (hq + 2 * hkv) * d, device="cuda", dtype=torch.bfloat16)
+    q2, k2, v2 = qkv[:, : hq * d], qkv[:, hq * d : (hq + hkv) * d], qkv[:, (hq + hkv) * d :]
+    base = torch.tensor([ctx], device="cuda", dtype=torch.int32)
+    q_out = torch.empty(b, hq, d, device="cuda", dtype=torch.bfloat16)
+    nat.qkv_rope_append(q2, k2, v2, q_out, kc, vc, base, b, 1, d, 10000.0)
+    out = nat.attn_decode(q_out, kc, vc, base, 1, splits=splits)
+
+    pos = torch.full((b, 1), ctx, device="cuda")
+    q_ref = OF.apply_rope_ref(q2.reshape(b, 1, hq, d).float(), pos, 10000.0)
+    k_new = OF.apply_rope_ref(k2.reshape(b, 1, hkv, d).float(), pos, 10000.0)
+    torch.testing.assert_close(kc[:, :, ctx].float(), k_new[:, 0], atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(vc[:, :, ctx], v2.reshape(b, hkv, d))
+    k_all = kc[:, :, : ctx + 1].transpose(1, 2).float()
+    v_all = vc[:, :, : ctx + 1].transpose(1, 2).float()
+    ref = OF.attention_ref(q_out.reshape(b, 1, hq, d).float(), k_all, v_all, causal=True)
+    torch.testing.assert_close(out.reshape(b, 1, hq, d).float(), ref, atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(q_out.float(), q_ref[:, 0], atol=2e-2, rtol=2e-2)
+
+
+def test_attention_autograd_path():
+    nat = _native()
+    torch.manual_seed(3)
+    q, k, v = (torch.randn(1, 64, 2, 64, device="cuda", dtype=torch.bfloat16, requires_grad=True) for _ in range(3))
+    out = nat.attention(q, k, v, True)
+    out.float().square().sum().backward()
+    qr, kr, vr = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    OF.attention_ref(qr, kr, vr, True).square().sum().backward()
+    torch.testing.assert_close(q.grad.float(), qr.grad, atol=5e-2, rtol=5e-2)
+    torch.testing.assert_close(v.grad.float(), vr.grad, atol=5e-2, rtol=5e-2)
