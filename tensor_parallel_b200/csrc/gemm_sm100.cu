@@ -55,6 +55,7 @@ struct GemmParams {
   int ld_out;         // elements between consecutive tokens in out / residual / partial slots
   __nv_bfloat16* out;
   const __nv_bfloat16* bias;      // [features] or null
+  float bias_scale;               // bias is multiplied by this before it is added (a row-parallel shard stores bias / world)
   const __nv_bfloat16* residual;  // [tokens, ld_out] or null
   int act;                        // 0 none, 1 relu, 2 gelu(erf), 3 gelu(tanh), 4 silu  (direct epilogue only)
   // reduce mode (k_splits > 1 or world > 1)
@@ -251,8 +252,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                   const uint32_t bw[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
                   for (int j = 0; j < 8; ++j) {
-                    v[2 * j] += bf16_bits_to_float(bw[j] & 0xFFFF);
-                    v[2 * j + 1] += bf16_bits_to_float(bw[j] >> 16);
+                    v[2 * j] += p.bias_scale * bf16_bits_to_float(bw[j] & 0xFFFF);
+                    v[2 * j + 1] += p.bias_scale * bf16_bits_to_float(bw[j] >> 16);
                   }
                 }
                 if (p.act) {
@@ -279,7 +280,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 op[1] = o1;
               } else {
                 for (int j = 0; j < 16 && n0 + j < p.n_extent; ++j) {
-                  float x = v[j] + (p.bias ? __bfloat162float(p.bias[n0 + j]) : 0.f);
+                  float x = v[j] + (p.bias ? p.bias_scale * __bfloat162float(p.bias[n0 + j]) : 0.f);
                   x = apply_act(x, p.act);
                   if (p.residual) x += __bfloat162float(p.residual[base + j]);
                   p.out[base + j] = __float2bfloat16(x);
@@ -289,7 +290,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           } else {
             // thread = feature m, registers = 16 consecutive tokens
             if (m_ok) {
-              const float b = p.bias ? __bfloat162float(p.bias[m]) : 0.f;
+              const float b = p.bias ? p.bias_scale * __bfloat162float(p.bias[m]) : 0.f;
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
                 const int t = n0 + j;
@@ -404,7 +405,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             if (f + j < feat0 + feat_n) {
-              float x = o[j] + (p.bias ? __bfloat162float(p.bias[f + j]) : 0.f);
+              float x = o[j] + (p.bias ? p.bias_scale * __bfloat162float(p.bias[f + j]) : 0.f);
               x = apply_act(x, p.act);
               if (p.residual) x += __bfloat162float(p.residual[idx + j]);
               p.out[idx + j] = __float2bfloat16(x);
@@ -534,8 +535,8 @@ extern "C" int tpb_gemm_plan(int tokens, int features, int k, int world, int for
 }
 
 extern "C" int tpb_gemm_bf16(const void* x, const void* w, void* out, const void* bias, const void* residual, int tokens,
-                             int features, int k, int ldx, int ldw, int ld_out, int act, const tpb_gemm_plan_t* plan,
-                             const tpb_reduce_ctx_t* rc, void* stream_) {
+                             int features, int k, int ldx, int ldw, int ld_out, int act, float bias_scale,
+                             const tpb_gemm_plan_t* plan, const tpb_reduce_ctx_t* rc, void* stream_) {
   if (!x || !w || !out || !plan) return TPB_ERR_ARG;
   if ((ldx & 7) || (ldw & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return TPB_ERR_ALIGN;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
@@ -555,6 +556,7 @@ extern "C" int tpb_gemm_bf16(const void* x, const void* w, void* out, const void
   p.bias = static_cast<const __nv_bfloat16*>(bias);
   p.residual = static_cast<const __nv_bfloat16*>(residual);
   p.act = act;
+  p.bias_scale = bias_scale;
   p.reduce = plan->reduce;
   p.world = 1;
   p.rank = 0;

@@ -46,10 +46,12 @@ typedef struct {
 
 int tpb_gemm_plan(int tokens, int features, int k, int world, int force_splits, tpb_gemm_plan_t* plan);
 
-// out[tokens, features] = act(x[tokens, k] @ w[features, k]^T + bias) + residual   (bf16, fp32 accumulate)
+// out[tokens, features] = act(x[tokens, k] @ w[features, k]^T + bias_scale * bias) + residual
+// (bf16 operands, fp32 accumulation).  With rc->world > 1 the product is additionally summed over all ranks
+// inside the same kernel (every rank must launch it with the same shapes).
 int tpb_gemm_bf16(const void* x, const void* w, void* out, const void* bias, const void* residual, int tokens,
-                  int features, int k, int ldx, int ldw, int ld_out, int act, const tpb_gemm_plan_t* plan,
-                  const tpb_reduce_ctx_t* rc, void* stream);
+                  int features, int k, int ldx, int ldw, int ld_out, int act, float bias_scale,
+                  const tpb_gemm_plan_t* plan, const tpb_reduce_ctx_t* rc, void* stream);
 
 #ifdef __cplusplus
 }

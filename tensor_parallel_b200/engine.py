@@ -1,0 +1,232 @@
+"""Serving engine for Llama-shaped tensor-parallel shards: kernel-level prefill and a decode step
+captured once as a CUDA graph and replayed per token.
+
+The engine is what ``generate()`` of a tensor-parallel Llama model runs on CUDA.  It reads the
+shard's own parameters (q/k/v and gate/up are re-pointed at fused buffers, so no weight is
+duplicated), keeps a pre-allocated head-sharded KV cache ``[batch, local_kv_heads, max_seq, head_dim]``
+per layer, and per layer launches::
+
+    rmsnorm -> qkv GEMM -> rope + cache append -> attention -> o_proj GEMM (+ all-reduce + residual)
+            -> rmsnorm -> gate/up GEMM -> swiglu -> down GEMM (+ all-reduce + residual)
+
+With several ranks the two row-parallel GEMMs push their partial tiles to every peer from the
+epilogue and reduce them in the same kernel (decode), or write into symmetric memory and run the
+two-shot device all-reduce (prefill); nothing goes through NCCL.  The reference reaches the same
+maths through Python wrappers, host barriers and one NCCL call per collective
+(``src/tensor_parallel/tensor_parallel.py:139-161``, ``src/tensor_parallel/communications.py:34-52``).
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional
+
+import torch
+
+from tensor_parallel_b200.ops import native
+
+
+def _unwrap(module):
+    return module.__dict__.get("tp_wrapped_module", module) if hasattr(module, "__dict__") else module
+
+
+class LlamaEngine:
+    def __init__(self, shard, comm=None, max_batch: int = 8, max_seq: int = 2560, use_graph: bool = True):
+        lm = _unwrap(shard)
+        cfg = lm.config
+        self.comm = comm
+        self.world = comm.world if comm is not None else 1
+        self.rank = comm.rank if comm is not None else 0
+        self.cfg = cfg
+        self.eps = cfg.rms_norm_eps
+        self.theta = float(cfg.rope_theta)
+        self.head_dim = cfg.hidden_size // cfg.num_attention_heads
+        self.hidden = cfg.hidden_size
+        self.max_batch, self.max_seq = max_batch, max_seq
+        self.use_graph = use_graph
+        model = _unwrap(lm.model)
+        embed = _unwrap(model.embed_tokens)
+        self.device = embed.weight.device
+        dev = self.device
+
+        # full embedding table (hidden-split shards are gathered once; 2 * vocab * hidden bytes per rank)
+        table = embed.weight.detach()
+        if table.shape[1] != self.hidden:
+            import torch.distributed as dist
+
+            parts = [torch.empty_like(table) for _ in range(self.world)]
+            dist.all_gather(parts, table.contiguous())
+            table = torch.cat(parts, dim=1)
+        self.embed = table.contiguous()
+
+        self.layers = []
+        for layer in model.layers:
+            attn, mlp = _unwrap(layer.self_attn), _unwrap(layer.mlp)
+            wq, wk, wv = attn.q_proj.weight, attn.k_proj.weight, attn.v_proj.weight
+            wqkv = torch.cat([wq.detach(), wk.detach(), wv.detach()], dim=0).contiguous()
+            nq, nk = wq.shape[0], wk.shape[0]
+            wq.data, wk.data, wv.data = wqkv[:nq], wqkv[nq : nq + nk], wqkv[nq + nk :]
+            wg, wu = mlp.gate_proj.weight, mlp.up_proj.weight
+            wgu = torch.cat([wg.detach(), wu.detach()], dim=0).contiguous()
+            ff = wg.shape[0]
+            wg.data, wu.data = wgu[:ff], wgu[ff:]
+            self.layers.append(dict(
+                wqkv=wqkv, wo=attn.o_proj.weight.detach(), wgu=wgu, wd=mlp.down_proj.weight.detach(),
+                ln1=layer.input_layernorm.weight.detach(), ln2=layer.post_attention_layernorm.weight.detach(),
+                nq=nq // self.head_dim, nkv=nk // self.head_dim, ff=ff,
+            ))
+        self.final_norm = _unwrap(model.norm).weight.detach()
+        self.lm_head = _unwrap(lm.lm_head).weight.detach()
+        self.vocab_local = self.lm_head.shape[0]
+        self.nq, self.nkv, self.ff = self.layers[0]["nq"], self.layers[0]["nkv"], self.layers[0]["ff"]
+
+        B, D = max_batch, self.head_dim
+        bf = dict(dtype=torch.bfloat16, device=dev)
+        self.kcache = [torch.zeros(B, self.nkv, max_seq, D, **bf) for _ in self.layers]
+        self.vcache = [torch.zeros(B, self.nkv, max_seq, D, **bf) for _ in self.layers]
+        # static decode buffers
+        self.ids = torch.zeros(B, dtype=torch.int64, device=dev)
+        self.pos = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.x = torch.zeros(B, self.hidden, **bf)
+        self.n = torch.zeros(B, self.hidden, **bf)
+        self.qkv = torch.zeros(B, (self.nq + 2 * self.nkv) * D, **bf)
+        self.q_rot = torch.zeros(B, self.nq, D, **bf)
+        self.attn = torch.zeros(B, self.nq * D, **bf)
+        self.gu = torch.zeros(B, 2 * self.ff, **bf)
+        self.act = torch.zeros(B, self.ff, **bf)
+        self.logits_local = torch.zeros(B, self.vocab_local, **bf)
+        self.next_ids = torch.zeros(B, dtype=torch.int64, device=dev)
+        self.splits = max(1, min(16, math.ceil(2 * 148 / (B * self.nkv))))
+        self.attn_ws = (torch.empty(B * self.nq * self.splits * D, dtype=torch.float32, device=dev),
+                        torch.empty(B * self.nq * self.splits * 2, dtype=torch.float32, device=dev))
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.graph_batch = 0
+        self.kernels_per_step = 0
+
+    # -- building blocks --------------------------------------------------------------------------
+
+    def _row_parallel(self, x2d, weight, residual_out):
+        """``residual_out += all-reduce(x2d @ weight.T)`` (in place)."""
+        tokens = x2d.shape[0]
+        if self.world == 1:
+            native.gemm_nt(x2d, weight, residual=residual_out, out=residual_out)
+        elif self.comm.fits_fused(tokens, weight.shape[0], weight.shape[1]) and tokens <= 64:
+            self.comm.gemm_allreduce(x2d, weight, residual=residual_out, out=residual_out)
+        else:
+            staged = self.comm.staging_view("in", (tokens, weight.shape[0]), torch.bfloat16)
+            native.gemm_nt(x2d, weight, out=staged)
+            reduced = self.comm.all_reduce(staged)
+            residual_out.add_(reduced)
+
+    def _layer(self, i, x, n, qkv, q_rot, attn, gu, act, batch, seq, decode: bool):
+        L = self.layers[i]
+        D = self.head_dim
+        native.norm_forward(x, L["ln1"], None, self.eps, 0, out=n)
+        native.gemm_nt(n, L["wqkv"], out=qkv)
+        nq_w, nk_w = self.nq * D, self.nkv * D
+        q2, k2, v2 = qkv[:, :nq_w], qkv[:, nq_w : nq_w + nk_w], qkv[:, nq_w + nk_w :]
+        native.qkv_rope_append(q2, k2, v2, q_rot, self.kcache[i], self.vcache[i], self.pos, batch, seq, D, self.theta)
+        if decode:
+            native.attn_decode(q_rot, self.kcache[i][:batch], self.vcache[i][:batch], self.pos, 1, splits=self.splits,
+                               workspace=self.attn_ws, out=attn.view(batch, self.nq, D))
+        else:
+            total = self._prefill_base + seq
+            k = self.kcache[i][:batch, :, :total].transpose(1, 2)
+            v = self.vcache[i][:batch, :, :total].transpose(1, 2)
+            out, _ = native.attention_forward(q_rot.view(batch, seq, self.nq, D), k, v, True, None)
+            attn = out.view(batch * seq, self.nq * D)
+        self._row_parallel(attn, L["wo"], x)
+        native.norm_forward(x, L["ln2"], None, self.eps, 0, out=n)
+        native.gemm_nt(n, L["wgu"], out=gu)
+        native.act_forward(gu[:, : self.ff], gu[:, self.ff :], 4, out=act)
+        self._row_parallel(act, L["wd"], x)
+
+    def _head(self, x, n, logits_local, batch):
+        native.norm_forward(x, self.final_norm, None, self.eps, 0, out=n)
+        native.gemm_nt(n, self.lm_head, out=logits_local)
+        if self.world == 1:
+            return logits_local[:batch]
+        gathered = self.comm.all_gather(logits_local[:batch].contiguous())  # [world, batch, vocab_local]
+        return gathered.permute(1, 0, 2).reshape(batch, self.world * self.vocab_local)
+
+    # -- prefill ----------------------------------------------------------------------------------
+
+    @torch.no_grad()
+    def prefill(self, input_ids: torch.Tensor, base: int = 0) -> torch.Tensor:
+        """Run ``input_ids [batch, seq]`` through the model, fill the cache from position ``base`` and
+        return the logits of the last position ``[batch, vocab]`` (fp32)."""
+        batch, seq = input_ids.shape
+        if batch > self.max_batch or base + seq > self.max_seq:
+            raise ValueError("prompt does not fit the engine's cache (max_batch / max_seq)")
+        dev, D = self.device, self.head_dim
+        bf = dict(dtype=torch.bfloat16, device=dev)
+        self._prefill_base = base
+        self.pos.fill_(base)
+        tokens = batch * seq
+        x = native.embedding(input_ids.to(dev).reshape(-1), self.embed)
+        n = torch.empty(tokens, self.hidden, **bf)
+        qkv = torch.empty(tokens, (self.nq + 2 * self.nkv) * D, **bf)
+        q_rot = torch.empty(tokens, self.nq, D, **bf)
+        gu = torch.empty(tokens, 2 * self.ff, **bf)
+        act = torch.empty(tokens, self.ff, **bf)
+        for i in range(len(self.layers)):
+            self._layer(i, x, n, qkv, q_rot, None, gu, act, batch, seq, decode=False)
+        last = x.view(batch, seq, self.hidden)[:, -1].contiguous()
+        n_last = torch.empty_like(last)
+        logits_local = torch.empty(batch, self.vocab_local, **bf)
+        logits = self._head(last, n_last, logits_local, batch)
+        self.pos.fill_(base + seq)
+        return logits.float()
+
+    # -- decode -----------------------------------------------------------------------------------
+
+    def _decode_body(self, batch: int):
+        before = native.launch_count
+        native.embedding(self.ids[:batch], self.embed, out=self.x[:batch])
+        x, n = self.x[:batch], self.n[:batch]
+        for i in range(len(self.layers)):
+            self._layer(i, x, n, self.qkv[:batch], self.q_rot[:batch], self.attn[:batch], self.gu[:batch], self.act[:batch],
+                        batch, 1, decode=True)
+        logits = self._head(x, n, self.logits_local[:batch], batch)
+        torch.argmax(logits.float(), dim=-1, out=self.next_ids[:batch])
+        self.ids[:batch].copy_(self.next_ids[:batch])
+        self.pos.add_(1)
+        self.kernels_per_step = native.launch_count - before
+
+    @torch.no_grad()
+    def decode_step(self, batch: int):
+        """One greedy token for every sequence: consumes ``self.ids``, leaves the new ids in ``self.ids``
+        / ``self.next_ids`` and advances the cache position.  Captured once per batch size."""
+        if not self.use_graph:
+            self._decode_body(batch)
+            return
+        if self.graph is None or self.graph_batch != batch:
+            saved_pos, saved_ids = self.pos.clone(), self.ids.clone()
+            stream = torch.cuda.Stream(device=self.device)
+            stream.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(stream):
+                for _ in range(2):  # warm-up outside capture (allocations, plan cache, smem attributes)
+                    self._decode_body(batch)
+            torch.cuda.current_stream(self.device).wait_stream(stream)
+            torch.cuda.synchronize(self.device)
+            if self.comm is not None and (self.comm._call & 1):
+                self.comm._call += 1  # keep the workspace alternation phase identical on every replay
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph):
+                self._decode_body(batch)
+            self.graph_batch = batch
+            self.pos.copy_(saved_pos)
+            self.ids.copy_(saved_ids)
+        self.graph.replay()
+
+    @torch.no_grad()
+    def generate(self, input_ids: torch.Tensor, max_new_tokens: int) -> torch.Tensor:
+        """Greedy generation: prefill + ``max_new_tokens - 1`` graph-replayed decode steps."""
+        batch = input_ids.shape[0]
+        logits = self.prefill(input_ids)
+        first = logits.argmax(-1)
+        out = [first]
+        self.ids[:batch].copy_(first)
+        for _ in range(max_new_tokens - 1):
+            self.decode_step(batch)
+            out.append(self.next_ids[:batch].clone())
+        return torch.cat([input_ids.to(self.device), torch.stack(out, dim=1)], dim=1)

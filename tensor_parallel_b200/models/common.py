@@ -107,12 +107,19 @@ def past_length(past) -> int:
 
 
 def init_weights_(module: nn.Module, std: float = 0.02, seed: Optional[int] = None):
-    """N(0, std) for matrices / embeddings, zeros for biases, ones for norm scales."""
+    """N(0, std) for matrices / embeddings, zeros for biases, ones for norm scales.  Parameters are
+    filled in place on whatever device they live on (a 7B model initialises on the GPU in seconds);
+    with ``seed`` the values are drawn on the CPU from a private generator instead."""
     gen = torch.Generator().manual_seed(seed) if seed is not None else None
     for name, p in module.named_parameters():
+        if p.device.type == "meta":
+            continue
         with torch.no_grad():
             if p.ndim >= 2:
-                p.copy_(torch.randn(p.shape, generator=gen, dtype=torch.float32).mul_(std).to(p.dtype))
+                if gen is None:
+                    p.normal_(0.0, std)
+                else:
+                    p.copy_(torch.randn(p.shape, generator=gen, dtype=torch.float32).mul_(std).to(p.dtype))
             elif name.endswith("bias"):
                 p.zero_()
 

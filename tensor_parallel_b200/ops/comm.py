@@ -1,0 +1,378 @@
+"""Symmetric heap and device-side collectives (Python side of ``csrc/comm.cu``).
+
+Every rank owns one ``cudaMalloc``'ed region of identical layout that all ranks map:
+``cudaDeviceEnablePeerAccess`` + plain pointers when all ranks live in one process (threaded
+mode), CUDA IPC handles exchanged through ``torch.distributed`` when there is one process per
+GPU.  Kernels address peers' regions directly over NVLink; no NCCL call is on these paths.
+
+Layout of a region (offsets identical on all ranks)::
+
+    signals   : uint32 [2][64][8]            start / end barrier words of the collectives
+    arrivals  : uint32 [2 regions][MAX_TILES] per-tile arrival counters of the fused GEMM epilogue
+    slots     : fp32   [2 regions][max_slots][slot_stride]  partial tiles pushed by peers
+    staging   : two payload buffers for the stand-alone collectives (input side / output side)
+
+The two "regions" alternate between consecutive fused GEMM calls: a rank that runs ahead writes
+into the other half than the one a slower peer may still be reducing from.
+"""
+from __future__ import annotations
+
+import ctypes
+import logging
+import threading
+from typing import Dict, List, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+from tensor_parallel_b200.ops import native
+from tensor_parallel_b200.ops.native import LIB, ReduceCtx, c_int, c_ll, c_void_p, check
+
+logger = logging.getLogger(__name__)
+
+MAX_WORLD = 8
+COMM_MAX_BLOCKS = 64
+SIGNAL_BYTES = 2 * COMM_MAX_BLOCKS * MAX_WORLD * 4
+MAX_TILES = native.MAX_TILES
+
+LIB.tpb_malloc.argtypes = [ctypes.POINTER(c_void_p), ctypes.c_size_t]
+LIB.tpb_free.argtypes = [c_void_p]
+LIB.tpb_enable_peer_access.argtypes = [c_int]
+LIB.tpb_ipc_get_handle.argtypes = [c_void_p, c_void_p]
+LIB.tpb_ipc_open_handle.argtypes = [c_void_p, ctypes.POINTER(c_void_p)]
+LIB.tpb_ipc_close_handle.argtypes = [c_void_p]
+LIB.tpb_collective.argtypes = [c_int, c_int, c_int, c_int, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p),
+                               ctypes.POINTER(c_void_p), c_void_p, c_void_p, c_ll, c_int, ctypes.c_double, c_void_p]
+LIB.tpb_wait_flag_test.argtypes = [c_void_p, ctypes.c_uint, c_void_p, ctypes.c_double, c_void_p]
+
+
+class _DeviceBlob:
+    """Exposes raw device memory to ``torch.as_tensor`` (zero-copy) via the CUDA array interface."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
+
+
+def tensor_from_ptr(ptr: int, nbytes: int, device: torch.device) -> torch.Tensor:
+    with torch.cuda.device(device):
+        return torch.as_tensor(_DeviceBlob(ptr, nbytes), device=device)
+
+
+def _align(n: int, a: int = 1024) -> int:
+    return (n + a - 1) // a * a
+
+
+class HeapLayout:
+    def __init__(self, slot_stride: int, max_slots: int, staging_bytes: int):
+        self.slot_stride, self.max_slots, self.staging_bytes = slot_stride, max_slots, staging_bytes
+        self.off_signals = 0
+        self.off_arrivals = _align(SIGNAL_BYTES)
+        self.off_slots = self.off_arrivals + _align(2 * MAX_TILES * 4)
+        self.region_slot_bytes = _align(max_slots * slot_stride * 4)
+        self.off_staging_in = self.off_slots + 2 * self.region_slot_bytes
+        self.off_staging_out = self.off_staging_in + _align(staging_bytes)
+        self.total = self.off_staging_out + _align(staging_bytes)
+
+
+class RankComm:
+    """One rank's view of the symmetric heap: its own region plus peer-mapped pointers."""
+
+    def __init__(self, world: int, rank: int, device: torch.device, layout: HeapLayout, base_ptrs: Sequence[int]):
+        self.world, self.rank, self.device, self.layout = world, rank, device, layout
+        self.base = list(base_ptrs)
+        with torch.cuda.device(device):
+            self.epochs = torch.zeros(COMM_MAX_BLOCKS, dtype=torch.int32, device=device)
+            self.expected = torch.zeros(2 * MAX_TILES, dtype=torch.int32, device=device)
+            self.status = torch.zeros(4, dtype=torch.int32, device=device)
+        self.local = tensor_from_ptr(self.base[rank], layout.total, device)
+        self.staging_in = self.local[layout.off_staging_in : layout.off_staging_in + layout.staging_bytes]
+        self.staging_out = self.local[layout.off_staging_out : layout.off_staging_out + layout.staging_bytes]
+        self._call = 0
+        self._ctxs = [self._make_ctx(0), self._make_ctx(1)]
+        self._ptr_arrays: Dict[str, ctypes.Array] = {}
+        for name, off in (("in", layout.off_staging_in), ("out", layout.off_staging_out), ("sig", layout.off_signals)):
+            arr = (c_void_p * MAX_WORLD)()
+            for r in range(world):
+                arr[r] = self.base[r] + off
+            self._ptr_arrays[name] = arr
+        self.wait_seconds = 2.0
+
+    def _make_ctx(self, region: int) -> ReduceCtx:
+        ctx = ReduceCtx()
+        ctx.world, ctx.rank = self.world, self.rank
+        for r in range(self.world):
+            ctx.slots[r] = self.base[r] + self.layout.off_slots + region * self.layout.region_slot_bytes
+            ctx.arrivals[r] = self.base[r] + self.layout.off_arrivals + region * MAX_TILES * 4
+        ctx.expected = self.expected.data_ptr() + region * MAX_TILES * 4
+        ctx.status = self.status.data_ptr()
+        ctx.slot_stride = self.layout.slot_stride
+        ctx.max_slots, ctx.max_tiles = self.layout.max_slots, MAX_TILES
+        return ctx
+
+    # -- fused GEMM + all-reduce ------------------------------------------------------------------
+
+    def next_reduce_ctx(self) -> ReduceCtx:
+        """Context for the next fused call; consecutive calls alternate workspace halves.  Every rank
+        must issue the same sequence of fused calls."""
+        ctx = self._ctxs[self._call & 1]
+        self._call += 1
+        return ctx
+
+    def gemm_allreduce(self, x2d, weight, bias=None, residual=None, out=None, bias_scale: float = 1.0):
+        """``sum over ranks of (x2d @ weight.T) + bias_scale * bias + residual`` in ONE kernel: partial tiles are
+        pushed to every peer from the GEMM epilogue and reduced as they arrive."""
+        tokens, features = x2d.shape[0], weight.shape[0]
+        if tokens * features > self.layout.slot_stride:
+            raise ValueError(f"fused GEMM+all-reduce workspace holds {self.layout.slot_stride} elements per slot, need {tokens * features}")
+        return native.gemm_nt(x2d, weight, bias=bias, residual=residual, out=out, reduce_ctx=self.next_reduce_ctx(),
+                              world=self.world, bias_scale=bias_scale)
+
+    def fits_fused(self, tokens: int, features: int, k: int) -> bool:
+        if tokens * features > self.layout.slot_stride:
+            return False
+        plan = native.gemm_plan(tokens, features, k, self.world)
+        return self.world * plan.k_splits <= self.layout.max_slots and plan.tiles <= MAX_TILES
+
+    # -- stand-alone collectives on the staging buffers -------------------------------------------
+
+    def _collective(self, kind: int, dtype: torch.dtype, n: int, force_algo: int = -1):
+        code = 0 if dtype == torch.bfloat16 else 1
+        check(LIB.tpb_collective(kind, code, self.world, self.rank, self._ptr_arrays["in"], self._ptr_arrays["out"],
+                                 self._ptr_arrays["sig"], c_void_p(self.epochs.data_ptr()), c_void_p(self.status.data_ptr()), n,
+                                 force_algo, self.wait_seconds, native._stream()), "tpb_collective")
+        native.launch_count += 1
+
+    def staging_view(self, which: str, shape, dtype) -> torch.Tensor:
+        buf = self.staging_in if which == "in" else self.staging_out
+        nbytes = int(torch.Size(shape).numel()) * torch.empty((), dtype=dtype).element_size()
+        if nbytes > buf.numel():
+            raise ValueError(f"collective payload of {nbytes} bytes exceeds the staging buffer ({buf.numel()} bytes)")
+        return buf[:nbytes].view(dtype).view(shape)
+
+    def all_reduce(self, x: torch.Tensor, force_algo: int = -1) -> torch.Tensor:
+        """Sum over ranks.  ``x`` is copied into symmetric memory unless it already is the staging-in view."""
+        dtype = x.dtype if x.dtype in (torch.bfloat16, torch.float32) else torch.float32
+        n = x.numel()
+        per = 8 if dtype == torch.bfloat16 else 4
+        n_pad = (n + per - 1) // per * per
+        src = self.staging_view("in", (n_pad,), dtype)
+        if x.data_ptr() != src.data_ptr():
+            src[:n].copy_(x.reshape(-1))
+            if n_pad != n:
+                src[n:].zero_()
+        self._collective(0, dtype, n_pad, force_algo)
+        return self.staging_view("out", (n_pad,), dtype)[:n].view(x.shape)
+
+    def all_gather(self, x: torch.Tensor) -> torch.Tensor:
+        """Returns ``[world, *x.shape]`` (every rank's ``x``); all ranks must pass the same shape."""
+        dtype = x.dtype if x.dtype in (torch.bfloat16, torch.float32) else torch.float32
+        n = x.numel()
+        per = 8 if dtype == torch.bfloat16 else 4
+        n_pad = (n + per - 1) // per * per
+        src = self.staging_view("in", (n_pad,), dtype)
+        if x.data_ptr() != src.data_ptr():
+            src[:n].copy_(x.reshape(-1))
+        self._collective(2, dtype, n_pad)
+        return self.staging_view("out", (self.world, n_pad), dtype)[:, :n].reshape(self.world, *x.shape)
+
+    def reduce_scatter(self, x: torch.Tensor) -> torch.Tensor:
+        """``x`` is ``[world, ...]``; returns the sum over ranks of ``x[rank]``."""
+        dtype = x.dtype if x.dtype in (torch.bfloat16, torch.float32) else torch.float32
+        per = 8 if dtype == torch.bfloat16 else 4
+        n = x[0].numel()
+        if n % per:
+            raise ValueError("reduce_scatter slices must be a multiple of 16 bytes")
+        src = self.staging_view("in", (self.world * n,), dtype)
+        if x.data_ptr() != src.data_ptr():
+            src.copy_(x.reshape(-1))
+        self._collective(3, dtype, n)
+        return self.staging_view("out", (n,), dtype).view(x.shape[1:])
+
+    def check_status(self):
+        code = int(self.status[0].item())
+        if code:
+            self.status.zero_()
+            from tensor_parallel_b200.parallel.collectives import TPCollectiveError
+
+            raise TPCollectiveError({1: "an mbarrier wait", 2: "a wait for a peer GPU"}.get(code, f"status {code}") + " timed out inside a kernel")
+
+
+def _alloc_region(device: torch.device, nbytes: int) -> int:
+    ptr = c_void_p()
+    with torch.cuda.device(device):
+        check(LIB.tpb_malloc(ctypes.byref(ptr), nbytes), "tpb_malloc")
+    return ptr.value
+
+
+DEFAULT_SLOT_STRIDE = 64 * 16384       # fp32 elements per partial slot: 64 tokens x 16384 features
+DEFAULT_STAGING = 288 * 1024 * 1024    # bytes per staging buffer (16384 x 8192 bf16 fits)
+
+
+def make_process_comm(device: torch.device, process_group=None, slot_stride: int = DEFAULT_SLOT_STRIDE,
+                      max_slots: int = 64, staging_bytes: int = DEFAULT_STAGING) -> RankComm:
+    """One process per GPU: allocate the local region, exchange CUDA IPC handles, map the peers."""
+    world, rank = dist.get_world_size(process_group), dist.get_rank(process_group)
+    if world > MAX_WORLD:
+        raise ValueError(f"at most {MAX_WORLD} ranks are supported by the device collectives")
+    layout = HeapLayout(slot_stride, max(max_slots, world), staging_bytes)
+    base = _alloc_region(device, layout.total)
+    handle = ctypes.create_string_buffer(64)
+    with torch.cuda.device(device):
+        check(LIB.tpb_ipc_get_handle(c_void_p(base), handle), "tpb_ipc_get_handle")
+    handles: List[Optional[bytes]] = [None] * world
+    dist.all_gather_object(handles, handle.raw, group=process_group)
+    ptrs = []
+    for r in range(world):
+        if r == rank:
+            ptrs.append(base)
+            continue
+        peer = c_void_p()
+        with torch.cuda.device(device):
+            check(LIB.tpb_ipc_open_handle(ctypes.create_string_buffer(handles[r], 64), ctypes.byref(peer)), "tpb_ipc_open_handle")
+        ptrs.append(peer.value)
+    comm = RankComm(world, rank, device, layout, ptrs)
+    dist.barrier(group=process_group)  # nobody launches before every mapping exists
+    return comm
+
+
+def make_thread_comms(devices: Sequence[torch.device], slot_stride: int = DEFAULT_SLOT_STRIDE, max_slots: int = 64,
+                      staging_bytes: int = DEFAULT_STAGING) -> Optional[List[RankComm]]:
+    """All ranks in one process: enable peer access pairwise and share plain pointers."""
+    world = len(devices)
+    if world > MAX_WORLD or len({d.index for d in devices}) != world:
+        return None
+    for d in devices:
+        with torch.cuda.device(d):
+            for peer in devices:
+                if peer != d and LIB.tpb_enable_peer_access(peer.index) != 0:
+                    logger.warning("no peer access between %s and %s; device collectives disabled", d, peer)
+                    return None
+    layout = HeapLayout(slot_stride, max(max_slots, world), staging_bytes)
+    bases = [_alloc_region(d, layout.total) for d in devices]
+    return [RankComm(world, r, devices[r], layout, bases) for r in range(world)]
+
+
+# ------------------------------------------------------------------------------------------------
+# rule-action adaptors ("sum" / "gather d") and autograd
+# ------------------------------------------------------------------------------------------------
+
+
+class _AllReduceFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, comm: RankComm):
+        ctx.comm = comm
+        return comm.all_reduce(x.contiguous()).clone()
+
+    @staticmethod
+    def backward(ctx, grad):
+        return ctx.comm.all_reduce(grad.contiguous()).clone(), None
+
+
+class _AllGatherFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, dim, comm: RankComm):
+        ctx.comm, ctx.dim, ctx.shape = comm, dim, x.shape
+        stacked = comm.all_gather(x.contiguous())  # [world, ...]
+        return torch.cat(list(stacked.unbind(0)), dim=dim)
+
+    @staticmethod
+    def backward(ctx, grad):
+        comm, dim = ctx.comm, ctx.dim
+        parts = torch.stack(grad.chunk(comm.world, dim=dim))  # [world, *x.shape]
+        return comm.reduce_scatter(parts.contiguous()).clone(), None, None
+
+
+class DeviceAllReduce:
+    """``"sum"`` on the symmetric heap (one process per rank)."""
+
+    def __init__(self, comm: RankComm):
+        self.comm = comm
+
+    def __call__(self, x: torch.Tensor, rank: int = 0):
+        return _AllReduceFn.apply(x, self.comm)
+
+
+class DeviceAllGather:
+    """``"gather d"`` on the symmetric heap; falls back to the process group for uneven slices."""
+
+    def __init__(self, comm: RankComm, dim: int, fallback):
+        self.comm, self.dim, self.fallback = comm, dim, fallback
+        self._even: Dict[tuple, bool] = {}
+
+    def __call__(self, x: torch.Tensor, rank: int = 0):
+        dim = self.dim % x.ndim
+        key = (tuple(x.shape), dim)
+        even = self._even.get(key)
+        if even is None:
+            sizes = torch.tensor([x.shape[dim]], device=x.device)
+            gathered = [torch.zeros_like(sizes) for _ in range(self.comm.world)]
+            dist.all_gather(gathered, sizes)
+            even = self._even[key] = len({int(t.item()) for t in gathered}) == 1
+        per = 8 if x.dtype == torch.bfloat16 else 4
+        if not even or x.numel() % per or x.dtype not in (torch.bfloat16, torch.float32):
+            return self.fallback(x, rank)
+        return _AllGatherFn.apply(x, dim, self.comm)
+
+
+class _FlatGatherFn(torch.autograd.Function):
+    """ZeRO-3 flat-shard gather: ``[L] -> [world, L]``; backward = summing reduce-scatter."""
+
+    @staticmethod
+    def forward(ctx, flat, comm: RankComm):
+        ctx.comm = comm
+        return comm.all_gather(flat.detach()).clone()
+
+    @staticmethod
+    def backward(ctx, grad):
+        return ctx.comm.reduce_scatter(grad.contiguous()).clone(), None
+
+
+class DeviceFlatGather:
+    def __init__(self, comm: RankComm, fallback):
+        self.comm, self.fallback = comm, fallback
+
+    def all_gather_flat(self, flats):
+        flat = flats[0]
+        per = 8 if flat.dtype == torch.bfloat16 else 4
+        if flat.dtype not in (torch.bfloat16, torch.float32) or flat.numel() % per:
+            return self.fallback.all_gather_flat(flats)
+        return [_FlatGatherFn.apply(flat, self.comm)]
+
+
+class ProcessBackend:
+    """Collective factory used by ``Config.create_collective_ops`` in the one-process-per-GPU mode."""
+
+    def __init__(self, comm: RankComm, process_group=None):
+        self.comm, self.pg = comm, process_group
+
+    def all_reduce_op(self, group):
+        return DeviceAllReduce(self.comm)
+
+    def all_gather_op(self, group, dim):
+        from tensor_parallel_b200.parallel.collectives import DistributedAllGather
+
+        return DeviceAllGather(self.comm, dim, DistributedAllGather(self.comm.world, dim, self.pg))
+
+    def flat_gather(self):
+        from tensor_parallel_b200.parallel.distributed import ProcessGroupFlatGather
+
+        return DeviceFlatGather(self.comm, ProcessGroupFlatGather(self.pg))
+
+
+_process_backends: Dict[int, ProcessBackend] = {}
+_lock = threading.Lock()
+
+
+def process_backend(device: torch.device, process_group=None) -> Optional[ProcessBackend]:
+    key = id(process_group)
+    with _lock:
+        backend = _process_backends.get(key)
+        if backend is None:
+            backend = _process_backends[key] = ProcessBackend(make_process_comm(device, process_group), process_group)
+        return backend
+
+
+def thread_backend(devices: Sequence[torch.device]):
+    """Single-process multi-GPU mode keeps the portable thread collectives for rule actions; fused
+    operators reach the heap through :func:`make_thread_comms`."""
+    return None

@@ -135,7 +135,7 @@ def device_state(device: torch.device) -> DeviceState:
 
 LIB.tpb_gemm_plan.argtypes = [c_int, c_int, c_int, c_int, c_int, ctypes.POINTER(GemmPlan)]
 LIB.tpb_gemm_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                              c_int, ctypes.POINTER(GemmPlan), ctypes.POINTER(ReduceCtx), c_void_p]
+                              c_int, c_float, ctypes.POINTER(GemmPlan), ctypes.POINTER(ReduceCtx), c_void_p]
 ACT_CODES = {None: 0, "none": 0, "relu": 1, "gelu": 2, "gelu_tanh": 3, "silu": 4}
 _plan_cache: Dict[Tuple, GemmPlan] = {}
 
@@ -159,7 +159,7 @@ def gemm_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
 
 
 def gemm_nt(x2d: torch.Tensor, w: torch.Tensor, bias=None, residual=None, act=None, out=None, force_splits: int = 0,
-            reduce_ctx: Optional[ReduceCtx] = None, world: int = 1) -> torch.Tensor:
+            reduce_ctx: Optional[ReduceCtx] = None, world: int = 1, bias_scale: float = 1.0) -> torch.Tensor:
     """``out[tokens, features] = act(x2d @ w.T + bias) + residual`` on the tcgen05 kernel."""
     global launch_count
     tokens, k = x2d.shape
@@ -178,7 +178,7 @@ def gemm_nt(x2d: torch.Tensor, w: torch.Tensor, bias=None, residual=None, act=No
             state.ensure_slots(tokens * out.stride(0))
         ctx = state.ctx
     check(LIB.tpb_gemm_bf16(_ptr(x2d), _ptr(w), _ptr(out), _ptr(bias), _ptr(residual), tokens, features, k, x2d.stride(0),
-                            w.stride(0), out.stride(0), ACT_CODES[act], ctypes.byref(plan), ctypes.byref(ctx), _stream()),
+                            w.stride(0), out.stride(0), ACT_CODES[act], bias_scale, ctypes.byref(plan), ctypes.byref(ctx), _stream()),
           "tpb_gemm_bf16")
     launch_count += 1
     return out

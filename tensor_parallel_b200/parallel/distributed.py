@@ -24,6 +24,7 @@ from torch import nn
 from tensor_parallel_b200.parallel.autoconfig import get_default_config
 from tensor_parallel_b200.parallel.collectives import mute_gradient
 from tensor_parallel_b200.parallel.rules import WRAPPED_PREFIX, Config, add_lora_rules
+from tensor_parallel_b200.parallel.serving import ServingMixin
 from tensor_parallel_b200.parallel.surgery import make_shard
 from tensor_parallel_b200.parallel.zero import Sharded
 from tensor_parallel_b200.utils.nested import nested_map
@@ -57,7 +58,7 @@ class ProcessGroupFlatGather:
         return [_FlatGatherFn.apply(flats[0], self.pg)]
 
 
-class DistributedTensorParallel(nn.Module):
+class DistributedTensorParallel(ServingMixin, nn.Module):
     is_distributed = True
 
     def __init__(

@@ -20,6 +20,7 @@ from torch import nn
 from tensor_parallel_b200.parallel.autoconfig import get_default_config
 from tensor_parallel_b200.parallel.collectives import TPCollectiveError
 from tensor_parallel_b200.parallel.rules import WRAPPED_PREFIX, Config, add_lora_rules
+from tensor_parallel_b200.parallel.serving import ServingMixin
 from tensor_parallel_b200.parallel.surgery import make_shard
 from tensor_parallel_b200.parallel.zero import Sharded
 from tensor_parallel_b200.utils.nested import nested_flatten, nested_pack
@@ -183,7 +184,7 @@ def parallel_apply_simple(modules, inputs, kwargs_tup=None, devices=None, execut
             executor.shutdown()
 
 
-class TensorParallel(nn.Module):
+class TensorParallel(ServingMixin, nn.Module):
     def __init__(
         self,
         module: nn.Module,
