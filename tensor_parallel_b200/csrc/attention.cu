@@ -112,30 +112,40 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kcache, 
   const bf16* kbase = kcache + (long long)bh * max_seq * D + part * EPL;
   const bf16* vbase = vcache + (long long)bh * max_seq * D + part * EPL;
 
-  // the trip count is uniform across the warp (the shuffles below need all 32 lanes); lanes whose key
-  // falls beyond the range load nothing and skip the update
-  for (int key_base = k0 + warp * 4; key_base < k1; key_base += DEC_WARPS * 4) {
-    const int key = key_base + sub;
-    const bool valid = key < k1;
+  // Software-pipelined key loop: the loads of the next 4-key group are issued before the current group
+  // is consumed, so every warp always has K/V traffic in flight.  The trip count is uniform across the
+  // warp (the shuffles need all 32 lanes); lanes whose key falls beyond the range load nothing and skip
+  // the update.
+  uint4 kraw[EPL / 8], vraw[EPL / 8];
+  auto fetch = [&](int key_base_) {
+    const int key_ = key_base_ + sub;
+    if (key_ < k1) {
+      const uint4* kp = reinterpret_cast<const uint4*>(kbase + (long long)key_ * D);
+      const uint4* vp = reinterpret_cast<const uint4*>(vbase + (long long)key_ * D);
+#pragma unroll
+      for (int c = 0; c < EPL / 8; ++c) { kraw[c] = __ldg(kp + c); vraw[c] = __ldg(vp + c); }
+    } else {
+#pragma unroll
+      for (int c = 0; c < EPL / 8; ++c) { kraw[c] = make_uint4(0, 0, 0, 0); vraw[c] = make_uint4(0, 0, 0, 0); }
+    }
+  };
+  int key_base = k0 + warp * 4;
+  if (key_base < k1) fetch(key_base);
+  for (; key_base < k1; key_base += DEC_WARPS * 4) {
+    const bool valid = key_base + sub < k1;
     float kf[EPL], vf[EPL];
 #pragma unroll
-    for (int e = 0; e < EPL; ++e) { kf[e] = 0.f; vf[e] = 0.f; }
-    if (valid) {
-      const uint4* kp = reinterpret_cast<const uint4*>(kbase + (long long)key * D);
-      const uint4* vp = reinterpret_cast<const uint4*>(vbase + (long long)key * D);
+    for (int c = 0; c < EPL / 8; ++c) {
+      const uint32_t kw[4] = {kraw[c].x, kraw[c].y, kraw[c].z, kraw[c].w}, vw[4] = {vraw[c].x, vraw[c].y, vraw[c].z, vraw[c].w};
 #pragma unroll
-      for (int c = 0; c < EPL / 8; ++c) {
-        const uint4 ku = __ldg(kp + c), vu = __ldg(vp + c);
-        const uint32_t kw[4] = {ku.x, ku.y, ku.z, ku.w}, vw[4] = {vu.x, vu.y, vu.z, vu.w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          kf[c * 8 + 2 * j] = __uint_as_float(kw[j] << 16);
-          kf[c * 8 + 2 * j + 1] = __uint_as_float(kw[j] & 0xFFFF0000u);
-          vf[c * 8 + 2 * j] = __uint_as_float(vw[j] << 16);
-          vf[c * 8 + 2 * j + 1] = __uint_as_float(vw[j] & 0xFFFF0000u);
-        }
+      for (int j = 0; j < 4; ++j) {
+        kf[c * 8 + 2 * j] = __uint_as_float(kw[j] << 16);
+        kf[c * 8 + 2 * j + 1] = __uint_as_float(kw[j] & 0xFFFF0000u);
+        vf[c * 8 + 2 * j] = __uint_as_float(vw[j] << 16);
+        vf[c * 8 + 2 * j + 1] = __uint_as_float(vw[j] & 0xFFFF0000u);
       }
     }
+    if (key_base + DEC_WARPS * 4 < k1) fetch(key_base + DEC_WARPS * 4);  // prefetch the next group
 #pragma unroll
     for (int g = 0; g < G; ++g) {
       float s = 0.f;

@@ -61,9 +61,11 @@ struct GemmParams {
   // reduce mode (k_splits > 1 or world > 1)
   int reduce;
   int world, rank;
-  float* slots[MAX_WORLD];        // per destination rank: [world * k_splits][tokens_pad][ld_out] fp32
+  float* slots[MAX_WORLD];        // per destination rank: slots [0, world) = one partial per source rank; on the local
+                                  // rank slots [world, world + k_splits) additionally park this rank's split-K partials
   uint32_t* arrivals[MAX_WORLD];  // per destination rank: [tiles] arrival counters
   uint32_t* expected;             // local: [tiles] counter value reached after the previous call
+  uint32_t* split_counters;       // local: [tiles] arrivals of split-K partials (self re-arming)
   size_t slot_stride;             // elements between consecutive slots
   uint32_t* status;               // local status word (0 = ok)
 };
@@ -81,15 +83,24 @@ __device__ __forceinline__ float apply_act(float x, int act) {
   }
 }
 
-template <int BN>
+// KBOX = number of consecutive 64-column k-blocks fetched per pipeline stage.  With KBOX > 1 a stage
+// pulls KBOX * 128 contiguous bytes of every operand row in back-to-back TMA boxes.
+// NACC = number of independent TMEM accumulators per tile.  Consecutive tcgen05.mma instructions that
+// accumulate into the same TMEM columns serialise on the accumulator; at N = 16 / 32 one instruction is
+// far shorter than that dependent latency, so the k-steps are dealt round-robin to NACC accumulators that
+// the epilogue adds up.  (At N >= 64 one accumulator keeps the tensor pipe busy.)
+template <int BN, int KBOX, int NACC>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                          const GemmParams p) {
   constexpr uint32_t A_BYTES = BM * BK * 2;
   constexpr uint32_t B_BYTES = BN * BK * 2;
-  constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
-  constexpr uint32_t TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;  // power of two for BN in {16,...,256}
+  constexpr uint32_t STAGE_BYTES = KBOX * (A_BYTES + B_BYTES);
+  constexpr uint32_t ACC_COLS = NACC * BN;                                  // columns of one accumulator set
+  constexpr uint32_t TMEM_COLS = (2 * ACC_COLS < 32) ? 32 : 2 * ACC_COLS;   // two sets; power of two by construction
+  static_assert(TMEM_COLS <= 512 && (TMEM_COLS & (TMEM_COLS - 1)) == 0, "TMEM allocation must be a power of two <= 512");
   constexpr uint32_t IDESC = make_idesc_bf16(BM, BN);
+  constexpr int MMAS_PER_STAGE = KBOX * (BK / UMMA_K);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -100,6 +111,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   volatile uint32_t* epi_ok = tmem_slot + 2;
+  volatile uint32_t* epi_last = tmem_slot + 3;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -150,9 +162,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             break;
           }
           uint8_t* a_dst = smem + size_t(s) * STAGE_BYTES;
+          uint8_t* b_dst = a_dst + KBOX * A_BYTES;
           mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-          tma_load_2d(a_dst, &tmap_a, &full_bar[s], kb * BK, mt * BM);
-          tma_load_2d(a_dst + A_BYTES, &tmap_b, &full_bar[s], kb * BK, nt * BN);
+#pragma unroll
+          for (int j = 0; j < KBOX; ++j)  // columns past K are filled with zeros by TMA and cost no DRAM traffic
+            tma_load_2d(a_dst + j * A_BYTES, &tmap_a, &full_bar[s], (kb * KBOX + j) * BK, mt * BM);
+#pragma unroll
+          for (int j = 0; j < KBOX; ++j)
+            tma_load_2d(b_dst + j * B_BYTES, &tmap_b, &full_bar[s], (kb * KBOX + j) * BK, nt * BN);
         }
       }
     }
@@ -173,7 +190,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           break;
         }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
+        const uint32_t d_tmem = tmem_base + acc * ACC_COLS;
+        uint32_t issued = 0;  // MMAs issued for this work item; MMA i accumulates into accumulator i % NACC
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % p.stages;
           const uint32_t ph = (it / p.stages) & 1;
@@ -184,16 +202,20 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           }
           tc_fence_after();
           const uint32_t a_addr = smem_u32(smem + size_t(s) * STAGE_BYTES);
-          const uint32_t b_addr = a_addr + A_BYTES;
+          const uint32_t b_addr = a_addr + KBOX * A_BYTES;
 #pragma unroll
-          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-            const uint64_t adesc = make_desc_kmajor_sw128(a_addr + kk * UMMA_K * 2);
-            const uint64_t bdesc = make_desc_kmajor_sw128(b_addr + kk * UMMA_K * 2);
-            umma_bf16(d_tmem, adesc, bdesc, IDESC, (kb > kb0 || kk > 0) ? 1u : 0u);
+          for (int j = 0; j < KBOX; ++j) {
+#pragma unroll
+            for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+              const uint64_t adesc = make_desc_kmajor_sw128(a_addr + j * A_BYTES + kk * UMMA_K * 2);
+              const uint64_t bdesc = make_desc_kmajor_sw128(b_addr + j * B_BYTES + kk * UMMA_K * 2);
+              umma_bf16(d_tmem + (issued % NACC) * BN, adesc, bdesc, IDESC, issued >= NACC ? 1u : 0u);
+              ++issued;
+            }
           }
           umma_commit(&empty_bar[s]);  // frees the smem stage when these MMAs retire
         }
-        umma_commit(&acc_full[acc]);  // accumulator complete
+        umma_commit(&acc_full[acc]);  // accumulators complete
       }
     }
   } else {
@@ -222,130 +244,178 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       tc_fence_after();
       const int m = mt * BM + row;
       const bool m_ok = m < p.m_extent;
-      const uint32_t t_lane = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
+      const uint32_t t_lane = tmem_base + (uint32_t(quarter * 32) << 16) + acc * ACC_COLS;
+      const int kb0 = split * p.kb_per_split;
+      const int n_mma = (min(p.k_blocks, kb0 + p.kb_per_split) - kb0) * MMAS_PER_STAGE;
+      const int n_acc = n_mma < NACC ? n_mma : NACC;  // accumulators that were written for this item
 
-      float* my_slots[MAX_WORLD];
-      if (p.reduce) {
+      // A chunk is 16 accumulator columns of this thread's row: (token m, features n0..n0+15) in the normal
+      // orientation, (feature m, tokens n0..n0+15) in the swapped one.  idx(j) addresses out[token, feature].
+      auto chunk_valid = [&](int n0) { return m_ok && n0 < p.n_extent; };
+      auto read_acc = [&](int c0, float (&v)[16]) {
 #pragma unroll
-        for (int d = 0; d < MAX_WORLD; ++d)
-          my_slots[d] = d < p.world ? p.slots[d] + size_t(p.rank * p.k_splits + split) * p.slot_stride : nullptr;
-      }
-
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 16) {
-        uint32_t r[16];
-        tmem_ld_x16(t_lane + c0, r);
-        tmem_ld_wait();
-        const int n0 = nt * BN + c0;
-        if (!p.reduce) {
-          if (!p.swapped) {
-            // thread = token m, registers = 16 consecutive features
-            if (m_ok && n0 < p.n_extent) {
-              float v[16];
+        for (int j = 0; j < 16; ++j) v[j] = 0.f;
 #pragma unroll
-              for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
-              const size_t base = size_t(m) * p.ld_out + n0;
-              if (n0 + 16 <= p.n_extent && (p.ld_out & 7) == 0) {
-                if (p.bias) {
-                  const uint4* bp = reinterpret_cast<const uint4*>(p.bias + n0);
-                  uint4 b0 = bp[0], b1 = bp[1];
-                  const uint32_t bw[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+        for (int a = 0; a < NACC; ++a) {
+          if (a < n_acc) {
+            uint32_t r[16];
+            tmem_ld_x16(t_lane + a * BN + c0, r);
+            tmem_ld_wait();
 #pragma unroll
-                  for (int j = 0; j < 8; ++j) {
-                    v[2 * j] += p.bias_scale * bf16_bits_to_float(bw[j] & 0xFFFF);
-                    v[2 * j + 1] += p.bias_scale * bf16_bits_to_float(bw[j] >> 16);
-                  }
-                }
-                if (p.act) {
+            for (int j = 0; j < 16; ++j) v[j] += __uint_as_float(r[j]);
+          }
+        }
+      };
+      auto store_partial = [&](float* slot, int n0, const float (&v)[16]) {
+        if (!chunk_valid(n0)) return;
+        if (!p.swapped) {
+          const size_t base = size_t(m) * p.ld_out + n0;
+          if (n0 + 16 <= p.n_extent && (p.ld_out & 3) == 0) {
+            float4* dst = reinterpret_cast<float4*>(slot + base);
 #pragma unroll
-                  for (int j = 0; j < 16; ++j) v[j] = apply_act(v[j], p.act);
-                }
-                if (p.residual) {
-                  const uint4* rp = reinterpret_cast<const uint4*>(p.residual + base);
-                  uint4 r0 = rp[0], r1 = rp[1];
-                  const uint32_t rw[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+            for (int q = 0; q < 4; ++q) dst[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+          } else {
+            for (int j = 0; j < 16 && n0 + j < p.n_extent; ++j) slot[base + j] = v[j];
+          }
+        } else {
 #pragma unroll
-                  for (int j = 0; j < 8; ++j) {
-                    v[2 * j] += bf16_bits_to_float(rw[j] & 0xFFFF);
-                    v[2 * j + 1] += bf16_bits_to_float(rw[j] >> 16);
-                  }
-                }
-                uint4 o0, o1;
-                o0.x = pack_bf16x2(v[0], v[1]);   o0.y = pack_bf16x2(v[2], v[3]);
-                o0.z = pack_bf16x2(v[4], v[5]);   o0.w = pack_bf16x2(v[6], v[7]);
-                o1.x = pack_bf16x2(v[8], v[9]);   o1.y = pack_bf16x2(v[10], v[11]);
-                o1.z = pack_bf16x2(v[12], v[13]); o1.w = pack_bf16x2(v[14], v[15]);
-                uint4* op = reinterpret_cast<uint4*>(p.out + base);
-                op[0] = o0;
-                op[1] = o1;
-              } else {
-                for (int j = 0; j < 16 && n0 + j < p.n_extent; ++j) {
-                  float x = v[j] + (p.bias ? p.bias_scale * __bfloat162float(p.bias[n0 + j]) : 0.f);
-                  x = apply_act(x, p.act);
-                  if (p.residual) x += __bfloat162float(p.residual[base + j]);
-                  p.out[base + j] = __float2bfloat16(x);
-                }
-              }
+          for (int j = 0; j < 16; ++j)
+            if (n0 + j < p.n_extent) slot[size_t(n0 + j) * p.ld_out + m] = v[j];
+        }
+      };
+      auto add_partial = [&](const float* slot, int n0, float (&v)[16]) {
+        if (!chunk_valid(n0)) return;
+        if (!p.swapped) {
+          const size_t base = size_t(m) * p.ld_out + n0;
+          if (n0 + 16 <= p.n_extent && (p.ld_out & 3) == 0) {
+            const float4* src = reinterpret_cast<const float4*>(slot + base);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const float4 t = __ldcg(src + q);
+              v[4 * q] += t.x; v[4 * q + 1] += t.y; v[4 * q + 2] += t.z; v[4 * q + 3] += t.w;
             }
           } else {
-            // thread = feature m, registers = 16 consecutive tokens
-            if (m_ok) {
-              const float b = p.bias ? p.bias_scale * __bfloat162float(p.bias[m]) : 0.f;
+            for (int j = 0; j < 16 && n0 + j < p.n_extent; ++j) v[j] += __ldcg(slot + base + j);
+          }
+        } else {
 #pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                const int t = n0 + j;
-                if (t < p.n_extent) {
-                  float x = apply_act(__uint_as_float(r[j]) + b, p.act);
-                  const size_t idx = size_t(t) * p.ld_out + m;
-                  if (p.residual) x += __bfloat162float(p.residual[idx]);
-                  p.out[idx] = __float2bfloat16(x);
-                }
+          for (int j = 0; j < 16; ++j)
+            if (n0 + j < p.n_extent) v[j] += __ldcg(slot + size_t(n0 + j) * p.ld_out + m);
+        }
+      };
+      auto finalize = [&](int n0, float (&v)[16]) {  // bias, activation, residual, bf16 store
+        if (!chunk_valid(n0)) return;
+        if (!p.swapped) {
+          const size_t base = size_t(m) * p.ld_out + n0;
+          if (n0 + 16 <= p.n_extent && (p.ld_out & 7) == 0) {
+            if (p.bias) {
+              const uint4* bp = reinterpret_cast<const uint4*>(p.bias + n0);
+              const uint4 b0 = bp[0], b1 = bp[1];
+              const uint32_t bw[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                v[2 * j] += p.bias_scale * bf16_bits_to_float(bw[j] & 0xFFFF);
+                v[2 * j + 1] += p.bias_scale * bf16_bits_to_float(bw[j] >> 16);
               }
+            }
+            if (p.act) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) v[j] = apply_act(v[j], p.act);
+            }
+            if (p.residual) {
+              const uint4* rp = reinterpret_cast<const uint4*>(p.residual + base);
+              const uint4 r0 = rp[0], r1 = rp[1];
+              const uint32_t rw[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                v[2 * j] += bf16_bits_to_float(rw[j] & 0xFFFF);
+                v[2 * j + 1] += bf16_bits_to_float(rw[j] >> 16);
+              }
+            }
+            uint4 o0, o1;
+            o0.x = pack_bf16x2(v[0], v[1]);   o0.y = pack_bf16x2(v[2], v[3]);
+            o0.z = pack_bf16x2(v[4], v[5]);   o0.w = pack_bf16x2(v[6], v[7]);
+            o1.x = pack_bf16x2(v[8], v[9]);   o1.y = pack_bf16x2(v[10], v[11]);
+            o1.z = pack_bf16x2(v[12], v[13]); o1.w = pack_bf16x2(v[14], v[15]);
+            uint4* op = reinterpret_cast<uint4*>(p.out + base);
+            op[0] = o0;
+            op[1] = o1;
+          } else {
+            for (int j = 0; j < 16 && n0 + j < p.n_extent; ++j) {
+              float x = v[j] + (p.bias ? p.bias_scale * __bfloat162float(p.bias[n0 + j]) : 0.f);
+              x = apply_act(x, p.act);
+              if (p.residual) x += __bfloat162float(p.residual[base + j]);
+              p.out[base + j] = __float2bfloat16(x);
             }
           }
         } else {
-          // push the fp32 partial to every rank's slot
-          if (!p.swapped) {
-            if (m_ok && n0 < p.n_extent) {
-              const size_t base = size_t(m) * p.ld_out + n0;
-              if (n0 + 16 <= p.n_extent && (p.ld_out & 3) == 0) {
+          const float b = p.bias ? p.bias_scale * __bfloat162float(p.bias[m]) : 0.f;
 #pragma unroll
-                for (int d = 0; d < MAX_WORLD; ++d) {
-                  if (d < p.world) {
-                    uint4* dst = reinterpret_cast<uint4*>(my_slots[d] + base);
-                    dst[0] = make_uint4(r[0], r[1], r[2], r[3]);
-                    dst[1] = make_uint4(r[4], r[5], r[6], r[7]);
-                    dst[2] = make_uint4(r[8], r[9], r[10], r[11]);
-                    dst[3] = make_uint4(r[12], r[13], r[14], r[15]);
-                  }
-                }
-              } else {
-                for (int d = 0; d < p.world; ++d)
-                  for (int j = 0; j < 16 && n0 + j < p.n_extent; ++j) my_slots[d][base + j] = __uint_as_float(r[j]);
-              }
-            }
-          } else {
-            if (m_ok) {
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                const int t = n0 + j;
-                if (t < p.n_extent) {
-                  const size_t idx = size_t(t) * p.ld_out + m;
-#pragma unroll
-                  for (int d = 0; d < MAX_WORLD; ++d)
-                    if (d < p.world) my_slots[d][idx] = __uint_as_float(r[j]);
-                }
-              }
+          for (int j = 0; j < 16; ++j) {
+            if (n0 + j < p.n_extent) {
+              float x = apply_act(v[j] + b, p.act);
+              const size_t idx = size_t(n0 + j) * p.ld_out + m;
+              if (p.residual) x += __bfloat162float(p.residual[idx]);
+              p.out[idx] = __float2bfloat16(x);
             }
           }
         }
-      }
-      // accumulator buffer may be overwritten by the MMA warp from here on
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      };
+      auto push_to_peers = [&](int n0, const float (&v)[16]) {  // this rank's (split-reduced) partial -> slot[rank] everywhere
+#pragma unroll
+        for (int d = 0; d < MAX_WORLD; ++d)
+          if (d < p.world) store_partial(p.slots[d] + size_t(p.rank) * p.slot_stride, n0, v);
+      };
 
-      if (p.reduce) {
+      const bool split_k = p.k_splits > 1;
+      if (!split_k) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+          float v[16];
+          read_acc(c0, v);
+          if (p.world > 1) push_to_peers(nt * BN + c0, v);
+          else finalize(nt * BN + c0, v);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[acc]);  // accumulators may be overwritten from here on
+      } else {
+        // split-K: park the partial in a local slot; the LAST split to arrive for this tile adds them up in split
+        // order (deterministic) and carries on - nobody ever waits for another CTA.
+        float* my_slot = p.slots[p.rank] + size_t(p.world + split) * p.slot_stride;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+          float v[16];
+          read_acc(c0, v);
+          store_partial(my_slot, nt * BN + c0, v);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[acc]);
+        __threadfence();
+        asm volatile("bar.sync 2, %0;" ::"n"(EPI_THREADS) : "memory");
+        if (threadIdx.x == 64) {
+          const uint32_t old = atomicAdd(p.split_counters + tile, 1u);
+          const bool last = old == uint32_t(p.k_splits - 1);
+          if (last) p.split_counters[tile] = 0;  // every other split has arrived: safe to re-arm for the next call
+          *epi_last = last ? 1u : 0u;
+        }
+        asm volatile("bar.sync 2, %0;" ::"n"(EPI_THREADS) : "memory");
+        if (*epi_last) {
+          __threadfence();
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += 16) {
+            float v[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = 0.f;
+            for (int sp = 0; sp < p.k_splits; ++sp)
+              add_partial(p.slots[p.rank] + size_t(p.world + sp) * p.slot_stride, nt * BN + c0, v);
+            if (p.world > 1) push_to_peers(nt * BN + c0, v);
+            else finalize(nt * BN + c0, v);
+          }
+        }
+      }
+      if (p.world > 1 && (!split_k || *epi_last)) {
         // make this tile's partial visible system-wide, then count one arrival on every rank
         __threadfence_system();
         asm volatile("bar.sync 2, %0;" ::"n"(EPI_THREADS) : "memory");
@@ -356,11 +426,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     }
   }
 
-  // ---------------- reduce phase ----------------
+  // ---------------- cross-rank reduce phase ----------------
   __syncthreads();
-  if (p.reduce) {
-    const uint32_t contributions = uint32_t(p.world * p.k_splits);
-    const int n_slots = p.world * p.k_splits;
+  if (p.world > 1) {
+    const uint32_t contributions = uint32_t(p.world);
     const float* base_slot = p.slots[p.rank];
     // token / feature extents of one tile in out[token, feature] coordinates
     const int tok_tile = p.swapped ? BN : BM;
@@ -392,13 +461,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           const size_t idx = size_t(t) * p.ld_out + f;
           float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
           if (vec_ok) {
-            for (int k = 0; k < n_slots; ++k) {
+            for (int k = 0; k < p.world; ++k) {
               const float4 v = __ldcg(reinterpret_cast<const float4*>(base_slot + size_t(k) * p.slot_stride + idx));
               s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
             }
           } else {
             float* sp = &s.x;
-            for (int k = 0; k < n_slots; ++k)
+            for (int k = 0; k < p.world; ++k)
               for (int j = 0; j < 4 && f + j < feat0 + feat_n; ++j) sp[j] += __ldcg(base_slot + size_t(k) * p.slot_stride + idx + j);
           }
           float o[4] = {s.x, s.y, s.z, s.w};
@@ -457,11 +526,12 @@ static int make_tmap_2d(CUtensorMap* map, const void* ptr, uint64_t rows, uint64
   return r == CUDA_SUCCESS ? TPB_OK : TPB_ERR_TMAP;
 }
 
-template <int BN>
+template <int BN, int KBOX, int NACC>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, int grid, cudaStream_t stream) {
-  constexpr size_t stage_bytes = size_t(BM * BK * 2 + BN * BK * 2);
-  int stages = int((200 * 1024) / stage_bytes);
+  constexpr size_t stage_bytes = size_t(KBOX) * size_t(BM * BK * 2 + BN * BK * 2);
+  int stages = int((227 * 1024 - 2048) / stage_bytes);
   if (stages > MAX_STAGES) stages = MAX_STAGES;
+  if (stages < 2) stages = 2;
   if (stages > p.kb_per_split + 1 && p.m_tiles * p.n_tiles * p.k_splits <= grid) stages = max(2, p.kb_per_split + 1);
   p.stages = stages;
   size_t smem = stages * stage_bytes + 1024 /*align*/ + (2 * MAX_STAGES + 4) * 8 + 16;
@@ -470,11 +540,11 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams&
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && configured[dev] < smem) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BN, KBOX, NACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     if (e != cudaSuccess) return TPB_ERR_CUDA;
     configured[dev] = smem;
   }
-  gemm_bf16_tcgen05_kernel<BN><<<grid, NUM_THREADS, smem, stream>>>(ta, tb, p);
+  gemm_bf16_tcgen05_kernel<BN, KBOX, NACC><<<grid, NUM_THREADS, smem, stream>>>(ta, tb, p);
   return cudaGetLastError() == cudaSuccess ? TPB_OK : TPB_ERR_CUDA;
 }
 
@@ -492,7 +562,9 @@ static int sm_count() {
 using namespace tpb;
 
 // Plan of a linear layer out[tokens, features] = x[tokens, K] @ w[features, K]^T.
-extern "C" int tpb_gemm_plan(int tokens, int features, int k, int world, int force_splits, tpb_gemm_plan_t* plan) {
+// force_splits > 0 fixes the split-K factor; force_kbox > 0 fixes the k-blocks per stage (1, 2 or 4).
+extern "C" int tpb_gemm_plan(int tokens, int features, int k, int world, int force_splits, int force_kbox,
+                             tpb_gemm_plan_t* plan) {
   if (!plan || tokens <= 0 || features <= 0 || k <= 0) return TPB_ERR_ARG;
   const int sms = sm_count();
   plan->swapped = tokens <= 64 ? 1 : 0;
@@ -509,18 +581,25 @@ extern "C" int tpb_gemm_plan(int tokens, int features, int k, int world, int for
     plan->n_tiles = (features + bn - 1) / bn;
   }
   plan->bn = bn;
-  plan->k_blocks = (k + BK - 1) / BK;
-  int splits = 1;
+  int kbox = (bn <= 32) ? 2 : 1;  // decode-sized GEMMs are a pure weight stream: fetch 256 contiguous bytes per row
+  if (force_kbox > 0) kbox = force_kbox;
+  if (bn > 32 || (kbox != 1 && kbox != 2 && kbox != 4)) kbox = 1;
+  plan->kbox = kbox;
+  plan->k_blocks = ((k + BK - 1) / BK + kbox - 1) / kbox;  // in units of one pipeline stage (kbox * 64 columns)
   const int tiles = plan->m_tiles * plan->n_tiles;
+  int splits = 1;
   if (force_splits > 0) {
     splits = force_splits;
-  } else if (tiles < sms && plan->k_blocks >= 8) {
+  } else if (tiles * 2 <= sms) {
+    // few output tiles: split K so that more SMs stream weights, but keep >= 8 stages of work per split and at
+    // most 4 splits (measured on B200: beyond that the extra partial tiles cost more than the added SMs bring)
     splits = sms / tiles;
-    const int max_by_k = plan->k_blocks / 4;  // at least 4 k-blocks per split
-    if (splits > max_by_k) splits = max_by_k;
-    if (splits > 16) splits = 16;
+    const int by_k = plan->k_blocks / 8;
+    if (splits > by_k) splits = by_k;
+    if (splits > 4) splits = 4;
     if (splits < 1) splits = 1;
   }
+  if (splits > plan->k_blocks) splits = plan->k_blocks;
   int per = (plan->k_blocks + splits - 1) / splits;
   splits = (plan->k_blocks + per - 1) / per;  // no empty split
   plan->k_splits = splits;
@@ -563,7 +642,7 @@ extern "C" int tpb_gemm_bf16(const void* x, const void* w, void* out, const void
   if (plan->reduce) {
     if (!rc || rc->world < 1 || rc->world > MAX_WORLD) return TPB_ERR_ARG;
     if (size_t(tokens) * size_t(ld_out) > rc->slot_stride) return TPB_ERR_WORKSPACE;
-    if (size_t(rc->world) * plan->k_splits > size_t(rc->max_slots) || plan->tiles > rc->max_tiles) return TPB_ERR_WORKSPACE;
+    if (rc->world + plan->k_splits > rc->max_slots || plan->tiles > rc->max_tiles || !rc->split_counters) return TPB_ERR_WORKSPACE;
     p.world = rc->world;
     p.rank = rc->rank;
     for (int d = 0; d < rc->world; ++d) {
@@ -571,6 +650,7 @@ extern "C" int tpb_gemm_bf16(const void* x, const void* w, void* out, const void
       p.arrivals[d] = static_cast<uint32_t*>(rc->arrivals[d]);
     }
     p.expected = static_cast<uint32_t*>(rc->expected);
+    p.split_counters = static_cast<uint32_t*>(rc->split_counters);
     p.slot_stride = rc->slot_stride;
     p.status = static_cast<uint32_t*>(rc->status);
   } else {
@@ -588,12 +668,16 @@ extern "C" int tpb_gemm_bf16(const void* x, const void* w, void* out, const void
   rcode = make_tmap_2d(&tb, b_ptr, b_rows, k, ldb, plan->bn);
   if (rcode != TPB_OK) return rcode;
 
-  switch (plan->bn) {
-    case 16: return launch_gemm<16>(ta, tb, p, plan->grid, stream);
-    case 32: return launch_gemm<32>(ta, tb, p, plan->grid, stream);
-    case 64: return launch_gemm<64>(ta, tb, p, plan->grid, stream);
-    case 128: return launch_gemm<128>(ta, tb, p, plan->grid, stream);
-    case 256: return launch_gemm<256>(ta, tb, p, plan->grid, stream);
+  switch (plan->bn * 10 + plan->kbox) {
+    case 161: return launch_gemm<16, 1, 8>(ta, tb, p, plan->grid, stream);
+    case 162: return launch_gemm<16, 2, 8>(ta, tb, p, plan->grid, stream);
+    case 164: return launch_gemm<16, 4, 8>(ta, tb, p, plan->grid, stream);
+    case 321: return launch_gemm<32, 1, 8>(ta, tb, p, plan->grid, stream);
+    case 322: return launch_gemm<32, 2, 8>(ta, tb, p, plan->grid, stream);
+    case 324: return launch_gemm<32, 4, 8>(ta, tb, p, plan->grid, stream);
+    case 641: return launch_gemm<64, 1, 2>(ta, tb, p, plan->grid, stream);
+    case 1281: return launch_gemm<128, 1, 1>(ta, tb, p, plan->grid, stream);
+    case 2561: return launch_gemm<256, 1, 1>(ta, tb, p, plan->grid, stream);
     default: return TPB_ERR_ARG;
   }
 }

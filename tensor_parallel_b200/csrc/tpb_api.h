@@ -24,6 +24,7 @@ enum {
 typedef struct {
   int swapped;  // 1: weight rows fill the 128 tensor-core rows (few tokens), 0: tokens do
   int bn;       // accumulator columns per tile
+  int kbox;     // 64-column k-blocks fetched per pipeline stage (k_blocks / kb_per_split count stages)
   int m_tiles, n_tiles, k_blocks, k_splits, kb_per_split;
   int reduce;   // partial tiles go through the slot workspace (split-K and / or several ranks)
   int grid;
@@ -36,15 +37,17 @@ typedef struct {
 // launching GPU; slots[d] / arrivals[d] point into rank d's memory (peer-mapped for d != rank).
 typedef struct {
   int world, rank;
-  void* slots[TPB_MAX_WORLD];     // fp32 [max_slots][slot_stride]
+  void* slots[TPB_MAX_WORLD];     // fp32 [max_slots][slot_stride]; needs world + k_splits slots
   void* arrivals[TPB_MAX_WORLD];  // uint32 [max_tiles]
   void* expected;                 // local uint32 [max_tiles]
+  void* split_counters;           // local uint32 [max_tiles], zero-initialised
   void* status;                   // local uint32 status word
   size_t slot_stride;             // elements per slot
   int max_slots, max_tiles;
 } tpb_reduce_ctx_t;
 
-int tpb_gemm_plan(int tokens, int features, int k, int world, int force_splits, tpb_gemm_plan_t* plan);
+int tpb_gemm_plan(int tokens, int features, int k, int world, int force_splits, int force_kbox,
+                  tpb_gemm_plan_t* plan);
 
 // out[tokens, features] = act(x[tokens, k] @ w[features, k]^T + bias_scale * bias) + residual
 // (bf16 operands, fp32 accumulation).  With rc->world > 1 the product is additionally summed over all ranks

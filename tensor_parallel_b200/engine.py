@@ -18,6 +18,7 @@ maths through Python wrappers, host barriers and one NCCL call per collective
 from __future__ import annotations
 
 import math
+import os
 from typing import List, Optional
 
 import torch
@@ -42,7 +43,7 @@ class LlamaEngine:
         self.head_dim = cfg.hidden_size // cfg.num_attention_heads
         self.hidden = cfg.hidden_size
         self.max_batch, self.max_seq = max_batch, max_seq
-        self.use_graph = use_graph
+        self.use_graph = use_graph and not os.environ.get("TPB_NO_GRAPH")
         model = _unwrap(lm.model)
         embed = _unwrap(model.embed_tokens)
         self.device = embed.weight.device

@@ -83,6 +83,7 @@ class RankComm:
         with torch.cuda.device(device):
             self.epochs = torch.zeros(COMM_MAX_BLOCKS, dtype=torch.int32, device=device)
             self.expected = torch.zeros(2 * MAX_TILES, dtype=torch.int32, device=device)
+            self.split_counters = torch.zeros(2 * MAX_TILES, dtype=torch.int32, device=device)
             self.status = torch.zeros(4, dtype=torch.int32, device=device)
         self.local = tensor_from_ptr(self.base[rank], layout.total, device)
         self.staging_in = self.local[layout.off_staging_in : layout.off_staging_in + layout.staging_bytes]
@@ -104,6 +105,7 @@ class RankComm:
             ctx.slots[r] = self.base[r] + self.layout.off_slots + region * self.layout.region_slot_bytes
             ctx.arrivals[r] = self.base[r] + self.layout.off_arrivals + region * MAX_TILES * 4
         ctx.expected = self.expected.data_ptr() + region * MAX_TILES * 4
+        ctx.split_counters = self.split_counters.data_ptr() + region * MAX_TILES * 4
         ctx.status = self.status.data_ptr()
         ctx.slot_stride = self.layout.slot_stride
         ctx.max_slots, ctx.max_tiles = self.layout.max_slots, MAX_TILES
@@ -131,7 +133,7 @@ class RankComm:
         if tokens * features > self.layout.slot_stride:
             return False
         plan = native.gemm_plan(tokens, features, k, self.world)
-        return self.world * plan.k_splits <= self.layout.max_slots and plan.tiles <= MAX_TILES
+        return self.world + plan.k_splits <= self.layout.max_slots and plan.tiles <= MAX_TILES
 
     # -- stand-alone collectives on the staging buffers -------------------------------------------
 

@@ -34,14 +34,14 @@ c_void_p, c_int, c_float, c_ll, c_size_t = ctypes.c_void_p, ctypes.c_int, ctypes
 
 
 class GemmPlan(ctypes.Structure):
-    _fields_ = [("swapped", c_int), ("bn", c_int), ("m_tiles", c_int), ("n_tiles", c_int), ("k_blocks", c_int),
+    _fields_ = [("swapped", c_int), ("bn", c_int), ("kbox", c_int), ("m_tiles", c_int), ("n_tiles", c_int), ("k_blocks", c_int),
                 ("k_splits", c_int), ("kb_per_split", c_int), ("reduce", c_int), ("grid", c_int), ("tokens_pad", c_int),
                 ("tiles", c_int), ("slot_elems", c_size_t)]
 
 
 class ReduceCtx(ctypes.Structure):
     _fields_ = [("world", c_int), ("rank", c_int), ("slots", c_void_p * 8), ("arrivals", c_void_p * 8),
-                ("expected", c_void_p), ("status", c_void_p), ("slot_stride", c_size_t), ("max_slots", c_int),
+                ("expected", c_void_p), ("split_counters", c_void_p), ("status", c_void_p), ("slot_stride", c_size_t), ("max_slots", c_int),
                 ("max_tiles", c_int)]
 
 
@@ -76,7 +76,7 @@ def _dtype_code(t: torch.Tensor) -> int:
 # ------------------------------------------------------------------------------------------------
 
 MAX_TILES = 4096
-MAX_SLOTS = 16
+MAX_SLOTS = 17  # 1 cross-rank slot (world = 1) + up to 16 split-K partials
 
 
 class DeviceState:
@@ -87,6 +87,7 @@ class DeviceState:
         self.status = torch.zeros(4, dtype=torch.int32, device=device)
         self.arrivals = torch.zeros(MAX_TILES, dtype=torch.int32, device=device)
         self.expected = torch.zeros(MAX_TILES, dtype=torch.int32, device=device)
+        self.split_counters = torch.zeros(MAX_TILES, dtype=torch.int32, device=device)
         self.slots: Optional[torch.Tensor] = None
         self.slot_stride = 0
         self.ctx = ReduceCtx()
@@ -98,6 +99,7 @@ class DeviceState:
         ctx.slots[0] = self.slots.data_ptr() if self.slots is not None else 0
         ctx.arrivals[0] = self.arrivals.data_ptr()
         ctx.expected = self.expected.data_ptr()
+        ctx.split_counters = self.split_counters.data_ptr()
         ctx.status = self.status.data_ptr()
         ctx.slot_stride = self.slot_stride
         ctx.max_slots, ctx.max_tiles = MAX_SLOTS, MAX_TILES
@@ -133,19 +135,19 @@ def device_state(device: torch.device) -> DeviceState:
 # GEMM
 # ------------------------------------------------------------------------------------------------
 
-LIB.tpb_gemm_plan.argtypes = [c_int, c_int, c_int, c_int, c_int, ctypes.POINTER(GemmPlan)]
+LIB.tpb_gemm_plan.argtypes = [c_int, c_int, c_int, c_int, c_int, c_int, ctypes.POINTER(GemmPlan)]
 LIB.tpb_gemm_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                               c_int, c_float, ctypes.POINTER(GemmPlan), ctypes.POINTER(ReduceCtx), c_void_p]
 ACT_CODES = {None: 0, "none": 0, "relu": 1, "gelu": 2, "gelu_tanh": 3, "silu": 4}
 _plan_cache: Dict[Tuple, GemmPlan] = {}
 
 
-def gemm_plan(tokens: int, features: int, k: int, world: int = 1, force_splits: int = 0) -> GemmPlan:
-    key = (tokens, features, k, world, force_splits, torch.cuda.current_device())
+def gemm_plan(tokens: int, features: int, k: int, world: int = 1, force_splits: int = 0, force_kbox: int = 0) -> GemmPlan:
+    key = (tokens, features, k, world, force_splits, force_kbox, torch.cuda.current_device())
     plan = _plan_cache.get(key)
     if plan is None:
         plan = GemmPlan()
-        check(LIB.tpb_gemm_plan(tokens, features, k, world, force_splits, ctypes.byref(plan)), "gemm_plan")
+        check(LIB.tpb_gemm_plan(tokens, features, k, world, force_splits, force_kbox, ctypes.byref(plan)), "gemm_plan")
         _plan_cache[key] = plan
     return plan
 
@@ -159,7 +161,7 @@ def gemm_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
 
 
 def gemm_nt(x2d: torch.Tensor, w: torch.Tensor, bias=None, residual=None, act=None, out=None, force_splits: int = 0,
-            reduce_ctx: Optional[ReduceCtx] = None, world: int = 1, bias_scale: float = 1.0) -> torch.Tensor:
+            reduce_ctx: Optional[ReduceCtx] = None, world: int = 1, bias_scale: float = 1.0, force_kbox: int = 0) -> torch.Tensor:
     """``out[tokens, features] = act(x2d @ w.T + bias) + residual`` on the tcgen05 kernel."""
     global launch_count
     tokens, k = x2d.shape
@@ -170,7 +172,7 @@ def gemm_nt(x2d: torch.Tensor, w: torch.Tensor, bias=None, residual=None, act=No
         w = w.contiguous()
     if out is None:
         out = torch.empty(tokens, features, dtype=torch.bfloat16, device=x2d.device)
-    plan = gemm_plan(tokens, features, k, world, force_splits)
+    plan = gemm_plan(tokens, features, k, world, force_splits, force_kbox)
     state = device_state(x2d.device)
     ctx = reduce_ctx
     if ctx is None:
