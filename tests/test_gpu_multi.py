@@ -1,0 +1,145 @@
+"""Two-GPU tests of the device-side communication path (one process per GPU, NCCL only as the
+oracle): stand-alone collectives on the symmetric heap, the fused GEMM + all-reduce kernel, the
+distributed tensor-parallel wrapper (training parity incl. ZeRO-3) and the serving engine at TP=2.
+Child processes run with NVLS disabled; every device-side wait is time-bounded."""
+import os
+import socket
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _setup(rank, world, port):
+    sys.path.insert(0, REPO)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+
+
+def _collectives_worker(rank, world, port, out_dir):
+    _setup(rank, world, port)
+    try:
+        from tensor_parallel_b200.ops import comm as C
+
+        dev = torch.device("cuda", rank)
+        rc = C.make_process_comm(dev, staging_bytes=64 << 20)
+        torch.manual_seed(100 + rank)
+        for dtype in (torch.bfloat16, torch.float32):
+            for n, algo in ((4096, 0), (4096, 1), (1 << 20, -1), (1000 * 8, 1)):
+                x = torch.randn(n, device=dev, dtype=dtype)
+                want = x.float().clone()
+                dist.all_reduce(want)
+                for _ in range(3):  # repeated calls: epochs only grow
+                    got = rc.all_reduce(x, force_algo=algo).clone()
+                tol = dict(atol=3e-2, rtol=3e-2) if dtype == torch.bfloat16 else dict(atol=1e-5, rtol=1e-5)
+                torch.testing.assert_close(got.float(), want, **tol)
+            x = torch.randn(3, 1000, device=dev, dtype=dtype)
+            parts = [torch.empty_like(x) for _ in range(world)]
+            dist.all_gather(parts, x)
+            torch.testing.assert_close(rc.all_gather(x).clone(), torch.stack(parts))
+            y = torch.randn(world, 5, 1000, device=dev, dtype=dtype)
+            want = y.float().clone()
+            dist.all_reduce(want)
+            tol = dict(atol=3e-2, rtol=3e-2) if dtype == torch.bfloat16 else dict(atol=1e-5, rtol=1e-5)
+            torch.testing.assert_close(rc.reduce_scatter(y).clone().float(), want[rank], **tol)
+        torch.cuda.synchronize()
+        rc.check_status()
+
+        # fused GEMM + all-reduce (row-parallel linear): decode shapes with and without split-K, with bias / residual
+        from tensor_parallel_b200.ops import native
+
+        for tokens, features, k in ((8, 4096, 512), (8, 4096, 1376), (16, 1024, 2048), (1, 256, 64)):
+            x = torch.randn(tokens, k, device=dev, dtype=torch.bfloat16)
+            w = torch.randn(features, k, device=dev, dtype=torch.bfloat16) * 0.05
+            bias = torch.randn(features, device=dev, dtype=torch.bfloat16)
+            dist.broadcast(bias, 0)
+            res = torch.randn(tokens, features, device=dev, dtype=torch.bfloat16)
+            dist.broadcast(res, 0)
+            want = x.float() @ w.float().t()
+            dist.all_reduce(want)
+            want = want + bias.float() + res.float()
+            for _ in range(4):  # alternates the two workspace halves
+                got = rc.gemm_allreduce(x, w, bias=bias, residual=res, bias_scale=1.0)
+            torch.cuda.synchronize()
+            rc.check_status()
+            err = (got.float() - want).abs().max().item()
+            assert err <= 0.02 * want.abs().max().item() + 0.05, (tokens, features, k, err)
+        open(os.path.join(out_dir, f"ok{rank}"), "w").close()
+    finally:
+        dist.destroy_process_group()
+
+
+def _model_worker(rank, world, port, out_dir):
+    _setup(rank, world, port)
+    try:
+        import tensor_parallel_b200 as tp
+        from tensor_parallel_b200.models.llama import LlamaConfig, LlamaForCausalLM
+
+        dev = torch.device("cuda", rank)
+        torch.manual_seed(0)
+        cfg = LlamaConfig(vocab_size=512, hidden_size=256, intermediate_size=688, num_hidden_layers=2, num_attention_heads=4,
+                          num_key_value_heads=2)
+        # fp32 training parity (stock torch compute, device-side collectives with autograd)
+        model = LlamaForCausalLM(cfg).to(dev)
+        ids = torch.randint(0, 512, (2, 24), device=dev)
+        dist.broadcast(ids, 0)
+        ref = model(input_ids=ids, labels=ids)
+        ref.loss.backward()
+        ref_grads = {n: p.grad.clone() for n, p in model.named_parameters()}
+        model.zero_grad()
+        wrapped = tp.tensor_parallel(model, [dev], sharded=True)
+        assert wrapped._device_backend is not None, "device collectives were not selected"
+        out = wrapped(input_ids=ids, labels=ids)
+        torch.testing.assert_close(out.logits, ref.logits, atol=2e-3, rtol=1e-3)
+        out.loss.backward()
+        gate = wrapped.module_shards[0].model.layers[0].mlp.tp_wrapped_module.gate_proj.weight.grad
+        want = torch.tensor_split(ref_grads["model.layers.0.mlp.gate_proj.weight"], world, dim=0)[rank]
+        torch.testing.assert_close(gate, want, atol=2e-3, rtol=1e-2)
+        mgr = wrapped.sharding_manager
+        flats = [torch.zeros_like(mgr.flat_shards[0].grad) for _ in range(world)]
+        dist.all_gather(flats, mgr.flat_shards[0].grad)
+        for name, grad in zip(mgr.sharded_param_names, mgr._combine(torch.stack(flats))):
+            torch.testing.assert_close(grad, ref_grads[name.replace("tp_wrapped_module.", "")], atol=2e-3, rtol=1e-2, msg=name)
+
+        # bf16 serving engine at TP=2 vs the single-GPU engine on the same weights
+        torch.manual_seed(1)
+        full = LlamaForCausalLM(cfg).to(device=dev, dtype=torch.bfloat16).eval()
+        for p in full.parameters():
+            dist.broadcast(p.data, 0)
+        prompt = torch.randint(0, 512, (3, 40), device=dev)
+        dist.broadcast(prompt, 0)
+        single = tp.TensorParallel(full, [dev])  # one device: the module itself
+        want_logits = single.prefill(prompt.cpu(), max_new_tokens=8)
+        want_tokens = single.generate(prompt.cpu(), max_new_tokens=8)
+        import copy
+
+        tp2 = tp.tensor_parallel(copy.deepcopy(full), [dev])
+        got_logits = tp2.prefill(prompt.cpu(), max_new_tokens=8)
+        torch.testing.assert_close(got_logits, want_logits, atol=0.1, rtol=0.05)
+        got_tokens = tp2.generate(prompt.cpu(), max_new_tokens=8)
+        assert tp2._engine.world == world and tp2._engine.graph is not None
+        agree = (got_tokens == want_tokens).float().mean().item()
+        assert agree > 0.9, agree  # bf16 summation order differs between 1 and 2 ranks; near-ties may flip
+        torch.cuda.synchronize()
+        tp2._engine.comm.check_status()
+        open(os.path.join(out_dir, f"ok{rank}"), "w").close()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("worker", [_collectives_worker, _model_worker])
+def test_two_gpus(worker, tmp_path):
+    mp.spawn(worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    assert sorted(os.listdir(tmp_path)) == ["ok0", "ok1"]
