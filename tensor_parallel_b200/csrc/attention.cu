@@ -527,3 +527,50 @@ extern "C" int tpb_attn_prefill(const void* q, const void* k, const void* v, voi
   }
   return cudaGetLastError() == cudaSuccess ? TPB_OK : TPB_ERR_CUDA;
 }
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free variant of tpb_attn_decode (declared and documented in tpb_noalloc.h).
+// ------------------------------------------------------------------------------------------------
+#include <mutex>
+
+#include "tpb_noalloc.h"
+
+// Workspace of the split-KV partial results, owned by the library.  In host code this name is only a
+// handle for cudaGetSymbolAddress, never a pointer that a kernel could use.
+static __device__ __align__(256) float g_noalloc_decode_scratch[TPB_NOALLOC_SCRATCH_FLOATS];
+
+namespace {
+std::mutex g_noalloc_mutex;
+float* g_noalloc_scratch_addr[64] = {nullptr};  // per device: device address of the array above
+
+// Device address of the workspace on the current device; resolved once per device.
+int noalloc_scratch(float** addr) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return TPB_ERR_CUDA;
+  std::lock_guard<std::mutex> guard(g_noalloc_mutex);
+  if (!g_noalloc_scratch_addr[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_noalloc_decode_scratch) != cudaSuccess || !p) return TPB_ERR_CUDA;
+    g_noalloc_scratch_addr[dev] = static_cast<float*>(p);
+  }
+  *addr = g_noalloc_scratch_addr[dev];
+  return TPB_OK;
+}
+}  // namespace
+
+extern "C" int tpb_attn_decode_noalloc(const void* q, const void* kcache, const void* vcache, void* out,
+                                       const int* len_ptr, int len_add, int batch, int q_heads, int kv_heads,
+                                       int head_dim, int max_seq, int splits, float scale, void* stream_) {
+  if (!q || !kcache || !vcache || !out || batch <= 0 || q_heads <= 0 || kv_heads <= 0 || splits < 1) return TPB_ERR_ARG;
+  if (head_dim != 64 && head_dim != 128) return TPB_ERR_SIZE;
+  const long long rows = (long long)batch * q_heads * splits;
+  if (rows * (head_dim + 2) > (long long)TPB_NOALLOC_SCRATCH_FLOATS) return TPB_ERR_SIZE;
+  float* scratch = nullptr;
+  const int rc = noalloc_scratch(&scratch);
+  if (rc != TPB_OK) return rc;
+  // layout inside the workspace: [rows * head_dim] partial outputs, then [rows * 2] (max, sum) pairs
+  float* part_o = scratch;
+  float* part_ml = scratch + rows * head_dim;
+  return tpb_attn_decode(q, kcache, vcache, out, part_o, part_ml, len_ptr, len_add, batch, q_heads, kv_heads, head_dim,
+                         max_seq, splits, scale, stream_);
+}
