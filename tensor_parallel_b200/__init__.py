@@ -28,6 +28,7 @@ from tensor_parallel_b200.parallel.legacy import Sharded
 from tensor_parallel_b200.parallel.rules import Config
 from tensor_parallel_b200.parallel.runtime import TensorParallel
 from tensor_parallel_b200.parallel.surgery import make_distributed_shard, make_shard
+from tensor_parallel_b200 import optim  # noqa: E402,F401
 
 
 def __getattr__(name):

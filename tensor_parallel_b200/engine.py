@@ -96,7 +96,8 @@ class LlamaEngine:
         self.act = torch.zeros(B, self.ff, **bf)
         self.logits_local = torch.zeros(B, self.vocab_local, **bf)
         self.next_ids = torch.zeros(B, dtype=torch.int64, device=dev)
-        self.splits = max(1, min(16, math.ceil(2 * 148 / (B * self.nkv))))
+        # split the key range only when (batch x kv heads) alone cannot occupy the SMs
+        self.splits = 1 if B * self.nkv >= 128 else max(1, min(8, math.ceil(256 / (B * self.nkv))))
         self.attn_ws = (torch.empty(B * self.nq * self.splits * D, dtype=torch.float32, device=dev),
                         torch.empty(B * self.nq * self.splits * 2, dtype=torch.float32, device=dev))
         self.graph: Optional[torch.cuda.CUDAGraph] = None

@@ -1,0 +1,130 @@
+"""Small single-kernel workloads for timing and for Nsight Compute captures.
+
+    python -m tensor_parallel_b200.profiling <case> [--iters N]
+
+Each case allocates a few hundred MB at most (inputs larger than the 126 MB L2 where the kernel is
+memory-bound), warms up, then launches the kernel ``--iters`` times with a fresh operand each time (a
+ring of buffers defeats L2 reuse) and prints the median CUDA-event time with the achieved bandwidth or
+FLOP rate.  Under ``ncu -k regex:<kernel> -c 3`` the same command captures those launches.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+
+import torch
+
+from tensor_parallel_b200.ops import native
+
+
+def _time(fn, iters: int):
+    for i in range(3):
+        fn(i)
+    torch.cuda.synchronize()
+    times = []
+    for i in range(iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn(i + 3)
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) * 1e3)
+    return statistics.median(times)
+
+
+def case_gemm(tokens, features, k, iters, ring=None):
+    ring = ring or max(2, int(300e6 // (features * k * 2)) + 1)
+    ws = [torch.randn(features, k, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(ring)]
+    x = torch.randn(tokens, k, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(tokens, features, device="cuda", dtype=torch.bfloat16)
+    us = _time(lambda i: native.gemm_nt(x, ws[i % ring], out=out), iters)
+    flops = 2.0 * tokens * features * k
+    bytes_ = 2.0 * (features * k + tokens * k + tokens * features)
+    return {"us": us, "tflops": flops / us / 1e6, "tbps": bytes_ / us / 1e6, "plan": {f: getattr(native.gemm_plan(tokens, features, k), f) for f in ("swapped", "bn", "kbox", "k_splits", "grid")}}
+
+
+def case_attn_decode(batch, heads, kv_heads, ctx, iters, splits=1):
+    d, smax, ring = 128, ctx + 64, 3
+    ks = [torch.randn(batch, kv_heads, smax, d, device="cuda", dtype=torch.bfloat16) for _ in range(ring)]
+    vs = [torch.randn(batch, kv_heads, smax, d, device="cuda", dtype=torch.bfloat16) for _ in range(ring)]
+    q = torch.randn(batch, heads, d, device="cuda", dtype=torch.bfloat16)
+    length = torch.tensor([ctx], device="cuda", dtype=torch.int32)
+    ws = (torch.empty(batch * heads * splits * d, device="cuda"), torch.empty(batch * heads * splits * 2, device="cuda"))
+    us = _time(lambda i: native.attn_decode(q, ks[i % ring], vs[i % ring], length, 0, splits=splits, workspace=ws), iters)
+    return {"us": us, "tbps": 2.0 * batch * kv_heads * ctx * d * 2 / us / 1e6}
+
+
+def case_attn_prefill(batch, seq, heads, d, iters):
+    q, k, v = (torch.randn(batch, seq, heads, d, device="cuda", dtype=torch.bfloat16) for _ in range(3))
+    us = _time(lambda i: native.attention_forward(q, k, v, True, None), iters)
+    return {"us": us, "tflops": 4.0 * batch * heads * seq * seq * d / 2 / us / 1e6}
+
+
+def case_norm(rows, cols, iters):
+    xs = [torch.randn(rows, cols, device="cuda", dtype=torch.bfloat16) for _ in range(3)]
+    w = torch.ones(cols, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty_like(xs[0])
+    us = _time(lambda i: native.norm_forward(xs[i % 3], w, None, 1e-6, 0, out=out), iters)
+    return {"us": us, "tbps": 2.0 * rows * cols * 2 / us / 1e6}
+
+
+def case_swiglu(rows, cols, iters):
+    gus = [torch.randn(rows, 2 * cols, device="cuda", dtype=torch.bfloat16) for _ in range(3)]
+    out = torch.empty(rows, cols, device="cuda", dtype=torch.bfloat16)
+    us = _time(lambda i: native.act_forward(gus[i % 3][:, :cols], gus[i % 3][:, cols:], 4, out=out), iters)
+    return {"us": us, "tbps": 3.0 * rows * cols * 2 / us / 1e6}
+
+
+def case_rope_append(batch, seq, heads, iters):
+    d = 128
+    qkv = torch.randn(batch * seq, 3 * heads * d, device="cuda", dtype=torch.bfloat16)
+    kc = torch.zeros(batch, heads, seq, d, device="cuda", dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    q_out = torch.empty(batch * seq, heads, d, device="cuda", dtype=torch.bfloat16)
+    pos = torch.zeros(1, device="cuda", dtype=torch.int32)
+    w = heads * d
+    us = _time(lambda i: native.qkv_rope_append(qkv[:, :w], qkv[:, w : 2 * w], qkv[:, 2 * w :], q_out, kc, vc, pos, batch, seq, d, 1e4), iters)
+    return {"us": us, "tbps": 2.0 * qkv.numel() * 2 / us / 1e6}
+
+
+def case_adamw(n, iters):
+    p = torch.randn(n, device="cuda", dtype=torch.bfloat16)
+    g = torch.randn(n, device="cuda", dtype=torch.bfloat16)
+    m, v, master = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda"), p.float()
+    us = _time(lambda i: native.adamw_step(p, g, m, v, i + 1, 1e-4, 0.9, 0.95, 1e-8, 0.1, master=master), iters)
+    return {"us": us, "tbps": n * (2 + 2 + 3 * 4 + 2 + 3 * 4) / us / 1e6}
+
+
+CASES = {
+    "gemm_decode_qkv": lambda it: case_gemm(8, 12288, 4096, it),
+    "gemm_decode_gate_up": lambda it: case_gemm(8, 22016, 4096, it),
+    "gemm_decode_down": lambda it: case_gemm(8, 4096, 11008, it),
+    "gemm_decode_o_tp8": lambda it: case_gemm(8, 4096, 512, it),
+    "gemm_prefill": lambda it: case_gemm(8192, 8192, 4096, it, ring=2),
+    "gemm_prefill_gate_up": lambda it: case_gemm(4096, 22016, 4096, it, ring=2),
+    "attn_decode": lambda it: case_attn_decode(8, 32, 32, 2048, it),
+    "attn_decode_tp8": lambda it: case_attn_decode(8, 4, 4, 2048, it, splits=8),
+    "attn_prefill": lambda it: case_attn_prefill(4, 2048, 32, 128, it),
+    "rmsnorm": lambda it: case_norm(32768, 4096, it),
+    "swiglu": lambda it: case_swiglu(16384, 11008, it),
+    "rope_append": lambda it: case_rope_append(8, 2048, 32, it),
+    "adamw": lambda it: case_adamw(64 * 1024 * 1024, it),
+}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("case", choices=sorted(CASES) + ["all"])
+    ap.add_argument("--iters", type=int, default=10)
+    args = ap.parse_args()
+    for name in (sorted(CASES) if args.case == "all" else [args.case]):
+        result = CASES[name](args.iters)
+        torch.cuda.synchronize()
+        native.device_state(torch.device("cuda", torch.cuda.current_device())).check_status()
+        print(json.dumps({"case": name, **result}), flush=True)
+        torch.cuda.empty_cache()
+
+
+if __name__ == "__main__":
+    main()
