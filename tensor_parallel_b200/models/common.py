@@ -132,6 +132,24 @@ class CausalLMBase(nn.Module):
             return None
         return OF.cross_entropy(logits[:, :-1], labels[:, 1:].to(logits.device))
 
+    def head_and_loss(self, head: nn.Module, hidden: torch.Tensor, labels: Optional[torch.Tensor]):
+        """``(logits, loss)``.  With ``config.fused_lm_loss`` and labels on a CUDA bf16 model the head GEMM is
+        fused with a (vocab-parallel) cross-entropy and full logits are never formed: ``logits`` is then None."""
+        inner = head.__dict__.get("tp_wrapped_module", head)
+        fused = (
+            labels is not None and getattr(self.config, "fused_lm_loss", False) and hidden.is_cuda
+            and hidden.dtype == torch.bfloat16 and isinstance(inner, nn.Linear) and inner.bias is None
+            and (inner.weight.shape[0] == self.config.vocab_size or "_tp_vocab_parallel" in self.__dict__)
+        )
+        if fused:
+            from tensor_parallel_b200.ops.loss import lm_head_cross_entropy
+
+            extra = self.__dict__.get("_tp_vocab_parallel", {})
+            loss = lm_head_cross_entropy(hidden[:, :-1], inner.weight, labels[:, 1:], **extra)
+            return None, loss
+        logits = head(hidden)
+        return logits, self.lm_loss(logits, labels)
+
     def generate(self, input_ids, **kwargs):
         from tensor_parallel_b200.models.generation import generate
 

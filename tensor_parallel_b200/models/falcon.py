@@ -62,6 +62,8 @@ class FalconMLP(nn.Module):
 
 
 class FalconDecoderLayer(nn.Module):
+    parallel_block = True  # attention and MLP read the same input; their partial outputs may share one all-reduce
+
     def __init__(self, config: FalconConfig):
         super().__init__()
         self.ln_attn = LayerNorm(config.hidden_size, eps=config.layer_norm_epsilon)
@@ -72,7 +74,9 @@ class FalconDecoderLayer(nn.Module):
     def forward(self, hidden, layer_past=None, attention_mask=None, position_ids=None, use_cache=False):
         attn_out, present = self.self_attention(self.ln_attn(hidden), layer_past=layer_past, attention_mask=attention_mask,
                                                 position_ids=position_ids, use_cache=use_cache)
-        return hidden + attn_out + self.mlp(self.ln_mlp(hidden)), present
+        partial = attn_out + self.mlp(self.ln_mlp(hidden))
+        reduce = self.__dict__.get("_tp_block_reduce")
+        return hidden + (partial if reduce is None else reduce(partial)), present
 
 
 class FalconModel(nn.Module):

@@ -59,6 +59,7 @@ class GPTNeoXLayer(nn.Module):
     def __init__(self, config: GPTNeoXConfig):
         super().__init__()
         self.use_parallel_residual = config.use_parallel_residual
+        self.parallel_block = bool(config.use_parallel_residual)
         self.input_layernorm = LayerNorm(config.hidden_size, eps=config.layer_norm_eps)
         self.post_attention_layernorm = LayerNorm(config.hidden_size, eps=config.layer_norm_eps)
         self.attention = GPTNeoXAttention(config)
@@ -68,7 +69,9 @@ class GPTNeoXLayer(nn.Module):
         attn_out, present = self.attention(self.input_layernorm(hidden), attention_mask=attention_mask, position_ids=position_ids,
                                            layer_past=layer_past, use_cache=use_cache)
         if self.use_parallel_residual:
-            return hidden + attn_out + self.mlp(self.post_attention_layernorm(hidden)), present
+            partial = attn_out + self.mlp(self.post_attention_layernorm(hidden))
+            reduce = self.__dict__.get("_tp_block_reduce")
+            return hidden + (partial if reduce is None else reduce(partial)), present
         hidden = hidden + attn_out
         return hidden + self.mlp(self.post_attention_layernorm(hidden)), present
 
@@ -104,5 +107,5 @@ class GPTNeoXForCausalLM(CausalLMBase):
     def forward(self, input_ids=None, past_key_values=None, attention_mask=None, position_ids=None, inputs_embeds=None,
                 labels=None, use_cache=False, **unused):
         hidden, presents = self.gpt_neox(input_ids, past_key_values, attention_mask, position_ids, inputs_embeds, use_cache)
-        logits = self.embed_out(hidden)
-        return ModelOutput(loss=self.lm_loss(logits, labels), logits=logits, past_key_values=presents)
+        logits, loss = self.head_and_loss(self.embed_out, hidden, labels)
+        return ModelOutput(loss=loss, logits=logits, past_key_values=presents)

@@ -83,6 +83,7 @@ class GPTJMLP(nn.Module):
 
 class GPTJBlock(nn.Module):
     attention_class = GPTJAttention
+    parallel_block = True  # attention and MLP read the same input; their partial outputs may share one all-reduce
 
     def __init__(self, config: GPTJConfig):
         super().__init__()
@@ -93,7 +94,9 @@ class GPTJBlock(nn.Module):
     def forward(self, hidden, layer_past=None, attention_mask=None, position_ids=None, use_cache=False):
         normed = self.ln_1(hidden)
         attn_out, present = self.attn(normed, layer_past=layer_past, attention_mask=attention_mask, position_ids=position_ids, use_cache=use_cache)
-        return hidden + attn_out + self.mlp(normed), present
+        partial = attn_out + self.mlp(normed)
+        reduce = self.__dict__.get("_tp_block_reduce")
+        return hidden + (partial if reduce is None else reduce(partial)), present
 
 
 class CodeGenBlock(GPTJBlock):
@@ -139,8 +142,8 @@ class GPTJForCausalLM(CausalLMBase):
     def forward(self, input_ids=None, past_key_values=None, attention_mask=None, position_ids=None, inputs_embeds=None,
                 labels=None, use_cache=False, **unused):
         hidden, presents = self.transformer(input_ids, past_key_values, attention_mask, position_ids, inputs_embeds, use_cache)
-        logits = self.lm_head(hidden)
-        return ModelOutput(loss=self.lm_loss(logits, labels), logits=logits, past_key_values=presents)
+        logits, loss = self.head_and_loss(self.lm_head, hidden, labels)
+        return ModelOutput(loss=loss, logits=logits, past_key_values=presents)
 
 
 class CodeGenForCausalLM(GPTJForCausalLM):

@@ -120,5 +120,5 @@ class LlamaForCausalLM(CausalLMBase):
     def forward(self, input_ids=None, attention_mask=None, position_ids=None, past_key_values=None,
                 inputs_embeds=None, labels=None, use_cache=False, **unused):
         hidden, presents = self.model(input_ids, attention_mask, position_ids, past_key_values, inputs_embeds, use_cache)
-        logits = self.lm_head(hidden)
-        return ModelOutput(loss=self.lm_loss(logits, labels), logits=logits, past_key_values=presents)
+        logits, loss = self.head_and_loss(self.lm_head, hidden, labels)
+        return ModelOutput(loss=loss, logits=logits, past_key_values=presents)

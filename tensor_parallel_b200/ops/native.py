@@ -155,8 +155,7 @@ def gemm_plan(tokens: int, features: int, k: int, world: int = 1, force_splits: 
 def gemm_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
     return (
         x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.ndim == 2 and x.shape[-1] == weight.shape[1]
-        and weight.shape[1] % 8 == 0 and weight.stride(1) == 1 and weight.stride(0) % 8 == 0 and x.numel() > 0
-        and weight.shape[0] > 0
+        and x.numel() > 0 and weight.shape[0] > 0
     )
 
 
@@ -166,10 +165,7 @@ def gemm_nt(x2d: torch.Tensor, w: torch.Tensor, bias=None, residual=None, act=No
     global launch_count
     tokens, k = x2d.shape
     features = w.shape[0]
-    if x2d.stride(1) != 1 or x2d.stride(0) % 8 or x2d.data_ptr() % 16:
-        x2d = x2d.contiguous()
-    if w.data_ptr() % 16:
-        w = w.contiguous()
+    x2d, w = _tma_ready(x2d), _tma_ready(w)
     if out is None:
         out = torch.empty(tokens, features, dtype=torch.bfloat16, device=x2d.device)
     plan = gemm_plan(tokens, features, k, world, force_splits, force_kbox)
@@ -186,6 +182,20 @@ def gemm_nt(x2d: torch.Tensor, w: torch.Tensor, bias=None, residual=None, act=No
     return out
 
 
+def _tma_ready(t: torch.Tensor) -> torch.Tensor:
+    """TMA needs a unit inner stride, a 16-byte aligned base and a row pitch that is a multiple of 16 bytes.
+    Tensors that break a rule are copied into a buffer with a padded row pitch (the pad is never read: columns
+    past the logical width are out of bounds for the tensor map and come back as zeros)."""
+    if t.stride(1) == 1 and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0:
+        return t
+    rows, cols = t.shape
+    pitch = (cols + 7) // 8 * 8
+    buf = torch.empty(rows, pitch, dtype=t.dtype, device=t.device)
+    view = buf[:, :cols]
+    view.copy_(t)
+    return view
+
+
 LIB.tpb_transpose_bf16.argtypes = [c_void_p, c_void_p, c_int, c_int, c_ll, c_ll, c_void_p]
 
 
@@ -194,8 +204,9 @@ def transpose(x2d: torch.Tensor) -> torch.Tensor:
     rows, cols = x2d.shape
     if x2d.stride(1) != 1:
         x2d = x2d.contiguous()
-    out = torch.empty(cols, rows, dtype=x2d.dtype, device=x2d.device)
-    check(LIB.tpb_transpose_bf16(_ptr(x2d), _ptr(out), rows, cols, x2d.stride(0), rows, _stream()), "tpb_transpose_bf16")
+    pitch = (rows + 7) // 8 * 8  # keeps the result usable as a TMA operand
+    out = torch.empty(cols, pitch, dtype=x2d.dtype, device=x2d.device)[:, :rows]
+    check(LIB.tpb_transpose_bf16(_ptr(x2d), _ptr(out), rows, cols, x2d.stride(0), pitch, _stream()), "tpb_transpose_bf16")
     launch_count += 1
     return out
 

@@ -115,18 +115,17 @@ class DistributedTensorParallel(ServingMixin, nn.Module):
         live = tensor_parallel_config.create_collective_ops(
             [device] * self.world_size, True, process_group=process_group, backend=backend
         )
+        self._live_config = live
         shard, sliced = make_shard(module, device, live, rank=self.rank, world_size=self.world_size)
         self.module_shards.append(shard)
         self.modified_parameters_names = set(sliced)
         self._sanity_check_params = nn.ParameterList([nn.Parameter(torch.empty(0, device=device), requires_grad=False)])
         self.comm = backend.flat_gather() if backend is not None and hasattr(backend, "flat_gather") else ProcessGroupFlatGather(process_group)
 
-        if fuse is None:
-            fuse = backend is not None
-        if fuse:
+        if fuse is None or fuse:
             from tensor_parallel_b200.parallel.planner import apply_fusion_plan
 
-            apply_fusion_plan(self)
+            self.fused_sites = apply_fusion_plan(self)
         if sharded:
             self.apply_sharding(sharded_param_names)
 

@@ -49,6 +49,7 @@ class Config:
         self.attr_rules = _compile_table(attr_rules)
         #: failure domain of the live collectives; set by :meth:`create_collective_ops`
         self.rank_group: Optional[C.RankGroup] = None
+        self.op_factory = None
 
     def replace(self, **tables) -> "Config":
         clone = copy.copy(self)
@@ -69,6 +70,7 @@ class Config:
             input_rules=factory.instantiate(self.input_rules), output_rules=factory.instantiate(self.output_rules)
         )
         clone.rank_group = group
+        clone.op_factory = factory  # lets the fusion planner create further collectives in the same failure domain
         return clone
 
     def __repr__(self):
@@ -83,6 +85,12 @@ class _OpFactory:
         self.world_size, self.devices, self.use_pg, self.pg, self.group = world_size, devices, use_pg, process_group, group
         self.backend = backend
         self._cache: Dict[str, Any] = {}
+
+    def make(self, spec: str):
+        """Live collective for an action string (cached per spelling)."""
+        if spec not in self._cache:
+            self._cache[spec] = self._make(spec)
+        return self._cache[spec]
 
     def _make(self, spec: str):
         kind, *opts = spec.split()

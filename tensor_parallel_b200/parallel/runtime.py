@@ -242,6 +242,7 @@ class TensorParallel(ServingMixin, nn.Module):
         self._device_backend = backend
         live = tensor_parallel_config.create_collective_ops(devices, distributed, backend=backend)
         self._rank_group = live.rank_group
+        self._live_config = live
 
         self.modified_parameters_names = set()
         for rank, device in enumerate(devices):
@@ -267,12 +268,10 @@ class TensorParallel(ServingMixin, nn.Module):
         self._sanity_check_params = nn.ParameterList(
             [nn.Parameter(torch.empty(0, device=d), requires_grad=False) for d in devices]
         )
-        if fuse is None:
-            fuse = self.all_cuda and backend is not None
-        if fuse:
+        if fuse is None or fuse:
             from tensor_parallel_b200.parallel.planner import apply_fusion_plan
 
-            apply_fusion_plan(self)
+            self.fused_sites = apply_fusion_plan(self)
         if sharded:
             self.apply_sharding(sharded_param_names)
 

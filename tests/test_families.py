@@ -166,3 +166,38 @@ def test_predefined_table_lookup():
         model_type = "not-a-model"
 
     assert tp.find_predefined_tensor_parallel_config(Unknown(), ["cpu", "cpu"]) is None
+
+
+@pytest.mark.parametrize("name", ["falcon", "gptj", "codegen", "gpt_neox"])
+def test_parallel_blocks_use_a_single_all_reduce(name):
+    """The planner merges the two "sum" sites of parallel attention+MLP blocks; fuse=False keeps the reference's two."""
+    from tensor_parallel_b200.parallel import collectives as C
+
+    torch.manual_seed(0)
+    model = DECODERS[name]()
+    ids = torch.randint(0, V, (2, 9))
+    ref = model(input_ids=ids, labels=ids)
+    calls = {"n": 0}
+    original = C.ThreadAllReduce.__call__
+
+    def counting(self, x, rank):
+        if rank == 0:
+            calls["n"] += 1
+        return original(self, x, rank)
+
+    C.ThreadAllReduce.__call__ = counting
+    try:
+        merged = tp.tensor_parallel(model, ["cpu", "cpu"], sharded=False)
+        out = merged(input_ids=ids, labels=ids)
+        n_merged = calls["n"]
+        calls["n"] = 0
+        plain = tp.tensor_parallel(model, ["cpu", "cpu"], sharded=False, fuse=False)
+        out_plain = plain(input_ids=ids, labels=ids)
+        n_plain = calls["n"]
+    finally:
+        C.ThreadAllReduce.__call__ = original
+    layers = 2
+    assert n_plain - n_merged == layers, (n_plain, n_merged)
+    torch.testing.assert_close(out.logits, ref.logits, atol=3e-5, rtol=1e-5)
+    torch.testing.assert_close(out_plain.logits, ref.logits, atol=3e-5, rtol=1e-5)
+    out.loss.backward()

@@ -120,6 +120,18 @@ def test_linear_autograd():
     _check(b.grad, br.grad, 384)
 
 
+def test_gemm_k_not_multiple_of_8():
+    nat = _native()
+    torch.manual_seed(5)
+    x = torch.randn(70, 150, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(96, 150, device="cuda", dtype=torch.bfloat16) * 0.05
+    out = nat.gemm_nt(x, w)
+    torch.cuda.synchronize()
+    _check(out, _ref(x, w), 150)
+    xt = nat.transpose(x)  # [150, 70] with a padded row pitch
+    assert xt.stride(0) % 8 == 0 and torch.equal(xt, x.t())
+
+
 def test_transpose():
     nat = _native()
     x = torch.randn(300, 136, device="cuda", dtype=torch.bfloat16)

@@ -139,7 +139,67 @@ def _model_worker(rank, world, port, out_dir):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("worker", [_collectives_worker, _model_worker])
+def _fused_training_worker(rank, world, port, out_dir):
+    """bf16 shards: the planner swaps row-parallel linears for GEMM + all-reduce and the head for the
+    vocab-parallel cross-entropy; loss and gradients must track the fp32 unsplit model."""
+    _setup(rank, world, port)
+    try:
+        import tensor_parallel_b200 as tp
+        from tensor_parallel_b200.models.llama import LlamaConfig, LlamaForCausalLM
+        from tensor_parallel_b200.ops import native
+
+        dev = torch.device("cuda", rank)
+        torch.manual_seed(0)
+        cfg = LlamaConfig(vocab_size=1024, hidden_size=256, intermediate_size=688, num_hidden_layers=2, num_attention_heads=4,
+                          fused_lm_loss=True)
+        ref = LlamaForCausalLM(cfg)
+        for p in ref.parameters():
+            p.data = p.data.to(torch.bfloat16).float()  # bf16-representable weights, fp32 maths
+        model = LlamaForCausalLM(cfg)
+        model.load_state_dict(ref.state_dict())
+        model = model.to(device=dev, dtype=torch.bfloat16)
+        ids = torch.randint(0, 1024, (4, 80), generator=torch.Generator().manual_seed(3))
+        cfg.fused_lm_loss = False
+        want = ref(input_ids=ids, labels=ids)
+        want.loss.backward()
+        cfg.fused_lm_loss = True
+        wrapped = tp.tensor_parallel(model, [dev], sharded=True)
+        o_proj = wrapped.module_shards[0].model.layers[0].self_attn.tp_wrapped_module.o_proj
+        assert getattr(o_proj, "_tp_fused_row_parallel", False), "planner did not fuse the row-parallel linear"
+        before = native.launch_count
+        out = wrapped(input_ids=ids.to(dev), labels=ids.to(dev))
+        assert out.logits is None  # fused head + loss: logits are never materialised
+        out.loss.backward()
+        torch.cuda.synchronize()
+        wrapped._device_backend.comm.check_status()
+        assert native.launch_count - before > 40
+        torch.testing.assert_close(out.loss.float().cpu(), want.loss, atol=3e-2, rtol=2e-2)
+        ref_grads = {n: p.grad for n, p in ref.named_parameters()}
+        cfgr = wrapped.tensor_parallel_config
+        checked = 0
+        for shard_name, p in wrapped.module_shards[0].named_parameters():
+            original = shard_name.replace("tp_wrapped_module.", "")
+            for pattern, action in cfgr.state_rules.items():
+                if pattern.search(original):
+                    expected = action(ref_grads[original], rank)
+                    got = p.grad.float().cpu()
+                    rel = (got - expected).norm().item() / (expected.norm().item() + 1e-9)
+                    with open(os.path.join(out_dir, f"grad_errors_{rank}.txt"), "a") as fh:
+                        fh.write(f"{rel:.4f} {shard_name}\n")
+                    assert (got - expected).norm().item() <= 0.1 * expected.norm().item() + 2e-5 * expected.numel() ** 0.5, (shard_name, rank, rel)
+                    checked += 1
+                    break
+        assert checked >= 10
+        opt = tp.optim.AdamW(wrapped.parameters(), lr=1e-3)
+        opt.step()
+        out2 = wrapped(input_ids=ids.to(dev), labels=ids.to(dev))
+        assert out2.loss.item() < out.loss.item()
+        open(os.path.join(out_dir, f"ok{rank}"), "w").close()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("worker", [_collectives_worker, _model_worker, _fused_training_worker])
 def test_two_gpus(worker, tmp_path):
     mp.spawn(worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
-    assert sorted(os.listdir(tmp_path)) == ["ok0", "ok1"]
+    assert sorted(f for f in os.listdir(tmp_path) if f.startswith("ok")) == ["ok0", "ok1"]

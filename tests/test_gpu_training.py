@@ -38,11 +38,31 @@ def test_bf16_native_training_step_tracks_fp32_reference(kind):
     grads = dict(model.named_parameters())
     for name, p in ref.named_parameters():
         g, w = grads[name].grad.float().cpu(), p.grad
-        denom = w.abs().max().item() + 1e-6
-        assert (g - w).abs().max().item() / denom < 0.08, name
+        # bf16 gradients vs the fp32 oracle; the absolute term covers gradients that are analytically zero (key bias)
+        assert (g - w).norm().item() <= 0.1 * w.norm().item() + 2e-5 * w.numel() ** 0.5, name
     opt = tp.optim.AdamW(model.parameters(), lr=1e-3)
     opt.step()
     torch.cuda.synchronize()
     native.device_state(torch.device("cuda", 0)).check_status()
     out2 = model(input_ids=ids.cuda(), labels=ids.cuda())
     assert out2.loss.item() < out.loss.item()
+
+
+@pytest.mark.parametrize("vocab", [1024, 4000])
+def test_fused_head_cross_entropy_single_rank(vocab):
+    from tensor_parallel_b200.ops.loss import lm_head_cross_entropy, lm_head_cross_entropy_ref
+
+    torch.manual_seed(2)
+    hidden = (torch.randn(3, 50, 256, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_(True)
+    weight = (torch.randn(vocab, 256, device="cuda") * 0.05).to(torch.bfloat16).requires_grad_(True)
+    labels = torch.randint(0, vocab, (3, 50), device="cuda")
+    labels[0, :7] = -100
+    loss = lm_head_cross_entropy(hidden, weight, labels)
+    loss.backward()
+    h32, w32 = hidden.detach().float().requires_grad_(True), weight.detach().float().requires_grad_(True)
+    want = lm_head_cross_entropy_ref(h32, w32, labels)
+    want.backward()
+    torch.testing.assert_close(loss, want, atol=2e-2, rtol=1e-2)
+    for got, ref in ((hidden.grad, h32.grad), (weight.grad, w32.grad)):
+        denom = ref.abs().max().item() + 1e-9
+        assert (got.float() - ref).abs().max().item() / denom < 0.06
