@@ -374,7 +374,121 @@ def process_backend(device: torch.device, process_group=None) -> Optional[Proces
         return backend
 
 
-def thread_backend(devices: Sequence[torch.device]):
-    """Single-process multi-GPU mode keeps the portable thread collectives for rule actions; fused
-    operators reach the heap through :func:`make_thread_comms`."""
-    return None
+# ------------------------------------------------------------------------------------------------
+# single-process multi-GPU mode: one host thread per rank, kernels launched for all ranks by one thread
+# ------------------------------------------------------------------------------------------------
+
+
+class _MultiRankAllReduce(torch.autograd.Function):
+    """All ranks' tensors in, all ranks' sums out: one autograd node spanning every device, so the backward
+    pass (driven by a single thread) launches the mirrored collective on all devices as well."""
+
+    @staticmethod
+    def forward(ctx, comms, *xs):
+        ctx.comms = comms
+        outs = []
+        for comm, x in zip(comms, xs):
+            with torch.cuda.device(comm.device):
+                outs.append(comm.all_reduce(x.contiguous()).clone())
+        return tuple(outs)
+
+    @staticmethod
+    def backward(ctx, *grads):
+        outs = []
+        shapes = [g for g in grads if g is not None]
+        for comm, g in zip(ctx.comms, grads):
+            with torch.cuda.device(comm.device):
+                if g is None:
+                    g = torch.zeros(shapes[0].shape, dtype=shapes[0].dtype, device=comm.device)
+                outs.append(comm.all_reduce(g.contiguous()).clone())
+        return (None, *outs)
+
+
+class _MultiRankAllGather(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, comms, dim, *xs):
+        ctx.comms, ctx.dim = comms, dim
+        outs = []
+        for comm, x in zip(comms, xs):
+            with torch.cuda.device(comm.device):
+                stacked = comm.all_gather(x.contiguous())
+                outs.append(torch.cat(list(stacked.unbind(0)), dim=dim))
+        return tuple(outs)
+
+    @staticmethod
+    def backward(ctx, *grads):
+        outs = []
+        shapes = [g for g in grads if g is not None]
+        world = len(ctx.comms)
+        for comm, g in zip(ctx.comms, grads):
+            with torch.cuda.device(comm.device):
+                if g is None:
+                    g = torch.zeros(shapes[0].shape, dtype=shapes[0].dtype, device=comm.device)
+                parts = torch.stack(g.chunk(world, dim=ctx.dim)).contiguous()
+                outs.append(comm.reduce_scatter(parts).clone())
+        return (None, None, *outs)
+
+
+class ThreadDeviceAllReduce:
+    """``"sum"`` for the threaded mode on CUDA: ranks meet at a host rendezvous, then the authoritative thread
+    launches the device all-reduce for every rank on that rank's stream (no NCCL, no host-side reduction)."""
+
+    def __init__(self, group, comms, fallback):
+        from tensor_parallel_b200.parallel.collectives import CollectiveOperation
+
+        self.comms, self.fallback = comms, fallback
+        self._op = CollectiveOperation(len(comms), lambda *xs: _MultiRankAllReduce.apply(comms, *xs), group=group)
+
+    def __call__(self, x: torch.Tensor, rank: int):
+        if not x.is_cuda or x.dtype not in (torch.bfloat16, torch.float32) or x.numel() * x.element_size() > self.comms[0].layout.staging_bytes:
+            return self.fallback(x, rank)
+        return self._op(x, rank)
+
+
+class ThreadDeviceAllGather:
+    def __init__(self, group, comms, dim, fallback):
+        from tensor_parallel_b200.parallel.collectives import CollectiveOperation, Rendezvous
+
+        self.comms, self.dim, self.fallback = comms, dim, fallback
+        self._shapes = Rendezvous(group)
+        self._op = CollectiveOperation(len(comms), lambda *xs: _MultiRankAllGather.apply(comms, self.dim % xs[0].ndim, *xs), group=group)
+
+    def __call__(self, x: torch.Tensor, rank: int):
+        shapes = self._shapes.exchange(rank, (tuple(x.shape), x.dtype, x.is_cuda))
+        per = 8 if x.dtype == torch.bfloat16 else 4
+        world = len(self.comms)
+        ok = (len(set(shapes)) == 1 and x.is_cuda and x.dtype in (torch.bfloat16, torch.float32) and x.numel() % per == 0
+              and world * x.numel() * x.element_size() <= self.comms[0].layout.staging_bytes)
+        if not ok:
+            return self.fallback(x, rank)
+        return self._op(x, rank)
+
+
+class ThreadBackend:
+    """Collective factory for ``Config.create_collective_ops`` when all ranks are CUDA devices of one process."""
+
+    def __init__(self, comms):
+        self.comms = comms
+
+    def all_reduce_op(self, group):
+        from tensor_parallel_b200.parallel.collectives import ThreadAllReduce
+
+        return ThreadDeviceAllReduce(group, self.comms, ThreadAllReduce(group))
+
+    def all_gather_op(self, group, dim):
+        from tensor_parallel_b200.parallel.collectives import ThreadAllGather
+
+        return ThreadDeviceAllGather(group, self.comms, dim, ThreadAllGather(group, dim))
+
+
+_thread_backends: Dict[tuple, Optional[ThreadBackend]] = {}
+
+
+def thread_backend(devices: Sequence[torch.device], staging_bytes: int = 64 << 20) -> Optional[ThreadBackend]:
+    """Symmetric heaps for all ``devices`` of this process (peer access must be available), or ``None``."""
+    key = tuple(d.index for d in devices)
+    with _lock:
+        if key not in _thread_backends:
+            comms = make_thread_comms(devices, staging_bytes=staging_bytes)
+            _thread_backends[key] = ThreadBackend(comms) if comms is not None else None
+        return _thread_backends[key]

@@ -4,8 +4,9 @@ The reference gathers (or all-reduces) full ``[tokens, vocab]`` logits onto ever
 loss redundantly (``src/tensor_parallel/slicing_configs.py:381,390``; SURVEY "Q12").  Here every rank
 multiplies the hidden states with its vocabulary slice of the head on the tcgen05 GEMM, reduces each row
 of its local logits to four numbers (max, sum-exp, target logit, ownership flag), exchanges only those
-``[tokens, 4]`` floats, and turns the local logits in place into their gradient.  ``grad(hidden)`` is the
-sum over ranks of ``dlogits_local @ W_local`` (one all-reduce), ``grad(W_local)`` stays local.
+``[tokens, 4]`` floats, and turns the local logits in place into their gradient.  Every rank returns its own share
+``dlogits_local @ W_local`` of ``grad(hidden)`` (the shares are summed by the adjoint of whichever collective
+produced the replicated hidden state), ``grad(W_local)`` stays local.
 """
 from __future__ import annotations
 
@@ -61,10 +62,10 @@ class _VocabParallelCE(torch.autograd.Function):
         dlogits = logits  # overwritten in place
         gx = gw = None
         if ctx.needs_input_grad[0]:
-            gx = native.gemm_nt(dlogits, native.transpose(weight))
-            if reduce_hidden_grad is not None:
-                gx = reduce_hidden_grad(gx)
-            gx = gx.view(hidden_shape)
+            # this rank's share of d loss / d hidden (through its vocabulary slice).  It is NOT summed over ranks
+            # here: the replicated hidden state receives partial cotangents on every rank, and the adjoint of the
+            # collective that produced it (the previous row-parallel all-reduce, the embedding gather) adds them up.
+            gx = native.gemm_nt(dlogits, native.transpose(weight)).view(hidden_shape)
         if ctx.needs_input_grad[1]:
             gw = native.gemm_nt(native.transpose(dlogits), native.transpose(x2d))
         return gx, gw, None, None, None, None, None
@@ -76,8 +77,8 @@ def lm_head_cross_entropy(hidden: torch.Tensor, weight: torch.Tensor, labels: to
     """Mean cross-entropy of ``softmax(hidden @ W_full^T)`` against ``labels`` where this rank only owns
     ``weight = W_full[vocab_start : vocab_start + weight.shape[0]]``.
 
-    ``gather_stats([rows, 4]) -> [world, rows, 4]`` and ``reduce_hidden_grad(x) -> sum over ranks`` are the two
-    collectives (``None`` on a single rank).  Requires CUDA bf16 tensors."""
+    ``gather_stats([rows, 4]) -> [world, rows, 4]`` and ``reduce_hidden_grad(x) -> sum over ranks`` (applied to the
+    scalar loss cotangent only) are the two collectives (``None`` on a single rank).  Requires CUDA bf16 tensors."""
     return _VocabParallelCE.apply(hidden, weight, labels, vocab_start, gather_stats, reduce_hidden_grad, ignore_index)
 
 

@@ -454,25 +454,43 @@ def attention_forward(q, k, v, causal, scale, want_lse=False):
     return out, lse
 
 
-class _AttentionFn(torch.autograd.Function):
-    """Forward on the native kernel; backward recomputes the scores with stock PyTorch operators."""
+LIB.tpb_attn_backward.argtypes = [c_void_p] * 10 + [c_int] * 6 + [c_ll] * 21 + [c_int, c_float, c_void_p]
 
+
+def attention_backward(q, k, v, out, dout, lse, causal, scale):
+    """Gradients of :func:`attention_forward` (scores are recomputed tile by tile)."""
+    global launch_count
+    q, k, v, dout = (t if _strided_ok(t) else t.contiguous() for t in (q, k, v, dout))
+    b, sq, hq, d = q.shape
+    sk, hkv = k.shape[1], k.shape[2]
+    dq = torch.empty(b, sq, hq, d, dtype=q.dtype, device=q.device)
+    dk = torch.empty(b, sk, hkv, d, dtype=q.dtype, device=q.device)
+    dv = torch.empty(b, sk, hkv, d, dtype=q.dtype, device=q.device)
+    delta = torch.empty(b, hq, sq, dtype=torch.float32, device=q.device)
+    scale = 1.0 / math.sqrt(d) if scale is None else scale
+    check(LIB.tpb_attn_backward(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(dout), _ptr(lse), _ptr(delta), _ptr(dq), _ptr(dk), _ptr(dv),
+                                b, sq, sk, hq, hkv, d,
+                                q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
+                                v.stride(0), v.stride(1), v.stride(2), out.stride(0), out.stride(1), out.stride(2),
+                                dout.stride(0), dout.stride(1), dout.stride(2), dq.stride(0), dq.stride(1), dq.stride(2),
+                                dk.stride(0), dk.stride(1), dk.stride(2), int(causal), scale, _stream()), "tpb_attn_backward")
+    launch_count += 3
+    return dq, dk, dv
+
+
+class _AttentionFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, causal, scale):
-        out, _ = attention_forward(q, k, v, causal, scale)
-        ctx.save_for_backward(q, k, v)
+        out, lse = attention_forward(q, k, v, causal, scale, want_lse=True)
+        ctx.save_for_backward(q, k, v, out, lse)
         ctx.causal, ctx.scale = causal, scale
         return out
 
     @staticmethod
     def backward(ctx, grad):
-        from tensor_parallel_b200.ops.functional import attention_ref
-
-        q, k, v = (t.detach().requires_grad_(True) for t in ctx.saved_tensors)
-        with torch.enable_grad():
-            out = attention_ref(q, k, v, ctx.causal, None, ctx.scale)
-        gq, gk, gv = torch.autograd.grad(out, (q, k, v), grad.to(out.dtype))
-        return gq, gk, gv, None, None
+        q, k, v, out, lse = ctx.saved_tensors
+        dq, dk, dv = attention_backward(q, k, v, out, grad.to(q.dtype), lse, ctx.causal, ctx.scale)
+        return dq, dk, dv, None, None
 
 
 def attention(q, k, v, causal, bias=None, scale=None):

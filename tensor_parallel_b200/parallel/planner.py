@@ -23,7 +23,7 @@ logger = logging.getLogger(__name__)
 def _is_all_reduce(action) -> bool:
     if isinstance(action, (C.ThreadAllReduce, C.DistributedAllReduce)):
         return True
-    return type(action).__name__ == "DeviceAllReduce"
+    return type(action).__name__ in ("DeviceAllReduce", "ThreadDeviceAllReduce")
 
 
 def merge_parallel_block_reductions(tp_module) -> int:
