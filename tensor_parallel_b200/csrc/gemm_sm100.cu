@@ -68,6 +68,16 @@ struct GemmParams {
   uint32_t* split_counters;       // local: [tiles] arrivals of split-K partials (self re-arming)
   size_t slot_stride;             // elements between consecutive slots
   uint32_t* status;               // local status word (0 = ok)
+  // fused all-gather of the token-side operand (ag_world > 1): every rank owns a column slice [rows, ag_cols] of x;
+  // the kernel first pushes its slice into every rank's gathered buffer, then consumes k-blocks slice by slice
+  // (own slice first) as the peers' pushes arrive
+  int ag_world, ag_rank, ag_kb_per_rank, ag_rows, ag_cols;
+  uint32_t ag_epoch;                          // flags of this call reach at least this value
+  const __nv_bfloat16* ag_src;                // local slice
+  long long ag_src_ld, ag_dst_ld;
+  __nv_bfloat16* ag_dst[MAX_WORLD];           // every rank's gathered buffer [rows, ag_world * ag_cols]
+  uint32_t* ag_flags[MAX_WORLD];              // every rank's arrival words [ag_world], indexed by source rank
+  uint32_t* ag_push_counter;                  // local: CTAs done pushing (self re-arming)
   int debug_skip_mma;             // measurement aid: stream the operands through the smem ring without issuing MMAs
 };
 
@@ -143,6 +153,30 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   const int tiles = p.m_tiles * p.n_tiles;
   const int work_items = tiles * p.k_splits;
 
+  if (p.ag_world > 1) {
+    // ---------------- all-gather push: local slice -> every rank's gathered buffer ----------------
+    const int vec_per_row = p.ag_cols >> 3;
+    const long long total = (long long)p.ag_rows * vec_per_row;
+    for (long long i = blockIdx.x * (long long)NUM_THREADS + threadIdx.x; i < total; i += (long long)gridDim.x * NUM_THREADS) {
+      const long long r = i / vec_per_row;
+      const int c = int(i % vec_per_row) * 8;
+      const uint4 val = *reinterpret_cast<const uint4*>(p.ag_src + r * p.ag_src_ld + c);
+#pragma unroll
+      for (int d = 0; d < MAX_WORLD; ++d)
+        if (d < p.ag_world) *reinterpret_cast<uint4*>(p.ag_dst[d] + r * p.ag_dst_ld + p.ag_rank * p.ag_cols + c) = val;
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const uint32_t old = atomicAdd(p.ag_push_counter, 1u);
+      if (old == gridDim.x - 1) {  // the whole slice has left this GPU: tell every rank
+        *p.ag_push_counter = 0;
+        __threadfence_system();
+        for (int d = 0; d < p.ag_world; ++d) red_add_release_sys(p.ag_flags[d] + p.ag_rank, 1u);
+      }
+    }
+  }
+
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (elect_one()) {
@@ -154,7 +188,23 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         const int nt = tile / p.m_tiles;
         const int kb0 = split * p.kb_per_split;
         const int kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        int ag_ready_src = -1;
+        for (int kb_seq = kb0; kb_seq < kb1; ++kb_seq, ++it) {
+          int kb = kb_seq;
+          if (p.ag_world > 1) {
+            // start with the k-blocks of the local slice, then walk the other ranks' slices as they arrive
+            kb = (kb_seq + p.ag_rank * p.ag_kb_per_rank) % p.k_blocks;
+            const int src = kb / p.ag_kb_per_rank;
+            if (src != ag_ready_src) {
+              if (!wait_flag_ge(p.ag_flags[p.ag_rank] + src, p.ag_epoch)) {
+                atomicMax(p.status, STATUS_TIMEOUT_FLAG);
+                *abort_flag = 1;
+                break;
+              }
+              asm volatile("fence.proxy.async;" ::: "memory");  // peer-written rows must be visible to the TMA engine
+              ag_ready_src = src;
+            }
+          }
           const int s = it % p.stages;
           const uint32_t ph = (it / p.stages) & 1;
           if (!mbar_wait(&empty_bar[s], ph ^ 1)) {
@@ -630,9 +680,9 @@ extern "C" int tpb_gemm_plan(int tokens, int features, int k, int world, int for
   return TPB_OK;
 }
 
-extern "C" int tpb_gemm_bf16(const void* x, const void* w, void* out, const void* bias, const void* residual, int tokens,
-                             int features, int k, int ldx, int ldw, int ld_out, int act, float bias_scale,
-                             const tpb_gemm_plan_t* plan, const tpb_reduce_ctx_t* rc, void* stream_) {
+static int gemm_impl(const void* x, const void* w, void* out, const void* bias, const void* residual, int tokens,
+                     int features, int k, int ldx, int ldw, int ld_out, int act, float bias_scale,
+                     const tpb_gemm_plan_t* plan, const tpb_reduce_ctx_t* rc, const tpb_allgather_ctx_t* ag, void* stream_) {
   if (!x || !w || !out || !plan) return TPB_ERR_ARG;
   if ((ldx & 7) || (ldw & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return TPB_ERR_ALIGN;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
@@ -675,6 +725,26 @@ extern "C" int tpb_gemm_bf16(const void* x, const void* w, void* out, const void
     p.status = static_cast<uint32_t*>(rc->status);
   }
 
+  if (ag) {
+    if (ag->world < 2 || ag->world > MAX_WORLD || plan->k_splits != 1 || ag->cols_local % (plan->kbox * BK) || (ag->cols_local & 7) ||
+        ag->cols_local * ag->world != k || (ag->local_ld & 7) || ((uintptr_t)ag->local & 15))
+      return TPB_ERR_ARG;
+    p.ag_world = ag->world;
+    p.ag_rank = ag->rank;
+    p.ag_kb_per_rank = ag->cols_local / (plan->kbox * BK);
+    p.ag_rows = tokens;
+    p.ag_cols = ag->cols_local;
+    p.ag_epoch = ag->epoch;
+    p.ag_src = static_cast<const __nv_bfloat16*>(ag->local);
+    p.ag_src_ld = ag->local_ld;
+    p.ag_dst_ld = ldx;
+    for (int d = 0; d < ag->world; ++d) {
+      p.ag_dst[d] = static_cast<__nv_bfloat16*>(ag->gathered[d]);
+      p.ag_flags[d] = static_cast<uint32_t*>(ag->flags[d]);
+    }
+    p.ag_push_counter = static_cast<uint32_t*>(ag->push_counter);
+  }
+
   const void* a_ptr = plan->swapped ? w : x;
   const void* b_ptr = plan->swapped ? x : w;
   const int a_rows = p.m_extent, b_rows = p.n_extent;
@@ -697,4 +767,24 @@ extern "C" int tpb_gemm_bf16(const void* x, const void* w, void* out, const void
     case 2561: return launch_gemm<256, 1, 1>(ta, tb, p, plan->grid, stream);
     default: return TPB_ERR_ARG;
   }
+}
+
+extern "C" int tpb_gemm_bf16(const void* x, const void* w, void* out, const void* bias, const void* residual, int tokens,
+                             int features, int k, int ldx, int ldw, int ld_out, int act, float bias_scale,
+                             const tpb_gemm_plan_t* plan, const tpb_reduce_ctx_t* rc, void* stream_) {
+  return gemm_impl(x, w, out, bias, residual, tokens, features, k, ldx, ldw, ld_out, act, bias_scale, plan, rc, nullptr, stream_);
+}
+
+// All-gather fused with the GEMM that consumes it: x is split by columns over the ranks; every rank passes its
+// slice ag->local [tokens, ag->cols_local] and the kernel (1) pushes the slice into column block `rank` of every
+// rank's gathered buffer ag->gathered[d] [tokens, k] (row pitch ld_gathered) with plain peer stores and signals,
+// (2) multiplies gathered[rank] @ w^T, reading the k-blocks of the local slice first and each peer's slice as soon
+// as its arrival word reaches ag->epoch.  TMA only ever reads this GPU's own memory.  The plan must come from
+// tpb_gemm_plan(tokens, features, k, 1, 1, kbox) with cols_local % (kbox * 64) == 0.
+extern "C" int tpb_gemm_allgather_bf16(const void* w, void* out, const void* bias, int tokens, int features, int k,
+                                       int ld_gathered, int ldw, int ld_out, int act, const tpb_gemm_plan_t* plan,
+                                       const tpb_reduce_ctx_t* rc, const tpb_allgather_ctx_t* ag, void* stream_) {
+  if (!ag) return TPB_ERR_ARG;
+  return gemm_impl(ag->gathered[ag->rank], w, out, bias, nullptr, tokens, features, k, ld_gathered, ldw, ld_out, act, 1.0f, plan, rc,
+                   ag, stream_);
 }

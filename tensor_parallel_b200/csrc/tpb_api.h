@@ -46,6 +46,17 @@ typedef struct {
   int max_slots, max_tiles;
 } tpb_reduce_ctx_t;
 
+// Operands of the fused all-gather + GEMM (see tpb_gemm_allgather_bf16).
+typedef struct {
+  int world, rank;
+  const void* local;                  // this rank's column slice [tokens, cols_local] bf16
+  int local_ld, cols_local;
+  void* gathered[TPB_MAX_WORLD];      // every rank's gathered buffer [tokens, world * cols_local] (peer-mapped)
+  void* flags[TPB_MAX_WORLD];         // every rank's arrival words, uint32 [world], indexed by source rank
+  void* push_counter;                 // local uint32, zero-initialised
+  unsigned epoch;                     // number of fused all-gather calls issued on these flags, this one included
+} tpb_allgather_ctx_t;
+
 int tpb_gemm_plan(int tokens, int features, int k, int world, int force_splits, int force_kbox,
                   tpb_gemm_plan_t* plan);
 
@@ -55,6 +66,10 @@ int tpb_gemm_plan(int tokens, int features, int k, int world, int force_splits, 
 int tpb_gemm_bf16(const void* x, const void* w, void* out, const void* bias, const void* residual, int tokens,
                   int features, int k, int ldx, int ldw, int ld_out, int act, float bias_scale,
                   const tpb_gemm_plan_t* plan, const tpb_reduce_ctx_t* rc, void* stream);
+
+int tpb_gemm_allgather_bf16(const void* w, void* out, const void* bias, int tokens, int features, int k, int ld_gathered,
+                            int ldw, int ld_out, int act, const tpb_gemm_plan_t* plan, const tpb_reduce_ctx_t* rc,
+                            const tpb_allgather_ctx_t* ag, void* stream);
 
 #ifdef __cplusplus
 }

@@ -43,6 +43,15 @@ LIB.tpb_ipc_open_handle.argtypes = [c_void_p, ctypes.POINTER(c_void_p)]
 LIB.tpb_ipc_close_handle.argtypes = [c_void_p]
 LIB.tpb_collective.argtypes = [c_int, c_int, c_int, c_int, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p),
                                ctypes.POINTER(c_void_p), c_void_p, c_void_p, c_ll, c_int, ctypes.c_double, c_void_p]
+
+
+class AllGatherCtx(ctypes.Structure):
+    _fields_ = [("world", c_int), ("rank", c_int), ("local", c_void_p), ("local_ld", c_int), ("cols_local", c_int),
+                ("gathered", c_void_p * 8), ("flags", c_void_p * 8), ("push_counter", c_void_p), ("epoch", ctypes.c_uint)]
+
+
+LIB.tpb_gemm_allgather_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                        ctypes.POINTER(native.GemmPlan), ctypes.POINTER(ReduceCtx), ctypes.POINTER(AllGatherCtx), c_void_p]
 LIB.tpb_wait_flag_test.argtypes = [c_void_p, ctypes.c_uint, c_void_p, ctypes.c_double, c_void_p]
 
 
@@ -63,15 +72,18 @@ def _align(n: int, a: int = 1024) -> int:
 
 
 class HeapLayout:
-    def __init__(self, slot_stride: int, max_slots: int, staging_bytes: int):
+    def __init__(self, slot_stride: int, max_slots: int, staging_bytes: int, gather_bytes: int = 96 << 20):
         self.slot_stride, self.max_slots, self.staging_bytes = slot_stride, max_slots, staging_bytes
+        self.gather_bytes = gather_bytes
         self.off_signals = 0
-        self.off_arrivals = _align(SIGNAL_BYTES)
+        self.off_ag_flags = SIGNAL_BYTES  # uint32 [2 regions][MAX_WORLD] arrival words of the fused all-gather
+        self.off_arrivals = _align(SIGNAL_BYTES + 2 * MAX_WORLD * 4)
         self.off_slots = self.off_arrivals + _align(2 * MAX_TILES * 4)
         self.region_slot_bytes = _align(max_slots * slot_stride * 4)
         self.off_staging_in = self.off_slots + 2 * self.region_slot_bytes
         self.off_staging_out = self.off_staging_in + _align(staging_bytes)
-        self.total = self.off_staging_out + _align(staging_bytes)
+        self.off_gather = self.off_staging_out + _align(staging_bytes)  # two gathered-operand buffers
+        self.total = self.off_gather + 2 * _align(gather_bytes)
 
 
 class RankComm:
@@ -97,6 +109,9 @@ class RankComm:
                 arr[r] = self.base[r] + off
             self._ptr_arrays[name] = arr
         self.wait_seconds = 2.0
+        with torch.cuda.device(device):
+            self.ag_push_counter = torch.zeros(4, dtype=torch.int32, device=device)
+        self._ag_calls = [0, 0]
 
     def _make_ctx(self, region: int) -> ReduceCtx:
         ctx = ReduceCtx()
@@ -134,6 +149,45 @@ class RankComm:
             return False
         plan = native.gemm_plan(tokens, features, k, self.world)
         return self.world + plan.k_splits <= self.layout.max_slots and plan.tiles <= MAX_TILES
+
+    # -- fused all-gather + GEMM ------------------------------------------------------------------
+
+    def allgather_gemm(self, x_local: torch.Tensor, weight: torch.Tensor, bias=None, act=None, out=None):
+        """``concat_over_ranks(x_local, dim=1) @ weight.T`` in ONE kernel: every rank pushes its column slice
+        ``x_local [tokens, k / world]`` into all peers' gathered buffers from the kernel's prologue, and the GEMM
+        main loop consumes the k-blocks of a slice as soon as that slice has arrived (own slice first), so the
+        transfer overlaps the tensor-core work.  All ranks must call with the same shapes, in the same order."""
+        tokens, cols = x_local.shape
+        features, k = weight.shape
+        if k != cols * self.world or x_local.dtype != torch.bfloat16:
+            raise ValueError("weight.shape[1] must equal world * x_local.shape[1] (bf16 operands)")
+        if tokens * k * 2 > self.layout.gather_bytes:
+            raise ValueError(f"gathered operand of {tokens * k * 2} bytes exceeds the heap's gather buffers")
+        x_local = native._tma_ready(x_local)
+        weight = native._tma_ready(weight)
+        kbox = 4 if (tokens <= 32 and cols % 256 == 0) else (2 if (tokens <= 32 and cols % 128 == 0) else 1)
+        if cols % (64 * kbox):
+            raise ValueError("the per-rank column count must be a multiple of 64")
+        plan = native.gemm_plan(tokens, features, k, 1, 1, kbox)
+        region = (self._ag_calls[0] + self._ag_calls[1]) & 1
+        self._ag_calls[region] += 1
+        ctx = AllGatherCtx()
+        ctx.world, ctx.rank = self.world, self.rank
+        ctx.local, ctx.local_ld, ctx.cols_local = x_local.data_ptr(), x_local.stride(0), cols
+        for r in range(self.world):
+            ctx.gathered[r] = self.base[r] + self.layout.off_gather + region * _align(self.layout.gather_bytes)
+            ctx.flags[r] = self.base[r] + self.layout.off_ag_flags + region * MAX_WORLD * 4
+        ctx.push_counter = self.ag_push_counter.data_ptr()
+        ctx.epoch = self._ag_calls[region]
+        if out is None:
+            out = torch.empty(tokens, features, dtype=torch.bfloat16, device=x_local.device)
+        rctx = self._ctxs[0]
+        check(LIB.tpb_gemm_allgather_bf16(c_void_p(weight.data_ptr()), c_void_p(out.data_ptr()),
+                                          c_void_p(bias.data_ptr() if bias is not None else 0), tokens, features, k, k,
+                                          weight.stride(0), out.stride(0), native.ACT_CODES[act], ctypes.byref(plan),
+                                          ctypes.byref(rctx), ctypes.byref(ctx), native._stream()), "tpb_gemm_allgather_bf16")
+        native.launch_count += 1
+        return out
 
     # -- stand-alone collectives on the staging buffers -------------------------------------------
 

@@ -61,6 +61,29 @@ def case_attn_prefill(batch, seq, heads, d, iters):
     return {"us": us, "tflops": 4.0 * batch * heads * seq * seq * d / 2 / us / 1e6}
 
 
+def case_attn_backward(batch, seq, heads, d, iters):
+    q, k, v, g = (torch.randn(batch, seq, heads, d, device="cuda", dtype=torch.bfloat16) for _ in range(4))
+    out, lse = native.attention_forward(q, k, v, True, None, want_lse=True)
+    us = _time(lambda i: native.attention_backward(q, k, v, out, g, lse, True, None), iters)
+    return {"us": us, "tflops": 2.5 * 4.0 * batch * heads * seq * seq * d / 2 / us / 1e6, "note": "useful FLOPs = 2.5 x forward"}
+
+
+def case_cross_entropy(rows, vocab, hidden, iters):
+    from tensor_parallel_b200.ops.loss import lm_head_cross_entropy
+
+    h = (torch.randn(rows, hidden, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_(True)
+    w = (torch.randn(vocab, hidden, device="cuda") * 0.02).to(torch.bfloat16).requires_grad_(True)
+    labels = torch.randint(0, vocab, (rows,), device="cuda")
+
+    def step(i):
+        loss = lm_head_cross_entropy(h[None], w, labels[None])
+        loss.backward()
+        h.grad = w.grad = None
+
+    us = _time(step, iters)
+    return {"us": us, "tflops": 6.0 * rows * vocab * hidden / us / 1e6}
+
+
 def case_norm(rows, cols, iters):
     xs = [torch.randn(rows, cols, device="cuda", dtype=torch.bfloat16) for _ in range(3)]
     w = torch.ones(cols, device="cuda", dtype=torch.bfloat16)
@@ -106,6 +129,8 @@ CASES = {
     "attn_decode": lambda it: case_attn_decode(8, 32, 32, 2048, it),
     "attn_decode_tp8": lambda it: case_attn_decode(8, 4, 4, 2048, it, splits=8),
     "attn_prefill": lambda it: case_attn_prefill(4, 2048, 32, 128, it),
+    "attn_backward": lambda it: case_attn_backward(4, 2048, 32, 128, it),
+    "head_cross_entropy": lambda it: case_cross_entropy(8192, 32000, 4096, it),
     "rmsnorm": lambda it: case_norm(32768, 4096, it),
     "swiglu": lambda it: case_swiglu(16384, 11008, it),
     "rope_append": lambda it: case_rope_append(8, 2048, 32, it),

@@ -76,6 +76,19 @@ def _collectives_worker(rank, world, port, out_dir):
             rc.check_status()
             err = (got.float() - want).abs().max().item()
             assert err <= 0.02 * want.abs().max().item() + 0.05, (tokens, features, k, err)
+        # fused all-gather + GEMM (column-parallel linear fed by a hidden-split activation)
+        for tokens, cols, features in ((8, 256, 1536), (300, 128, 1000), (2048, 512, 4096)):
+            xl = torch.randn(tokens, cols, device=dev, dtype=torch.bfloat16)
+            w = torch.randn(features, cols * world, device=dev, dtype=torch.bfloat16) * 0.05
+            parts = [torch.empty_like(xl) for _ in range(world)]
+            dist.all_gather(parts, xl)
+            want = torch.cat(parts, dim=1).float() @ w.float().t()
+            for _ in range(3):
+                got = rc.allgather_gemm(xl, w)
+            torch.cuda.synchronize()
+            rc.check_status()
+            err = (got.float() - want).abs().max().item()
+            assert err <= 0.02 * want.abs().max().item() + 0.05, (tokens, cols, features, err)
         open(os.path.join(out_dir, f"ok{rank}"), "w").close()
     finally:
         dist.destroy_process_group()
