@@ -66,6 +66,92 @@ __global__ void qkv_rope_append_kernel(const bf16* __restrict__ q, const bf16* _
   }
 }
 
+// One thread moves 8 consecutive elements of the first rotary half together with their 8 partners of the second
+// half (or, for the interleaved layout / the non-rotary tail / v, one 16-byte chunk), so every access is a 16-byte
+// vector.  Requires head_dim, rotary_dim / 2 (non-interleaved) or rotary_dim (interleaved) to be multiples of 8.
+__global__ void qkv_rope_append_vec_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v,
+                                           bf16* __restrict__ q_out, bf16* __restrict__ kcache, bf16* __restrict__ vcache,
+                                           const int* __restrict__ base_pos, int batch, int seq, int q_heads, int kv_heads,
+                                           int head_dim, int rotary_dim, float log2_theta, int interleaved, int max_seq,
+                                           long long q_ld, long long k_ld, long long v_ld) {
+  const int half = rotary_dim >> 1;
+  // chunks per head: rotary part handled as (half / 8) pair-chunks when split, (rotary_dim / 8) chunks when interleaved
+  const int rot_chunks = interleaved ? rotary_dim / 8 : half / 8;
+  const int tail_chunks = (head_dim - rotary_dim) / 8;
+  const int qk_chunks = rot_chunks + tail_chunks;
+  const int v_chunks = head_dim / 8;
+  const long long per_token = (long long)(q_heads + kv_heads) * qk_chunks + (long long)kv_heads * v_chunks;
+  const long long total = (long long)batch * seq * per_token;
+  const int pos0 = base_pos ? base_pos[0] : 0;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / per_token;
+    long long w = i % per_token;
+    const int b = int(t / seq), sidx = int(t % seq);
+    const int pos = pos0 + sidx;
+    if (pos >= max_seq) continue;
+    const long long qk_total = (long long)(q_heads + kv_heads) * qk_chunks;
+    if (w >= qk_total) {  // v: straight 16-byte copy into the cache
+      w -= qk_total;
+      const int hv = int(w / v_chunks), c = int(w % v_chunks) * 8;
+      const uint4 val = *reinterpret_cast<const uint4*>(v + t * v_ld + (long long)hv * head_dim + c);
+      *reinterpret_cast<uint4*>(vcache + (((long long)b * kv_heads + hv) * max_seq + pos) * head_dim + c) = val;
+      continue;
+    }
+    const int h = int(w / qk_chunks), c = int(w % qk_chunks);
+    const bool is_q = h < q_heads;
+    const int hh = is_q ? h : h - q_heads;
+    const bf16* src = (is_q ? q + t * q_ld : k + t * k_ld) + (long long)hh * head_dim;
+    bf16* dst = is_q ? q_out + (t * q_heads + hh) * head_dim
+                     : kcache + (((long long)b * kv_heads + hh) * max_seq + pos) * head_dim;
+    if (c >= rot_chunks) {  // non-rotary tail
+      const int e = rotary_dim + (c - rot_chunks) * 8;
+      *reinterpret_cast<uint4*>(dst + e) = *reinterpret_cast<const uint4*>(src + e);
+      continue;
+    }
+    if (!interleaved) {
+      const int e = c * 8;
+      uint4 lo = *reinterpret_cast<const uint4*>(src + e), hi = *reinterpret_cast<const uint4*>(src + e + half);
+      uint32_t* lw = &lo.x;
+      uint32_t* hw = &hi.x;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float a[2] = {__uint_as_float(lw[j] << 16), __uint_as_float(lw[j] & 0xFFFF0000u)};
+        float bb[2] = {__uint_as_float(hw[j] << 16), __uint_as_float(hw[j] & 0xFFFF0000u)};
+        float ra[2], rb[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int p = e + 2 * j + u;
+          const float inv_freq = exp2f(-log2_theta * (2.f * float(p) / float(rotary_dim)));
+          float sn, cs;
+          sincosf(float(pos) * inv_freq, &sn, &cs);
+          ra[u] = a[u] * cs - bb[u] * sn;
+          rb[u] = bb[u] * cs + a[u] * sn;
+        }
+        __nv_bfloat162 o1 = __floats2bfloat162_rn(ra[0], ra[1]), o2 = __floats2bfloat162_rn(rb[0], rb[1]);
+        lw[j] = *reinterpret_cast<uint32_t*>(&o1);
+        hw[j] = *reinterpret_cast<uint32_t*>(&o2);
+      }
+      *reinterpret_cast<uint4*>(dst + e) = lo;
+      *reinterpret_cast<uint4*>(dst + e + half) = hi;
+    } else {
+      const int e = c * 8;  // pairs (e, e+1), (e+2, e+3), ...
+      uint4 val = *reinterpret_cast<const uint4*>(src + e);
+      uint32_t* vw = &val.x;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float a = __uint_as_float(vw[j] << 16), bb = __uint_as_float(vw[j] & 0xFFFF0000u);
+        const int p = (e >> 1) + j;
+        const float inv_freq = exp2f(-log2_theta * (2.f * float(p) / float(rotary_dim)));
+        float sn, cs;
+        sincosf(float(pos) * inv_freq, &sn, &cs);
+        __nv_bfloat162 o = __floats2bfloat162_rn(a * cs - bb * sn, bb * cs + a * sn);
+        vw[j] = *reinterpret_cast<uint32_t*>(&o);
+      }
+      *reinterpret_cast<uint4*>(dst + e) = val;
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------------
 // decode attention
 // ------------------------------------------------------------------------------------------------
@@ -402,6 +488,21 @@ extern "C" int tpb_qkv_rope_append(const void* q, const void* k, const void* v, 
   if (!q || !k || !v || !q_out || !kcache || !vcache || batch <= 0 || seq <= 0) return TPB_ERR_ARG;
   if ((head_dim & 1) || (rotary_dim & 1) || rotary_dim > head_dim || (q_ld & 1) || (k_ld & 1) || (v_ld & 1)) return TPB_ERR_ALIGN;
   cudaStream_t s = static_cast<cudaStream_t>(stream_);
+  const int half_ = rotary_dim / 2;
+  const bool vec_ok = (head_dim % 8 == 0) && (interleaved ? rotary_dim % 8 == 0 : half_ % 8 == 0) && !(q_ld & 7) && !(k_ld & 7) &&
+                      !(v_ld & 7) && !((uintptr_t)q & 15) && !((uintptr_t)k & 15) && !((uintptr_t)v & 15) && !((uintptr_t)q_out & 15) &&
+                      !((uintptr_t)kcache & 15) && !((uintptr_t)vcache & 15);
+  if (vec_ok) {
+    const int rot_chunks = interleaved ? rotary_dim / 8 : half_ / 8;
+    const long long per_token = (long long)(q_heads + kv_heads) * (rot_chunks + (head_dim - rotary_dim) / 8) + (long long)kv_heads * (head_dim / 8);
+    const long long vwork = (long long)batch * seq * per_token;
+    long long vgrid = (vwork + 255) / 256;
+    if (vgrid > 148 * 32) vgrid = 148 * 32;
+    qkv_rope_append_vec_kernel<<<int(vgrid), 256, 0, s>>>((const bf16*)q, (const bf16*)k, (const bf16*)v, (bf16*)q_out, (bf16*)kcache,
+                                                          (bf16*)vcache, base_pos, batch, seq, q_heads, kv_heads, head_dim, rotary_dim,
+                                                          log2f(theta), interleaved, max_seq, q_ld, k_ld, v_ld);
+    return cudaGetLastError() == cudaSuccess ? TPB_OK : TPB_ERR_CUDA;
+  }
   const long long work = (long long)batch * seq * (q_heads + 2 * kv_heads) * (head_dim / 2);
   long long grid = (work + 255) / 256;
   if (grid > 148 * 16) grid = 148 * 16;

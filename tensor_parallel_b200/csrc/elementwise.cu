@@ -82,7 +82,9 @@ __device__ __forceinline__ void block_sum2(float& a, float& b) {
 constexpr int NORM_THREADS = 256;
 constexpr int NORM_MAXV = 8;  // cols <= 16384
 
-template <typename T, int MODE>
+// MAXV = vectors of 8 elements a thread may hold (cols <= 256 * 8 * MAXV); small MAXV keeps the register count
+// low so that more rows are in flight per SM.
+template <typename T, int MODE, int MAXV>
 __global__ void __launch_bounds__(NORM_THREADS)
 norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ residual, const T* __restrict__ weight,
                 const T* __restrict__ bias, T* __restrict__ out, T* __restrict__ sum_out, float* __restrict__ rstd_out,
@@ -90,10 +92,10 @@ norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ residual, const T
   const size_t row = blockIdx.x;
   const T* xr = x + row * cols;
   const int nvec = cols >> 3;
-  float v[NORM_MAXV][8];
+  float v[MAXV][8];
   float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-  for (int i = 0; i < NORM_MAXV; ++i) {
+  for (int i = 0; i < MAXV; ++i) {
     const int vi = threadIdx.x + i * NORM_THREADS;
     if (vi < nvec) {
       Vec8<T>::load(xr + vi * 8, v[i]);
@@ -122,7 +124,7 @@ norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ residual, const T
     if (mean_out) mean_out[row] = mean;
   }
 #pragma unroll
-  for (int i = 0; i < NORM_MAXV; ++i) {
+  for (int i = 0; i < MAXV; ++i) {
     const int vi = threadIdx.x + i * NORM_THREADS;
     if (vi < nvec) {
       float w[8], b[8], o[8];
@@ -391,12 +393,20 @@ extern "C" int tpb_norm_fwd(const void* x, const void* residual, const void* wei
   if (!x || !out || rows <= 0 || cols <= 0) return TPB_ERR_ARG;
   if ((cols & 7) || cols > NORM_THREADS * 8 * NORM_MAXV) return TPB_ERR_SIZE;
   cudaStream_t s = static_cast<cudaStream_t>(stream_);
-#define LAUNCH(T, M)                                                                                               \
-  norm_fwd_kernel<T, M><<<rows, NORM_THREADS, 0, s>>>((const T*)x, (const T*)residual, (const T*)weight, (const T*)bias, \
-                                                      (T*)out, (T*)sum_out, rstd_out, mean_out, cols, eps)
+#define LAUNCH3(T, M, V)                                                                                              \
+  norm_fwd_kernel<T, M, V><<<rows, NORM_THREADS, 0, s>>>((const T*)x, (const T*)residual, (const T*)weight, (const T*)bias, \
+                                                         (T*)out, (T*)sum_out, rstd_out, mean_out, cols, eps)
+#define LAUNCH(T, M)                                                                     \
+  do {                                                                                   \
+    if (cols <= NORM_THREADS * 8) LAUNCH3(T, M, 1);                                      \
+    else if (cols <= NORM_THREADS * 16) LAUNCH3(T, M, 2);                                \
+    else if (cols <= NORM_THREADS * 32) LAUNCH3(T, M, 4);                                \
+    else LAUNCH3(T, M, 8);                                                               \
+  } while (0)
   if (dtype == 0) { if (mode) LAUNCH(bf16, 1); else LAUNCH(bf16, 0); }
   else            { if (mode) LAUNCH(float, 1); else LAUNCH(float, 0); }
 #undef LAUNCH
+#undef LAUNCH3
   TPB_CHECK_LAUNCH();
 }
 

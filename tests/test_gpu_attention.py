@@ -103,3 +103,25 @@ def test_attention_backward(b, sq, sk, hq, hkv, d, causal):
     for name, got, want in (("dq", q.grad, qr.grad), ("dk", k.grad, kr.grad), ("dv", v.grad, vr.grad)):
         err = (got.float() - want).norm().item() / (want.norm().item() + 1e-9)
         assert err < 0.03, (name, err)
+
+
+@pytest.mark.parametrize("interleaved,rotary_dim", [(False, 128), (False, 64), (True, 128), (True, 32)])
+def test_rope_append_variants(interleaved, rotary_dim):
+    """Prefill-sized append (many tokens per sequence) with full / partial and split / interleaved rotary layouts."""
+    nat = _native()
+    torch.manual_seed(4)
+    b, s, hq, hkv, d, smax, base = 2, 37, 4, 2, 128, 64, 5
+    qkv = torch.randn(b * s, (hq + 2 * hkv) * d, device="cuda", dtype=torch.bfloat16)
+    q2, k2, v2 = qkv[:, : hq * d], qkv[:, hq * d : (hq + hkv) * d], qkv[:, (hq + hkv) * d :]
+    kc = torch.zeros(b, hkv, smax, d, device="cuda", dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    q_out = torch.empty(b * s, hq, d, device="cuda", dtype=torch.bfloat16)
+    pos0 = torch.tensor([base], device="cuda", dtype=torch.int32)
+    nat.qkv_rope_append(q2, k2, v2, q_out, kc, vc, pos0, b, s, rotary_dim, 10000.0, interleaved=interleaved)
+    pos = torch.arange(base, base + s, device="cuda")[None].expand(b, s)
+    q_ref = OF.apply_rope_ref(q2.reshape(b, s, hq, d).float(), pos, 10000.0, rotary_dim, interleaved)
+    k_ref = OF.apply_rope_ref(k2.reshape(b, s, hkv, d).float(), pos, 10000.0, rotary_dim, interleaved)
+    torch.testing.assert_close(q_out.view(b, s, hq, d).float(), q_ref, atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(kc[:, :, base : base + s].transpose(1, 2).float(), k_ref, atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(vc[:, :, base : base + s].transpose(1, 2), v2.reshape(b, s, hkv, d))
+    assert kc[:, :, :base].abs().sum().item() == 0 and kc[:, :, base + s :].abs().sum().item() == 0
