@@ -143,7 +143,8 @@ def run_ours(args):
             dist.barrier()
             torch.cuda.synchronize(device)
 
-    # prefill (timed once for information)
+    # build the engine and run one untimed prefill (library / plan / allocation warm-up), then time a second prefill
+    tp_model.prefill(prompt, max_new_tokens=max_new)
     sync_all()
     t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
     t0.record()

@@ -317,6 +317,223 @@ __global__ void attn_decode_combine_kernel(const float* __restrict__ part_o, con
 }
 
 // ------------------------------------------------------------------------------------------------
+// fused decode step: RoPE on q / k, cache append, split-KV attention and the split combine in ONE kernel
+// ------------------------------------------------------------------------------------------------
+// q / k / v are rows of the fused projection output (one new token per sequence).  The CTA whose key range
+// contains the new position takes that key / value from the projection (rotated on the fly) instead of the
+// cache and also stores them into the cache for later steps.  With splits > 1 every CTA parks its partial
+// result; the last CTA to arrive for a (sequence, KV head) merges the partials (no second launch).
+// counters: uint32 [batch * kv_heads], zero-initialised once; they re-arm themselves.
+template <int D, int G>
+__global__ void __launch_bounds__(DEC_THREADS)
+attn_decode_fused_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v,
+                         bf16* __restrict__ kcache, bf16* __restrict__ vcache, bf16* __restrict__ out,
+                         float* __restrict__ part_o, float* __restrict__ part_ml, uint32_t* __restrict__ counters,
+                         const int* __restrict__ pos_ptr, int q_heads, int kv_heads, int g_total, int g_offset, int max_seq,
+                         int splits, float scale_log2e, int rotary_dim, float log2_theta, int interleaved, long long q_ld,
+                         long long k_ld, long long v_ld) {
+  constexpr int EPL = D / 8;
+  const int bh = blockIdx.x;
+  const int b = bh / kv_heads, kvh = bh % kv_heads;
+  const int split = blockIdx.y;
+  const int pos = pos_ptr[0];
+  const int len = min(pos + 1, max_seq);
+  const int chunk = (len + splits - 1) / splits;
+  const int k0 = split * chunk, k1 = min(len, k0 + chunk);
+  const bool owns_new = pos < max_seq && pos >= k0 && pos < k1;
+  const int k1_cache = owns_new ? pos : k1;  // keys taken from the cache
+
+  __shared__ float q_s[G][D];
+  __shared__ float knew_s[D], vnew_s[D];
+  __shared__ float red_o[DEC_WARPS][G][D];
+  __shared__ float red_m[DEC_WARPS][G], red_l[DEC_WARPS][G];
+  __shared__ uint32_t is_last;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sub = lane >> 3, part = lane & 7;
+  const int half = rotary_dim >> 1;
+
+  // rotate q (G heads) and the new k into shared memory; one thread per element pair
+  for (int i = threadIdx.x; i < (G + 1) * (D / 2); i += DEC_THREADS) {
+    const int hsel = i / (D / 2), p = i % (D / 2);
+    const bool is_k = hsel == G;
+    const bf16* src = is_k ? k + b * k_ld + (long long)kvh * D : q + b * q_ld + (long long)(kvh * g_total + g_offset + hsel) * D;
+    float* dst = is_k ? knew_s : q_s[hsel];
+    const float mul = is_k ? 1.f : scale_log2e;
+    if (p < half) {
+      const int ia = interleaved ? 2 * p : p;
+      const int ib = interleaved ? 2 * p + 1 : p + half;
+      const float inv_freq = exp2f(-log2_theta * (2.f * float(p) / float(rotary_dim)));
+      float sn, cs;
+      sincosf(float(pos) * inv_freq, &sn, &cs);
+      const float a = __bfloat162float(src[ia]), c = __bfloat162float(src[ib]);
+      // round through bf16 like the stand-alone append kernel, so cached and in-flight keys agree bit for bit
+      dst[ia] = __bfloat162float(__float2bfloat16(a * cs - c * sn)) * mul;
+      dst[ib] = __bfloat162float(__float2bfloat16(c * cs + a * sn)) * mul;
+    } else {
+      const int e = rotary_dim + 2 * (p - half);
+      dst[e] = __bfloat162float(src[e]) * mul;
+      dst[e + 1] = __bfloat162float(src[e + 1]) * mul;
+    }
+  }
+  for (int i = threadIdx.x; i < D; i += DEC_THREADS) vnew_s[i] = __bfloat162float(v[b * v_ld + (long long)kvh * D + i]);
+  __syncthreads();
+  if (owns_new) {  // persist the new key / value for later steps
+    for (int i = threadIdx.x; i < D; i += DEC_THREADS) {
+      kcache[((long long)bh * max_seq + pos) * D + i] = __float2bfloat16(knew_s[i]);
+      vcache[((long long)bh * max_seq + pos) * D + i] = __float2bfloat16(vnew_s[i]);
+    }
+  }
+
+  float m[G], l[G], acc[G][EPL];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    m[g] = -INFINITY;
+    l[g] = 0.f;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) acc[g][e] = 0.f;
+  }
+  const bf16* kbase = kcache + (long long)bh * max_seq * D + part * EPL;
+  const bf16* vbase = vcache + (long long)bh * max_seq * D + part * EPL;
+
+  auto consume = [&](const float (&kf)[EPL], const float (&vf)[EPL], bool valid) {
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float sc = 0.f;
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) sc += kf[e] * q_s[g][part * EPL + e];
+      sc += __shfl_xor_sync(0xffffffffu, sc, 1);
+      sc += __shfl_xor_sync(0xffffffffu, sc, 2);
+      sc += __shfl_xor_sync(0xffffffffu, sc, 4);
+      if (valid) {
+        const float m_new = fmaxf(m[g], sc);
+        const float corr = exp2f(m[g] - m_new);
+        const float pexp = exp2f(sc - m_new);
+        l[g] = l[g] * corr + pexp;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) acc[g][e] = acc[g][e] * corr + pexp * vf[e];
+        m[g] = m_new;
+      }
+    }
+  };
+
+  uint4 kraw[EPL / 8], vraw[EPL / 8];
+  auto fetch = [&](int key_base_) {
+    const int key_ = key_base_ + sub;
+    if (key_ < k1_cache) {
+      const uint4* kp = reinterpret_cast<const uint4*>(kbase + (long long)key_ * D);
+      const uint4* vp = reinterpret_cast<const uint4*>(vbase + (long long)key_ * D);
+#pragma unroll
+      for (int c = 0; c < EPL / 8; ++c) { kraw[c] = __ldg(kp + c); vraw[c] = __ldg(vp + c); }
+    } else {
+#pragma unroll
+      for (int c = 0; c < EPL / 8; ++c) { kraw[c] = make_uint4(0, 0, 0, 0); vraw[c] = make_uint4(0, 0, 0, 0); }
+    }
+  };
+  int key_base = k0 + warp * 4;
+  if (key_base < k1_cache) fetch(key_base);
+  for (; key_base < k1_cache; key_base += DEC_WARPS * 4) {
+    const bool valid = key_base + sub < k1_cache;
+    float kf[EPL], vf[EPL];
+#pragma unroll
+    for (int c = 0; c < EPL / 8; ++c) {
+      const uint32_t kw[4] = {kraw[c].x, kraw[c].y, kraw[c].z, kraw[c].w}, vw[4] = {vraw[c].x, vraw[c].y, vraw[c].z, vraw[c].w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        kf[c * 8 + 2 * j] = __uint_as_float(kw[j] << 16);
+        kf[c * 8 + 2 * j + 1] = __uint_as_float(kw[j] & 0xFFFF0000u);
+        vf[c * 8 + 2 * j] = __uint_as_float(vw[j] << 16);
+        vf[c * 8 + 2 * j + 1] = __uint_as_float(vw[j] & 0xFFFF0000u);
+      }
+    }
+    if (key_base + DEC_WARPS * 4 < k1_cache) fetch(key_base + DEC_WARPS * 4);
+    consume(kf, vf, valid);
+  }
+  if (owns_new && warp == 0) {  // the new token's key / value come straight from shared memory (warp-uniform branch)
+    float kf[EPL], vf[EPL];
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) {
+      kf[e] = __bfloat162float(__float2bfloat16(knew_s[part * EPL + e]));
+      vf[e] = __bfloat162float(__float2bfloat16(vnew_s[part * EPL + e]));
+    }
+    consume(kf, vf, sub == 0);
+  }
+
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+#pragma unroll
+    for (int off = 8; off <= 16; off <<= 1) {
+      const float m_o = __shfl_xor_sync(0xffffffffu, m[g], off);
+      const float l_o = __shfl_xor_sync(0xffffffffu, l[g], off);
+      const float m_new = fmaxf(m[g], m_o);
+      const float c_me = m[g] == -INFINITY ? 0.f : exp2f(m[g] - m_new);
+      const float c_o = m_o == -INFINITY ? 0.f : exp2f(m_o - m_new);
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) {
+        const float a_o = __shfl_xor_sync(0xffffffffu, acc[g][e], off);
+        acc[g][e] = acc[g][e] * c_me + a_o * c_o;
+      }
+      l[g] = l[g] * c_me + l_o * c_o;
+      m[g] = m_new;
+    }
+    if (sub == 0) {
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) red_o[warp][g][part * EPL + e] = acc[g][e];
+      if (part == 0) { red_m[warp][g] = m[g]; red_l[warp][g] = l[g]; }
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < G * D; i += DEC_THREADS) {
+    const int g = i / D, d = i % D;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) mm = fmaxf(mm, red_m[w][g]);
+    float ll = 0.f, oo = 0.f;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) {
+      const float c = red_m[w][g] == -INFINITY ? 0.f : exp2f(red_m[w][g] - mm);
+      ll += red_l[w][g] * c;
+      oo += red_o[w][g][d] * c;
+    }
+    const int qh = kvh * g_total + g_offset + g;
+    const long long row = (long long)b * q_heads + qh;
+    if (splits == 1) {
+      out[row * D + d] = __float2bfloat16(ll > 0.f ? oo / ll : 0.f);
+    } else {
+      part_o[(row * splits + split) * D + d] = oo;
+      if (d == 0) { part_ml[(row * splits + split) * 2] = mm; part_ml[(row * splits + split) * 2 + 1] = ll; }
+    }
+  }
+  if (splits == 1) return;
+  // last split to arrive merges the partial results of all splits
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t old = atomicAdd(counters + bh, 1u);
+    const bool last = old == uint32_t(splits - 1);
+    if (last) counters[bh] = 0;
+    is_last = last ? 1u : 0u;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  for (int i = threadIdx.x; i < G * D; i += DEC_THREADS) {
+    const int g = i / D, d = i % D;
+    const long long row = (long long)b * q_heads + kvh * g_total + g_offset + g;
+    float mm = -INFINITY;
+    for (int sp = 0; sp < splits; ++sp) mm = fmaxf(mm, __ldcg(part_ml + (row * splits + sp) * 2));
+    float ll = 0.f, oo = 0.f;
+    for (int sp = 0; sp < splits; ++sp) {
+      const float ms = __ldcg(part_ml + (row * splits + sp) * 2);
+      const float c = ms == -INFINITY ? 0.f : exp2f(ms - mm);
+      ll += __ldcg(part_ml + (row * splits + sp) * 2 + 1) * c;
+      oo += __ldcg(part_o + (row * splits + sp) * D + d) * c;
+    }
+    out[row * D + d] = __float2bfloat16(ll > 0.f ? oo / ll : 0.f);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
 // prefill attention (legacy mma.sync tensor path; 64 query rows x 64 keys per step, 4 warps)
 // ------------------------------------------------------------------------------------------------
 template <int D>
@@ -580,6 +797,44 @@ extern "C" int tpb_attn_prefill(const void* q, const void* k, const void* v, voi
     attn_prefill_kernel<64><<<grid, PF_THREADS, smem, s>>>((const bf16*)q, (const bf16*)k, (const bf16*)v, (bf16*)out, lse, sq, sk,
                                                            q_heads, kv_heads, q_sb, q_ss, q_sh, k_sb, k_ss, k_sh, v_sb, v_ss, v_sh,
                                                            o_sb, o_ss, o_sh, causal, sl2);
+  }
+  return cudaGetLastError() == cudaSuccess ? TPB_OK : TPB_ERR_CUDA;
+}
+
+// One launch per decode step and layer: RoPE(q, k) + cache append + attention over [0, pos] + split combine.
+// q / k / v: rows of the projection output for ONE new token per sequence ([batch, heads * head_dim], row pitches
+// q_ld / k_ld / v_ld); pos_ptr[0] = position of the new token = number of tokens already cached.
+// part_o / part_ml as for tpb_attn_decode; counters: uint32 [batch * kv_heads], zeroed once by the caller.
+extern "C" int tpb_attn_decode_fused(const void* q, const void* k, const void* v, void* kcache, void* vcache, void* out,
+                                     float* part_o, float* part_ml, void* counters, const int* pos_ptr, int batch, int q_heads,
+                                     int kv_heads, int head_dim, int max_seq, int splits, float scale, int rotary_dim, float theta,
+                                     int interleaved, long long q_ld, long long k_ld, long long v_ld, void* stream_) {
+  if (!q || !k || !v || !kcache || !vcache || !out || !pos_ptr || batch <= 0 || splits < 1 || q_heads % kv_heads) return TPB_ERR_ARG;
+  if (splits > 1 && (!part_o || !part_ml || !counters)) return TPB_ERR_ARG;
+  if (head_dim != 64 && head_dim != 128) return TPB_ERR_SIZE;
+  if ((rotary_dim & 1) || rotary_dim > head_dim) return TPB_ERR_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream_);
+  const int g_total = q_heads / kv_heads;
+  const float sl2 = scale * 1.4426950408889634f;
+  const float l2t = log2f(theta);
+  dim3 grid(batch * kv_heads, splits);
+  int done = 0;
+  while (done < g_total) {
+    const int left = g_total - done;
+    const int gmax = head_dim == 128 ? 4 : 8;
+    int gnow = 1;
+    while (gnow * 2 <= left && gnow * 2 <= gmax) gnow *= 2;
+#define DECF(D, G)                                                                                                           \
+  attn_decode_fused_kernel<D, G><<<grid, DEC_THREADS, 0, s>>>((const bf16*)q, (const bf16*)k, (const bf16*)v, (bf16*)kcache, \
+      (bf16*)vcache, (bf16*)out, part_o, part_ml, (uint32_t*)counters, pos_ptr, q_heads, kv_heads, g_total, done, max_seq,   \
+      splits, sl2, rotary_dim, l2t, interleaved, q_ld, k_ld, v_ld)
+    if (head_dim == 128) {
+      if (gnow == 1) DECF(128, 1); else if (gnow == 2) DECF(128, 2); else DECF(128, 4);
+    } else {
+      if (gnow == 1) DECF(64, 1); else if (gnow == 2) DECF(64, 2); else if (gnow == 4) DECF(64, 4); else DECF(64, 8);
+    }
+#undef DECF
+    done += gnow;
   }
   return cudaGetLastError() == cudaSuccess ? TPB_OK : TPB_ERR_CUDA;
 }

@@ -241,6 +241,64 @@ __global__ void rope_kernel(const T* __restrict__ x, T* __restrict__ out, const 
   }
 }
 
+// bf16 fast path: one thread rotates 8 consecutive elements of the first rotary half with their partners in the
+// second half (split layout) or 4 adjacent pairs (interleaved layout) using 16-byte accesses.
+__global__ void rope_vec_kernel(const bf16* __restrict__ x, bf16* __restrict__ out, const int64_t* __restrict__ positions,
+                                const int* __restrict__ base_pos, int seq, int tokens, int heads, int head_dim, int rotary_dim,
+                                float log2_theta, int interleaved, int inverse, long long x_stride_tok, long long out_stride_tok) {
+  const int half = rotary_dim >> 1;
+  const int chunks = interleaved ? rotary_dim / 8 : half / 8;
+  const long long total = (long long)tokens * heads * chunks;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int c = int(i % chunks);
+    const int h = int((i / chunks) % heads);
+    const int t = int(i / ((long long)chunks * heads));
+    const float pos = positions ? float(positions[t]) : float(base_pos[0] + (t % seq));
+    const bf16* xp = x + t * x_stride_tok + (long long)h * head_dim;
+    bf16* op = out + t * out_stride_tok + (long long)h * head_dim;
+    const int e = c * 8;
+    if (!interleaved) {
+      uint4 lo = *reinterpret_cast<const uint4*>(xp + e), hi = *reinterpret_cast<const uint4*>(xp + e + half);
+      uint32_t* lw = &lo.x;
+      uint32_t* hw = &hi.x;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float a[2] = {__uint_as_float(lw[j] << 16), __uint_as_float(lw[j] & 0xFFFF0000u)};
+        const float b[2] = {__uint_as_float(hw[j] << 16), __uint_as_float(hw[j] & 0xFFFF0000u)};
+        float ra[2], rb[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const float inv_freq = exp2f(-log2_theta * (2.f * float(e + 2 * j + u) / float(rotary_dim)));
+          float sn, cs;
+          sincosf(pos * inv_freq, &sn, &cs);
+          if (inverse) sn = -sn;
+          ra[u] = a[u] * cs - b[u] * sn;
+          rb[u] = b[u] * cs + a[u] * sn;
+        }
+        __nv_bfloat162 o1 = __floats2bfloat162_rn(ra[0], ra[1]), o2 = __floats2bfloat162_rn(rb[0], rb[1]);
+        lw[j] = *reinterpret_cast<uint32_t*>(&o1);
+        hw[j] = *reinterpret_cast<uint32_t*>(&o2);
+      }
+      *reinterpret_cast<uint4*>(op + e) = lo;
+      *reinterpret_cast<uint4*>(op + e + half) = hi;
+    } else {
+      uint4 val = *reinterpret_cast<const uint4*>(xp + e);
+      uint32_t* vw = &val.x;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float a = __uint_as_float(vw[j] << 16), b = __uint_as_float(vw[j] & 0xFFFF0000u);
+        const float inv_freq = exp2f(-log2_theta * (2.f * float((e >> 1) + j) / float(rotary_dim)));
+        float sn, cs;
+        sincosf(pos * inv_freq, &sn, &cs);
+        if (inverse) sn = -sn;
+        __nv_bfloat162 o = __floats2bfloat162_rn(a * cs - b * sn, b * cs + a * sn);
+        vw[j] = *reinterpret_cast<uint32_t*>(&o);
+      }
+      *reinterpret_cast<uint4*>(op + e) = val;
+    }
+  }
+}
+
 // pass-through of the non-rotary tail when out != x
 template <typename T>
 __global__ void rope_tail_kernel(const T* __restrict__ x, T* __restrict__ out, int tokens, int heads, int head_dim,
@@ -435,7 +493,14 @@ extern "C" int tpb_rope(const void* x, void* out, const int64_t* positions, cons
   cudaStream_t s = static_cast<cudaStream_t>(stream_);
   const long long work = (long long)tokens * heads * (rotary_dim / 2);
   const float l2t = log2f(theta);
-  if (dtype == 0)
+  const int half_ = rotary_dim / 2;
+  const bool vec_ok = dtype == 0 && head_dim % 8 == 0 && (interleaved ? rotary_dim % 8 == 0 : half_ % 8 == 0) && rotary_dim > 0 &&
+                      !(x_stride_tok & 7) && !(out_stride_tok & 7) && !((uintptr_t)x & 15) && !((uintptr_t)out & 15);
+  if (vec_ok) {
+    const long long vwork = (long long)tokens * heads * (interleaved ? rotary_dim / 8 : half_ / 8);
+    rope_vec_kernel<<<grid_for(vwork, 256), 256, 0, s>>>((const bf16*)x, (bf16*)out, positions, base_pos, seq, tokens, heads, head_dim,
+                                                         rotary_dim, l2t, interleaved, inverse, x_stride_tok, out_stride_tok);
+  } else if (dtype == 0)
     rope_kernel<bf16><<<grid_for(work, 256), 256, 0, s>>>((const bf16*)x, (bf16*)out, positions, base_pos, seq, tokens, heads,
                                                           head_dim, rotary_dim, l2t, interleaved, inverse, x_stride_tok, out_stride_tok);
   else

@@ -52,12 +52,14 @@ struct GemmParams {
   int m_tiles, n_tiles, k_blocks, k_splits, kb_per_split;
   int stages;
   int swapped;        // 0: A rows are tokens, B rows are features; 1: A rows are features, B rows are tokens
-  int ld_out;         // elements between consecutive tokens in out / residual / partial slots
+  int ld_out;         // elements between consecutive tokens in out / residual
+  int ld_slot;        // elements between consecutive tokens in the fp32 partial slots (= GEMM feature count)
   __nv_bfloat16* out;
   const __nv_bfloat16* bias;      // [features] or null
   float bias_scale;               // bias is multiplied by this before it is added (a row-parallel shard stores bias / world)
   const __nv_bfloat16* residual;  // [tokens, ld_out] or null
-  int act;                        // 0 none, 1 relu, 2 gelu(erf), 3 gelu(tanh), 4 silu  (direct epilogue only)
+  int act;                        // 0 none, 1 relu, 2 gelu(erf), 3 gelu(tanh), 4 silu, 5 gated silu: the GEMM features come in
+                                  // groups of [16 gate | 16 up] rows and out[t, 16 g + i] = silu(gate_i) * up_i (half as wide)
   // reduce mode (k_splits > 1 or world > 1)
   int reduce;
   int world, rank;
@@ -324,8 +326,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       auto store_partial = [&](float* slot, int n0, const float (&v)[16]) {
         if (!chunk_valid(n0)) return;
         if (!p.swapped) {
-          const size_t base = size_t(m) * p.ld_out + n0;
-          if (n0 + 16 <= p.n_extent && (p.ld_out & 3) == 0) {
+          const size_t base = size_t(m) * p.ld_slot + n0;
+          if (n0 + 16 <= p.n_extent && (p.ld_slot & 3) == 0) {
             float4* dst = reinterpret_cast<float4*>(slot + base);
 #pragma unroll
             for (int q = 0; q < 4; ++q) dst[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
@@ -335,14 +337,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         } else {
 #pragma unroll
           for (int j = 0; j < 16; ++j)
-            if (n0 + j < p.n_extent) slot[size_t(n0 + j) * p.ld_out + m] = v[j];
+            if (n0 + j < p.n_extent) slot[size_t(n0 + j) * p.ld_slot + m] = v[j];
         }
       };
       auto add_partial = [&](const float* slot, int n0, float (&v)[16]) {
         if (!chunk_valid(n0)) return;
         if (!p.swapped) {
-          const size_t base = size_t(m) * p.ld_out + n0;
-          if (n0 + 16 <= p.n_extent && (p.ld_out & 3) == 0) {
+          const size_t base = size_t(m) * p.ld_slot + n0;
+          if (n0 + 16 <= p.n_extent && (p.ld_slot & 3) == 0) {
             const float4* src = reinterpret_cast<const float4*>(slot + base);
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
@@ -355,11 +357,49 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         } else {
 #pragma unroll
           for (int j = 0; j < 16; ++j)
-            if (n0 + j < p.n_extent) v[j] += __ldcg(slot + size_t(n0 + j) * p.ld_out + m);
+            if (n0 + j < p.n_extent) v[j] += __ldcg(slot + size_t(n0 + j) * p.ld_slot + m);
+        }
+      };
+      // gated silu, normal orientation: vg = 16 gate columns, vu = the 16 up columns that follow them
+      auto finalize_gated = [&](int n0_gate, float (&vg)[16], float (&vu)[16]) {
+        if (!chunk_valid(n0_gate)) return;
+        const size_t base = size_t(m) * p.ld_out + (n0_gate >> 1);
+        float o[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float gte = vg[j] + (p.bias ? p.bias_scale * __bfloat162float(p.bias[n0_gate + j]) : 0.f);
+          const float upv = vu[j] + (p.bias ? p.bias_scale * __bfloat162float(p.bias[n0_gate + 16 + j]) : 0.f);
+          o[j] = gte / (1.f + __expf(-gte)) * upv;
+        }
+        if ((p.ld_out & 7) == 0) {
+          uint4 o0, o1;
+          o0.x = pack_bf16x2(o[0], o[1]);   o0.y = pack_bf16x2(o[2], o[3]);
+          o0.z = pack_bf16x2(o[4], o[5]);   o0.w = pack_bf16x2(o[6], o[7]);
+          o1.x = pack_bf16x2(o[8], o[9]);   o1.y = pack_bf16x2(o[10], o[11]);
+          o1.z = pack_bf16x2(o[12], o[13]); o1.w = pack_bf16x2(o[14], o[15]);
+          uint4* op = reinterpret_cast<uint4*>(p.out + base);
+          op[0] = o0;
+          op[1] = o1;
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) p.out[base + j] = __float2bfloat16(o[j]);
         }
       };
       auto finalize = [&](int n0, float (&v)[16]) {  // bias, activation, residual, bf16 store
         if (!chunk_valid(n0)) return;
+        if (p.act == 5) {
+          // gated silu, swapped orientation: lanes 0-15 of a warp hold gate rows, lanes 16-31 the matching up rows
+          const float b = p.bias ? p.bias_scale * __bfloat162float(p.bias[m]) : 0.f;
+          const int f_out = (m >> 5) * 16 + (m & 15);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float x = v[j] + b;
+            const float partner = __shfl_xor_sync(0xffffffffu, x, 16);
+            if ((lane & 16) == 0 && n0 + j < p.n_extent)
+              p.out[size_t(n0 + j) * p.ld_out + f_out] = __float2bfloat16(x / (1.f + __expf(-x)) * partner);
+          }
+          return;
+        }
         if (!p.swapped) {
           const size_t base = size_t(m) * p.ld_out + n0;
           if (n0 + 16 <= p.n_extent && (p.ld_out & 7) == 0) {
@@ -423,13 +463,26 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       };
 
       const bool split_k = p.k_splits > 1;
+      const bool gated_cols = p.act == 5 && !p.swapped;  // column chunks alternate gate / up
       if (!split_k) {
+        if (gated_cols) {
+          if constexpr (BN >= 32) {
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 16) {
-          float v[16];
-          read_acc(c0, v);
-          if (p.world > 1) push_to_peers(nt * BN + c0, v);
-          else finalize(nt * BN + c0, v);
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+              float vg[16], vu[16];
+              read_acc(c0, vg);
+              read_acc(c0 + 16, vu);
+              finalize_gated(nt * BN + c0, vg, vu);
+            }
+          }
+        } else {
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += 16) {
+            float v[16];
+            read_acc(c0, v);
+            if (p.world > 1) push_to_peers(nt * BN + c0, v);
+            else finalize(nt * BN + c0, v);
+          }
         }
         tc_fence_before();
         __syncwarp();
@@ -458,15 +511,31 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         asm volatile("bar.sync 2, %0;" ::"n"(EPI_THREADS) : "memory");
         if (*epi_last) {
           __threadfence();
+          if (gated_cols) {
+            if constexpr (BN >= 32) {
 #pragma unroll 1
-          for (int c0 = 0; c0 < BN; c0 += 16) {
-            float v[16];
+              for (int c0 = 0; c0 < BN; c0 += 32) {
+                float vg[16], vu[16];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = 0.f;
-            for (int sp = 0; sp < p.k_splits; ++sp)
-              add_partial(p.slots[p.rank] + size_t(p.world + sp) * p.slot_stride, nt * BN + c0, v);
-            if (p.world > 1) push_to_peers(nt * BN + c0, v);
-            else finalize(nt * BN + c0, v);
+                for (int j = 0; j < 16; ++j) { vg[j] = 0.f; vu[j] = 0.f; }
+                for (int sp = 0; sp < p.k_splits; ++sp) {
+                  add_partial(p.slots[p.rank] + size_t(p.world + sp) * p.slot_stride, nt * BN + c0, vg);
+                  add_partial(p.slots[p.rank] + size_t(p.world + sp) * p.slot_stride, nt * BN + c0 + 16, vu);
+                }
+                finalize_gated(nt * BN + c0, vg, vu);
+              }
+            }
+          } else {
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+              float v[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) v[j] = 0.f;
+              for (int sp = 0; sp < p.k_splits; ++sp)
+                add_partial(p.slots[p.rank] + size_t(p.world + sp) * p.slot_stride, nt * BN + c0, v);
+              if (p.world > 1) push_to_peers(nt * BN + c0, v);
+              else finalize(nt * BN + c0, v);
+            }
           }
         }
       }
@@ -684,6 +753,7 @@ static int gemm_impl(const void* x, const void* w, void* out, const void* bias, 
                      int features, int k, int ldx, int ldw, int ld_out, int act, float bias_scale,
                      const tpb_gemm_plan_t* plan, const tpb_reduce_ctx_t* rc, const tpb_allgather_ctx_t* ag, void* stream_) {
   if (!x || !w || !out || !plan) return TPB_ERR_ARG;
+  if (act == 5 && ((features & 31) || residual || (rc && rc->world > 1 && plan->reduce && rc->world != 1))) return TPB_ERR_ARG;
   if ((ldx & 7) || (ldw & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return TPB_ERR_ALIGN;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   GemmParams p;
@@ -698,6 +768,7 @@ static int gemm_impl(const void* x, const void* w, void* out, const void* bias, 
   p.k_splits = plan->k_splits;
   p.kb_per_split = plan->kb_per_split;
   p.ld_out = ld_out;
+  p.ld_slot = act == 5 ? features : ld_out;
   p.out = static_cast<__nv_bfloat16*>(out);
   p.bias = static_cast<const __nv_bfloat16*>(bias);
   p.residual = static_cast<const __nv_bfloat16*>(residual);
@@ -708,7 +779,7 @@ static int gemm_impl(const void* x, const void* w, void* out, const void* bias, 
   p.rank = 0;
   if (plan->reduce) {
     if (!rc || rc->world < 1 || rc->world > MAX_WORLD) return TPB_ERR_ARG;
-    if (size_t(tokens) * size_t(ld_out) > rc->slot_stride) return TPB_ERR_WORKSPACE;
+    if (size_t(tokens) * size_t(act == 5 ? features : ld_out) > rc->slot_stride) return TPB_ERR_WORKSPACE;
     if (rc->world + plan->k_splits > rc->max_slots || plan->tiles > rc->max_tiles || !rc->split_counters) return TPB_ERR_WORKSPACE;
     p.world = rc->world;
     p.rank = rc->rank;

@@ -2,12 +2,14 @@
 captured once as a CUDA graph and replayed per token.
 
 The engine is what ``generate()`` of a tensor-parallel Llama model runs on CUDA.  It reads the
-shard's own parameters (q/k/v and gate/up are re-pointed at fused buffers, so no weight is
-duplicated), keeps a pre-allocated head-sharded KV cache ``[batch, local_kv_heads, max_seq, head_dim]``
+shard's own parameters (q/k/v are re-pointed at one fused buffer; gate/up are copied once into an
+interleaved layout that lets the GEMM epilogue apply SwiGLU), keeps a pre-allocated head-sharded KV cache ``[batch, local_kv_heads, max_seq, head_dim]``
 per layer, and per layer launches::
 
-    rmsnorm -> qkv GEMM -> rope + cache append -> attention -> o_proj GEMM (+ all-reduce + residual)
-            -> rmsnorm -> gate/up GEMM -> swiglu -> down GEMM (+ all-reduce + residual)
+    rmsnorm -> qkv GEMM -> [rope + cache append + attention + split merge] -> o_proj GEMM (+ all-reduce + residual)
+            -> rmsnorm -> gate/up GEMM (+ SwiGLU epilogue) -> down GEMM (+ all-reduce + residual)
+
+(seven kernels per layer in a decode step; prefill keeps rope/append and attention as separate launches)
 
 With several ranks the two row-parallel GEMMs push their partial tiles to every peer from the
 epilogue and reduce them in the same kernel (decode), or write into symmetric memory and run the
@@ -67,9 +69,9 @@ class LlamaEngine:
             nq, nk = wq.shape[0], wk.shape[0]
             wq.data, wk.data, wv.data = wqkv[:nq], wqkv[nq : nq + nk], wqkv[nq + nk :]
             wg, wu = mlp.gate_proj.weight, mlp.up_proj.weight
-            wgu = torch.cat([wg.detach(), wu.detach()], dim=0).contiguous()
             ff = wg.shape[0]
-            wg.data, wu.data = wgu[:ff], wgu[ff:]
+            # engine-owned copy, rows interleaved [16 gate | 16 up] so that the GEMM epilogue applies SwiGLU itself
+            wgu = native.interleave_gate_up(wg.detach(), wu.detach())
             self.layers.append(dict(
                 wqkv=wqkv, wo=attn.o_proj.weight.detach(), wgu=wgu, wd=mlp.down_proj.weight.detach(),
                 ln1=layer.input_layernorm.weight.detach(), ln2=layer.post_attention_layernorm.weight.detach(),
@@ -92,14 +94,15 @@ class LlamaEngine:
         self.qkv = torch.zeros(B, (self.nq + 2 * self.nkv) * D, **bf)
         self.q_rot = torch.zeros(B, self.nq, D, **bf)
         self.attn = torch.zeros(B, self.nq * D, **bf)
-        self.gu = torch.zeros(B, 2 * self.ff, **bf)
+        self.gu = None  # the gate|up product never reaches memory (SwiGLU is applied in the GEMM epilogue)
         self.act = torch.zeros(B, self.ff, **bf)
         self.logits_local = torch.zeros(B, self.vocab_local, **bf)
         self.next_ids = torch.zeros(B, dtype=torch.int64, device=dev)
         # split the key range only when (batch x kv heads) alone cannot occupy the SMs
         self.splits = 1 if B * self.nkv >= 128 else max(1, min(8, math.ceil(256 / (B * self.nkv))))
         self.attn_ws = (torch.empty(B * self.nq * self.splits * D, dtype=torch.float32, device=dev),
-                        torch.empty(B * self.nq * self.splits * 2, dtype=torch.float32, device=dev))
+                        torch.empty(B * self.nq * self.splits * 2, dtype=torch.float32, device=dev),
+                        torch.zeros(B * self.nkv, dtype=torch.int32, device=dev))
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.graph_batch = 0
         self.kernels_per_step = 0
@@ -126,11 +129,12 @@ class LlamaEngine:
         native.gemm_nt(n, L["wqkv"], out=qkv)
         nq_w, nk_w = self.nq * D, self.nkv * D
         q2, k2, v2 = qkv[:, :nq_w], qkv[:, nq_w : nq_w + nk_w], qkv[:, nq_w + nk_w :]
-        native.qkv_rope_append(q2, k2, v2, q_rot, self.kcache[i], self.vcache[i], self.pos, batch, seq, D, self.theta)
         if decode:
-            native.attn_decode(q_rot, self.kcache[i][:batch], self.vcache[i][:batch], self.pos, 1, splits=self.splits,
-                               workspace=self.attn_ws, out=attn.view(batch, self.nq, D))
+            # RoPE, cache append, split-KV attention and the split merge: one launch
+            native.attn_decode_fused(q2, k2, v2, self.kcache[i][:batch], self.vcache[i][:batch], self.pos, D, self.theta,
+                                     splits=self.splits, workspace=self.attn_ws, out=attn.view(batch, self.nq, D))
         else:
+            native.qkv_rope_append(q2, k2, v2, q_rot, self.kcache[i], self.vcache[i], self.pos, batch, seq, D, self.theta)
             total = self._prefill_base + seq
             k = self.kcache[i][:batch, :, :total].transpose(1, 2)
             v = self.vcache[i][:batch, :, :total].transpose(1, 2)
@@ -138,8 +142,7 @@ class LlamaEngine:
             attn = out.view(batch * seq, self.nq * D)
         self._row_parallel(attn, L["wo"], x)
         native.norm_forward(x, L["ln2"], None, self.eps, 0, out=n)
-        native.gemm_nt(n, L["wgu"], out=gu)
-        native.act_forward(gu[:, : self.ff], gu[:, self.ff :], 4, out=act)
+        native.gemm_nt(n, L["wgu"], out=act, act="swiglu16")  # gate/up projection with SwiGLU in the epilogue
         self._row_parallel(act, L["wd"], x)
 
     def _head(self, x, n, logits_local, batch):
@@ -168,7 +171,7 @@ class LlamaEngine:
         n = torch.empty(tokens, self.hidden, **bf)
         qkv = torch.empty(tokens, (self.nq + 2 * self.nkv) * D, **bf)
         q_rot = torch.empty(tokens, self.nq, D, **bf)
-        gu = torch.empty(tokens, 2 * self.ff, **bf)
+        gu = None
         act = torch.empty(tokens, self.ff, **bf)
         for i in range(len(self.layers)):
             self._layer(i, x, n, qkv, q_rot, None, gu, act, batch, seq, decode=False)
@@ -186,7 +189,7 @@ class LlamaEngine:
         native.embedding(self.ids[:batch], self.embed, out=self.x[:batch])
         x, n = self.x[:batch], self.n[:batch]
         for i in range(len(self.layers)):
-            self._layer(i, x, n, self.qkv[:batch], self.q_rot[:batch], self.attn[:batch], self.gu[:batch], self.act[:batch],
+            self._layer(i, x, n, self.qkv[:batch], self.q_rot[:batch], self.attn[:batch], None, self.act[:batch],
                         batch, 1, decode=True)
         logits = self._head(x, n, self.logits_local[:batch], batch)
         torch.argmax(logits.float(), dim=-1, out=self.next_ids[:batch])

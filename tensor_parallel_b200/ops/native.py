@@ -138,7 +138,7 @@ def device_state(device: torch.device) -> DeviceState:
 LIB.tpb_gemm_plan.argtypes = [c_int, c_int, c_int, c_int, c_int, c_int, ctypes.POINTER(GemmPlan)]
 LIB.tpb_gemm_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                               c_int, c_float, ctypes.POINTER(GemmPlan), ctypes.POINTER(ReduceCtx), c_void_p]
-ACT_CODES = {None: 0, "none": 0, "relu": 1, "gelu": 2, "gelu_tanh": 3, "silu": 4}
+ACT_CODES = {None: 0, "none": 0, "relu": 1, "gelu": 2, "gelu_tanh": 3, "silu": 4, "swiglu16": 5}
 _plan_cache: Dict[Tuple, GemmPlan] = {}
 
 
@@ -167,13 +167,13 @@ def gemm_nt(x2d: torch.Tensor, w: torch.Tensor, bias=None, residual=None, act=No
     features = w.shape[0]
     x2d, w = _tma_ready(x2d), _tma_ready(w)
     if out is None:
-        out = torch.empty(tokens, features, dtype=torch.bfloat16, device=x2d.device)
+        out = torch.empty(tokens, features // 2 if act == "swiglu16" else features, dtype=torch.bfloat16, device=x2d.device)
     plan = gemm_plan(tokens, features, k, world, force_splits, force_kbox)
     state = device_state(x2d.device)
     ctx = reduce_ctx
     if ctx is None:
         if plan.reduce:
-            state.ensure_slots(tokens * out.stride(0))
+            state.ensure_slots(tokens * (features if act == "swiglu16" else out.stride(0)))
         ctx = state.ctx
     check(LIB.tpb_gemm_bf16(_ptr(x2d), _ptr(w), _ptr(out), _ptr(bias), _ptr(residual), tokens, features, k, x2d.stride(0),
                             w.stride(0), out.stride(0), ACT_CODES[act], bias_scale, ctypes.byref(plan), ctypes.byref(ctx), _stream()),
@@ -194,6 +194,15 @@ def _tma_ready(t: torch.Tensor) -> torch.Tensor:
     view = buf[:, :cols]
     view.copy_(t)
     return view
+
+
+def interleave_gate_up(gate_w: torch.Tensor, up_w: torch.Tensor) -> torch.Tensor:
+    """Weight of a fused gate|up projection for ``gemm_nt(..., act="swiglu16")``: rows alternate in groups of
+    16 gate rows followed by their 16 up rows, so the GEMM epilogue can form ``silu(gate) * up`` in registers."""
+    f, h = gate_w.shape
+    if f % 16:
+        raise ValueError("the gated width must be a multiple of 16")
+    return torch.stack((gate_w.reshape(f // 16, 16, h), up_w.reshape(f // 16, 16, h)), dim=1).reshape(2 * f, h).contiguous()
 
 
 LIB.tpb_transpose_bf16.argtypes = [c_void_p, c_void_p, c_int, c_int, c_ll, c_ll, c_void_p]
@@ -515,6 +524,33 @@ def attn_decode(q, kcache, vcache, len_ptr, len_add, scale=None, splits=1, works
     check(LIB.tpb_attn_decode(_ptr(q), _ptr(kcache), _ptr(vcache), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(len_ptr), len_add,
                               b, hq, hkv, d, smax, splits, scale, _stream()), "tpb_attn_decode")
     launch_count += 1 + (1 if splits > 1 else 0) + max(0, (hq // hkv) // (4 if d == 128 else 8) - 1)
+    return out
+
+
+LIB.tpb_attn_decode_fused.argtypes = [c_void_p] * 10 + [c_int] * 6 + [c_float, c_int, c_float, c_int, c_ll, c_ll, c_ll, c_void_p]
+
+
+def attn_decode_fused(q, k, v, kcache, vcache, pos_ptr, rotary_dim, theta, interleaved=False, scale=None, splits=1,
+                      workspace=None, out=None):
+    """One decode step of attention in a single launch: rotate q / k of the new token (``q/k/v``: 2-D row views of the
+    projection output), append k, v to the cache at ``pos_ptr[0]``, attend over ``[0, pos]`` and merge the key splits.
+    ``workspace = (part_o, part_ml, counters)`` with ``counters`` an int32 tensor ``[batch * kv_heads]`` zeroed once."""
+    global launch_count
+    d = kcache.shape[3]
+    b, hq, hkv, smax = q.shape[0], q.shape[1] // d, kcache.shape[1], kcache.shape[2]
+    out = torch.empty(b, hq, d, dtype=q.dtype, device=q.device) if out is None else out
+    part_o = part_ml = counters = None
+    if splits > 1:
+        if workspace is None:
+            workspace = (torch.empty(b * hq * splits * d, dtype=torch.float32, device=q.device),
+                         torch.empty(b * hq * splits * 2, dtype=torch.float32, device=q.device),
+                         torch.zeros(b * hkv, dtype=torch.int32, device=q.device))
+        part_o, part_ml, counters = workspace
+    scale = 1.0 / math.sqrt(d) if scale is None else scale
+    check(LIB.tpb_attn_decode_fused(_ptr(q), _ptr(k), _ptr(v), _ptr(kcache), _ptr(vcache), _ptr(out), _ptr(part_o), _ptr(part_ml),
+                                    _ptr(counters), _ptr(pos_ptr), b, hq, hkv, d, smax, splits, scale, rotary_dim, theta,
+                                    int(interleaved), q.stride(0), k.stride(0), v.stride(0), _stream()), "tpb_attn_decode_fused")
+    launch_count += max(1, (hq // hkv) // (4 if d == 128 else 8))
     return out
 
 

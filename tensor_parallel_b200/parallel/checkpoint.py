@@ -95,15 +95,21 @@ def load_sharded_state_dict_(tp_model, state: Mapping, strict: bool = True):
     unexpected = [k for k in state if k not in slots]
     if strict and (unexpected or [k for k in missing if "_sanity_check" not in k]):
         raise KeyError(f"missing keys {missing[:5]}..., unexpected keys {unexpected[:5]}...")
+    replaced = {}  # id(old tensor) -> new tensor, so that tied slots keep sharing one tensor
     with torch.no_grad():
         for key, value in state.items():
             if key not in slots:
                 continue
             sub, store, local = slots[key]
             old = store[local]
+            if id(old) in replaced:
+                continue
             new = value.to(device_map[key])
             if isinstance(old, torch.nn.Parameter):
-                store[local] = torch.nn.Parameter(new, requires_grad=old.requires_grad)
-            else:
-                store[local] = new
+                new = torch.nn.Parameter(new, requires_grad=old.requires_grad)
+            replaced[id(old)] = new
+        for sub, store, local in slots.values():
+            old = store[local]
+            if id(old) in replaced:
+                store[local] = replaced[id(old)]
     return missing, unexpected

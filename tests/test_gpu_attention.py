@@ -125,3 +125,33 @@ def test_rope_append_variants(interleaved, rotary_dim):
     torch.testing.assert_close(kc[:, :, base : base + s].transpose(1, 2).float(), k_ref, atol=2e-2, rtol=2e-2)
     torch.testing.assert_close(vc[:, :, base : base + s].transpose(1, 2), v2.reshape(b, s, hkv, d))
     assert kc[:, :, :base].abs().sum().item() == 0 and kc[:, :, base + s :].abs().sum().item() == 0
+
+
+@pytest.mark.parametrize("hq,hkv,d", [(8, 8, 128), (8, 2, 128), (16, 1, 64), (6, 2, 64)])
+@pytest.mark.parametrize("splits", [1, 4])
+def test_fused_decode_step_matches_separate_kernels(hq, hkv, d, splits):
+    """rope + append + attention + split merge in one launch vs the three stand-alone kernels, two steps in a row."""
+    nat = _native()
+    torch.manual_seed(5)
+    b, ctx, smax = 3, 150, 256
+    kc = torch.zeros(b, hkv, smax, d, device="cuda", dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    kc[:, :, :ctx] = torch.randn(b, hkv, ctx, d, device="cuda")
+    vc[:, :, :ctx] = torch.randn(b, hkv, ctx, d, device="cuda")
+    kc2, vc2 = kc.clone(), vc.clone()
+    pos = torch.tensor([ctx], device="cuda", dtype=torch.int32)
+    ws = None
+    for step in range(2):
+        qkv = torch.randn(b, (hq + 2 * hkv) * d, device="cuda", dtype=torch.bfloat16)
+        q2, k2, v2 = qkv[:, : hq * d], qkv[:, hq * d : (hq + hkv) * d], qkv[:, (hq + hkv) * d :]
+        q_out = torch.empty(b, hq, d, device="cuda", dtype=torch.bfloat16)
+        nat.qkv_rope_append(q2, k2, v2, q_out, kc, vc, pos, b, 1, d, 10000.0)
+        want = nat.attn_decode(q_out, kc, vc, pos, 1, splits=splits)
+        if ws is None and splits > 1:
+            ws = (torch.empty(b * hq * splits * d, device="cuda"), torch.empty(b * hq * splits * 2, device="cuda"),
+                  torch.zeros(b * hkv, dtype=torch.int32, device="cuda"))
+        got = nat.attn_decode_fused(q2, k2, v2, kc2, vc2, pos, d, 10000.0, splits=splits, workspace=ws)
+        torch.testing.assert_close(got.float(), want.float(), atol=1e-2, rtol=1e-2)
+        torch.testing.assert_close(kc2, kc)
+        torch.testing.assert_close(vc2, vc)
+        pos += 1

@@ -120,6 +120,22 @@ def test_linear_autograd():
     _check(b.grad, br.grad, 384)
 
 
+@pytest.mark.parametrize("tokens,splits", [(8, 0), (8, 3), (40, 0), (300, 0), (2048, 0)])
+def test_gemm_fused_swiglu_epilogue(tokens, splits):
+    nat = _native()
+    torch.manual_seed(6)
+    f, k = 1376, 1024
+    x = torch.randn(tokens, k, device="cuda", dtype=torch.bfloat16)
+    wg = torch.randn(f, k, device="cuda", dtype=torch.bfloat16) * 0.05
+    wu = torch.randn(f, k, device="cuda", dtype=torch.bfloat16) * 0.05
+    out = nat.gemm_nt(x, nat.interleave_gate_up(wg, wu), act="swiglu16", force_splits=splits)
+    torch.cuda.synchronize()
+    nat.device_state(x.device).check_status()
+    assert out.shape == (tokens, f)
+    ref = torch.nn.functional.silu(x.float() @ wg.float().t()) * (x.float() @ wu.float().t())
+    _check(out, ref, k)
+
+
 def test_gemm_k_not_multiple_of_8():
     nat = _native()
     torch.manual_seed(5)

@@ -98,6 +98,19 @@ def test_convert_state_dict_and_meta_loading(world):
     assert all(("module_shards." in k) or ("_sanity_check_params." in k) or ("flat_shards." in k) for k in device_map)
 
 
+def test_meta_loading_keeps_tied_weights_tied():
+    model = _models()["gpt2"]
+    with torch.device("meta"):
+        skeleton = GPT2LMHeadModel(model.config)
+    wrapped = tp.tensor_parallel(skeleton, ["cpu", "cpu"], sharded=False)
+    converted = tp.convert_state_dict(model.state_dict(), wrapped.tensor_parallel_config, world_size=2)
+    tp.load_sharded_state_dict_(wrapped, converted, strict=False)
+    for shard in wrapped.module_shards:
+        assert shard.lm_head.tp_wrapped_module.weight is shard.transformer.wte.tp_wrapped_module.weight
+    ids = torch.randint(0, 90, (2, 6))
+    torch.testing.assert_close(wrapped(input_ids=ids).logits, model(input_ids=ids).logits, atol=3e-5, rtol=1e-5)
+
+
 def test_converted_keys_match_live_keys():
     model = _models()["gpt2"]
     wrapped = tp.tensor_parallel(model, ["cpu", "cpu"], sharded=False)
