@@ -12,6 +12,8 @@
 #include <stdint.h>
 
 #include "attn_common.cuh"
+#include "launch.cuh"
+#include "ptx_sm100.cuh"
 #include "tpb_api.h"
 
 namespace tpb {
@@ -333,6 +335,8 @@ attn_decode_fused_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k,
                          int splits, float scale_log2e, int rotary_dim, float log2_theta, int interleaved, long long q_ld,
                          long long k_ld, long long v_ld) {
   constexpr int EPL = D / 8;
+  pdl_trigger();
+  pdl_wait();
   const int bh = blockIdx.x;
   const int b = bh / kv_heads, kvh = bh % kv_heads;
   const int split = blockIdx.y;
@@ -825,9 +829,9 @@ extern "C" int tpb_attn_decode_fused(const void* q, const void* k, const void* v
     int gnow = 1;
     while (gnow * 2 <= left && gnow * 2 <= gmax) gnow *= 2;
 #define DECF(D, G)                                                                                                           \
-  attn_decode_fused_kernel<D, G><<<grid, DEC_THREADS, 0, s>>>((const bf16*)q, (const bf16*)k, (const bf16*)v, (bf16*)kcache, \
-      (bf16*)vcache, (bf16*)out, part_o, part_ml, (uint32_t*)counters, pos_ptr, q_heads, kv_heads, g_total, done, max_seq,   \
-      splits, sl2, rotary_dim, l2t, interleaved, q_ld, k_ld, v_ld)
+  launch_kernel(attn_decode_fused_kernel<D, G>, grid, dim3(DEC_THREADS), 0, s, (const bf16*)q, (const bf16*)k, (const bf16*)v,     \
+                (bf16*)kcache, (bf16*)vcache, (bf16*)out, part_o, part_ml, (uint32_t*)counters, pos_ptr, q_heads, kv_heads, g_total, \
+                done, max_seq, splits, sl2, rotary_dim, l2t, interleaved, q_ld, k_ld, v_ld)
     if (head_dim == 128) {
       if (gnow == 1) DECF(128, 1); else if (gnow == 2) DECF(128, 2); else DECF(128, 4);
     } else {

@@ -7,6 +7,8 @@
 #include <math.h>
 #include <stdint.h>
 
+#include "launch.cuh"
+#include "ptx_sm100.cuh"
 #include "tpb_api.h"
 
 namespace tpb {
@@ -89,6 +91,8 @@ __global__ void __launch_bounds__(NORM_THREADS)
 norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ residual, const T* __restrict__ weight,
                 const T* __restrict__ bias, T* __restrict__ out, T* __restrict__ sum_out, float* __restrict__ rstd_out,
                 float* __restrict__ mean_out, int cols, float eps) {
+  pdl_trigger();
+  pdl_wait();
   const size_t row = blockIdx.x;
   const T* xr = x + row * cols;
   const int nvec = cols >> 3;
@@ -386,6 +390,8 @@ __global__ void act_bwd_kernel(const T* __restrict__ dout, const T* __restrict__
 template <typename T>
 __global__ void embedding_kernel(const int64_t* __restrict__ ids, const T* __restrict__ table, T* __restrict__ out,
                                  int tokens, int cols, long long table_ld, long long out_ld) {
+  pdl_trigger();
+  pdl_wait();
   const int vec_per_row = cols >> 3;
   const long long total = (long long)tokens * vec_per_row;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -452,8 +458,8 @@ extern "C" int tpb_norm_fwd(const void* x, const void* residual, const void* wei
   if ((cols & 7) || cols > NORM_THREADS * 8 * NORM_MAXV) return TPB_ERR_SIZE;
   cudaStream_t s = static_cast<cudaStream_t>(stream_);
 #define LAUNCH3(T, M, V)                                                                                              \
-  norm_fwd_kernel<T, M, V><<<rows, NORM_THREADS, 0, s>>>((const T*)x, (const T*)residual, (const T*)weight, (const T*)bias, \
-                                                         (T*)out, (T*)sum_out, rstd_out, mean_out, cols, eps)
+  launch_kernel(norm_fwd_kernel<T, M, V>, dim3(rows), dim3(NORM_THREADS), 0, s, (const T*)x, (const T*)residual, (const T*)weight, \
+                (const T*)bias, (T*)out, (T*)sum_out, rstd_out, mean_out, cols, eps)
 #define LAUNCH(T, M)                                                                     \
   do {                                                                                   \
     if (cols <= NORM_THREADS * 8) LAUNCH3(T, M, 1);                                      \
@@ -549,7 +555,7 @@ extern "C" int tpb_embedding(const int64_t* ids, const void* table, void* out, i
   cudaStream_t s = static_cast<cudaStream_t>(stream_);
   const long long work = (long long)tokens * (cols / 8);
   if (dtype == 0)
-    embedding_kernel<bf16><<<grid_for(work, 256), 256, 0, s>>>(ids, (const bf16*)table, (bf16*)out, tokens, cols, table_ld, out_ld);
+    launch_kernel(embedding_kernel<bf16>, dim3(grid_for(work, 256)), dim3(256), 0, s, ids, (const bf16*)table, (bf16*)out, tokens, cols, table_ld, out_ld);
   else
     embedding_kernel<float><<<grid_for(work, 256), 256, 0, s>>>(ids, (const float*)table, (float*)out, tokens, cols, table_ld, out_ld);
   TPB_CHECK_LAUNCH();

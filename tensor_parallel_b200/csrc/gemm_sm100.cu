@@ -32,6 +32,7 @@
 #include <stdio.h>
 #include <string.h>
 
+#include "launch.cuh"
 #include "ptx_sm100.cuh"
 #include "tpb_api.h"
 
@@ -147,10 +148,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
   }
+  pdl_trigger();  // the next kernel in the stream may start its own prologue now
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();     // everything below reads what earlier kernels wrote
 
   const int tiles = p.m_tiles * p.n_tiles;
   const int work_items = tiles * p.k_splits;
@@ -672,8 +675,9 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams&
     if (e != cudaSuccess) return TPB_ERR_CUDA;
     configured[dev] = smem;
   }
-  gemm_bf16_tcgen05_kernel<BN, KBOX, NACC><<<grid, NUM_THREADS, smem, stream>>>(ta, tb, p);
-  return cudaGetLastError() == cudaSuccess ? TPB_OK : TPB_ERR_CUDA;
+  return launch_kernel(gemm_bf16_tcgen05_kernel<BN, KBOX, NACC>, dim3(grid), dim3(NUM_THREADS), smem, stream, ta, tb, p) == cudaSuccess
+             ? TPB_OK
+             : TPB_ERR_CUDA;
 }
 
 static int g_sm_count[16] = {0};
@@ -726,13 +730,13 @@ extern "C" int tpb_gemm_plan(int tokens, int features, int k, int world, int for
   int splits = 1;
   if (force_splits > 0) {
     splits = force_splits;
-  } else if (tiles * 2 <= sms) {
-    // few output tiles: split K so that more SMs stream weights, but keep >= 8 stages of work per split and at
-    // most 4 splits (measured on B200: beyond that the extra partial tiles cost more than the added SMs bring)
+  } else if (tiles * 2 <= sms && plan->k_blocks * kbox >= 128) {
+    // few output tiles and a long K (>= 8192): split K so that more SMs stream weights.  Measured on B200 (kernel
+    // time inside a CUDA graph): for shorter K the extra partial-tile pass costs more than the added SMs bring.
     splits = sms / tiles;
-    const int by_k = plan->k_blocks / 4;
+    const int by_k = (plan->k_blocks * kbox) / 64;
     if (splits > by_k) splits = by_k;
-    if (splits > 4) splits = 4;
+    if (splits > 3) splits = 3;
     if (splits < 1) splits = 1;
   }
   if (splits > plan->k_blocks) splits = plan->k_blocks;

@@ -229,6 +229,13 @@ __device__ __forceinline__ bool wait_flag_ge(const uint32_t* p, uint32_t target,
   }
 }
 
+// Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute may start while
+// its predecessor in the stream is still running.  pdl_trigger() lets the successor be scheduled early;
+// pdl_wait() blocks until the predecessor grid has completed and its writes are visible.  Both are no-ops for a
+// kernel launched the ordinary way.  Nothing that depends on earlier kernels may be touched before pdl_wait().
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ float bf16_bits_to_float(uint16_t b) { return __uint_as_float(static_cast<uint32_t>(b) << 16); }
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
