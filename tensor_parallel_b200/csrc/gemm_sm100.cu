@@ -82,7 +82,18 @@ struct GemmParams {
   uint32_t* ag_flags[MAX_WORLD];              // every rank's arrival words [ag_world], indexed by source rank
   uint32_t* ag_push_counter;                  // local: CTAs done pushing (self re-arming)
   int debug_skip_mma;             // measurement aid: stream the operands through the smem ring without issuing MMAs
+  int trace_block;                // measurement aid: CTA (index + 1) that records %globaltimer stamps into g_gemm_trace; 0 = off
 };
+
+// %globaltimer stamps of one CTA of the most recent traced launch (see tpb_gemm_trace):
+// 0 entry, 1 setup done, 2 first accumulator ready, 3 partial stored / pushed, 4 system fence + barrier passed,
+// 5 arrival counters bumped, 6 reduce phase entered, 7 all arrivals seen, 8 reduced tile written.
+__device__ unsigned long long g_gemm_trace[16];
+#define TPB_TRACE(i)                                                                         \
+  do {                                                                                       \
+    if (p.trace_block && int(blockIdx.x) == p.trace_block - 1) g_gemm_trace[i] = globaltimer_ns(); \
+  } while (0)
+
 
 __device__ __forceinline__ float apply_act(float x, int act) {
   switch (act) {
@@ -131,6 +142,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
+    TPB_TRACE(0);
     prefetch_tmap(&tmap_a);
     prefetch_tmap(&tmap_b);
     for (int s = 0; s < p.stages; ++s) {
@@ -154,6 +166,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   pdl_wait();     // everything below reads what earlier kernels wrote
+  if (threadIdx.x == 0) TPB_TRACE(1);
 
   const int tiles = p.m_tiles * p.n_tiles;
   const int work_items = tiles * p.k_splits;
@@ -177,7 +190,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       if (old == gridDim.x - 1) {  // the whole slice has left this GPU: tell every rank
         *p.ag_push_counter = 0;
         __threadfence_system();
-        for (int d = 0; d < p.ag_world; ++d) red_add_release_sys(p.ag_flags[d] + p.ag_rank, 1u);
+        for (int d = 0; d < p.ag_world; ++d) red_add_relaxed_sys(p.ag_flags[d] + p.ag_rank, 1u);
       }
     }
   }
@@ -302,6 +315,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
       if (!*epi_ok) break;
       tc_fence_after();
+      if (threadIdx.x == 64) TPB_TRACE(2);
       const int m = mt * BM + row;
       const bool m_ok = m < p.m_extent;
       const uint32_t t_lane = tmem_base + (uint32_t(quarter * 32) << 16) + acc * ACC_COLS;
@@ -544,10 +558,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       }
       if (p.world > 1 && (!split_k || *epi_last)) {
         // make this tile's partial visible system-wide, then count one arrival on every rank
+        if (threadIdx.x == 64) TPB_TRACE(3);
         __threadfence_system();
         asm volatile("bar.sync 2, %0;" ::"n"(EPI_THREADS) : "memory");
         if (threadIdx.x == 64) {
-          for (int d = 0; d < p.world; ++d) red_add_release_sys(p.arrivals[d] + tile, 1u);
+          TPB_TRACE(4);
+          __threadfence_system();  // one release fence for all peers (orders the partial tiles the barrier made visible)
+          for (int d = 0; d < p.world; ++d) red_add_relaxed_sys(p.arrivals[d] + tile, 1u);
+          TPB_TRACE(5);
         }
       }
     }
@@ -568,8 +586,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       const int mt = tile % p.m_tiles;
       const int nt = tile / p.m_tiles;
       if (threadIdx.x == 0) {
+        TPB_TRACE(6);
         const uint32_t target = p.expected[tile] + contributions;
         bool ok = !*abort_flag && wait_flag_ge(p.arrivals[p.rank] + tile, target);
+        TPB_TRACE(7);
         if (!ok) atomicMax(p.status, STATUS_TIMEOUT_FLAG);
         p.expected[tile] = target;
         wait_ok = ok ? 1u : 0u;
@@ -610,6 +630,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         }
       }
       __syncthreads();
+      if (threadIdx.x == 0) TPB_TRACE(8);
     }
   }
 
@@ -653,7 +674,7 @@ static int make_tmap_2d(CUtensorMap* map, const void* ptr, uint64_t rows, uint64
   return r == CUDA_SUCCESS ? TPB_OK : TPB_ERR_TMAP;
 }
 
-static int g_debug_stages = 0, g_debug_skip_mma = 0;  // measurement aids, see tpb_gemm_debug
+static int g_debug_stages = 0, g_debug_skip_mma = 0, g_trace_block = 0;  // measurement aids, see tpb_gemm_debug
 
 template <int BN, int KBOX, int NACC>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, int grid, cudaStream_t stream) {
@@ -665,6 +686,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams&
   if (g_debug_stages > 0 && g_debug_stages < stages) stages = g_debug_stages;
   p.stages = stages;
   p.debug_skip_mma = g_debug_skip_mma;
+  p.trace_block = g_trace_block;
   size_t smem = stages * stage_bytes + 1024 /*align*/ + (2 * MAX_STAGES + 4) * 8 + 16;
   // opt in to large dynamic shared memory (per device); static + dynamic must stay within 227 KB
   static size_t configured[64] = {0};
@@ -698,6 +720,17 @@ extern "C" int tpb_gemm_debug(int stages, int skip_mma) {
   g_debug_stages = stages;
   g_debug_skip_mma = skip_mma;
   return TPB_OK;
+}
+
+// Measurement aid: CTA `block` (>= 0) of every following GEMM launch records %globaltimer stamps of its phases
+// (block < 0 switches it off).  tpb_gemm_trace_read copies the 16 stamps of the current device to the host
+// (synchronous; call it after synchronising the stream).
+extern "C" int tpb_gemm_trace(int block) {
+  g_trace_block = block < 0 ? 0 : block + 1;
+  return TPB_OK;
+}
+extern "C" int tpb_gemm_trace_read(unsigned long long* out16) {
+  return cudaMemcpyFromSymbol(out16, g_gemm_trace, sizeof(unsigned long long) * 16) == cudaSuccess ? TPB_OK : TPB_ERR_CUDA;
 }
 
 // Plan of a linear layer out[tokens, features] = x[tokens, K] @ w[features, K]^T.

@@ -71,6 +71,13 @@ int tpb_gemm_allgather_bf16(const void* w, void* out, const void* bias, int toke
                             int ldw, int ld_out, int act, const tpb_gemm_plan_t* plan, const tpb_reduce_ctx_t* rc,
                             const tpb_allgather_ctx_t* ag, void* stream);
 
+// Measurement aids.  tpb_gemm_debug caps the smem ring depth / skips the MMAs (0, 0 restores the defaults).
+// tpb_gemm_trace makes CTA `block` of every following GEMM launch record %globaltimer stamps of its phases
+// (block < 0: off); tpb_gemm_trace_read copies the 16 stamps of the current device to the host.
+int tpb_gemm_debug(int stages, int skip_mma);
+int tpb_gemm_trace(int block);
+int tpb_gemm_trace_read(unsigned long long* out16);
+
 #ifdef __cplusplus
 }
 #endif

@@ -68,12 +68,17 @@ class LlamaEngine:
             wqkv = torch.cat([wq.detach(), wk.detach(), wv.detach()], dim=0).contiguous()
             nq, nk = wq.shape[0], wk.shape[0]
             wq.data, wk.data, wv.data = wqkv[:nq], wqkv[nq : nq + nk], wqkv[nq + nk :]
-            wg, wu = mlp.gate_proj.weight, mlp.up_proj.weight
+            wg, wu, wd = mlp.gate_proj.weight.detach(), mlp.up_proj.weight.detach(), mlp.down_proj.weight.detach()
             ff = wg.shape[0]
+            if ff % 16:  # zero rows (and the matching zero columns of down_proj) fill the last group of 16: they contribute silu(0) * 0 = 0
+                pad = 16 - ff % 16
+                wg, wu = (torch.cat([w, w.new_zeros(pad, w.shape[1])], dim=0) for w in (wg, wu))
+                wd = torch.cat([wd, wd.new_zeros(wd.shape[0], pad)], dim=1).contiguous()
+                ff += pad
             # engine-owned copy, rows interleaved [16 gate | 16 up] so that the GEMM epilogue applies SwiGLU itself
-            wgu = native.interleave_gate_up(wg.detach(), wu.detach())
+            wgu = native.interleave_gate_up(wg, wu)
             self.layers.append(dict(
-                wqkv=wqkv, wo=attn.o_proj.weight.detach(), wgu=wgu, wd=mlp.down_proj.weight.detach(),
+                wqkv=wqkv, wo=attn.o_proj.weight.detach(), wgu=wgu, wd=wd,
                 ln1=layer.input_layernorm.weight.detach(), ln2=layer.post_attention_layernorm.weight.detach(),
                 nq=nq // self.head_dim, nkv=nk // self.head_dim, ff=ff,
             ))

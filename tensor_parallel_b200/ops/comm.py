@@ -198,6 +198,12 @@ class RankComm:
                                  force_algo, self.wait_seconds, native._stream()), "tpb_collective")
         native.launch_count += 1
 
+    def _capacity(self, dtype: torch.dtype, in_copies: int, out_copies: int) -> int:
+        """Largest element count (a multiple of 16 bytes) whose ``in_copies`` / ``out_copies`` fit the staging buffers."""
+        size = 2 if dtype == torch.bfloat16 else 4
+        per = 16 // size
+        return min(self.staging_in.numel() // (size * in_copies), self.staging_out.numel() // (size * out_copies)) // per * per
+
     def staging_view(self, which: str, shape, dtype) -> torch.Tensor:
         buf = self.staging_in if which == "in" else self.staging_out
         nbytes = int(torch.Size(shape).numel()) * torch.empty((), dtype=dtype).element_size()
@@ -211,6 +217,12 @@ class RankComm:
         n = x.numel()
         per = 8 if dtype == torch.bfloat16 else 4
         n_pad = (n + per - 1) // per * per
+        cap = self._capacity(dtype, 1, 1)
+        if n_pad > cap:  # larger than the staging buffers: one collective per staging-sized piece
+            flat, out = x.reshape(-1), torch.empty(n, dtype=dtype, device=x.device)
+            for s in range(0, n, cap):
+                out[s : s + cap].copy_(self.all_reduce(flat[s : s + cap], force_algo))
+            return out.view(x.shape)
         src = self.staging_view("in", (n_pad,), dtype)
         if x.data_ptr() != src.data_ptr():
             src[:n].copy_(x.reshape(-1))
@@ -225,6 +237,12 @@ class RankComm:
         n = x.numel()
         per = 8 if dtype == torch.bfloat16 else 4
         n_pad = (n + per - 1) // per * per
+        cap = self._capacity(dtype, 1, self.world)
+        if n_pad > cap:
+            flat, out = x.reshape(-1), torch.empty(self.world, n, dtype=dtype, device=x.device)
+            for s in range(0, n, cap):
+                out[:, s : s + cap].copy_(self.all_gather(flat[s : s + cap]))
+            return out.view(self.world, *x.shape)
         src = self.staging_view("in", (n_pad,), dtype)
         if x.data_ptr() != src.data_ptr():
             src[:n].copy_(x.reshape(-1))
@@ -238,6 +256,12 @@ class RankComm:
         n = x[0].numel()
         if n % per:
             raise ValueError("reduce_scatter slices must be a multiple of 16 bytes")
+        cap = self._capacity(dtype, self.world, 1)
+        if n > cap:
+            flat, out = x.reshape(self.world, n), torch.empty(n, dtype=dtype, device=x.device)
+            for s in range(0, n, cap):
+                out[s : s + cap].copy_(self.reduce_scatter(flat[:, s : s + cap].contiguous()))
+            return out.view(x.shape[1:])
         src = self.staging_view("in", (self.world * n,), dtype)
         if x.data_ptr() != src.data_ptr():
             src.copy_(x.reshape(-1))

@@ -39,9 +39,12 @@ class _RowParallelFn(torch.autograd.Function):
         if tokens <= 64 and comm.fits_fused(tokens, features, weight.shape[1]):
             out = comm.gemm_allreduce(x2d, weight, bias=bias, bias_scale=float(comm.world))
         else:
-            staged = comm.staging_view("in", (tokens, features), torch.bfloat16)
-            native.gemm_nt(x2d, weight, out=staged)
-            out = comm.all_reduce(staged).clone()
+            if tokens * features <= comm._capacity(torch.bfloat16, 1, 1):  # the GEMM writes straight into symmetric memory
+                staged = comm.staging_view("in", (tokens, features), torch.bfloat16)
+                native.gemm_nt(x2d, weight, out=staged)
+                out = comm.all_reduce(staged).clone()
+            else:
+                out = comm.all_reduce(native.gemm_nt(x2d, weight))
             if bias is not None:
                 out += bias * comm.world
         ctx.save_for_backward(x2d, weight)

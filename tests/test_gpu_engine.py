@@ -9,9 +9,9 @@ from tensor_parallel_b200.models.llama import LlamaConfig, LlamaForCausalLM
 pytestmark = pytest.mark.gpu
 
 
-def _models(kv_heads):
+def _models(kv_heads, ffn=1376):
     torch.manual_seed(0)
-    cfg = LlamaConfig(vocab_size=1024, hidden_size=512, intermediate_size=1376, num_hidden_layers=3, num_attention_heads=4,
+    cfg = LlamaConfig(vocab_size=1024, hidden_size=512, intermediate_size=ffn, num_hidden_layers=3, num_attention_heads=4,
                       num_key_value_heads=kv_heads)
     ref = LlamaForCausalLM(cfg)          # fp32 CPU copy = oracle
     model = LlamaForCausalLM(cfg)
@@ -21,11 +21,11 @@ def _models(kv_heads):
     return ref.eval(), model
 
 
-@pytest.mark.parametrize("kv_heads", [4, 2])
-def test_engine_prefill_and_decode_logits(kv_heads):
+@pytest.mark.parametrize("kv_heads,ffn", [(4, 1376), (2, 1376), (4, 344)])  # 344 is not a multiple of the 16-row SwiGLU groups
+def test_engine_prefill_and_decode_logits(kv_heads, ffn):
     from tensor_parallel_b200.ops import native
 
-    ref, model = _models(kv_heads)
+    ref, model = _models(kv_heads, ffn)
     wrapped = tp.tensor_parallel(model, ["cuda:0"])
     ids = torch.randint(0, 1024, (3, 70), generator=torch.Generator().manual_seed(1))
     logits = wrapped.prefill(ids, max_new_tokens=16)

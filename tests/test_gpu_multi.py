@@ -54,6 +54,23 @@ def _collectives_worker(rank, world, port, out_dir):
             dist.all_reduce(want)
             tol = dict(atol=3e-2, rtol=3e-2) if dtype == torch.bfloat16 else dict(atol=1e-5, rtol=1e-5)
             torch.testing.assert_close(rc.reduce_scatter(y).clone().float(), want[rank], **tol)
+        # payloads larger than the staging buffers go through in pieces
+        full_in, full_out = rc.staging_in, rc.staging_out
+        rc.staging_in, rc.staging_out = full_in[: 256 << 10], full_out[: 256 << 10]
+        try:
+            x = torch.randn(300_001, device=dev, dtype=torch.bfloat16)
+            want = x.float().clone()
+            dist.all_reduce(want)
+            torch.testing.assert_close(rc.all_reduce(x).float(), want, atol=3e-2, rtol=3e-2)
+            parts = [torch.empty_like(x) for _ in range(world)]
+            dist.all_gather(parts, x)
+            torch.testing.assert_close(rc.all_gather(x), torch.stack(parts))
+            y = torch.randn(world, 200_000, device=dev, dtype=torch.float32)
+            want = y.clone()
+            dist.all_reduce(want)
+            torch.testing.assert_close(rc.reduce_scatter(y), want[rank], atol=1e-5, rtol=1e-5)
+        finally:
+            rc.staging_in, rc.staging_out = full_in, full_out
         torch.cuda.synchronize()
         rc.check_status()
 
