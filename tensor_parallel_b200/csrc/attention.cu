@@ -159,6 +159,66 @@ __global__ void qkv_rope_append_vec_kernel(const bf16* __restrict__ q, const bf1
 // ------------------------------------------------------------------------------------------------
 constexpr int DEC_WARPS = 8;
 constexpr int DEC_THREADS = DEC_WARPS * 32;
+constexpr int DEC_STAGES = 4;  // depth of the per-thread K/V ring: DEC_STAGES - 1 key groups are in flight while one is consumed
+
+// Dynamic shared memory of the decode kernels: DEC_STAGES x {K, V} x 16-byte chunks x one slot per thread.
+template <int D> constexpr size_t dec_ring_bytes() { return size_t(DEC_STAGES) * 2 * (D / 64) * DEC_THREADS * 16; }
+
+// Element of the head vector that lane slice `part` (0..7) holds in position e of its registers: 16-byte chunk c = e / 8
+// of a lane sits at elements [64 c + 8 part, +8), so the 8 lanes of a key cover 128 contiguous bytes per copy instruction
+// (whole 32-byte sectors, no sector is requested twice).
+__device__ __forceinline__ int dec_elem(int part, int e) { return (e >> 3) * 64 + part * 8 + (e & 7); }
+
+template <int N> __device__ __forceinline__ void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Streams keys [k_begin, k_end) of one (sequence, KV head) through `consume(kf, vf, valid)`.  A warp takes four keys
+// per iteration (8 lanes per key, EPL elements of K and of V per lane).  Every lane copies its own slices with
+// cp.async into its private slots of a DEC_STAGES-deep ring, so several groups are in flight per lane without holding
+// them in registers, and nobody reads another thread's slot (no barrier).  kbase / vbase already point at this
+// lane's first chunk (element 8 * part of key 0); see dec_elem for the slice layout.  The trip count is uniform across the warp
+// (consume() shuffles); lanes whose key is out of range copy nothing and pass valid = false.
+template <int D, typename Consume>
+__device__ __forceinline__ void stream_keys(const bf16* kbase, const bf16* vbase, int k_begin, int k_end, int warp, int sub,
+                                            uint4* ring, Consume&& consume) {
+  constexpr int EPL = D / 8, C = EPL / 8, STEP = DEC_WARPS * 4;
+  auto slot = [&](int stage, int kv, int c) { return ring + ((stage * 2 + kv) * C + c) * DEC_THREADS + threadIdx.x; };
+  auto issue = [&](int stage, int group_base) {
+    const int key = group_base + sub;
+    if (key < k_end) {
+      const bf16* kp = kbase + (long long)key * D;
+      const bf16* vp = vbase + (long long)key * D;
+#pragma unroll
+      for (int c = 0; c < C; ++c) {
+        cp_async16(slot(stage, 0, c), kp + c * 64, true);
+        cp_async16(slot(stage, 1, c), vp + c * 64, true);
+      }
+    }
+    cp_async_commit();  // committed even when empty: the group count per iteration stays fixed
+  };
+  int key_base = k_begin + warp * 4;
+#pragma unroll
+  for (int st = 0; st < DEC_STAGES - 1; ++st) issue(st, key_base + st * STEP);
+  for (int it = 0; key_base < k_end; key_base += STEP, ++it) {
+    issue((it + DEC_STAGES - 1) % DEC_STAGES, key_base + (DEC_STAGES - 1) * STEP);
+    cp_async_wait_group<DEC_STAGES - 1>();
+    const int stage = it % DEC_STAGES;
+    float kf[EPL], vf[EPL];
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+      const uint4 kr = *slot(stage, 0, c), vr = *slot(stage, 1, c);
+      const uint32_t kw[4] = {kr.x, kr.y, kr.z, kr.w}, vw[4] = {vr.x, vr.y, vr.z, vr.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        kf[c * 8 + 2 * j] = __uint_as_float(kw[j] << 16);
+        kf[c * 8 + 2 * j + 1] = __uint_as_float(kw[j] & 0xFFFF0000u);
+        vf[c * 8 + 2 * j] = __uint_as_float(vw[j] << 16);
+        vf[c * 8 + 2 * j + 1] = __uint_as_float(vw[j] & 0xFFFF0000u);
+      }
+    }
+    consume(kf, vf, key_base + sub < k_end);
+  }
+  cp_async_wait_group<0>();
+}
 
 template <int D, int G>
 __global__ void __launch_bounds__(DEC_THREADS)
@@ -196,48 +256,16 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kcache, 
 #pragma unroll
     for (int e = 0; e < EPL; ++e) acc[g][e] = 0.f;
   }
-  const bf16* kbase = kcache + (long long)bh * max_seq * D + part * EPL;
-  const bf16* vbase = vcache + (long long)bh * max_seq * D + part * EPL;
+  const bf16* kbase = kcache + (long long)bh * max_seq * D + part * 8;
+  const bf16* vbase = vcache + (long long)bh * max_seq * D + part * 8;
 
-  // Software-pipelined key loop: the loads of the next 4-key group are issued before the current group
-  // is consumed, so every warp always has K/V traffic in flight.  The trip count is uniform across the
-  // warp (the shuffles need all 32 lanes); lanes whose key falls beyond the range load nothing and skip
-  // the update.
-  uint4 kraw[EPL / 8], vraw[EPL / 8];
-  auto fetch = [&](int key_base_) {
-    const int key_ = key_base_ + sub;
-    if (key_ < k1) {
-      const uint4* kp = reinterpret_cast<const uint4*>(kbase + (long long)key_ * D);
-      const uint4* vp = reinterpret_cast<const uint4*>(vbase + (long long)key_ * D);
-#pragma unroll
-      for (int c = 0; c < EPL / 8; ++c) { kraw[c] = __ldg(kp + c); vraw[c] = __ldg(vp + c); }
-    } else {
-#pragma unroll
-      for (int c = 0; c < EPL / 8; ++c) { kraw[c] = make_uint4(0, 0, 0, 0); vraw[c] = make_uint4(0, 0, 0, 0); }
-    }
-  };
-  int key_base = k0 + warp * 4;
-  if (key_base < k1) fetch(key_base);
-  for (; key_base < k1; key_base += DEC_WARPS * 4) {
-    const bool valid = key_base + sub < k1;
-    float kf[EPL], vf[EPL];
-#pragma unroll
-    for (int c = 0; c < EPL / 8; ++c) {
-      const uint32_t kw[4] = {kraw[c].x, kraw[c].y, kraw[c].z, kraw[c].w}, vw[4] = {vraw[c].x, vraw[c].y, vraw[c].z, vraw[c].w};
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        kf[c * 8 + 2 * j] = __uint_as_float(kw[j] << 16);
-        kf[c * 8 + 2 * j + 1] = __uint_as_float(kw[j] & 0xFFFF0000u);
-        vf[c * 8 + 2 * j] = __uint_as_float(vw[j] << 16);
-        vf[c * 8 + 2 * j + 1] = __uint_as_float(vw[j] & 0xFFFF0000u);
-      }
-    }
-    if (key_base + DEC_WARPS * 4 < k1) fetch(key_base + DEC_WARPS * 4);  // prefetch the next group
+  extern __shared__ uint4 dec_ring[];
+  stream_keys<D>(kbase, vbase, k0, k1, warp, sub, dec_ring, [&](const float (&kf)[EPL], const float (&vf)[EPL], bool valid) {
 #pragma unroll
     for (int g = 0; g < G; ++g) {
       float s = 0.f;
 #pragma unroll
-      for (int e = 0; e < EPL; ++e) s += kf[e] * q_s[g][part * EPL + e];
+      for (int e = 0; e < EPL; ++e) s += kf[e] * q_s[g][dec_elem(part, e)];
       s += __shfl_xor_sync(0xffffffffu, s, 1);
       s += __shfl_xor_sync(0xffffffffu, s, 2);
       s += __shfl_xor_sync(0xffffffffu, s, 4);
@@ -251,7 +279,7 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kcache, 
         m[g] = m_new;
       }
     }
-  }
+  });
 
   // merge the 4 key sub-groups of a warp (lanes differing in bits 3,4), then the warps
 #pragma unroll
@@ -273,7 +301,7 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kcache, 
     }
     if (sub == 0) {
 #pragma unroll
-      for (int e = 0; e < EPL; ++e) red_o[warp][g][part * EPL + e] = acc[g][e];
+      for (int e = 0; e < EPL; ++e) red_o[warp][g][dec_elem(part, e)] = acc[g][e];
       if (part == 0) { red_m[warp][g] = m[g]; red_l[warp][g] = l[g]; }
     }
   }
@@ -306,14 +334,30 @@ __global__ void attn_decode_combine_kernel(const float* __restrict__ part_o, con
                                            bf16* __restrict__ out, int splits) {
   const long long row = blockIdx.x;
   const int d = threadIdx.x;
-  float mm = -INFINITY;
-  for (int s = 0; s < splits; ++s) mm = fmaxf(mm, part_ml[(row * splits + s) * 2]);
-  float ll = 0.f, oo = 0.f;
-  for (int s = 0; s < splits; ++s) {
-    const float ms = part_ml[(row * splits + s) * 2];
-    const float c = ms == -INFINITY ? 0.f : exp2f(ms - mm);
-    ll += part_ml[(row * splits + s) * 2 + 1] * c;
-    oo += part_o[(row * splits + s) * D + d] * c;
+  float mm = -INFINITY, ll = 0.f, oo = 0.f;
+  for (int s0 = 0; s0 < splits; s0 += 8) {  // loads of 8 splits in flight at once
+    float ms[8], ls[8], os[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const bool live = s0 + q < splits;
+      const long long pr = row * splits + s0 + q;
+      ms[q] = live ? part_ml[pr * 2] : -INFINITY;
+      ls[q] = live ? part_ml[pr * 2 + 1] : 0.f;
+      os[q] = live ? part_o[pr * D + d] : 0.f;
+    }
+    float m_new = mm;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) m_new = fmaxf(m_new, ms[q]);
+    const float c_old = mm == -INFINITY ? 0.f : exp2f(mm - m_new);
+    ll *= c_old;
+    oo *= c_old;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const float c = ms[q] == -INFINITY ? 0.f : exp2f(ms[q] - m_new);
+      ll += ls[q] * c;
+      oo += os[q] * c;
+    }
+    mm = m_new;
   }
   out[row * D + d] = __float2bfloat16(ll > 0.f ? oo / ll : 0.f);
 }
@@ -397,15 +441,15 @@ attn_decode_fused_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k,
 #pragma unroll
     for (int e = 0; e < EPL; ++e) acc[g][e] = 0.f;
   }
-  const bf16* kbase = kcache + (long long)bh * max_seq * D + part * EPL;
-  const bf16* vbase = vcache + (long long)bh * max_seq * D + part * EPL;
+  const bf16* kbase = kcache + (long long)bh * max_seq * D + part * 8;
+  const bf16* vbase = vcache + (long long)bh * max_seq * D + part * 8;
 
   auto consume = [&](const float (&kf)[EPL], const float (&vf)[EPL], bool valid) {
 #pragma unroll
     for (int g = 0; g < G; ++g) {
       float sc = 0.f;
 #pragma unroll
-      for (int e = 0; e < EPL; ++e) sc += kf[e] * q_s[g][part * EPL + e];
+      for (int e = 0; e < EPL; ++e) sc += kf[e] * q_s[g][dec_elem(part, e)];
       sc += __shfl_xor_sync(0xffffffffu, sc, 1);
       sc += __shfl_xor_sync(0xffffffffu, sc, 2);
       sc += __shfl_xor_sync(0xffffffffu, sc, 4);
@@ -421,44 +465,14 @@ attn_decode_fused_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k,
     }
   };
 
-  uint4 kraw[EPL / 8], vraw[EPL / 8];
-  auto fetch = [&](int key_base_) {
-    const int key_ = key_base_ + sub;
-    if (key_ < k1_cache) {
-      const uint4* kp = reinterpret_cast<const uint4*>(kbase + (long long)key_ * D);
-      const uint4* vp = reinterpret_cast<const uint4*>(vbase + (long long)key_ * D);
-#pragma unroll
-      for (int c = 0; c < EPL / 8; ++c) { kraw[c] = __ldg(kp + c); vraw[c] = __ldg(vp + c); }
-    } else {
-#pragma unroll
-      for (int c = 0; c < EPL / 8; ++c) { kraw[c] = make_uint4(0, 0, 0, 0); vraw[c] = make_uint4(0, 0, 0, 0); }
-    }
-  };
-  int key_base = k0 + warp * 4;
-  if (key_base < k1_cache) fetch(key_base);
-  for (; key_base < k1_cache; key_base += DEC_WARPS * 4) {
-    const bool valid = key_base + sub < k1_cache;
-    float kf[EPL], vf[EPL];
-#pragma unroll
-    for (int c = 0; c < EPL / 8; ++c) {
-      const uint32_t kw[4] = {kraw[c].x, kraw[c].y, kraw[c].z, kraw[c].w}, vw[4] = {vraw[c].x, vraw[c].y, vraw[c].z, vraw[c].w};
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        kf[c * 8 + 2 * j] = __uint_as_float(kw[j] << 16);
-        kf[c * 8 + 2 * j + 1] = __uint_as_float(kw[j] & 0xFFFF0000u);
-        vf[c * 8 + 2 * j] = __uint_as_float(vw[j] << 16);
-        vf[c * 8 + 2 * j + 1] = __uint_as_float(vw[j] & 0xFFFF0000u);
-      }
-    }
-    if (key_base + DEC_WARPS * 4 < k1_cache) fetch(key_base + DEC_WARPS * 4);
-    consume(kf, vf, valid);
-  }
+  extern __shared__ uint4 dec_ring[];
+  stream_keys<D>(kbase, vbase, k0, k1_cache, warp, sub, dec_ring, consume);
   if (owns_new && warp == 0) {  // the new token's key / value come straight from shared memory (warp-uniform branch)
     float kf[EPL], vf[EPL];
 #pragma unroll
     for (int e = 0; e < EPL; ++e) {
-      kf[e] = __bfloat162float(__float2bfloat16(knew_s[part * EPL + e]));
-      vf[e] = __bfloat162float(__float2bfloat16(vnew_s[part * EPL + e]));
+      kf[e] = __bfloat162float(__float2bfloat16(knew_s[dec_elem(part, e)]));
+      vf[e] = __bfloat162float(__float2bfloat16(vnew_s[dec_elem(part, e)]));
     }
     consume(kf, vf, sub == 0);
   }
@@ -482,7 +496,7 @@ attn_decode_fused_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k,
     }
     if (sub == 0) {
 #pragma unroll
-      for (int e = 0; e < EPL; ++e) red_o[warp][g][part * EPL + e] = acc[g][e];
+      for (int e = 0; e < EPL; ++e) red_o[warp][g][dec_elem(part, e)] = acc[g][e];
       if (part == 0) { red_m[warp][g] = m[g]; red_l[warp][g] = l[g]; }
     }
   }
@@ -524,14 +538,32 @@ attn_decode_fused_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k,
   for (int i = threadIdx.x; i < G * D; i += DEC_THREADS) {
     const int g = i / D, d = i % D;
     const long long row = (long long)b * q_heads + kvh * g_total + g_offset + g;
-    float mm = -INFINITY;
-    for (int sp = 0; sp < splits; ++sp) mm = fmaxf(mm, __ldcg(part_ml + (row * splits + sp) * 2));
-    float ll = 0.f, oo = 0.f;
-    for (int sp = 0; sp < splits; ++sp) {
-      const float ms = __ldcg(part_ml + (row * splits + sp) * 2);
-      const float c = ms == -INFINITY ? 0.f : exp2f(ms - mm);
-      ll += __ldcg(part_ml + (row * splits + sp) * 2 + 1) * c;
-      oo += __ldcg(part_o + (row * splits + sp) * D + d) * c;
+    // all loads of a batch of 8 splits are issued before the first one is used (each dependent load would cost a
+    // full memory round trip); batches are folded with the running (max, sum, output) like one more online-softmax step
+    float mm = -INFINITY, ll = 0.f, oo = 0.f;
+    for (int s0 = 0; s0 < splits; s0 += 8) {
+      float ms[8], ls[8], os[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const bool live = s0 + q < splits;
+        const long long pr = row * splits + s0 + q;
+        ms[q] = live ? __ldcg(part_ml + pr * 2) : -INFINITY;
+        ls[q] = live ? __ldcg(part_ml + pr * 2 + 1) : 0.f;
+        os[q] = live ? __ldcg(part_o + pr * D + d) : 0.f;
+      }
+      float m_new = mm;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) m_new = fmaxf(m_new, ms[q]);
+      const float c_old = mm == -INFINITY ? 0.f : exp2f(mm - m_new);
+      ll *= c_old;
+      oo *= c_old;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const float c = ms[q] == -INFINITY ? 0.f : exp2f(ms[q] - m_new);
+        ll += ls[q] * c;
+        oo += os[q] * c;
+      }
+      mm = m_new;
     }
     out[row * D + d] = __float2bfloat16(ll > 0.f ? oo / ll : 0.f);
   }
@@ -733,6 +765,19 @@ extern "C" int tpb_qkv_rope_append(const void* q, const void* k, const void* v, 
   return cudaGetLastError() == cudaSuccess ? TPB_OK : TPB_ERR_CUDA;
 }
 
+// Opts a decode kernel instantiation in to its dynamic shared memory (once per kernel and device).
+template <auto Kernel>
+static bool dec_smem_ready(size_t bytes) {
+  static bool done[64] = {false};  // one array per kernel instantiation
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+  if (!done[dev]) {
+    if (cudaFuncSetAttribute(Kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes)) != cudaSuccess) return false;
+    done[dev] = true;
+  }
+  return true;
+}
+
 // workspace: part_o fp32 [batch*q_heads*splits*head_dim], part_ml fp32 [batch*q_heads*splits*2]
 extern "C" int tpb_attn_decode(const void* q, const void* kcache, const void* vcache, void* out, float* part_o,
                                float* part_ml, const int* len_ptr, int len_add, int batch, int q_heads, int kv_heads,
@@ -751,13 +796,14 @@ extern "C" int tpb_attn_decode(const void* q, const void* kcache, const void* vc
     int gnow = 1;
     while (gnow * 2 <= left && gnow * 2 <= gmax) gnow *= 2;
 #define DEC(D, G)                                                                                                      \
-  attn_decode_kernel<D, G><<<grid, DEC_THREADS, 0, s>>>((const bf16*)q, (const bf16*)kcache, (const bf16*)vcache, (bf16*)out, \
-                                                        part_o, part_ml, len_ptr, len_add, q_heads, kv_heads, g_total, done, \
-                                                        max_seq, splits, sl2)
+  if (!dec_smem_ready<attn_decode_kernel<D, G>>(dec_ring_bytes<D>())) return TPB_ERR_CUDA;                               \
+  attn_decode_kernel<D, G><<<grid, DEC_THREADS, dec_ring_bytes<D>(), s>>>(                                                \
+      (const bf16*)q, (const bf16*)kcache, (const bf16*)vcache, (bf16*)out, part_o, part_ml, len_ptr, len_add, q_heads,   \
+      kv_heads, g_total, done, max_seq, splits, sl2)
     if (head_dim == 128) {
-      if (gnow == 1) DEC(128, 1); else if (gnow == 2) DEC(128, 2); else DEC(128, 4);
+      if (gnow == 1) { DEC(128, 1); } else if (gnow == 2) { DEC(128, 2); } else { DEC(128, 4); }
     } else {
-      if (gnow == 1) DEC(64, 1); else if (gnow == 2) DEC(64, 2); else if (gnow == 4) DEC(64, 4); else DEC(64, 8);
+      if (gnow == 1) { DEC(64, 1); } else if (gnow == 2) { DEC(64, 2); } else if (gnow == 4) { DEC(64, 4); } else { DEC(64, 8); }
     }
 #undef DEC
     done += gnow;
@@ -829,13 +875,14 @@ extern "C" int tpb_attn_decode_fused(const void* q, const void* k, const void* v
     int gnow = 1;
     while (gnow * 2 <= left && gnow * 2 <= gmax) gnow *= 2;
 #define DECF(D, G)                                                                                                           \
-  launch_kernel(attn_decode_fused_kernel<D, G>, grid, dim3(DEC_THREADS), 0, s, (const bf16*)q, (const bf16*)k, (const bf16*)v,     \
+  if (!dec_smem_ready<attn_decode_fused_kernel<D, G>>(dec_ring_bytes<D>())) return TPB_ERR_CUDA;                               \
+  launch_kernel(attn_decode_fused_kernel<D, G>, grid, dim3(DEC_THREADS), dec_ring_bytes<D>(), s, (const bf16*)q, (const bf16*)k, (const bf16*)v, \
                 (bf16*)kcache, (bf16*)vcache, (bf16*)out, part_o, part_ml, (uint32_t*)counters, pos_ptr, q_heads, kv_heads, g_total, \
                 done, max_seq, splits, sl2, rotary_dim, l2t, interleaved, q_ld, k_ld, v_ld)
     if (head_dim == 128) {
-      if (gnow == 1) DECF(128, 1); else if (gnow == 2) DECF(128, 2); else DECF(128, 4);
+      if (gnow == 1) { DECF(128, 1); } else if (gnow == 2) { DECF(128, 2); } else { DECF(128, 4); }
     } else {
-      if (gnow == 1) DECF(64, 1); else if (gnow == 2) DECF(64, 2); else if (gnow == 4) DECF(64, 4); else DECF(64, 8);
+      if (gnow == 1) { DECF(64, 1); } else if (gnow == 2) { DECF(64, 2); } else if (gnow == 4) { DECF(64, 4); } else { DECF(64, 8); }
     }
 #undef DECF
     done += gnow;

@@ -45,6 +45,7 @@ constexpr int MAX_STAGES = 12;
 constexpr int NUM_THREADS = 192;
 constexpr int EPI_THREADS = 128;
 constexpr int MAX_WORLD = 8;
+constexpr int LL_FIRST_SLOT = 32;  // first fp32 slot of the flagged-word area (slots below hold plain partials)
 
 struct GemmParams {
   int m_extent;   // rows of A (lanes side)
@@ -71,6 +72,10 @@ struct GemmParams {
   uint32_t* split_counters;       // local: [tiles] arrivals of split-K partials (self re-arming)
   size_t slot_stride;             // elements between consecutive slots
   uint32_t* status;               // local status word (0 = ok)
+  // flagged-word exchange for the cross-rank sum of small (swapped) problems: every fp32 partial travels as one
+  // 8-byte word {value, epoch}; the receiver spins on the word itself, so no fence and no arrival counter is needed
+  int ll;
+  uint32_t* ll_epochs;            // local: [tiles] epoch of the previous flagged call (device-resident: graph replays advance it)
   // fused all-gather of the token-side operand (ag_world > 1): every rank owns a column slice [rows, ag_cols] of x;
   // the kernel first pushes its slice into every rank's gathered buffer, then consumes k-blocks slice by slice
   // (own slice first) as the peers' pushes arrive
@@ -81,14 +86,17 @@ struct GemmParams {
   __nv_bfloat16* ag_dst[MAX_WORLD];           // every rank's gathered buffer [rows, ag_world * ag_cols]
   uint32_t* ag_flags[MAX_WORLD];              // every rank's arrival words [ag_world], indexed by source rank
   uint32_t* ag_push_counter;                  // local: CTAs done pushing (self re-arming)
+  int stream_k;                   // 1: every CTA owns one contiguous range of (tile, k-block) units (see WorkIter)
   int debug_skip_mma;             // measurement aid: stream the operands through the smem ring without issuing MMAs
   int trace_block;                // measurement aid: CTA (index + 1) that records %globaltimer stamps into g_gemm_trace; 0 = off
 };
 
 // %globaltimer stamps of one CTA of the most recent traced launch (see tpb_gemm_trace):
 // 0 entry, 1 setup done, 2 first accumulator ready, 3 partial stored / pushed, 4 system fence + barrier passed,
-// 5 arrival counters bumped, 6 reduce phase entered, 7 all arrivals seen, 8 reduced tile written.
-__device__ unsigned long long g_gemm_trace[16];
+// 5 arrival counters bumped, 6 reduce phase entered, 7 all arrivals seen, 8 reduced tile written; partial-tile path
+// (last item of the CTA): 9 partial parked, 10 fence + barrier passed, 11 counter bumped, 12 last contributor starts
+// the sum; 13 teardown; whole-tile path: 14 accumulators read, 15 tile written.
+__device__ unsigned long long g_gemm_trace[32];
 #define TPB_TRACE(i)                                                                         \
   do {                                                                                       \
     if (p.trace_block && int(blockIdx.x) == p.trace_block - 1) g_gemm_trace[i] = globaltimer_ns(); \
@@ -107,6 +115,88 @@ __device__ __forceinline__ float apply_act(float x, int act) {
     default: return x;
   }
 }
+
+// Out-of-line copy for the few-token epilogues.  Those run once per CTA, straight through code that is cold in the
+// instruction cache; with the activation switch (erf, tanh, exp expansions) inlined into every one of the 16 unrolled
+// iterations, each iteration started with an instruction-cache miss (~0.25 us apiece, measured with %globaltimer).
+__device__ __noinline__ float apply_act_call(float x, int act) { return apply_act(x, act); }
+
+// Retry loop of the flagged exchange (out of line: it is inlined 16 times otherwise).  Bounded by wall time.
+__device__ __noinline__ uint4 poll_flagged_word(const uint4* ptr, uint32_t flag, bool* ok) {
+  const uint64_t start = globaltimer_ns();
+  uint4 w;
+  for (uint32_t i = 0;; ++i) {
+    w = ld_relaxed_sys_v4(ptr);
+    if (w.y == flag && w.w == flag) {
+      *ok = true;
+      return w;
+    }
+    if (i > 64) __nanosleep(20);
+    if ((i & 63) == 63 && globaltimer_ns() - start > TPB_WAIT_LIMIT_NS) {
+      *ok = false;
+      return w;
+    }
+  }
+}
+
+// Work decomposition, walked identically by the producer, the MMA issuer and the epilogue warps of a CTA.
+//  * uniform: item w = (split, tile) for w = blockIdx.x, blockIdx.x + gridDim.x, ...; every tile has k_splits
+//    contributors of kb_per_split k-blocks each.
+//  * stream-K: the tiles * k_blocks units (one unit = one pipeline stage of one tile) are dealt out as one contiguous
+//    range per CTA, boundary(c) = c * units / gridDim.x, so every CTA streams the same number of bytes whatever the
+//    tile count; a range is cut into items at tile boundaries.  A tile covered by several CTAs gets its partial sums
+//    parked and added up by the last contributor to arrive, exactly like split-K.
+struct WorkItem {
+  int tile, kb0, kb1;
+  int ordinal, contributors;  // this item's index among the contributors of its tile / their number
+};
+
+struct WorkIter {
+  int w, tiles;              // uniform mode
+  long long u, u_end, units; // stream-K mode
+  __device__ __forceinline__ long long boundary(long long c) const { return c * units / (long long)gridDim.x; }
+  __device__ __forceinline__ int owner(long long unit) const {  // CTA whose range holds `unit`
+    long long c = unit * (long long)gridDim.x / units;
+    while (boundary(c + 1) <= unit) ++c;
+    return int(c);
+  }
+  __device__ __forceinline__ WorkIter(const GemmParams& p) {
+    tiles = p.m_tiles * p.n_tiles;
+    w = blockIdx.x;
+    units = (long long)tiles * p.k_blocks;
+    u = boundary(blockIdx.x);
+    u_end = boundary(blockIdx.x + 1);
+  }
+  __device__ __forceinline__ bool next(const GemmParams& p, WorkItem& item) {
+    if (!p.stream_k) {
+      if (w >= tiles * p.k_splits) return false;
+      const int split = w / tiles;
+      item.tile = w - split * tiles;
+      item.kb0 = split * p.kb_per_split;
+      item.kb1 = min(p.k_blocks, item.kb0 + p.kb_per_split);
+      item.ordinal = split;
+      item.contributors = p.k_splits;
+      w += gridDim.x;
+      return true;
+    }
+    if (u >= u_end) return false;
+    item.tile = int(u / p.k_blocks);
+    item.kb0 = int(u - (long long)item.tile * p.k_blocks);
+    const long long len = min((long long)(p.k_blocks - item.kb0), u_end - u);
+    item.kb1 = item.kb0 + int(len);
+    if (len == p.k_blocks) {
+      item.ordinal = 0;
+      item.contributors = 1;
+    } else {
+      const long long t0 = (long long)item.tile * p.k_blocks;
+      const int first = owner(t0);
+      item.ordinal = int(blockIdx.x) - first;
+      item.contributors = owner(t0 + p.k_blocks - 1) - first + 1;
+    }
+    u += len;
+    return true;
+  }
+};
 
 // KBOX = number of consecutive 64-column k-blocks fetched per pipeline stage.  With KBOX > 1 a stage
 // pulls KBOX * 128 contiguous bytes of every operand row in back-to-back TMA boxes.
@@ -169,7 +259,6 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   if (threadIdx.x == 0) TPB_TRACE(1);
 
   const int tiles = p.m_tiles * p.n_tiles;
-  const int work_items = tiles * p.k_splits;
 
   if (p.ag_world > 1) {
     // ---------------- all-gather push: local slice -> every rank's gathered buffer ----------------
@@ -199,13 +288,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     // ---------------- TMA producer ----------------
     if (elect_one()) {
       uint32_t it = 0;
-      for (int w = blockIdx.x; w < work_items && !*abort_flag; w += gridDim.x) {
-        const int split = w / tiles;
-        const int tile = w - split * tiles;
-        const int mt = tile % p.m_tiles;
-        const int nt = tile / p.m_tiles;
-        const int kb0 = split * p.kb_per_split;
-        const int kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
+      WorkIter work(p);
+      WorkItem item;
+      while (!*abort_flag && work.next(p, item)) {
+        const int mt = item.tile % p.m_tiles;
+        const int nt = item.tile / p.m_tiles;
+        const int kb0 = item.kb0, kb1 = item.kb1;
         int ag_ready_src = -1;
         for (int kb_seq = kb0; kb_seq < kb1; ++kb_seq, ++it) {
           int kb = kb_seq;
@@ -247,10 +335,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     if (elect_one()) {
       uint32_t it = 0;
       uint32_t local = 0;
-      for (int w = blockIdx.x; w < work_items && !*abort_flag; w += gridDim.x, ++local) {
-        const int split = w / tiles;
-        const int kb0 = split * p.kb_per_split;
-        const int kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
+      WorkIter work(p);
+      WorkItem item;
+      for (; !*abort_flag && work.next(p, item); ++local) {
+        const int kb0 = item.kb0, kb1 = item.kb1;
         const int acc = local & 1;
         const uint32_t acc_ph = (local >> 1) & 1;
         if (!mbar_wait(&acc_empty[acc], acc_ph ^ 1)) {
@@ -295,10 +383,21 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     // ---------------- epilogue warps ----------------
     const int quarter = warp & 3;  // TMEM lane quarter this warp may access
     const int row = quarter * 32 + lane;
+    // The epilogue of a decode GEMM runs once per CTA, right on the critical path, and every kernel parameter it
+    // touches for the first time is a constant-cache miss served from L2 (a good fraction of a microsecond each, one
+    // after the other).  Read them into registers now, while the first tiles are still streaming in.
+    __nv_bfloat16* hot_out = p.out;
+    const __nv_bfloat16* hot_bias = p.bias;
+    const __nv_bfloat16* hot_residual = p.residual;
+    int hot_ld_out = p.ld_out, hot_act = p.act, hot_n_extent = p.n_extent, hot_m_extent = p.m_extent;
+    float hot_bias_scale = p.bias_scale;
+    asm volatile("" : "+l"(hot_out), "+l"(hot_bias), "+l"(hot_residual), "+r"(hot_ld_out), "+r"(hot_act), "+r"(hot_n_extent),
+                 "+r"(hot_m_extent), "+f"(hot_bias_scale));
     uint32_t local = 0;
-    for (int w = blockIdx.x; w < work_items; w += gridDim.x, ++local) {
-      const int split = w / tiles;
-      const int tile = w - split * tiles;
+    WorkIter work(p);
+    WorkItem item;
+    for (; work.next(p, item); ++local) {
+      const int tile = item.tile;
       const int mt = tile % p.m_tiles;
       const int nt = tile / p.m_tiles;
       const int acc = local & 1;
@@ -312,6 +411,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         }
         *epi_ok = ok ? 1u : 0u;
       }
+      uint32_t ll_flag = 0;
+      if (p.ll) {  // read before the barrier; thread 64 advances the word only after it
+        ll_flag = __ldcg(p.ll_epochs + tile) + 1u;
+        if (ll_flag == 0) ll_flag = 1u;
+      }
       asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
       if (!*epi_ok) break;
       tc_fence_after();
@@ -319,8 +423,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       const int m = mt * BM + row;
       const bool m_ok = m < p.m_extent;
       const uint32_t t_lane = tmem_base + (uint32_t(quarter * 32) << 16) + acc * ACC_COLS;
-      const int kb0 = split * p.kb_per_split;
-      const int n_mma = (min(p.k_blocks, kb0 + p.kb_per_split) - kb0) * MMAS_PER_STAGE;
+      const int n_mma = (item.kb1 - item.kb0) * MMAS_PER_STAGE;
       const int n_acc = n_mma < NACC ? n_mma : NACC;  // accumulators that were written for this item
 
       // A chunk is 16 accumulator columns of this thread's row: (token m, features n0..n0+15) in the normal
@@ -329,15 +432,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       auto read_acc = [&](int c0, float (&v)[16]) {
 #pragma unroll
         for (int j = 0; j < 16; ++j) v[j] = 0.f;
+#pragma unroll 1  // (rolled on purpose: this runs once per tile from a cold instruction cache, small code wins)
+        for (int a = 0; a < n_acc; ++a) {
+          uint32_t r[16];
+          tmem_ld_x16(t_lane + a * BN + c0, r);
+          tmem_ld_wait();
 #pragma unroll
-        for (int a = 0; a < NACC; ++a) {
-          if (a < n_acc) {
-            uint32_t r[16];
-            tmem_ld_x16(t_lane + a * BN + c0, r);
-            tmem_ld_wait();
-#pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] += __uint_as_float(r[j]);
-          }
+          for (int j = 0; j < 16; ++j) v[j] += __uint_as_float(r[j]);
         }
       };
       auto store_partial = [&](float* slot, int n0, const float (&v)[16]) {
@@ -357,24 +458,47 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             if (n0 + j < p.n_extent) slot[size_t(n0 + j) * p.ld_slot + m] = v[j];
         }
       };
-      auto add_partial = [&](const float* slot, int n0, float (&v)[16]) {
+      // v = sum over the parked partials [first_slot, first_slot + count) of this tile, added in slot order.  The loads of
+      // four slots are issued before the first value is used: a load that is consumed right away costs one full memory
+      // round trip (more than a microsecond while the GPU streams weights), and those round trips would add up.
+      auto sum_partials = [&](int count, int n0, float (&v)[16]) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = 0.f;
         if (!chunk_valid(n0)) return;
-        if (!p.swapped) {
-          const size_t base = size_t(m) * p.ld_slot + n0;
-          if (n0 + 16 <= p.n_extent && (p.ld_slot & 3) == 0) {
-            const float4* src = reinterpret_cast<const float4*>(slot + base);
+        const float* base = p.slots[p.rank] + size_t(p.world) * p.slot_stride;
+        const bool vec = !p.swapped && n0 + 16 <= p.n_extent && (p.ld_slot & 3) == 0;
+#pragma unroll 1
+        for (int h = 0; h < 16; h += 8) {  // half a chunk at a time keeps the batch in registers
+          if (n0 + h >= p.n_extent) break;
+#pragma unroll 1
+          for (int s0 = 0; s0 < count; s0 += 4) {
+            float t[4][8];
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-              const float4 t = __ldcg(src + q);
-              v[4 * q] += t.x; v[4 * q + 1] += t.y; v[4 * q + 2] += t.z; v[4 * q + 3] += t.w;
-            }
-          } else {
-            for (int j = 0; j < 16 && n0 + j < p.n_extent; ++j) v[j] += __ldcg(slot + base + j);
-          }
-        } else {
+              const float* slot = base + size_t(s0 + q) * p.slot_stride;
+              const bool live = s0 + q < count;
+              if (vec) {
+                const float4* src = reinterpret_cast<const float4*>(slot + size_t(m) * p.ld_slot + n0 + h);
+                const float4 f0 = live ? __ldcg(src) : make_float4(0.f, 0.f, 0.f, 0.f);
+                const float4 f1 = live ? __ldcg(src + 1) : make_float4(0.f, 0.f, 0.f, 0.f);
+                t[q][0] = f0.x; t[q][1] = f0.y; t[q][2] = f0.z; t[q][3] = f0.w;
+                t[q][4] = f1.x; t[q][5] = f1.y; t[q][6] = f1.z; t[q][7] = f1.w;
+              } else {
 #pragma unroll
-          for (int j = 0; j < 16; ++j)
-            if (n0 + j < p.n_extent) v[j] += __ldcg(slot + size_t(n0 + j) * p.ld_slot + m);
+                for (int j = 0; j < 8; ++j) {
+                  const size_t idx = p.swapped ? size_t(n0 + h + j) * p.ld_slot + m : size_t(m) * p.ld_slot + n0 + h + j;
+                  t[q][j] = (live && n0 + h + j < p.n_extent) ? __ldcg(slot + idx) : 0.f;
+                }
+              }
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                if (h == 0) v[j] += t[q][j];
+                else v[8 + j] += t[q][j];
+              }
+          }
         }
       };
       // gated silu, normal orientation: vg = 16 gate columns, vu = the 16 up columns that follow them
@@ -403,7 +527,30 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         }
       };
       auto finalize = [&](int n0, float (&v)[16]) {  // bias, activation, residual, bf16 store
-        if (!chunk_valid(n0)) return;
+        if (n0 >= hot_n_extent) return;  // (uniform across the warp)
+        if (p.swapped && hot_act != 5) {
+          // tokens are the accumulator columns, a lane owns one feature: neighbouring lanes pair up so that every
+          // store carries two features (4 bytes); rows past the feature count only take part in the shuffle
+          const float b = (m_ok && hot_bias) ? hot_bias_scale * __bfloat162float(hot_bias[m]) : 0.f;
+          const bool pitch_even = (hot_ld_out & 1) == 0 && (reinterpret_cast<uintptr_t>(hot_out) & 3) == 0;
+          const bool writes_pair = pitch_even && !(lane & 1) && m + 1 < hot_m_extent;
+          const bool covered = pitch_even && (lane & 1);  // the even neighbour stores this lane's value
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if (n0 + j >= hot_n_extent) break;  // (uniform) the code of the remaining iterations is never fetched
+            const size_t idx = size_t(n0 + j) * hot_ld_out + m;
+            float x = v[j] + b;
+            if (hot_act) x = apply_act_call(x, hot_act);
+            if (hot_residual && m_ok) x += __bfloat162float(hot_residual[idx]);
+            const float up = __shfl_down_sync(0xffffffffu, x, 1);
+            if (m_ok) {
+              if (writes_pair) *reinterpret_cast<uint32_t*>(hot_out + idx) = pack_bf16x2(x, up);
+              else if (!covered) hot_out[idx] = __float2bfloat16(x);
+            }
+          }
+          return;
+        }
+        if (!m_ok) return;
         if (p.act == 5) {
           // gated silu, swapped orientation: lanes 0-15 of a warp hold gate rows, lanes 16-31 the matching up rows
           const float b = p.bias ? p.bias_scale * __bfloat162float(p.bias[m]) : 0.f;
@@ -455,20 +602,94 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           } else {
             for (int j = 0; j < 16 && n0 + j < p.n_extent; ++j) {
               float x = v[j] + (p.bias ? p.bias_scale * __bfloat162float(p.bias[n0 + j]) : 0.f);
-              x = apply_act(x, p.act);
+              if (p.act) x = apply_act_call(x, p.act);
               if (p.residual) x += __bfloat162float(p.residual[base + j]);
               p.out[base + j] = __float2bfloat16(x);
             }
           }
-        } else {
-          const float b = p.bias ? p.bias_scale * __bfloat162float(p.bias[m]) : 0.f;
+        }
+      };
+      // flagged-word variant (swapped orientation only: all tokens sit in one tile): slot k of rank d's flagged area
+      // holds rank k's partial as 16-byte words {value(t), epoch, value(t + 1), epoch} laid out [feature][token pair],
+      // so the thread that owns a feature row moves a whole row with a few wide accesses.  The area starts
+      // LL_FIRST_SLOT slots into the workspace and a flagged slot spans two fp32 slots.
+      bool ll_gave_up = false;
+      const int ll_pairs = (p.n_extent + 1) >> 1;  // token pairs per feature row
+      auto push_ll = [&](int n0, const float (&v)[16]) {
+        if (!chunk_valid(n0)) return;
+#pragma unroll 1  // (rolled: small code, see read_acc)
+        for (int d = 0; d < p.world; ++d) {
+          uint4* row = reinterpret_cast<uint4*>(p.slots[d] + size_t(LL_FIRST_SLOT + 2 * p.rank) * p.slot_stride) +
+                       size_t(m) * ll_pairs + (n0 >> 1);
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            if (n0 + j < p.n_extent) {
-              float x = apply_act(v[j] + b, p.act);
-              const size_t idx = size_t(n0 + j) * p.ld_out + m;
-              if (p.residual) x += __bfloat162float(p.residual[idx]);
-              p.out[idx] = __float2bfloat16(x);
+          for (int q = 0; q < 8; ++q) {
+            if (n0 + 2 * q >= p.n_extent) break;
+            st_relaxed_sys_v4(row + q, __float_as_uint(v[2 * q]), ll_flag,
+                              n0 + 2 * q + 1 < p.n_extent ? __float_as_uint(v[2 * q + 1]) : 0u, ll_flag);
+          }
+        }
+      };
+      auto wait_ll = [&](const uint4* ptr, uint4 first) -> uint4 {
+        if ((first.y == ll_flag && first.w == ll_flag) || ll_gave_up) return first;
+        bool ok;
+        first = poll_flagged_word(ptr, ll_flag, &ok);
+        if (!ok) {
+          atomicMax(p.status, STATUS_TIMEOUT_FLAG);
+          ll_gave_up = true;
+        }
+        return first;
+      };
+      auto reduce_ll = [&](int n0) {  // sum the ranks' partials in rank order (identical on every rank), then the usual epilogue
+        if (!chunk_valid(n0)) return;
+        const uint4* area = reinterpret_cast<const uint4*>(p.slots[p.rank] + size_t(LL_FIRST_SLOT) * p.slot_stride);
+        const size_t slot_words = p.slot_stride >> 1;  // 16-byte words per flagged slot (= 2 fp32 slots)
+        const float b = p.bias ? p.bias_scale * __bfloat162float(p.bias[m]) : 0.f;
+        constexpr int G = 4, KH = 4;  // G token pairs x KH ranks of flagged words are in flight before the first one is examined
+#pragma unroll 1
+        for (int q0 = 0; q0 < 8 && n0 + 2 * q0 < p.n_extent; q0 += G) {
+          float s0[G], s1[G];
+#pragma unroll
+          for (int g = 0; g < G; ++g) s0[g] = s1[g] = 0.f;
+#pragma unroll 1
+          for (int k0 = 0; k0 < p.world; k0 += KH) {  // ranks in ascending order: the sum is bitwise identical on every rank
+            uint4 a[G][KH];
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+              const bool live = q0 + g < 8 && n0 + 2 * (q0 + g) < p.n_extent;
+#pragma unroll
+              for (int k = 0; k < KH; ++k)
+                if (live && k0 + k < p.world)
+                  a[g][k] = ld_relaxed_sys_v4(area + size_t(k0 + k) * slot_words + size_t(m) * ll_pairs + (n0 >> 1) + q0 + g);
+            }
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+              if (q0 + g < 8 && n0 + 2 * (q0 + g) < p.n_extent) {
+#pragma unroll
+                for (int k = 0; k < KH; ++k) {
+                  if (k0 + k < p.world) {
+                    const uint4 w4 = wait_ll(area + size_t(k0 + k) * slot_words + size_t(m) * ll_pairs + (n0 >> 1) + q0 + g, a[g][k]);
+                    s0[g] += __uint_as_float(w4.x);
+                    s1[g] += __uint_as_float(w4.z);
+                  }
+                }
+              }
+            }
+          }
+#pragma unroll
+          for (int g = 0; g < G; ++g) {
+            const int t = n0 + 2 * (q0 + g);
+            if (q0 + g < 8 && t < p.n_extent) {
+              const size_t o0 = size_t(t) * p.ld_out + m;
+              float x0 = s0[g] + b;
+              if (p.act) x0 = apply_act_call(x0, p.act);
+              if (p.residual) x0 += __bfloat162float(p.residual[o0]);
+              p.out[o0] = __float2bfloat16(x0);
+              if (t + 1 < p.n_extent) {
+                float x1 = s1[g] + b;
+                if (p.act) x1 = apply_act_call(x1, p.act);
+                if (p.residual) x1 += __bfloat162float(p.residual[o0 + p.ld_out]);
+                p.out[o0 + p.ld_out] = __float2bfloat16(x1);
+              }
             }
           }
         }
@@ -479,7 +700,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           if (d < p.world) store_partial(p.slots[d] + size_t(p.rank) * p.slot_stride, n0, v);
       };
 
-      const bool split_k = p.k_splits > 1;
+      const bool split_k = item.contributors > 1;
       const bool gated_cols = p.act == 5 && !p.swapped;  // column chunks alternate gate / up
       if (!split_k) {
         if (gated_cols) {
@@ -497,17 +718,29 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           for (int c0 = 0; c0 < BN; c0 += 16) {
             float v[16];
             read_acc(c0, v);
-            if (p.world > 1) push_to_peers(nt * BN + c0, v);
+            if (threadIdx.x == 64) TPB_TRACE(14);
+            if (p.ll) push_ll(nt * BN + c0, v);
+            else if (p.world > 1) push_to_peers(nt * BN + c0, v);
             else finalize(nt * BN + c0, v);
           }
         }
+        if (threadIdx.x == 64) TPB_TRACE(15);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty[acc]);  // accumulators may be overwritten from here on
+        if (p.ll) {
+          if (threadIdx.x == 64) {
+            p.ll_epochs[tile] = ll_flag;
+            TPB_TRACE(3);
+          }
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += 16) reduce_ll(nt * BN + c0);
+          if (threadIdx.x == 64) TPB_TRACE(8);
+        }
       } else {
         // split-K: park the partial in a local slot; the LAST split to arrive for this tile adds them up in split
         // order (deterministic) and carries on - nobody ever waits for another CTA.
-        float* my_slot = p.slots[p.rank] + size_t(p.world + split) * p.slot_stride;
+        float* my_slot = p.slots[p.rank] + size_t(p.world + item.ordinal) * p.slot_stride;
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 16) {
           float v[16];
@@ -517,28 +750,28 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty[acc]);
+        if (threadIdx.x == 64) TPB_TRACE(9);
         __threadfence();
         asm volatile("bar.sync 2, %0;" ::"n"(EPI_THREADS) : "memory");
         if (threadIdx.x == 64) {
+          TPB_TRACE(10);
           const uint32_t old = atomicAdd(p.split_counters + tile, 1u);
-          const bool last = old == uint32_t(p.k_splits - 1);
+          TPB_TRACE(11);
+          const bool last = old == uint32_t(item.contributors - 1);
           if (last) p.split_counters[tile] = 0;  // every other split has arrived: safe to re-arm for the next call
           *epi_last = last ? 1u : 0u;
         }
         asm volatile("bar.sync 2, %0;" ::"n"(EPI_THREADS) : "memory");
         if (*epi_last) {
           __threadfence();
+          if (threadIdx.x == 64) TPB_TRACE(12);
           if (gated_cols) {
             if constexpr (BN >= 32) {
 #pragma unroll 1
               for (int c0 = 0; c0 < BN; c0 += 32) {
                 float vg[16], vu[16];
-#pragma unroll
-                for (int j = 0; j < 16; ++j) { vg[j] = 0.f; vu[j] = 0.f; }
-                for (int sp = 0; sp < p.k_splits; ++sp) {
-                  add_partial(p.slots[p.rank] + size_t(p.world + sp) * p.slot_stride, nt * BN + c0, vg);
-                  add_partial(p.slots[p.rank] + size_t(p.world + sp) * p.slot_stride, nt * BN + c0 + 16, vu);
-                }
+                sum_partials(item.contributors, nt * BN + c0, vg);
+                sum_partials(item.contributors, nt * BN + c0 + 16, vu);
                 finalize_gated(nt * BN + c0, vg, vu);
               }
             }
@@ -546,24 +779,28 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 16) {
               float v[16];
-#pragma unroll
-              for (int j = 0; j < 16; ++j) v[j] = 0.f;
-              for (int sp = 0; sp < p.k_splits; ++sp)
-                add_partial(p.slots[p.rank] + size_t(p.world + sp) * p.slot_stride, nt * BN + c0, v);
-              if (p.world > 1) push_to_peers(nt * BN + c0, v);
+              sum_partials(item.contributors, nt * BN + c0, v);
+              if (p.ll) push_ll(nt * BN + c0, v);
+              else if (p.world > 1) push_to_peers(nt * BN + c0, v);
               else finalize(nt * BN + c0, v);
+            }
+            if (p.ll) {
+              if (threadIdx.x == 64) p.ll_epochs[tile] = ll_flag;
+#pragma unroll 1
+              for (int c0 = 0; c0 < BN; c0 += 16) reduce_ll(nt * BN + c0);
             }
           }
         }
       }
-      if (p.world > 1 && (!split_k || *epi_last)) {
+      if (p.world > 1 && !p.ll && (!split_k || *epi_last)) {
         // make this tile's partial visible system-wide, then count one arrival on every rank
+        // (the barrier orders every epilogue thread's stores before thread 64's fence, which is cumulative: one
+        // system-scope fence per tile instead of one per thread - each costs microseconds)
         if (threadIdx.x == 64) TPB_TRACE(3);
-        __threadfence_system();
         asm volatile("bar.sync 2, %0;" ::"n"(EPI_THREADS) : "memory");
         if (threadIdx.x == 64) {
           TPB_TRACE(4);
-          __threadfence_system();  // one release fence for all peers (orders the partial tiles the barrier made visible)
+          __threadfence_system();
           for (int d = 0; d < p.world; ++d) red_add_relaxed_sys(p.arrivals[d] + tile, 1u);
           TPB_TRACE(5);
         }
@@ -573,7 +810,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
 
   // ---------------- cross-rank reduce phase ----------------
   __syncthreads();
-  if (p.world > 1) {
+  if (p.world > 1 && !p.ll) {
     const uint32_t contributions = uint32_t(p.world);
     const float* base_slot = p.slots[p.rank];
     // token / feature extents of one tile in out[token, feature] coordinates
@@ -622,7 +859,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           for (int j = 0; j < 4; ++j) {
             if (f + j < feat0 + feat_n) {
               float x = o[j] + (p.bias ? p.bias_scale * __bfloat162float(p.bias[f + j]) : 0.f);
-              x = apply_act(x, p.act);
+              if (p.act) x = apply_act_call(x, p.act);
               if (p.residual) x += __bfloat162float(p.residual[idx + j]);
               p.out[idx + j] = __float2bfloat16(x);
             }
@@ -637,6 +874,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   // ---------------- teardown ----------------
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) TPB_TRACE(13);
   if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
@@ -674,7 +912,7 @@ static int make_tmap_2d(CUtensorMap* map, const void* ptr, uint64_t rows, uint64
   return r == CUDA_SUCCESS ? TPB_OK : TPB_ERR_TMAP;
 }
 
-static int g_debug_stages = 0, g_debug_skip_mma = 0, g_trace_block = 0;  // measurement aids, see tpb_gemm_debug
+static int g_debug_stages = 0, g_debug_skip_mma = 0, g_trace_block = 0, g_disable_ll = 0, g_enable_stream_k = 0;  // measurement aids, see tpb_gemm_debug
 
 template <int BN, int KBOX, int NACC>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, int grid, cudaStream_t stream) {
@@ -682,7 +920,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams&
   int stages = int((227 * 1024 - 2048) / stage_bytes);
   if (stages > MAX_STAGES) stages = MAX_STAGES;
   if (stages < 2) stages = 2;
-  if (stages > p.kb_per_split + 1 && p.m_tiles * p.n_tiles * p.k_splits <= grid) stages = max(2, p.kb_per_split + 1);
+  if (stages > p.kb_per_split + 1 && (p.stream_k || p.m_tiles * p.n_tiles * p.k_splits <= grid)) stages = max(2, p.kb_per_split + 1);
   if (g_debug_stages > 0 && g_debug_stages < stages) stages = g_debug_stages;
   p.stages = stages;
   p.debug_skip_mma = g_debug_skip_mma;
@@ -723,14 +961,25 @@ extern "C" int tpb_gemm_debug(int stages, int skip_mma) {
 }
 
 // Measurement aid: CTA `block` (>= 0) of every following GEMM launch records %globaltimer stamps of its phases
-// (block < 0 switches it off).  tpb_gemm_trace_read copies the 16 stamps of the current device to the host
+// (block < 0 switches it off).  tpb_gemm_trace_read copies the 32 stamps of the current device to the host
 // (synchronous; call it after synchronising the stream).
+// The cross-rank sum of small problems exchanges flagged words by default; a non-zero argument makes every
+// following launch use the arrival-counter protocol instead (comparison / fallback).
+extern "C" int tpb_gemm_disable_flagged_exchange(int disable) {
+  g_disable_ll = disable;
+  return TPB_OK;
+}
+// Non-zero: tpb_gemm_plan deals the few-token shapes out as stream-K ranges (off by default, see tpb_gemm_plan).
+extern "C" int tpb_gemm_enable_stream_k(int enable) {
+  g_enable_stream_k = enable;
+  return TPB_OK;
+}
 extern "C" int tpb_gemm_trace(int block) {
   g_trace_block = block < 0 ? 0 : block + 1;
   return TPB_OK;
 }
-extern "C" int tpb_gemm_trace_read(unsigned long long* out16) {
-  return cudaMemcpyFromSymbol(out16, g_gemm_trace, sizeof(unsigned long long) * 16) == cudaSuccess ? TPB_OK : TPB_ERR_CUDA;
+extern "C" int tpb_gemm_trace_read(unsigned long long* out32) {
+  return cudaMemcpyFromSymbol(out32, g_gemm_trace, sizeof(unsigned long long) * 32) == cudaSuccess ? TPB_OK : TPB_ERR_CUDA;
 }
 
 // Plan of a linear layer out[tokens, features] = x[tokens, K] @ w[features, K]^T.
@@ -757,29 +1006,67 @@ extern "C" int tpb_gemm_plan(int tokens, int features, int k, int world, int for
                                   // and stage (measured on B200: 4 boxes per stage stream ~15% faster than 1)
   if (force_kbox > 0) kbox = force_kbox;
   if (bn > 32 || (kbox != 1 && kbox != 2 && kbox != 4)) kbox = 1;
-  plan->kbox = kbox;
-  plan->k_blocks = ((k + BK - 1) / BK + kbox - 1) / kbox;  // in units of one pipeline stage (kbox * 64 columns)
   const int tiles = plan->m_tiles * plan->n_tiles;
-  int splits = 1;
-  if (force_splits > 0) {
-    splits = force_splits;
-  } else if (tiles * 2 <= sms && plan->k_blocks * kbox >= 128) {
-    // few output tiles and a long K (>= 8192): split K so that more SMs stream weights.  Measured on B200 (kernel
-    // time inside a CUDA graph): for shorter K the extra partial-tile pass costs more than the added SMs bring.
-    splits = sms / tiles;
-    const int by_k = (plan->k_blocks * kbox) / 64;
-    if (splits > by_k) splits = by_k;
-    if (splits > 3) splits = 3;
-    if (splits < 1) splits = 1;
+  const int kb64 = (k + BK - 1) / BK;
+  plan->stream_k = 0;
+  // Stream-K for the weight-streaming (swapped) shapes: the time of such a GEMM is bytes / (CTAs x per-CTA stream rate),
+  // so what matters is that all SMs stream equal shares - whatever the number of 128-row tiles.  force_splits > 0
+  // keeps the uniform decomposition (1 = no split at all).
+  // OFF unless tpb_gemm_enable_stream_k(1): measured on B200 (CUDA-graph timing, 8 tokens) the streaming phase does
+  // get shorter (4096 x 4096: accumulators complete after 7 us instead of 12 us), but the partial-tile exchange - park,
+  // fence, counter, batched re-read - costs more than that on every shape tried (4096 x 4096: 18.9 vs 16.4 us,
+  // 1536 x 4096: 16.6 vs 15.7 us, 4096 x 11008: 27.2 vs 28.1 us).
+  const bool few_tiles = tiles * 10 <= sms * 6;
+  (void)few_tiles;
+  if (plan->swapped && force_splits <= 0 && g_enable_stream_k) {
+    if (force_kbox <= 0)
+      while (kbox > 1 && (long long)tiles * ((kb64 + kbox - 1) / kbox) < 4LL * sms) kbox >>= 1;  // keep >= 4 units per CTA if possible
+    const int kblocks = (kb64 + kbox - 1) / kbox;
+    const long long units = (long long)tiles * kblocks;
+    int grid = int(units / 2 < sms ? (units / 2 > 0 ? units / 2 : 1) : sms);
+    if (!(tiles >= grid && tiles % grid == 0)) {  // (an exact multiple of the grid is balanced already)
+      // a tile may not have more contributors than there are parking slots below the flagged-word area
+      const int max_contrib = 8;  // two batches of the partial-tile sum; also bounds the parking slots (world + 8 <= 17)
+      for (;;) {
+        const long long per = units / grid;  // shortest range
+        const int contrib = int((kblocks + per - 1) / per) + 1;
+        if (contrib <= max_contrib || grid == 1) {
+          plan->k_splits = contrib < 2 ? 2 : contrib;  // upper bound, sizes the workspace checks
+          break;
+        }
+        --grid;
+      }
+      plan->stream_k = 1;
+      plan->kbox = kbox;
+      plan->k_blocks = kblocks;
+      plan->kb_per_split = int((units + grid - 1) / grid);
+      plan->reduce = 1;
+      plan->grid = grid;
+    }
   }
-  if (splits > plan->k_blocks) splits = plan->k_blocks;
-  int per = (plan->k_blocks + splits - 1) / splits;
-  splits = (plan->k_blocks + per - 1) / per;  // no empty split
-  plan->k_splits = splits;
-  plan->kb_per_split = per;
-  plan->reduce = (splits > 1 || world > 1) ? 1 : 0;
-  const int work = tiles * splits;
-  plan->grid = work < sms ? work : sms;
+  if (!plan->stream_k) {
+    plan->kbox = kbox;
+    plan->k_blocks = (kb64 + kbox - 1) / kbox;  // in units of one pipeline stage (kbox * 64 columns)
+    int splits = 1;
+    if (force_splits > 0) {
+      splits = force_splits;
+    } else if (tiles * 2 <= sms && plan->k_blocks * kbox >= 128) {
+      // few output tiles and a long K (>= 8192): split K so that more SMs work on the problem
+      splits = sms / tiles;
+      const int by_k = (plan->k_blocks * kbox) / 64;
+      if (splits > by_k) splits = by_k;
+      if (splits > 3) splits = 3;
+      if (splits < 1) splits = 1;
+    }
+    if (splits > plan->k_blocks) splits = plan->k_blocks;
+    int per = (plan->k_blocks + splits - 1) / splits;
+    splits = (plan->k_blocks + per - 1) / per;  // no empty split
+    plan->k_splits = splits;
+    plan->kb_per_split = per;
+    plan->reduce = (splits > 1 || world > 1) ? 1 : 0;
+    const int work = tiles * splits;
+    plan->grid = work < sms ? work : sms;
+  }
   plan->tokens_pad = plan->swapped ? plan->n_tiles * bn : plan->m_tiles * BM;
   plan->slot_elems = size_t(tokens) * size_t(features);
   plan->tiles = tiles;
@@ -804,6 +1091,7 @@ static int gemm_impl(const void* x, const void* w, void* out, const void* bias, 
   p.k_blocks = plan->k_blocks;
   p.k_splits = plan->k_splits;
   p.kb_per_split = plan->kb_per_split;
+  p.stream_k = plan->stream_k;
   p.ld_out = ld_out;
   p.ld_slot = act == 5 ? features : ld_out;
   p.out = static_cast<__nv_bfloat16*>(out);
@@ -828,6 +1116,11 @@ static int gemm_impl(const void* x, const void* w, void* out, const void* bias, 
     p.split_counters = static_cast<uint32_t*>(rc->split_counters);
     p.slot_stride = rc->slot_stride;
     p.status = static_cast<uint32_t*>(rc->status);
+    if (rc->world > 1 && plan->swapped && act != 5 && rc->ll_epochs && !g_disable_ll && rc->max_slots >= LL_FIRST_SLOT + 2 * rc->world &&
+        rc->world + plan->k_splits <= LL_FIRST_SLOT) {
+      p.ll = 1;
+      p.ll_epochs = static_cast<uint32_t*>(rc->ll_epochs);
+    }
   } else {
     if (!rc || !rc->status) return TPB_ERR_ARG;
     p.status = static_cast<uint32_t*>(rc->status);

@@ -206,6 +206,25 @@ __device__ __forceinline__ void red_add_release_sys(uint32_t* p, uint32_t v) {
 }
 // Relaxed system-scope add: use after ONE __threadfence_system() when several peers have to be signalled - every
 // red.release carries its own system-wide release fence, which costs microseconds per peer over NVLink.
+// 8-byte {value, flag} words of the flagged exchange: one aligned 8-byte access is single-copy atomic, so a reader
+// that sees the expected flag also sees the value stored with it.
+__device__ __forceinline__ void st_relaxed_sys_v2(uint2* p, uint32_t x, uint32_t y) {
+  asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ uint2 ld_relaxed_sys_v2(const uint2* p) {
+  uint2 v;
+  asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
+// 16-byte form: two {value, flag} halves; the reader checks both flags, so only 8-byte atomicity is relied upon.
+__device__ __forceinline__ void st_relaxed_sys_v4(uint4* p, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+  asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+__device__ __forceinline__ uint4 ld_relaxed_sys_v4(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
 __device__ __forceinline__ void red_add_relaxed_sys(uint32_t* p, uint32_t v) {
   asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }

@@ -31,6 +31,8 @@ typedef struct {
   int tokens_pad;
   int tiles;
   size_t slot_elems;  // fp32 elements one slot must hold
+  int stream_k;       // 1: the (tile, k-block) units are dealt out as one contiguous range per CTA; k_splits then is an
+                      // upper bound of the CTAs that contribute to one tile
 } tpb_gemm_plan_t;
 
 // Workspace of the fused split-K / all-reduce epilogue.  All pointers are device pointers valid on the
@@ -44,6 +46,8 @@ typedef struct {
   void* status;                   // local uint32 status word
   size_t slot_stride;             // elements per slot
   int max_slots, max_tiles;
+  void* ll_epochs;                // local uint32 [max_tiles], zero-initialised: epochs of the flagged-word exchange that small
+                                  // cross-rank sums use (needs max_slots >= 32 + 2 * world); null selects arrival counters
 } tpb_reduce_ctx_t;
 
 // Operands of the fused all-gather + GEMM (see tpb_gemm_allgather_bf16).
@@ -73,10 +77,12 @@ int tpb_gemm_allgather_bf16(const void* w, void* out, const void* bias, int toke
 
 // Measurement aids.  tpb_gemm_debug caps the smem ring depth / skips the MMAs (0, 0 restores the defaults).
 // tpb_gemm_trace makes CTA `block` of every following GEMM launch record %globaltimer stamps of its phases
-// (block < 0: off); tpb_gemm_trace_read copies the 16 stamps of the current device to the host.
+// (block < 0: off); tpb_gemm_trace_read copies the 32 stamps of the current device to the host.
 int tpb_gemm_debug(int stages, int skip_mma);
 int tpb_gemm_trace(int block);
-int tpb_gemm_trace_read(unsigned long long* out16);
+int tpb_gemm_disable_flagged_exchange(int disable);
+int tpb_gemm_enable_stream_k(int enable);
+int tpb_gemm_trace_read(unsigned long long* out32);
 
 #ifdef __cplusplus
 }

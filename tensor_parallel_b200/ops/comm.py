@@ -96,6 +96,7 @@ class RankComm:
             self.epochs = torch.zeros(COMM_MAX_BLOCKS, dtype=torch.int32, device=device)
             self.expected = torch.zeros(2 * MAX_TILES, dtype=torch.int32, device=device)
             self.split_counters = torch.zeros(2 * MAX_TILES, dtype=torch.int32, device=device)
+            self.ll_epochs = torch.zeros(2 * MAX_TILES, dtype=torch.int32, device=device)
             self.status = torch.zeros(4, dtype=torch.int32, device=device)
         self.local = tensor_from_ptr(self.base[rank], layout.total, device)
         self.staging_in = self.local[layout.off_staging_in : layout.off_staging_in + layout.staging_bytes]
@@ -122,6 +123,7 @@ class RankComm:
         ctx.expected = self.expected.data_ptr() + region * MAX_TILES * 4
         ctx.split_counters = self.split_counters.data_ptr() + region * MAX_TILES * 4
         ctx.status = self.status.data_ptr()
+        ctx.ll_epochs = self.ll_epochs.data_ptr() + region * MAX_TILES * 4
         ctx.slot_stride = self.layout.slot_stride
         ctx.max_slots, ctx.max_tiles = self.layout.max_slots, MAX_TILES
         return ctx

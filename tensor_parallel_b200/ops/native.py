@@ -36,13 +36,13 @@ c_void_p, c_int, c_float, c_ll, c_size_t = ctypes.c_void_p, ctypes.c_int, ctypes
 class GemmPlan(ctypes.Structure):
     _fields_ = [("swapped", c_int), ("bn", c_int), ("kbox", c_int), ("m_tiles", c_int), ("n_tiles", c_int), ("k_blocks", c_int),
                 ("k_splits", c_int), ("kb_per_split", c_int), ("reduce", c_int), ("grid", c_int), ("tokens_pad", c_int),
-                ("tiles", c_int), ("slot_elems", c_size_t)]
+                ("tiles", c_int), ("slot_elems", c_size_t), ("stream_k", c_int)]
 
 
 class ReduceCtx(ctypes.Structure):
     _fields_ = [("world", c_int), ("rank", c_int), ("slots", c_void_p * 8), ("arrivals", c_void_p * 8),
                 ("expected", c_void_p), ("split_counters", c_void_p), ("status", c_void_p), ("slot_stride", c_size_t), ("max_slots", c_int),
-                ("max_tiles", c_int)]
+                ("max_tiles", c_int), ("ll_epochs", c_void_p)]
 
 
 def check(code: int, what: str):

@@ -91,6 +91,31 @@ def test_gemm_forced_split_k(splits):
     _check(out, _ref(x, w, bias), k)
 
 
+@pytest.mark.parametrize("tokens,features,k", [(8, 4096, 4096), (8, 1536, 4096), (16, 1000, 1376), (40, 4096, 11008), (3, 256, 64)])
+def test_gemm_stream_k_decomposition(tokens, features, k):
+    """Opt-in stream-K: every CTA owns one contiguous range of (tile, k-block) units; tiles shared by several CTAs are
+    summed by the last contributor.  Bias / activation / residual and the gated epilogue go through the same path."""
+    native = _native()
+    torch.manual_seed(tokens + features)
+    x = torch.randn(tokens, k, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(features, k, device="cuda", dtype=torch.bfloat16) * 0.05
+    bias = torch.randn(features, device="cuda", dtype=torch.bfloat16)
+    res = torch.randn(tokens, features, device="cuda", dtype=torch.bfloat16)
+    native.LIB.tpb_gemm_enable_stream_k(1)
+    native._plan_cache.clear()
+    try:
+        plan = native.gemm_plan(tokens, features, k)
+        for _ in range(3):  # the per-tile counters re-arm themselves
+            out = native.gemm_nt(x, w, bias=bias, residual=res, act="gelu")
+        torch.cuda.synchronize()
+        native.device_state(x.device).check_status()
+    finally:
+        native.LIB.tpb_gemm_enable_stream_k(0)
+        native._plan_cache.clear()
+    assert plan.stream_k == 1 or features * k < 256 * 64 * 2
+    _check(out, _ref(x, w, bias, res, "gelu"), k)
+
+
 def test_gemm_strided_input_and_output_views():
     nat = _native()
     torch.manual_seed(3)

@@ -2,6 +2,7 @@
 oracle): stand-alone collectives on the symmetric heap, the fused GEMM + all-reduce kernel, the
 distributed tensor-parallel wrapper (training parity incl. ZeRO-3) and the serving engine at TP=2.
 Child processes run with NVLS disabled; every device-side wait is time-bounded."""
+import itertools
 import os
 import socket
 import sys
@@ -77,7 +78,10 @@ def _collectives_worker(rank, world, port, out_dir):
         # fused GEMM + all-reduce (row-parallel linear): decode shapes with and without split-K, with bias / residual
         from tensor_parallel_b200.ops import native
 
-        for tokens, features, k in ((8, 4096, 512), (8, 4096, 1376), (16, 1024, 2048), (1, 256, 64)):
+        # both cross-rank protocols: flagged words (default for these shapes) and arrival counters
+        for flagged, (tokens, features, k) in itertools.product(
+                (True, False), ((8, 4096, 512), (8, 4096, 1376), (16, 1024, 2048), (1, 256, 64), (40, 1000, 512), (8, 1024, 16384))):
+            native.LIB.tpb_gemm_disable_flagged_exchange(0 if flagged else 1)
             x = torch.randn(tokens, k, device=dev, dtype=torch.bfloat16)
             w = torch.randn(features, k, device=dev, dtype=torch.bfloat16) * 0.05
             bias = torch.randn(features, device=dev, dtype=torch.bfloat16)
@@ -92,7 +96,8 @@ def _collectives_worker(rank, world, port, out_dir):
             torch.cuda.synchronize()
             rc.check_status()
             err = (got.float() - want).abs().max().item()
-            assert err <= 0.02 * want.abs().max().item() + 0.05, (tokens, features, k, err)
+            assert err <= 0.02 * want.abs().max().item() + 0.05, (flagged, tokens, features, k, err)
+        native.LIB.tpb_gemm_disable_flagged_exchange(0)
         # fused all-gather + GEMM (column-parallel linear fed by a hidden-split activation)
         for tokens, cols, features in ((8, 256, 1536), (300, 128, 1000), (2048, 512, 4096)):
             xl = torch.randn(tokens, cols, device=dev, dtype=torch.bfloat16)
