@@ -377,7 +377,7 @@ attn_decode_fused_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k,
                          float* __restrict__ part_o, float* __restrict__ part_ml, uint32_t* __restrict__ counters,
                          const int* __restrict__ pos_ptr, int q_heads, int kv_heads, int g_total, int g_offset, int max_seq,
                          int splits, float scale_log2e, int rotary_dim, float log2_theta, int interleaved, long long q_ld,
-                         long long k_ld, long long v_ld) {
+                         long long k_ld, long long v_ld, const float2* __restrict__ rope_table) {
   constexpr int EPL = D / 8;
   pdl_trigger();
   pdl_wait();
@@ -411,9 +411,15 @@ attn_decode_fused_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k,
     if (p < half) {
       const int ia = interleaved ? 2 * p : p;
       const int ib = interleaved ? 2 * p + 1 : p + half;
-      const float inv_freq = exp2f(-log2_theta * (2.f * float(p) / float(rotary_dim)));
       float sn, cs;
-      sincosf(float(pos) * inv_freq, &sn, &cs);
+      if (rope_table) {  // (cos, sin) of every position, filled by rope_table_kernel with the formula below
+        const float2 t = __ldg(rope_table + (long long)pos * half + p);
+        cs = t.x;
+        sn = t.y;
+      } else {
+        const float inv_freq = exp2f(-log2_theta * (2.f * float(p) / float(rotary_dim)));
+        sincosf(float(pos) * inv_freq, &sn, &cs);
+      }
       const float a = __bfloat162float(src[ia]), c = __bfloat162float(src[ib]);
       // round through bf16 like the stand-alone append kernel, so cached and in-flight keys agree bit for bit
       dst[ia] = __bfloat162float(__float2bfloat16(a * cs - c * sn)) * mul;
@@ -569,16 +575,31 @@ attn_decode_fused_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k,
   }
 }
 
+// table[pos * (rotary_dim / 2) + p] = (cos, sin)(pos * theta^(-2p / rotary_dim)), the angles of the rotary embedding
+__global__ void rope_table_kernel(float2* __restrict__ table, int positions, int half, int rotary_dim, float log2_theta) {
+  const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (i >= (long long)positions * half) return;
+  const int pos = int(i / half), p = int(i % half);
+  const float inv_freq = exp2f(-log2_theta * (2.f * float(p) / float(rotary_dim)));
+  float sn, cs;
+  sincosf(float(pos) * inv_freq, &sn, &cs);
+  table[i] = make_float2(cs, sn);
+}
+
 // ------------------------------------------------------------------------------------------------
 // prefill attention (legacy mma.sync tensor path; 64 query rows x 64 keys per step, 4 warps)
 // ------------------------------------------------------------------------------------------------
-template <int D>
+// BIAS: 0 none, 1 fp32, 2 bf16 additive score bias addressed as bias[b * bias_sb + h * bias_sh + i * bias_sq + j * bias_sk]
+// (a stride of 0 broadcasts: relative-position biases are [1, H, Sq, Sk], padding masks [B, 1, 1, Sk], ALiBi [1, H, 1, Sk]).
+// The bias is in natural-log units like the scores; -inf entries mask a key.
+template <int D, int BIAS = 0>
 __global__ void __launch_bounds__(PF_THREADS)
 attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v,
                     bf16* __restrict__ out, float* __restrict__ lse, int sq, int sk, int q_heads, int kv_heads,
                     long long q_sb, long long q_ss, long long q_sh, long long k_sb, long long k_ss, long long k_sh,
                     long long v_sb, long long v_ss, long long v_sh, long long o_sb, long long o_ss, long long o_sh,
-                    int causal, float scale_log2e) {
+                    int causal, float scale_log2e, const void* __restrict__ bias = nullptr, long long bias_sb = 0,
+                    long long bias_sh = 0, long long bias_sq = 0, long long bias_sk = 0) {
   extern __shared__ __align__(128) uint8_t pf_smem[];
   bf16* q_s = reinterpret_cast<bf16*>(pf_smem);
   bf16* k_s = q_s + PF_M * D;
@@ -651,7 +672,13 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, cons
         const int key = kv0 + nt * 8 + 2 * t4 + (j & 1);
         const int qi = qi0 + (j >> 1) * 8;
         const bool dead = key >= sk || (causal && key > qi + shift);
-        const float sv = dead ? -INFINITY : s_acc[nt][j] * scale_log2e;
+        float sv = dead ? -INFINITY : s_acc[nt][j] * scale_log2e;
+        if (BIAS != 0 && !dead && qi < sq) {
+          const long long bi = b * bias_sb + h * bias_sh + (long long)qi * bias_sq + (long long)key * bias_sk;
+          const float bv = BIAS == 1 ? __ldg(static_cast<const float*>(bias) + bi)
+                                     : __bfloat162float(static_cast<const bf16*>(bias)[bi]);
+          sv += bv * 1.4426950408889634f;
+        }
         s_acc[nt][j] = sv;
         m_new[j >> 1] = fmaxf(m_new[j >> 1], sv);
       }
@@ -817,12 +844,15 @@ extern "C" int tpb_attn_decode(const void* q, const void* kcache, const void* vc
   return cudaGetLastError() == cudaSuccess ? TPB_OK : TPB_ERR_CUDA;
 }
 
-// Strides are in elements; head_dim must be contiguous (stride 1) in q, k, v and out.
-extern "C" int tpb_attn_prefill(const void* q, const void* k, const void* v, void* out, float* lse, int batch, int sq,
-                                int sk, int q_heads, int kv_heads, int head_dim, long long q_sb, long long q_ss,
-                                long long q_sh, long long k_sb, long long k_ss, long long k_sh, long long v_sb,
-                                long long v_ss, long long v_sh, long long o_sb, long long o_ss, long long o_sh,
-                                int causal, float scale, void* stream_) {
+// Strides are in elements; head_dim must be contiguous (stride 1) in q, k, v and out.  bias (may be null) is an
+// additive score bias of dtype bias_dtype (0 bf16, 1 fp32) with element strides bias_s* over (batch, head, query, key);
+// a stride of 0 broadcasts that dimension.
+extern "C" int tpb_attn_prefill_bias(const void* q, const void* k, const void* v, void* out, float* lse, int batch, int sq,
+                                     int sk, int q_heads, int kv_heads, int head_dim, long long q_sb, long long q_ss,
+                                     long long q_sh, long long k_sb, long long k_ss, long long k_sh, long long v_sb,
+                                     long long v_ss, long long v_sh, long long o_sb, long long o_ss, long long o_sh,
+                                     int causal, float scale, const void* bias, int bias_dtype, long long bias_sb,
+                                     long long bias_sh, long long bias_sq, long long bias_sk, void* stream_) {
   if (!q || !k || !v || !out || batch <= 0 || sq <= 0 || sk <= 0 || q_heads % kv_heads) return TPB_ERR_ARG;
   if (head_dim != 64 && head_dim != 128) return TPB_ERR_SIZE;
   if ((q_ss & 7) || (q_sh & 7) || (q_sb & 7) || (k_ss & 7) || (k_sh & 7) || (k_sb & 7) || (v_ss & 7) || (v_sh & 7) ||
@@ -832,22 +862,40 @@ extern "C" int tpb_attn_prefill(const void* q, const void* k, const void* v, voi
   dim3 grid((sq + PF_M - 1) / PF_M, q_heads, batch);
   const float sl2 = scale * 1.4426950408889634f;
   const size_t smem = size_t(PF_M + 2 * PF_N) * head_dim * 2;
+  if (bias && bias_dtype != 0 && bias_dtype != 1) return TPB_ERR_ARG;
+#define PF_LAUNCH(D, B)                                                                                                   \
+  do {                                                                                                                    \
+    if (!dec_smem_ready<attn_prefill_kernel<D, B>>(smem)) return TPB_ERR_CUDA;                                            \
+    attn_prefill_kernel<D, B><<<grid, PF_THREADS, smem, s>>>((const bf16*)q, (const bf16*)k, (const bf16*)v, (bf16*)out, lse, sq, sk, \
+                                                             q_heads, kv_heads, q_sb, q_ss, q_sh, k_sb, k_ss, k_sh, v_sb, v_ss, v_sh,  \
+                                                             o_sb, o_ss, o_sh, causal, sl2, bias, bias_sb, bias_sh, bias_sq, bias_sk); \
+  } while (0)
+  const int mode = !bias ? 0 : (bias_dtype == 1 ? 1 : 2);
   if (head_dim == 128) {
-    static bool cfg[64] = {false};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !cfg[dev]) {
-      cudaFuncSetAttribute(attn_prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-      cfg[dev] = true;
-    }
-    attn_prefill_kernel<128><<<grid, PF_THREADS, smem, s>>>((const bf16*)q, (const bf16*)k, (const bf16*)v, (bf16*)out, lse, sq, sk,
-                                                            q_heads, kv_heads, q_sb, q_ss, q_sh, k_sb, k_ss, k_sh, v_sb, v_ss, v_sh,
-                                                            o_sb, o_ss, o_sh, causal, sl2);
+    if (mode == 0) PF_LAUNCH(128, 0); else if (mode == 1) PF_LAUNCH(128, 1); else PF_LAUNCH(128, 2);
   } else {
-    attn_prefill_kernel<64><<<grid, PF_THREADS, smem, s>>>((const bf16*)q, (const bf16*)k, (const bf16*)v, (bf16*)out, lse, sq, sk,
-                                                           q_heads, kv_heads, q_sb, q_ss, q_sh, k_sb, k_ss, k_sh, v_sb, v_ss, v_sh,
-                                                           o_sb, o_ss, o_sh, causal, sl2);
+    if (mode == 0) PF_LAUNCH(64, 0); else if (mode == 1) PF_LAUNCH(64, 1); else PF_LAUNCH(64, 2);
   }
+#undef PF_LAUNCH
+  return cudaGetLastError() == cudaSuccess ? TPB_OK : TPB_ERR_CUDA;
+}
+
+extern "C" int tpb_attn_prefill(const void* q, const void* k, const void* v, void* out, float* lse, int batch, int sq,
+                                int sk, int q_heads, int kv_heads, int head_dim, long long q_sb, long long q_ss,
+                                long long q_sh, long long k_sb, long long k_ss, long long k_sh, long long v_sb,
+                                long long v_ss, long long v_sh, long long o_sb, long long o_ss, long long o_sh,
+                                int causal, float scale, void* stream_) {
+  return tpb_attn_prefill_bias(q, k, v, out, lse, batch, sq, sk, q_heads, kv_heads, head_dim, q_sb, q_ss, q_sh, k_sb, k_ss,
+                               k_sh, v_sb, v_ss, v_sh, o_sb, o_ss, o_sh, causal, scale, nullptr, 0, 0, 0, 0, 0, stream_);
+}
+
+// Fills table [positions][rotary_dim / 2] of (cos, sin) pairs (fp32) for tpb_attn_decode_fused's rope_table argument:
+// the decode kernel then looks the angles of the new position up instead of evaluating sincosf in every CTA.
+extern "C" int tpb_rope_table(void* table, int positions, int rotary_dim, float theta, void* stream_) {
+  if (!table || positions <= 0 || rotary_dim <= 0 || (rotary_dim & 1)) return TPB_ERR_ARG;
+  const long long n = (long long)positions * (rotary_dim / 2);
+  rope_table_kernel<<<int((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream_)>>>(
+      static_cast<float2*>(table), positions, rotary_dim / 2, rotary_dim, log2f(theta));
   return cudaGetLastError() == cudaSuccess ? TPB_OK : TPB_ERR_CUDA;
 }
 
@@ -855,10 +903,12 @@ extern "C" int tpb_attn_prefill(const void* q, const void* k, const void* v, voi
 // q / k / v: rows of the projection output for ONE new token per sequence ([batch, heads * head_dim], row pitches
 // q_ld / k_ld / v_ld); pos_ptr[0] = position of the new token = number of tokens already cached.
 // part_o / part_ml as for tpb_attn_decode; counters: uint32 [batch * kv_heads], zeroed once by the caller.
+// rope_table: optional output of tpb_rope_table covering every position < max_seq (null: angles are computed in place).
 extern "C" int tpb_attn_decode_fused(const void* q, const void* k, const void* v, void* kcache, void* vcache, void* out,
                                      float* part_o, float* part_ml, void* counters, const int* pos_ptr, int batch, int q_heads,
                                      int kv_heads, int head_dim, int max_seq, int splits, float scale, int rotary_dim, float theta,
-                                     int interleaved, long long q_ld, long long k_ld, long long v_ld, void* stream_) {
+                                     int interleaved, long long q_ld, long long k_ld, long long v_ld, const void* rope_table,
+                                     void* stream_) {
   if (!q || !k || !v || !kcache || !vcache || !out || !pos_ptr || batch <= 0 || splits < 1 || q_heads % kv_heads) return TPB_ERR_ARG;
   if (splits > 1 && (!part_o || !part_ml || !counters)) return TPB_ERR_ARG;
   if (head_dim != 64 && head_dim != 128) return TPB_ERR_SIZE;
@@ -878,7 +928,7 @@ extern "C" int tpb_attn_decode_fused(const void* q, const void* k, const void* v
   if (!dec_smem_ready<attn_decode_fused_kernel<D, G>>(dec_ring_bytes<D>())) return TPB_ERR_CUDA;                               \
   launch_kernel(attn_decode_fused_kernel<D, G>, grid, dim3(DEC_THREADS), dec_ring_bytes<D>(), s, (const bf16*)q, (const bf16*)k, (const bf16*)v, \
                 (bf16*)kcache, (bf16*)vcache, (bf16*)out, part_o, part_ml, (uint32_t*)counters, pos_ptr, q_heads, kv_heads, g_total, \
-                done, max_seq, splits, sl2, rotary_dim, l2t, interleaved, q_ld, k_ld, v_ld)
+                done, max_seq, splits, sl2, rotary_dim, l2t, interleaved, q_ld, k_ld, v_ld, (const float2*)rope_table)
     if (head_dim == 128) {
       if (gnow == 1) { DECF(128, 1); } else if (gnow == 2) { DECF(128, 2); } else { DECF(128, 4); }
     } else {

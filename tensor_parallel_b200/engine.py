@@ -104,6 +104,7 @@ class LlamaEngine:
         self.logits_local = torch.zeros(B, self.vocab_local, **bf)
         self.next_ids = torch.zeros(B, dtype=torch.int64, device=dev)
         # split the key range only when (batch x kv heads) alone cannot occupy the SMs
+        self.rope_angles = native.rope_table(max_seq, D, self.theta, dev)  # (cos, sin) of every position, looked up by the decode kernel
         self.splits = 1 if B * self.nkv >= 128 else max(1, min(8, math.ceil(256 / (B * self.nkv))))
         self.attn_ws = (torch.empty(B * self.nq * self.splits * D, dtype=torch.float32, device=dev),
                         torch.empty(B * self.nq * self.splits * 2, dtype=torch.float32, device=dev),
@@ -137,7 +138,8 @@ class LlamaEngine:
         if decode:
             # RoPE, cache append, split-KV attention and the split merge: one launch
             native.attn_decode_fused(q2, k2, v2, self.kcache[i][:batch], self.vcache[i][:batch], self.pos, D, self.theta,
-                                     splits=self.splits, workspace=self.attn_ws, out=attn.view(batch, self.nq, D))
+                                     splits=self.splits, workspace=self.attn_ws, out=attn.view(batch, self.nq, D),
+                                     rope_angles=self.rope_angles)
         else:
             native.qkv_rope_append(q2, k2, v2, q_rot, self.kcache[i], self.vcache[i], self.pos, batch, seq, D, self.theta)
             total = self._prefill_base + seq

@@ -429,23 +429,34 @@ def geglu(gate, up, approximate="tanh"):
 # ------------------------------------------------------------------------------------------------
 
 LIB.tpb_attn_prefill.argtypes = [c_void_p] * 5 + [c_int] * 6 + [c_ll] * 12 + [c_int, c_float, c_void_p]
+LIB.tpb_attn_prefill_bias.argtypes = [c_void_p] * 5 + [c_int] * 6 + [c_ll] * 12 + [c_int, c_float, c_void_p, c_int] + [c_ll] * 4 + [c_void_p]
 LIB.tpb_attn_decode.argtypes = [c_void_p] * 7 + [c_int] * 7 + [c_float, c_void_p]
 LIB.tpb_qkv_rope_append.argtypes = [c_void_p] * 7 + [c_int] * 6 + [c_float, c_int, c_int, c_ll, c_ll, c_ll, c_void_p]
 
 
 def attention_supported(q, k, v, bias) -> bool:
-    return (
-        bias is None and q.dtype == torch.bfloat16 and q.shape[-1] in (64, 128) and q.shape[2] % k.shape[2] == 0
-        and q.numel() > 0 and k.numel() > 0
-    )
+    if not (q.dtype == torch.bfloat16 and q.shape[-1] in (64, 128) and q.shape[2] % k.shape[2] == 0 and q.numel() > 0 and k.numel() > 0):
+        return False
+    if bias is None:
+        return True
+    # additive bias: forward only (the backward kernels do not produce a bias gradient and do not re-add the bias)
+    needs_grad = torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad or bias.requires_grad)
+    return (not needs_grad and bias.is_cuda and bias.dtype in (torch.bfloat16, torch.float32) and bias.ndim <= 4
+            and _broadcastable(bias.shape, (q.shape[0], q.shape[2], q.shape[1], k.shape[1])))
+
+
+def _broadcastable(shape, target) -> bool:
+    shape = (1,) * (len(target) - len(shape)) + tuple(shape)
+    return all(s == t or s == 1 for s, t in zip(shape, target))
 
 
 def _strided_ok(t: torch.Tensor) -> bool:
     return t.stride(3) == 1 and all(s % 8 == 0 for s in t.stride()[:3]) and t.data_ptr() % 16 == 0
 
 
-def attention_forward(q, k, v, causal, scale, want_lse=False):
-    """q ``[B,Sq,Hq,D]``, k / v ``[B,Sk,Hkv,D]`` (any strides with contiguous head_dim) -> ``[B,Sq,Hq,D]``."""
+def attention_forward(q, k, v, causal, scale, want_lse=False, bias=None):
+    """q ``[B,Sq,Hq,D]``, k / v ``[B,Sk,Hkv,D]`` (any strides with contiguous head_dim) -> ``[B,Sq,Hq,D]``.
+    ``bias`` (bf16 / fp32, broadcastable to ``[B,Hq,Sq,Sk]``) is added to the scaled scores; ``-inf`` masks a key."""
     global launch_count
     q = q if _strided_ok(q) else q.contiguous()
     k = k if _strided_ok(k) else k.contiguous()
@@ -455,10 +466,19 @@ def attention_forward(q, k, v, causal, scale, want_lse=False):
     out = torch.empty(b, sq, hq, d, dtype=q.dtype, device=q.device)
     lse = torch.empty(b, hq, sq, dtype=torch.float32, device=q.device) if want_lse else None
     scale = 1.0 / math.sqrt(d) if scale is None else scale
-    check(LIB.tpb_attn_prefill(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(lse), b, sq, sk, hq, hkv, d,
-                               q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
-                               v.stride(0), v.stride(1), v.stride(2), out.stride(0), out.stride(1), out.stride(2),
-                               int(causal), scale, _stream()), "tpb_attn_prefill")
+    if bias is None:
+        check(LIB.tpb_attn_prefill(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(lse), b, sq, sk, hq, hkv, d,
+                                   q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
+                                   v.stride(0), v.stride(1), v.stride(2), out.stride(0), out.stride(1), out.stride(2),
+                                   int(causal), scale, _stream()), "tpb_attn_prefill")
+    else:
+        bias4 = bias.reshape((1,) * (4 - bias.ndim) + tuple(bias.shape))
+        strides = [0 if bias4.shape[i] == 1 else bias4.stride(i) for i in range(4)]  # size-1 dimensions broadcast
+        check(LIB.tpb_attn_prefill_bias(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(lse), b, sq, sk, hq, hkv, d,
+                                        q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
+                                        v.stride(0), v.stride(1), v.stride(2), out.stride(0), out.stride(1), out.stride(2),
+                                        int(causal), scale, _ptr(bias4), 1 if bias4.dtype == torch.float32 else 0,
+                                        strides[0], strides[1], strides[2], strides[3], _stream()), "tpb_attn_prefill_bias")
     launch_count += 1
     return out, lse
 
@@ -503,9 +523,9 @@ class _AttentionFn(torch.autograd.Function):
 
 
 def attention(q, k, v, causal, bias=None, scale=None):
-    if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad):
+    if bias is None and torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad):
         return _AttentionFn.apply(q, k, v, bool(causal), scale)
-    return attention_forward(q, k, v, causal, scale)[0]
+    return attention_forward(q, k, v, causal, scale, bias=bias)[0]
 
 
 def attn_decode(q, kcache, vcache, len_ptr, len_add, scale=None, splits=1, workspace=None, out=None):
@@ -527,11 +547,22 @@ def attn_decode(q, kcache, vcache, len_ptr, len_add, scale=None, splits=1, works
     return out
 
 
-LIB.tpb_attn_decode_fused.argtypes = [c_void_p] * 10 + [c_int] * 6 + [c_float, c_int, c_float, c_int, c_ll, c_ll, c_ll, c_void_p]
+LIB.tpb_attn_decode_fused.argtypes = [c_void_p] * 10 + [c_int] * 6 + [c_float, c_int, c_float, c_int, c_ll, c_ll, c_ll, c_void_p, c_void_p]
+LIB.tpb_rope_table.argtypes = [c_void_p, c_int, c_int, c_float, c_void_p]
+
+
+def rope_table(positions: int, rotary_dim: int, theta: float, device) -> torch.Tensor:
+    """fp32 ``[positions, rotary_dim // 2, 2]`` table of (cos, sin) rotary angles for :func:`attn_decode_fused`."""
+    global launch_count
+    table = torch.empty(positions, rotary_dim // 2, 2, dtype=torch.float32, device=device)
+    with torch.cuda.device(device):
+        check(LIB.tpb_rope_table(_ptr(table), positions, rotary_dim, theta, _stream()), "tpb_rope_table")
+    launch_count += 1
+    return table
 
 
 def attn_decode_fused(q, k, v, kcache, vcache, pos_ptr, rotary_dim, theta, interleaved=False, scale=None, splits=1,
-                      workspace=None, out=None):
+                      workspace=None, out=None, rope_angles=None):
     """One decode step of attention in a single launch: rotate q / k of the new token (``q/k/v``: 2-D row views of the
     projection output), append k, v to the cache at ``pos_ptr[0]``, attend over ``[0, pos]`` and merge the key splits.
     ``workspace = (part_o, part_ml, counters)`` with ``counters`` an int32 tensor ``[batch * kv_heads]`` zeroed once."""
@@ -549,7 +580,8 @@ def attn_decode_fused(q, k, v, kcache, vcache, pos_ptr, rotary_dim, theta, inter
     scale = 1.0 / math.sqrt(d) if scale is None else scale
     check(LIB.tpb_attn_decode_fused(_ptr(q), _ptr(k), _ptr(v), _ptr(kcache), _ptr(vcache), _ptr(out), _ptr(part_o), _ptr(part_ml),
                                     _ptr(counters), _ptr(pos_ptr), b, hq, hkv, d, smax, splits, scale, rotary_dim, theta,
-                                    int(interleaved), q.stride(0), k.stride(0), v.stride(0), _stream()), "tpb_attn_decode_fused")
+                                    int(interleaved), q.stride(0), k.stride(0), v.stride(0), _ptr(rope_angles), _stream()),
+          "tpb_attn_decode_fused")
     launch_count += max(1, (hq // hkv) // (4 if d == 128 else 8))
     return out
 

@@ -33,15 +33,64 @@ def _time(fn, iters: int):
     return statistics.median(times)
 
 
+GRAPH = False  # --graph: also time 16 launches replayed from one CUDA graph (device time without host launch gaps)
+
+
+def _graph_time(fn, launches: int = 16, reps: int = 5):
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        for i in range(3):
+            fn(i)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for i in range(launches):
+                fn(i)
+    graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / (launches * reps)
+
+
+def _timed(fn, iters: int) -> dict:
+    out = {"us": _time(fn, iters)}
+    if GRAPH:
+        out["graph_us"] = _graph_time(fn)
+    return out
+
+
+def case_attn_decode_fused(batch, heads, kv_heads, ctx, iters, splits=1):
+    """The serving engine's decode attention: RoPE + cache append + split-KV attention + merge in one launch."""
+    d, smax, ring = 128, ctx + 64, 3
+    ks = [torch.randn(batch, kv_heads, smax, d, device="cuda", dtype=torch.bfloat16) for _ in range(ring)]
+    vs = [torch.randn(batch, kv_heads, smax, d, device="cuda", dtype=torch.bfloat16) for _ in range(ring)]
+    qkv = torch.randn(batch, (heads + 2 * kv_heads) * d, device="cuda", dtype=torch.bfloat16)
+    q, k, v = qkv[:, : heads * d], qkv[:, heads * d : (heads + kv_heads) * d], qkv[:, (heads + kv_heads) * d :]
+    pos = torch.tensor([ctx], device="cuda", dtype=torch.int32)
+    out = torch.empty(batch, heads, d, device="cuda", dtype=torch.bfloat16)
+    ws = (torch.empty(batch * heads * splits * d, device="cuda"), torch.empty(batch * heads * splits * 2, device="cuda"),
+          torch.zeros(batch * kv_heads, dtype=torch.int32, device="cuda"))
+    res = _timed(lambda i: native.attn_decode_fused(q, k, v, ks[i % ring], vs[i % ring], pos, d, 10000.0, splits=splits,
+                                                    workspace=ws, out=out), iters)
+    best = res.get("graph_us", res["us"])
+    return {**res, "tbps": 2.0 * batch * kv_heads * ctx * d * 2 / best / 1e6}
+
+
 def case_gemm(tokens, features, k, iters, ring=None):
     ring = ring or max(2, int(300e6 // (features * k * 2)) + 1)
     ws = [torch.randn(features, k, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(ring)]
     x = torch.randn(tokens, k, device="cuda", dtype=torch.bfloat16)
     out = torch.empty(tokens, features, device="cuda", dtype=torch.bfloat16)
-    us = _time(lambda i: native.gemm_nt(x, ws[i % ring], out=out), iters)
+    res = _timed(lambda i: native.gemm_nt(x, ws[i % ring], out=out), iters)
+    us = res.get("graph_us", res["us"])
     flops = 2.0 * tokens * features * k
     bytes_ = 2.0 * (features * k + tokens * k + tokens * features)
-    return {"us": us, "tflops": flops / us / 1e6, "tbps": bytes_ / us / 1e6, "plan": {f: getattr(native.gemm_plan(tokens, features, k), f) for f in ("swapped", "bn", "kbox", "k_splits", "grid")}}
+    return {**res, "tflops": flops / us / 1e6, "tbps": bytes_ / us / 1e6, "plan": {f: getattr(native.gemm_plan(tokens, features, k), f) for f in ("swapped", "bn", "kbox", "k_splits", "grid")}}
 
 
 def case_attn_decode(batch, heads, kv_heads, ctx, iters, splits=1):
@@ -128,6 +177,8 @@ CASES = {
     "gemm_prefill_gate_up": lambda it: case_gemm(4096, 22016, 4096, it, ring=2),
     "attn_decode": lambda it: case_attn_decode(8, 32, 32, 2048, it),
     "attn_decode_tp8": lambda it: case_attn_decode(8, 4, 4, 2048, it, splits=8),
+    "attn_decode_fused": lambda it: case_attn_decode_fused(8, 32, 32, 2048, it),
+    "attn_decode_fused_tp8": lambda it: case_attn_decode_fused(8, 4, 4, 2048, it, splits=8),
     "attn_prefill": lambda it: case_attn_prefill(4, 2048, 32, 128, it),
     "attn_backward": lambda it: case_attn_backward(4, 2048, 32, 128, it),
     "head_cross_entropy": lambda it: case_cross_entropy(8192, 32000, 4096, it),
@@ -142,7 +193,10 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("case", choices=sorted(CASES) + ["all"])
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--graph", action="store_true", help="also report the per-launch time of a replayed CUDA graph")
     args = ap.parse_args()
+    global GRAPH
+    GRAPH = args.graph
     for name in (sorted(CASES) if args.case == "all" else [args.case]):
         result = CASES[name](args.iters)
         torch.cuda.synchronize()

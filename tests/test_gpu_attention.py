@@ -37,6 +37,36 @@ def test_prefill_attention(b, sq, sk, hq, hkv, d, causal):
     assert torch.isfinite(lse).all()
 
 
+@pytest.mark.parametrize("kind", ["relative_fp32", "padding_bf16", "alibi_causal", "full_bf16"])
+def test_prefill_attention_additive_bias(kind):
+    """Score biases of the model families: T5 relative positions [1,H,Sq,Sk], padding masks [B,1,1,Sk] with -inf,
+    ALiBi slopes [1,H,1,Sk] under a causal mask, and a dense per-batch bias."""
+    nat = _native()
+    torch.manual_seed(3)
+    b, sq, sk, h, d = 2, 150, 150, 4, 64
+    q = torch.randn(b, sq, h, d, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(b, sk, h, d, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(b, sk, h, d, device="cuda", dtype=torch.bfloat16)
+    causal = False
+    if kind == "relative_fp32":
+        bias = torch.randn(1, h, sq, sk, device="cuda")
+    elif kind == "padding_bf16":
+        bias = torch.zeros(b, 1, 1, sk, device="cuda", dtype=torch.bfloat16)
+        bias[0, :, :, 100:] = float("-inf")
+        bias[1, :, :, 37:] = float("-inf")
+    elif kind == "alibi_causal":
+        slopes = torch.tensor([0.5, 0.25, 0.125, 0.0625], device="cuda")
+        bias = (slopes[None, :, None, None] * torch.arange(sk, device="cuda")[None, None, None, :]).to(torch.bfloat16)
+        causal = True
+    else:
+        bias = torch.randn(b, h, sq, sk, device="cuda", dtype=torch.bfloat16)
+    assert nat.attention_supported(q, k, v, bias)
+    out = OF.attention(q, k, v, causal, bias=bias)
+    ref = OF.attention_ref(q.float(), k.float(), v.float(), causal, bias=bias.float())
+    torch.testing.assert_close(out.float(), ref, atol=2e-2, rtol=2e-2)
+    assert not nat.attention_supported(q.requires_grad_(), k, v, bias)  # training with a bias stays on the PyTorch path
+
+
 def test_prefill_attention_reads_cache_layout():
     """k / v handed over as transposed views of a [B, H, S, D] cache (strides, no copy)."""
     nat = _native()
@@ -128,8 +158,8 @@ def test_rope_append_variants(interleaved, rotary_dim):
 
 
 @pytest.mark.parametrize("hq,hkv,d", [(8, 8, 128), (8, 2, 128), (16, 1, 64), (6, 2, 64)])
-@pytest.mark.parametrize("splits", [1, 4])
-def test_fused_decode_step_matches_separate_kernels(hq, hkv, d, splits):
+@pytest.mark.parametrize("splits,angle_table", [(1, False), (4, False), (4, True)])
+def test_fused_decode_step_matches_separate_kernels(hq, hkv, d, splits, angle_table):
     """rope + append + attention + split merge in one launch vs the three stand-alone kernels, two steps in a row."""
     nat = _native()
     torch.manual_seed(5)
@@ -141,6 +171,7 @@ def test_fused_decode_step_matches_separate_kernels(hq, hkv, d, splits):
     kc2, vc2 = kc.clone(), vc.clone()
     pos = torch.tensor([ctx], device="cuda", dtype=torch.int32)
     ws = None
+    angles = nat.rope_table(smax, d, 10000.0, torch.device("cuda", 0)) if angle_table else None  # looked up instead of sincosf
     for step in range(2):
         qkv = torch.randn(b, (hq + 2 * hkv) * d, device="cuda", dtype=torch.bfloat16)
         q2, k2, v2 = qkv[:, : hq * d], qkv[:, hq * d : (hq + hkv) * d], qkv[:, (hq + hkv) * d :]
@@ -150,7 +181,7 @@ def test_fused_decode_step_matches_separate_kernels(hq, hkv, d, splits):
         if ws is None and splits > 1:
             ws = (torch.empty(b * hq * splits * d, device="cuda"), torch.empty(b * hq * splits * 2, device="cuda"),
                   torch.zeros(b * hkv, dtype=torch.int32, device="cuda"))
-        got = nat.attn_decode_fused(q2, k2, v2, kc2, vc2, pos, d, 10000.0, splits=splits, workspace=ws)
+        got = nat.attn_decode_fused(q2, k2, v2, kc2, vc2, pos, d, 10000.0, splits=splits, workspace=ws, rope_angles=angles)
         torch.testing.assert_close(got.float(), want.float(), atol=1e-2, rtol=1e-2)
         torch.testing.assert_close(kc2, kc)
         torch.testing.assert_close(vc2, vc)
