@@ -239,6 +239,19 @@ extern "C" int tpb_collective(int kind, int dtype, int world, int rank, void* co
   return cudaGetLastError() == cudaSuccess ? TPB_OK : TPB_ERR_CUDA;
 }
 
+// Loads every collective kernel on the current device.  With lazy module loading the first launch of a kernel may
+// have to synchronise the device; a host thread that drives several GPUs must not meet that behind a kernel that is
+// waiting for a peer the same thread has yet to launch.
+extern "C" int tpb_comm_preload(void) {
+  cudaFuncAttributes attr;
+  cudaError_t e = cudaSuccess;
+#define LOAD(T, M) if (e == cudaSuccess) e = cudaFuncGetAttributes(&attr, collective_kernel<T, M>)
+  LOAD(__nv_bfloat16, 0); LOAD(__nv_bfloat16, 1); LOAD(__nv_bfloat16, 2); LOAD(__nv_bfloat16, 3);
+  LOAD(float, 0); LOAD(float, 1); LOAD(float, 2); LOAD(float, 3);
+#undef LOAD
+  return e == cudaSuccess ? TPB_OK : TPB_ERR_CUDA;
+}
+
 // Launches a one-thread kernel that waits (bounded by wait_seconds) for *flag >= target and records a
 // timeout in *status.  Used to exercise the give-up path: the kernel always terminates.
 extern "C" int tpb_wait_flag_test(const void* flag, unsigned target, void* status, double wait_seconds, void* stream_) {

@@ -46,6 +46,7 @@ constexpr int NUM_THREADS = 192;
 constexpr int EPI_THREADS = 128;
 constexpr int MAX_WORLD = 8;
 constexpr int LL_FIRST_SLOT = 32;  // first fp32 slot of the flagged-word area (slots below hold plain partials)
+constexpr int LL_TILE_WORDS = 128 * 32;  // 16-byte flagged words owned by one tile: 128 feature rows x up to 32 token pairs
 
 struct GemmParams {
   int m_extent;   // rows of A (lanes side)
@@ -610,21 +611,23 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         }
       };
       // flagged-word variant (swapped orientation only: all tokens sit in one tile): slot k of rank d's flagged area
-      // holds rank k's partial as 16-byte words {value(t), epoch, value(t + 1), epoch} laid out [feature][token pair],
-      // so the thread that owns a feature row moves a whole row with a few wide accesses.  The area starts
-      // LL_FIRST_SLOT slots into the workspace and a flagged slot spans two fp32 slots.
+      // holds rank k's partial as 16-byte words {value(t), epoch, value(t + 1), epoch} laid out
+      // [tile][feature row][token pair], so the thread that owns a feature row moves a whole row with a few wide
+      // accesses.  A tile always owns the same LL_TILE_WORDS words whatever the shape of the call, and its epoch only
+      // grows, so a word left behind by an earlier call (of any shape) can never carry the epoch a later call waits
+      // for.  The area starts LL_FIRST_SLOT slots into the workspace and a flagged slot spans two fp32 slots.
       bool ll_gave_up = false;
       const int ll_pairs = (p.n_extent + 1) >> 1;  // token pairs per feature row
+      const size_t ll_row = size_t(tile) * LL_TILE_WORDS + size_t(row) * ll_pairs;  // first word of this thread's row
       auto push_ll = [&](int n0, const float (&v)[16]) {
         if (!chunk_valid(n0)) return;
 #pragma unroll 1  // (rolled: small code, see read_acc)
         for (int d = 0; d < p.world; ++d) {
-          uint4* row = reinterpret_cast<uint4*>(p.slots[d] + size_t(LL_FIRST_SLOT + 2 * p.rank) * p.slot_stride) +
-                       size_t(m) * ll_pairs + (n0 >> 1);
+          uint4* dst = reinterpret_cast<uint4*>(p.slots[d] + size_t(LL_FIRST_SLOT + 2 * p.rank) * p.slot_stride) + ll_row + (n0 >> 1);
 #pragma unroll
           for (int q = 0; q < 8; ++q) {
             if (n0 + 2 * q >= p.n_extent) break;
-            st_relaxed_sys_v4(row + q, __float_as_uint(v[2 * q]), ll_flag,
+            st_relaxed_sys_v4(dst + q, __float_as_uint(v[2 * q]), ll_flag,
                               n0 + 2 * q + 1 < p.n_extent ? __float_as_uint(v[2 * q + 1]) : 0u, ll_flag);
           }
         }
@@ -659,7 +662,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
 #pragma unroll
               for (int k = 0; k < KH; ++k)
                 if (live && k0 + k < p.world)
-                  a[g][k] = ld_relaxed_sys_v4(area + size_t(k0 + k) * slot_words + size_t(m) * ll_pairs + (n0 >> 1) + q0 + g);
+                  a[g][k] = ld_relaxed_sys_v4(area + size_t(k0 + k) * slot_words + ll_row + (n0 >> 1) + q0 + g);
             }
 #pragma unroll
             for (int g = 0; g < G; ++g) {
@@ -667,7 +670,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
 #pragma unroll
                 for (int k = 0; k < KH; ++k) {
                   if (k0 + k < p.world) {
-                    const uint4 w4 = wait_ll(area + size_t(k0 + k) * slot_words + size_t(m) * ll_pairs + (n0 >> 1) + q0 + g, a[g][k]);
+                    const uint4 w4 = wait_ll(area + size_t(k0 + k) * slot_words + ll_row + (n0 >> 1) + q0 + g, a[g][k]);
                     s0[g] += __uint_as_float(w4.x);
                     s1[g] += __uint_as_float(w4.z);
                   }
@@ -1117,7 +1120,7 @@ static int gemm_impl(const void* x, const void* w, void* out, const void* bias, 
     p.slot_stride = rc->slot_stride;
     p.status = static_cast<uint32_t*>(rc->status);
     if (rc->world > 1 && plan->swapped && act != 5 && rc->ll_epochs && !g_disable_ll && rc->max_slots >= LL_FIRST_SLOT + 2 * rc->world &&
-        rc->world + plan->k_splits <= LL_FIRST_SLOT) {
+        rc->world + plan->k_splits <= LL_FIRST_SLOT && size_t(plan->tiles) * LL_TILE_WORDS <= rc->slot_stride / 2) {
       p.ll = 1;
       p.ll_epochs = static_cast<uint32_t*>(rc->ll_epochs);
     }

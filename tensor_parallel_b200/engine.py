@@ -33,7 +33,7 @@ def _unwrap(module):
 
 
 class LlamaEngine:
-    def __init__(self, shard, comm=None, max_batch: int = 8, max_seq: int = 2560, use_graph: bool = True):
+    def __init__(self, shard, comm=None, max_batch: int = 8, max_seq: int = 2560, use_graph: bool = True, embed_table=None):
         lm = _unwrap(shard)
         cfg = lm.config
         self.comm = comm
@@ -52,7 +52,7 @@ class LlamaEngine:
         dev = self.device
 
         # full embedding table (hidden-split shards are gathered once; 2 * vocab * hidden bytes per rank)
-        table = embed.weight.detach()
+        table = embed.weight.detach() if embed_table is None else embed_table
         if table.shape[1] != self.hidden:
             import torch.distributed as dist
 
@@ -112,6 +112,32 @@ class LlamaEngine:
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.graph_batch = 0
         self.kernels_per_step = 0
+
+    @torch.no_grad()
+    def preload(self, batch: int = 1):
+        """Runs the prefill and decode paths once on this rank ALONE (no peer involved; the results are meaningless
+        for a shard) so that every kernel they launch - ours and PyTorch's - is loaded on this device.  A single host
+        thread that drives several GPUs calls this first: with lazy module loading the first launch of a kernel may
+        synchronise the device, which must not happen behind a kernel that waits for a peer not launched yet."""
+        comm, world = self.comm, self.world
+        self.comm, self.world = None, 1
+        try:
+            for seq in (8, 72):  # few-token and many-token GEMM orientations
+                self.prefill(torch.zeros(batch, min(seq, self.max_seq - 2), dtype=torch.int64, device=self.device))
+            for _ in range(2):
+                self._decode_body(batch)
+            # the PyTorch kernels that only the multi-rank path uses (strided copies, in-place add)
+            t = self.x[:batch]
+            t.add_(t)
+            g = self.logits_local[:batch, : max(8, self.vocab_local // 2)].contiguous()
+            torch.stack([g, g]).permute(1, 0, 2).reshape(batch, -1).float().argmax(-1)
+            self.pos.zero_()
+            self.ids.zero_()
+            torch.cuda.synchronize(self.device)
+        finally:
+            self.comm, self.world = comm, world
+        if comm is not None:
+            native.check(native.LIB.tpb_comm_preload(), "tpb_comm_preload")
 
     # -- building blocks --------------------------------------------------------------------------
 
@@ -212,23 +238,43 @@ class LlamaEngine:
             self._decode_body(batch)
             return
         if self.graph is None or self.graph_batch != batch:
-            saved_pos, saved_ids = self.pos.clone(), self.ids.clone()
-            stream = torch.cuda.Stream(device=self.device)
-            stream.wait_stream(torch.cuda.current_stream(self.device))
-            with torch.cuda.stream(stream):
-                for _ in range(2):  # warm-up outside capture (allocations, plan cache, smem attributes)
-                    self._decode_body(batch)
-            torch.cuda.current_stream(self.device).wait_stream(stream)
+            state = self._graph_warmup(batch)
             torch.cuda.synchronize(self.device)
-            if self.comm is not None and (self.comm._call & 1):
-                self.comm._call += 1  # keep the workspace alternation phase identical on every replay
-            self.graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(self.graph):
-                self._decode_body(batch)
-            self.graph_batch = batch
-            self.pos.copy_(saved_pos)
-            self.ids.copy_(saved_ids)
+            self._graph_capture(batch, state)
         self.graph.replay()
+
+    # The capture is split in two so that a single host thread can drive several ranks: warm every rank up (the
+    # warm-up steps really run and wait for their peers), synchronise all devices, then capture every rank.
+    def _graph_warmup(self, batch: int):
+        state = (self.pos.clone(), self.ids.clone())
+        stream = torch.cuda.Stream(device=self.device)
+        stream.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(stream):
+            for _ in range(2):  # warm-up outside capture (allocations, plan cache, smem attributes)
+                self._decode_body(batch)
+        torch.cuda.current_stream(self.device).wait_stream(stream)
+        return state
+
+    def _graph_capture(self, batch: int, state):
+        if self.comm is not None and (self.comm._call & 1):
+            self.comm._call += 1  # keep the workspace alternation phase identical on every replay
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self._decode_body(batch)
+        self.graph_batch = batch
+        self.pos.copy_(state[0])
+        self.ids.copy_(state[1])
+
+    def step_from_host(self, token_ids_host: torch.Tensor, out_host: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """One decode step driven from the host: pinned int64 ``[batch]`` ids in, next ids out (pinned)."""
+        batch = token_ids_host.shape[0]
+        self.ids[:batch].copy_(token_ids_host, non_blocking=True)
+        self.decode_step(batch)
+        if out_host is None:
+            out_host = torch.empty(batch, dtype=torch.int64).pin_memory()
+        out_host.copy_(self.next_ids[:batch], non_blocking=True)
+        torch.cuda.current_stream(self.device).synchronize()
+        return out_host
 
     @torch.no_grad()
     def generate(self, input_ids: torch.Tensor, max_new_tokens: int) -> torch.Tensor:
@@ -242,3 +288,82 @@ class LlamaEngine:
             self.decode_step(batch)
             out.append(self.next_ids[:batch].clone())
         return torch.cat([input_ids.to(self.device), torch.stack(out, dim=1)], dim=1)
+
+
+class EngineGroup:
+    """The engines of all ranks of a single-process model (one shard per GPU, all driven by the calling thread).
+
+    Every call enqueues the rank's work on that rank's GPU and moves on: the fused GEMM + all-reduce kernels and the
+    device collectives wait (bounded) for their peers on the GPU, never on the host, so one thread can feed all GPUs.
+    The only host synchronisation points are the ones the caller asks for (reading a result).
+
+    The decode step is launched kernel by kernel here, not replayed from CUDA graphs: when one thread replayed rank 0's
+    graph and then rank 1's, rank 1's graph did not start before rank 0's had run to its end (every peer wait of rank 0
+    hit its time limit; measured on two B200s), whereas eager launches of the same kernels in the same order overlap
+    as expected.  One process per GPU (:class:`LlamaEngine` with a graph per process) remains the fast path."""
+
+    def __init__(self, shards, comms, max_batch: int = 8, max_seq: int = 2560):
+        tables = [_unwrap(_unwrap(_unwrap(s).model).embed_tokens).weight.detach() for s in shards]
+        hidden = _unwrap(shards[0]).config.hidden_size
+        self.engines: List[LlamaEngine] = []
+        for shard, comm, own in zip(shards, comms, tables):
+            table = own
+            if own.shape[1] != hidden:  # hidden-split embedding: every rank keeps a full copy for the lookup kernel
+                table = torch.cat([t.to(own.device) for t in tables], dim=1).contiguous()
+            with torch.cuda.device(own.device):
+                engine = LlamaEngine(shard, comm, max_batch=max_batch, max_seq=max_seq, use_graph=False, embed_table=table)
+                engine.preload()
+                self.engines.append(engine)
+        first = self.engines[0]
+        self.max_batch, self.max_seq, self.world, self.device = first.max_batch, first.max_seq, len(self.engines), first.device
+        self.comm = first.comm
+
+    @property
+    def graph(self):
+        return self.engines[0].graph
+
+    @property
+    def kernels_per_step(self):
+        return self.engines[0].kernels_per_step
+
+    def _each(self, fn):
+        out = []
+        for e in self.engines:
+            with torch.cuda.device(e.device):
+                out.append(fn(e))
+        return out
+
+    @torch.no_grad()
+    def prefill(self, input_ids: torch.Tensor, base: int = 0) -> torch.Tensor:
+        ids = input_ids.cpu().pin_memory() if not input_ids.is_cuda else input_ids
+        return self._each(lambda e: e.prefill(ids, base))[0]
+
+    @torch.no_grad()
+    def decode_step(self, batch: int):
+        self._each(lambda e: e._decode_body(batch))
+
+    @torch.no_grad()
+    def generate(self, input_ids: torch.Tensor, max_new_tokens: int) -> torch.Tensor:
+        batch = input_ids.shape[0]
+        ids = input_ids.cpu().pin_memory() if not input_ids.is_cuda else input_ids
+        firsts = self._each(lambda e: e.prefill(ids).argmax(-1))  # every rank holds the same gathered logits
+        for e, f in zip(self.engines, firsts):
+            e.ids[:batch].copy_(f)
+        out = [firsts[0]]
+        lead = self.engines[0]
+        for _ in range(max_new_tokens - 1):
+            self.decode_step(batch)
+            out.append(lead.next_ids[:batch].clone())
+        return torch.cat([input_ids.to(lead.device), torch.stack(out, dim=1)], dim=1)
+
+    def step_from_host(self, token_ids_host: torch.Tensor, out_host: Optional[torch.Tensor] = None) -> torch.Tensor:
+        batch = token_ids_host.shape[0]
+        for e in self.engines:
+            e.ids[:batch].copy_(token_ids_host, non_blocking=True)
+        self.decode_step(batch)
+        lead = self.engines[0]
+        if out_host is None:
+            out_host = torch.empty(batch, dtype=torch.int64).pin_memory()
+        out_host.copy_(lead.next_ids[:batch], non_blocking=True)
+        torch.cuda.current_stream(lead.device).synchronize()
+        return out_host

@@ -21,8 +21,6 @@ class ServingMixin:
 
     def serving_engine(self, max_batch: int = 8, max_seq: int = 2560):
         """The kernel-level engine of this model, or ``None`` when it does not apply."""
-        if len(self.module_shards) != 1:
-            return None
         shard = self.module_shards[0]
         inner = shard.__dict__.get("tp_wrapped_module", shard)
         cfg = getattr(inner, "config", None)
@@ -32,15 +30,26 @@ class ServingMixin:
         if type(inner).__module__ != "tensor_parallel_b200.models.llama":
             return None
         world = getattr(self, "world_size", 1)
+        eng = self._engine
+        fits = eng is not None and eng.max_batch >= max_batch and eng.max_seq >= max_seq
+        if eng is not None and not fits:
+            max_batch, max_seq = max(max_batch, eng.max_batch), max(max_seq, eng.max_seq)
+        if len(self.module_shards) > 1:
+            # single process, one shard per GPU: one engine per rank on the shared symmetric heaps, one driving thread
+            comms = getattr(getattr(self, "_device_backend", None), "comms", None)
+            if comms is None or len(comms) != len(self.module_shards):
+                return None
+            if not fits:
+                from tensor_parallel_b200.engine import EngineGroup
+
+                self._engine = eng = EngineGroup(list(self.module_shards), comms, max_batch=max_batch, max_seq=max_seq)
+            return eng
         comm = self._engine_comm()
         if world > 1 and comm is None:
             return None
-        eng = self._engine
-        if eng is None or eng.max_batch < max_batch or eng.max_seq < max_seq:
+        if not fits:
             from tensor_parallel_b200.engine import LlamaEngine
 
-            if eng is not None:
-                max_batch, max_seq = max(max_batch, eng.max_batch), max(max_seq, eng.max_seq)
             self._engine = eng = LlamaEngine(shard, comm if world > 1 else None, max_batch=max_batch, max_seq=max_seq)
         return eng
 
@@ -70,11 +79,4 @@ class ServingMixin:
         engine = self._engine
         if engine is None:
             raise RuntimeError("call prefill() first")
-        batch = token_ids_host.shape[0]
-        engine.ids[:batch].copy_(token_ids_host, non_blocking=True)
-        engine.decode_step(batch)
-        if out_host is None:
-            out_host = torch.empty(batch, dtype=torch.int64).pin_memory()
-        out_host.copy_(engine.next_ids[:batch], non_blocking=True)
-        torch.cuda.current_stream(engine.device).synchronize()
-        return out_host
+        return engine.step_from_host(token_ids_host, out_host)
