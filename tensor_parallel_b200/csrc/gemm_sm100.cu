@@ -612,22 +612,22 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       };
       // flagged-word variant (swapped orientation only: all tokens sit in one tile): slot k of rank d's flagged area
       // holds rank k's partial as 16-byte words {value(t), epoch, value(t + 1), epoch} laid out
-      // [tile][feature row][token pair], so the thread that owns a feature row moves a whole row with a few wide
-      // accesses.  A tile always owns the same LL_TILE_WORDS words whatever the shape of the call, and its epoch only
+      // [tile][token pair][feature row]: the 32 lanes of a warp touch 512 contiguous bytes per access (whole sectors;
+      // a [row][pair] order was measured 2x slower at 8 ranks because every lane then touches its own sector).
+      // A tile always owns the same LL_TILE_WORDS words whatever the shape of the call, and its epoch only
       // grows, so a word left behind by an earlier call (of any shape) can never carry the epoch a later call waits
       // for.  The area starts LL_FIRST_SLOT slots into the workspace and a flagged slot spans two fp32 slots.
       bool ll_gave_up = false;
-      const int ll_pairs = (p.n_extent + 1) >> 1;  // token pairs per feature row
-      const size_t ll_row = size_t(tile) * LL_TILE_WORDS + size_t(row) * ll_pairs;  // first word of this thread's row
+      const size_t ll_row = size_t(tile) * LL_TILE_WORDS + size_t(row);  // this thread's word of token pair 0; pair q is 128 q words on
       auto push_ll = [&](int n0, const float (&v)[16]) {
         if (!chunk_valid(n0)) return;
 #pragma unroll 1  // (rolled: small code, see read_acc)
         for (int d = 0; d < p.world; ++d) {
-          uint4* dst = reinterpret_cast<uint4*>(p.slots[d] + size_t(LL_FIRST_SLOT + 2 * p.rank) * p.slot_stride) + ll_row + (n0 >> 1);
+          uint4* dst = reinterpret_cast<uint4*>(p.slots[d] + size_t(LL_FIRST_SLOT + 2 * p.rank) * p.slot_stride) + ll_row + size_t(n0 >> 1) * BM;
 #pragma unroll
           for (int q = 0; q < 8; ++q) {
             if (n0 + 2 * q >= p.n_extent) break;
-            st_relaxed_sys_v4(dst + q, __float_as_uint(v[2 * q]), ll_flag,
+            st_relaxed_sys_v4(dst + q * BM, __float_as_uint(v[2 * q]), ll_flag,
                               n0 + 2 * q + 1 < p.n_extent ? __float_as_uint(v[2 * q + 1]) : 0u, ll_flag);
           }
         }
@@ -662,7 +662,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
 #pragma unroll
               for (int k = 0; k < KH; ++k)
                 if (live && k0 + k < p.world)
-                  a[g][k] = ld_relaxed_sys_v4(area + size_t(k0 + k) * slot_words + ll_row + (n0 >> 1) + q0 + g);
+                  a[g][k] = ld_relaxed_sys_v4(area + size_t(k0 + k) * slot_words + ll_row + size_t((n0 >> 1) + q0 + g) * BM);
             }
 #pragma unroll
             for (int g = 0; g < G; ++g) {
@@ -670,7 +670,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
 #pragma unroll
                 for (int k = 0; k < KH; ++k) {
                   if (k0 + k < p.world) {
-                    const uint4 w4 = wait_ll(area + size_t(k0 + k) * slot_words + ll_row + (n0 >> 1) + q0 + g, a[g][k]);
+                    const uint4 w4 = wait_ll(area + size_t(k0 + k) * slot_words + ll_row + size_t((n0 >> 1) + q0 + g) * BM, a[g][k]);
                     s0[g] += __uint_as_float(w4.x);
                     s1[g] += __uint_as_float(w4.z);
                   }
@@ -966,8 +966,8 @@ extern "C" int tpb_gemm_debug(int stages, int skip_mma) {
 // Measurement aid: CTA `block` (>= 0) of every following GEMM launch records %globaltimer stamps of its phases
 // (block < 0 switches it off).  tpb_gemm_trace_read copies the 32 stamps of the current device to the host
 // (synchronous; call it after synchronising the stream).
-// The cross-rank sum of small problems exchanges flagged words by default; a non-zero argument makes every
-// following launch use the arrival-counter protocol instead (comparison / fallback).
+// The cross-rank sum of few-token problems exchanges flagged words by default when there are at most 4 ranks.
+// disable > 0: every following launch uses the arrival-counter protocol; disable < 0: flagged words at any rank count.
 extern "C" int tpb_gemm_disable_flagged_exchange(int disable) {
   g_disable_ll = disable;
   return TPB_OK;
@@ -1119,7 +1119,10 @@ static int gemm_impl(const void* x, const void* w, void* out, const void* bias, 
     p.split_counters = static_cast<uint32_t*>(rc->split_counters);
     p.slot_stride = rc->slot_stride;
     p.status = static_cast<uint32_t*>(rc->status);
-    if (rc->world > 1 && plan->swapped && act != 5 && rc->ll_epochs && !g_disable_ll && rc->max_slots >= LL_FIRST_SLOT + 2 * rc->world &&
+    // default: up to 4 ranks.  At 8 ranks the arrival-counter protocol measured faster (15.8 vs 17.6 us for the o_proj
+    // shard of a Llama-2-7B layer): a thread then polls 8 x tokens flagged words, which costs more than one fence.
+    const bool ll_wanted = g_disable_ll < 0 || (g_disable_ll == 0 && rc->world <= 4);
+    if (rc->world > 1 && plan->swapped && act != 5 && rc->ll_epochs && ll_wanted && rc->max_slots >= LL_FIRST_SLOT + 2 * rc->world &&
         rc->world + plan->k_splits <= LL_FIRST_SLOT && size_t(plan->tiles) * LL_TILE_WORDS <= rc->slot_stride / 2) {
       p.ll = 1;
       p.ll_epochs = static_cast<uint32_t*>(rc->ll_epochs);
