@@ -148,7 +148,7 @@ norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ residual, const T
 
 // Backward: dx per row; dweight / dbias accumulated with fp32 atomics into zero-initialised buffers.
 // Each CTA handles ROWS_PER_CTA consecutive rows and keeps its column partial sums in registers.
-constexpr int NORM_BWD_MAXV = 4;  // cols <= 8192 in the backward kernel (register budget)
+constexpr int NORM_BWD_MAXV = 4;  // cols <= 8192 in the backward kernel (register limit)
 
 template <typename T, int MODE>
 __global__ void __launch_bounds__(NORM_THREADS)

@@ -5,7 +5,7 @@
 //   * serving processes that hand the whole GPU to their KV cache at start-up, so that any later
 //     cudaMalloc simply fails;
 //   * hosts that embed this library behind a plain C interface and own every buffer themselves (another
-//     framework's allocator, a memory pool with a fixed budget), where a hidden allocation would escape
+//     framework's allocator, a memory pool of fixed size), where a hidden allocation would escape
 //     their accounting;
 //   * latency-critical loops that cannot afford the implicit device-wide synchronisation of cudaMalloc /
 //     cudaFree between two kernels.

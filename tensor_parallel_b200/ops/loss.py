@@ -1,7 +1,7 @@
 """Vocab-parallel lm_head fused with a distributed cross-entropy.
 
 The reference gathers (or all-reduces) full ``[tokens, vocab]`` logits onto every rank and computes the
-loss redundantly (``src/tensor_parallel/slicing_configs.py:381,390``; SURVEY "Q12").  Here every rank
+loss redundantly (``src/tensor_parallel/slicing_configs.py:381,390``).  Here every rank
 multiplies the hidden states with its vocabulary slice of the head on the tcgen05 GEMM, reduces each row
 of its local logits to four numbers (max, sum-exp, target logit, ownership flag), exchanges only those
 ``[tokens, 4]`` floats, and turns the local logits in place into their gradient.  Every rank returns its own share

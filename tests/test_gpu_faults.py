@@ -1,5 +1,5 @@
 """Device-side failure detection without faulting the GPU: a kernel that waits for a flag nobody sets
-gives up after its time budget, records a status code and terminates normally; the host turns the
+gives up after its time limit, records a status code and terminates normally; the host turns the
 status into an exception and the context stays usable."""
 import pytest
 import torch
