@@ -9,20 +9,31 @@
 // ("swapped"), so the tensor core still sees full 128-row tiles and weights stream through TMA once.
 // In both cases results are stored as out[token, feature].
 //
-// Structure of one CTA (192 threads), persistent over work items (m_tile, n_tile, k_split):
+// Structure of one CTA (192 threads), persistent over work items (tile, k range; see WorkIter):
 //   warp 0   : TMA producer  - cp.async.bulk.tensor loads of A/B k-blocks into a smem ring (no multicast)
 //   warp 1   : MMA issuer    - one elected lane issues tcgen05.mma (K = 16 per instruction) into TMEM;
 //                              tcgen05.commit releases smem stages and publishes finished accumulators
 //   warps 2-5: epilogue      - tcgen05.ld the accumulator (two TMEM buffers, so the next tile's MMAs
-//                              overlap this tile's epilogue), then either
-//                                (direct)  add bias / residual, convert to bf16, store; or
-//                                (reduce)  store the fp32 partial tile into slot [rank * k_splits + split]
-//                                          of EVERY rank's workspace with plain peer stores, then bump
-//                                          that tile's arrival counter on every rank (release, system scope).
-//   Reduce mode, second phase (all warps): for each output tile this CTA owns, wait (bounded) until
-//   world * k_splits partials have arrived, sum them in a fixed order (bit-identical on all ranks),
-//   add bias / residual and store bf16.  All of a CTA's pushes precede its first wait, and the grid is
-//   never larger than what is co-resident, so ranks cannot deadlock each other.
+//                              overlap this tile's epilogue), then
+//                                (whole tile, one rank)   bias / activation / residual, bf16 store;
+//                                (split-K / stream-K)     park the fp32 partial in a local slot; the LAST contributor of
+//                                                         the tile to arrive sums the partials in slot order and carries
+//                                                         on (nobody waits for another CTA);
+//                                (several ranks)          push the tile's partial to every rank with plain peer stores
+//                                                         and sum the ranks' partials in rank order (bit-identical
+//                                                         everywhere).  Two exchange protocols:
+//                                   flagged words     - few-token tiles, up to 4 ranks: every value travels inside a
+//                                                       16-byte {value, epoch, value, epoch} word and the thread that owns
+//                                                       the feature row polls the words in its own memory right away;
+//                                                       no fence, no counter;
+//                                   arrival counters  - one system-scope fence per tile, a relaxed add on every rank's
+//                                                       per-tile counter, and a second phase (all warps, after the CTA
+//                                                       has pushed all of its tiles) that waits (bounded) for the tiles
+//                                                       it owns.  All of a CTA's pushes precede its first wait and the
+//                                                       grid is never larger than what is co-resident, so ranks cannot
+//                                                       deadlock each other.
+//   Consecutive fused calls alternate between two workspace halves; a rank can run at most one call ahead of a peer
+//   (its next call needs that peer's partial), so a half is never overwritten while a peer still reads it.
 //
 // Every wait is bounded; on expiry the CTA records a status code in params.status and drains.
 #include <cuda.h>
