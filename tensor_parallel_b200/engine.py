@@ -26,6 +26,7 @@ from typing import List, Optional
 import torch
 
 from tensor_parallel_b200.ops import native
+from tensor_parallel_b200.utils.tracing import traced
 
 
 def _unwrap(module):
@@ -188,6 +189,7 @@ class LlamaEngine:
 
     # -- prefill ----------------------------------------------------------------------------------
 
+    @traced("tpb.engine.prefill")
     @torch.no_grad()
     def prefill(self, input_ids: torch.Tensor, base: int = 0) -> torch.Tensor:
         """Run ``input_ids [batch, seq]`` through the model, fill the cache from position ``base`` and
@@ -230,6 +232,7 @@ class LlamaEngine:
         self.pos.add_(1)
         self.kernels_per_step = native.launch_count - before
 
+    @traced("tpb.engine.decode_step")
     @torch.no_grad()
     def decode_step(self, batch: int):
         """One greedy token for every sequence: consumes ``self.ids``, leaves the new ids in ``self.ids``

@@ -26,6 +26,7 @@ import torch
 import torch.distributed as dist
 
 from tensor_parallel_b200.ops import native
+from tensor_parallel_b200.utils.tracing import traced
 from tensor_parallel_b200.ops.native import LIB, ReduceCtx, c_int, c_ll, c_void_p, check
 
 logger = logging.getLogger(__name__)
@@ -71,6 +72,10 @@ def _align(n: int, a: int = 1024) -> int:
     return (n + a - 1) // a * a
 
 
+GUARD_BYTES = 4096   # (a multiple of the 1024-byte area alignment)
+GUARD_PATTERN = 0xA5
+
+
 class HeapLayout:
     def __init__(self, slot_stride: int, max_slots: int, staging_bytes: int, gather_bytes: int = 96 << 20):
         self.slot_stride, self.max_slots, self.staging_bytes = slot_stride, max_slots, staging_bytes
@@ -78,12 +83,16 @@ class HeapLayout:
         self.off_signals = 0
         self.off_ag_flags = SIGNAL_BYTES  # uint32 [2 regions][MAX_WORLD] arrival words of the fused all-gather
         self.off_arrivals = _align(SIGNAL_BYTES + 2 * MAX_WORLD * 4)
-        self.off_slots = self.off_arrivals + _align(2 * MAX_TILES * 4)
+        # every area below is followed by a guard band holding a fixed byte pattern; a kernel that writes past the end
+        # of its area (on this GPU or through a peer mapping) shows up in RankComm.check_guards()
+        g = GUARD_BYTES
+        self.off_slots = self.off_arrivals + _align(2 * MAX_TILES * 4) + g
         self.region_slot_bytes = _align(max_slots * slot_stride * 4)
-        self.off_staging_in = self.off_slots + 2 * self.region_slot_bytes
-        self.off_staging_out = self.off_staging_in + _align(staging_bytes)
-        self.off_gather = self.off_staging_out + _align(staging_bytes)  # two gathered-operand buffers
-        self.total = self.off_gather + 2 * _align(gather_bytes)
+        self.off_staging_in = self.off_slots + 2 * self.region_slot_bytes + g
+        self.off_staging_out = self.off_staging_in + _align(staging_bytes) + g
+        self.off_gather = self.off_staging_out + _align(staging_bytes) + g  # two gathered-operand buffers
+        self.total = self.off_gather + 2 * _align(gather_bytes) + g
+        self.guards = [self.off_slots - g, self.off_staging_in - g, self.off_staging_out - g, self.off_gather - g, self.total - g]
 
 
 class RankComm:
@@ -101,6 +110,8 @@ class RankComm:
         self.local = tensor_from_ptr(self.base[rank], layout.total, device)
         self.staging_in = self.local[layout.off_staging_in : layout.off_staging_in + layout.staging_bytes]
         self.staging_out = self.local[layout.off_staging_out : layout.off_staging_out + layout.staging_bytes]
+        for off in layout.guards:
+            self.local[off : off + GUARD_BYTES].fill_(GUARD_PATTERN)
         self._call = 0
         self._ctxs = [self._make_ctx(0), self._make_ctx(1)]
         self._ptr_arrays: Dict[str, ctypes.Array] = {}
@@ -137,6 +148,7 @@ class RankComm:
         self._call += 1
         return ctx
 
+    @traced("tpb.gemm_allreduce")
     def gemm_allreduce(self, x2d, weight, bias=None, residual=None, out=None, bias_scale: float = 1.0):
         """``sum over ranks of (x2d @ weight.T) + bias_scale * bias + residual`` in ONE kernel: partial tiles are
         pushed to every peer from the GEMM epilogue and reduced as they arrive."""
@@ -154,6 +166,7 @@ class RankComm:
 
     # -- fused all-gather + GEMM ------------------------------------------------------------------
 
+    @traced("tpb.allgather_gemm")
     def allgather_gemm(self, x_local: torch.Tensor, weight: torch.Tensor, bias=None, act=None, out=None):
         """``concat_over_ranks(x_local, dim=1) @ weight.T`` in ONE kernel: every rank pushes its column slice
         ``x_local [tokens, k / world]`` into all peers' gathered buffers from the kernel's prologue, and the GEMM
@@ -213,6 +226,7 @@ class RankComm:
             raise ValueError(f"collective payload of {nbytes} bytes exceeds the staging buffer ({buf.numel()} bytes)")
         return buf[:nbytes].view(dtype).view(shape)
 
+    @traced("tpb.all_reduce")
     def all_reduce(self, x: torch.Tensor, force_algo: int = -1) -> torch.Tensor:
         """Sum over ranks.  ``x`` is copied into symmetric memory unless it already is the staging-in view."""
         dtype = x.dtype if x.dtype in (torch.bfloat16, torch.float32) else torch.float32
@@ -233,6 +247,7 @@ class RankComm:
         self._collective(0, dtype, n_pad, force_algo)
         return self.staging_view("out", (n_pad,), dtype)[:n].view(x.shape)
 
+    @traced("tpb.all_gather")
     def all_gather(self, x: torch.Tensor) -> torch.Tensor:
         """Returns ``[world, *x.shape]`` (every rank's ``x``); all ranks must pass the same shape."""
         dtype = x.dtype if x.dtype in (torch.bfloat16, torch.float32) else torch.float32
@@ -251,6 +266,7 @@ class RankComm:
         self._collective(2, dtype, n_pad)
         return self.staging_view("out", (self.world, n_pad), dtype)[:, :n].reshape(self.world, *x.shape)
 
+    @traced("tpb.reduce_scatter")
     def reduce_scatter(self, x: torch.Tensor) -> torch.Tensor:
         """``x`` is ``[world, ...]``; returns the sum over ranks of ``x[rank]``."""
         dtype = x.dtype if x.dtype in (torch.bfloat16, torch.float32) else torch.float32
@@ -269,6 +285,13 @@ class RankComm:
             src.copy_(x.reshape(-1))
         self._collective(3, dtype, n)
         return self.staging_view("out", (n,), dtype).view(x.shape[1:])
+
+    def check_guards(self):
+        """Raises if any guard band of this rank's heap region has been written to (synchronises the device)."""
+        for i, off in enumerate(self.layout.guards):
+            band = self.local[off : off + GUARD_BYTES]
+            if not bool((band == GUARD_PATTERN).all().item()):
+                raise RuntimeError(f"guard band {i} of rank {self.rank}'s symmetric heap was overwritten")
 
     def check_status(self):
         code = int(self.status[0].item())

@@ -1,0 +1,134 @@
+"""Executable host-side model of the flagged-word exchange that the fused GEMM + all-reduce kernel uses for few-token
+tiles (``csrc/gemm_sm100.cu``), so that the protocol itself can be exercised by CPU threads standing in for ranks.
+
+What is modelled, word for word:
+
+* every rank owns two workspace halves; consecutive calls alternate between them;
+* half ``h`` of rank ``d`` holds one slot per source rank; a slot is an array of 16-byte words
+  ``(value(t), flag, value(t + 1), flag)`` addressed ``tile * TILE_WORDS + pair * ROWS + row``
+  (or, with ``tile_keyed=False``, the shape-dependent ``(tile * ROWS + row) * pairs + pair`` order that an earlier
+  version of the kernel used and that this model shows to be unsafe when shapes are interleaved);
+* a call on tile ``t`` uses flag ``epoch[h][t] + 1`` and stores it back; epochs live with the rank and only grow;
+* the sender stores its words into every rank's slot (in any order, a word at a time); the receiver polls the words of
+  its own tile and accepts a word when both flags equal the flag it expects; values are summed in rank order.
+
+The two halves are enough because a rank can run at most one call ahead of a peer: its call ``i + 1`` cannot complete
+before that peer has pushed its own call ``i + 1``, which the peer does only after it has finished reading call ``i``.
+"""
+from __future__ import annotations
+
+import random
+import threading
+import time
+from typing import Dict, List, Sequence, Tuple
+
+ROWS = 128                    # feature rows per tile
+TILE_WORDS = ROWS * 32        # words one tile owns (up to 32 token pairs)
+
+
+class Heap:
+    """Flagged areas of all ranks: ``mem[dest][half][src]`` maps a word index to ``(v0, f0, v1, f1)``."""
+
+    def __init__(self, world: int):
+        self.world = world
+        self.mem: List[List[List[Dict[int, Tuple[float, int, float, int]]]]] = [
+            [[dict() for _ in range(world)] for _ in range(2)] for _ in range(world)
+        ]
+
+
+def _word_index(tile: int, row: int, pair: int, pairs: int, tile_keyed: bool) -> int:
+    if tile_keyed:
+        return tile * TILE_WORDS + pair * ROWS + row
+    return (tile * ROWS + row) * pairs + pair
+
+
+class Rank:
+    def __init__(self, heap: Heap, rank: int, tile_keyed: bool = True, jitter: float = 0.0, seed: int = 0):
+        self.heap, self.rank, self.tile_keyed = heap, rank, tile_keyed
+        self.epochs: List[Dict[int, int]] = [dict(), dict()]
+        self.calls = 0
+        self.rng = random.Random(seed * 7919 + rank)
+        self.jitter = jitter
+
+    def _pause(self):
+        if self.jitter:
+            time.sleep(self.rng.random() * self.jitter)
+
+    def all_reduce(self, partial: Sequence[Sequence[float]], features: int, timeout: float = 5.0) -> List[List[float]]:
+        """``partial[token][feature]`` of this rank; returns the sum over ranks (every rank gets the same lists)."""
+        tokens = len(partial)
+        pairs = (tokens + 1) // 2
+        half = self.calls & 1
+        self.calls += 1
+        tiles = (features + ROWS - 1) // ROWS
+        flags = {}
+        for t in range(tiles):
+            flags[t] = self.epochs[half].get(t, 0) + 1
+        # push: every word of every tile to every rank (own memory included), word by word
+        words = [(t, r, p) for t in range(tiles) for r in range(min(ROWS, features - t * ROWS)) for p in range(pairs)]
+        self.rng.shuffle(words)
+        for n, (t, r, p) in enumerate(words):
+            f = t * ROWS + r
+            v0 = partial[2 * p][f]
+            v1 = partial[2 * p + 1][f] if 2 * p + 1 < tokens else 0.0
+            idx = _word_index(t, r, p, pairs, self.tile_keyed)
+            for dest in range(self.heap.world):
+                self.heap.mem[dest][half][self.rank][idx] = (v0, flags[t], v1, flags[t])
+            if n % 64 == 0:
+                self._pause()
+        for t in range(tiles):
+            self.epochs[half][t] = flags[t]
+        # poll and reduce in rank order
+        out = [[0.0] * features for _ in range(tokens)]
+        deadline = time.monotonic() + timeout
+        for (t, r, p) in sorted(words, key=lambda w: (-w[0], w[1], w[2])):  # (tiles are polled concurrently on the GPU; any order is legal)
+            f = t * ROWS + r
+            idx = _word_index(t, r, p, pairs, self.tile_keyed)
+            for src in range(self.heap.world):
+                while True:
+                    w = self.heap.mem[self.rank][half][src].get(idx)
+                    if w is not None and w[1] == flags[t] and w[3] == flags[t]:
+                        break
+                    if time.monotonic() > deadline:
+                        raise TimeoutError(f"rank {self.rank}: word {idx} of rank {src} never arrived")
+                    time.sleep(0)
+                out[2 * p][f] += w[0]
+                if 2 * p + 1 < tokens:
+                    out[2 * p + 1][f] += w[2]
+        return out
+
+
+def run_ranks(world: int, calls: Sequence[Tuple[int, int]], tile_keyed: bool = True, jitter: float = 0.0, seed: int = 0,
+              late: Dict[Tuple[int, int], float] = None):
+    """Runs ``calls`` = [(tokens, features), ...] on ``world`` threads.  Rank ``k`` contributes ``(k + 1) * (1 + call +
+    token / 16 + feature / 4096)``; returns, per call, the largest absolute error of any rank's result.
+    ``late[(rank, call)]`` = seconds that rank sleeps before it starts that call (a straggler)."""
+    heap = Heap(world)
+    errors: List[List[float]] = [[] for _ in range(world)]
+    failures: List[BaseException] = []
+
+    def value(rank, call, tok, feat):
+        return (rank + 1) * (1.0 + call + tok / 16.0 + feat / 4096.0)
+
+    def body(rank):
+        me = Rank(heap, rank, tile_keyed, jitter, seed)
+        try:
+            for c, (tokens, features) in enumerate(calls):
+                if late and (rank, c) in late:
+                    time.sleep(late[(rank, c)])
+                part = [[value(rank, c, t, f) for f in range(features)] for t in range(tokens)]
+                got = me.all_reduce(part, features)
+                scale = sum(r + 1 for r in range(world))
+                worst = max(abs(got[t][f] - scale * (1.0 + c + t / 16.0 + f / 4096.0)) for t in range(tokens) for f in range(features))
+                errors[rank].append(worst)
+        except BaseException as e:  # surfaced to the caller
+            failures.append(e)
+
+    threads = [threading.Thread(target=body, args=(r,)) for r in range(world)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    if failures:
+        raise failures[0]
+    return [max(errors[r][c] for r in range(world)) for c in range(len(calls))]

@@ -123,6 +123,8 @@ def _collectives_worker(rank, world, port, out_dir):
             rc.check_status()
             err = (got.float() - want).abs().max().item()
             assert err <= 0.02 * want.abs().max().item() + 0.05, (tokens, cols, features, err)
+        dist.barrier()
+        rc.check_guards()  # nobody (this rank or a peer) wrote outside the areas of the symmetric heap
         open(os.path.join(out_dir, f"ok{rank}"), "w").close()
     finally:
         dist.destroy_process_group()
@@ -181,6 +183,8 @@ def _model_worker(rank, world, port, out_dir):
         assert agree > 0.9, agree  # bf16 summation order differs between 1 and 2 ranks; near-ties may flip
         torch.cuda.synchronize()
         tp2._engine.comm.check_status()
+        dist.barrier()
+        tp2._engine.comm.check_guards()
         open(os.path.join(out_dir, f"ok{rank}"), "w").close()
     finally:
         dist.destroy_process_group()
@@ -331,3 +335,4 @@ def test_threaded_mode_serving_engine():
         torch.cuda.synchronize(d)
     for comm in tp2._device_backend.comms:
         comm.check_status()
+        comm.check_guards()
