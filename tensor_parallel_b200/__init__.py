@@ -22,7 +22,8 @@ from tensor_parallel_b200.parallel.checkpoint import (
 from tensor_parallel_b200.parallel.collectives import CollectiveOperation, TPCollectiveError
 from tensor_parallel_b200.parallel.distributed import DistributedTensorParallel
 from tensor_parallel_b200.parallel.factory import tensor_parallel
-from tensor_parallel_b200.parallel.families import PREDEFINED_CONFIGS, find_predefined_tensor_parallel_config
+from tensor_parallel_b200.parallel.families import PREDEFINED_CONFIGS, find_predefined_tensor_parallel_config, register_predefined_config
+from tensor_parallel_b200.utils import tracing
 from tensor_parallel_b200.parallel.kv import PerDeviceTensors
 from tensor_parallel_b200.parallel.legacy import Sharded
 from tensor_parallel_b200.parallel.rules import Config

@@ -46,6 +46,17 @@ PREDEFINED_CONFIGS: Dict[str, ConfigGetter] = {
 }
 
 
+def register_predefined_config(model_type: str, getter: ConfigGetter, overwrite: bool = False) -> None:
+    """Adds a rule-table builder ``getter(model_config, devices) -> Config`` for ``model_config.model_type == model_type``.
+    The reference offers no such call; its users mutate ``PREDEFINED_CONFIGS`` directly
+    (``src/tensor_parallel/slicing_configs.py:465-474``), which still works here."""
+    if not callable(getter):
+        raise TypeError("getter must be callable as getter(model_config, devices)")
+    if model_type in PREDEFINED_CONFIGS and not overwrite:
+        raise ValueError(f"a predefined config for model type {model_type!r} exists already (pass overwrite=True to replace it)")
+    PREDEFINED_CONFIGS[model_type] = getter
+
+
 def find_predefined_tensor_parallel_config(model_config, device_ids: Optional[Sequence]) -> Optional[Config]:
     """Rule table for ``model_config.model_type`` or ``None`` (caller falls back to autoconfig)."""
     from tensor_parallel_b200.parallel.runtime import check_device_ids

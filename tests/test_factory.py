@@ -50,3 +50,45 @@ def test_hf_model_gets_pretrained_wrapper():
     assert isinstance(wrapped, transformers.PreTrainedModel)
     assert isinstance(wrapped, tp.TensorParallelPreTrainedModel)
     assert isinstance(wrapped.wrapped_model, tp.TensorParallel)
+
+
+def test_register_predefined_config():
+    """A user-supplied rule table for a new ``model_type`` is picked up by the factory; double registration is refused."""
+    import tensor_parallel_b200 as tp
+    from torch import nn
+
+    class Cfg:
+        model_type = "my_two_layer_net"
+
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.config = Cfg()
+            self.up = nn.Linear(8, 16)
+            self.down = nn.Linear(16, 8)
+
+        def forward(self, x):
+            return self.down(torch.relu(self.up(x)))
+
+    seen = []
+
+    def getter(model_config, devices):
+        seen.append(len(devices))
+        return tp.Config(
+            state_rules={r"up\.(weight|bias)$": tp.Split(world_size=len(devices), dim=0), r"down\.weight$": tp.Split(world_size=len(devices), dim=1),
+                         r"down\.bias$": tp.Scale(world_size=len(devices))},
+            input_rules={}, output_rules={r"^down$": {0: "sum"}}, attr_rules={})
+
+    tp.register_predefined_config("my_two_layer_net", getter)
+    try:
+        with pytest.raises(ValueError):
+            tp.register_predefined_config("my_two_layer_net", getter)
+        torch.manual_seed(0)
+        net = Net()
+        x = torch.randn(3, 8)
+        want = net(x)
+        wrapped = tp.tensor_parallel(net, ["cpu", "cpu"])
+        torch.testing.assert_close(wrapped(x), want, atol=1e-5, rtol=1e-5)
+        assert seen == [2]
+    finally:
+        tp.PREDEFINED_CONFIGS.pop("my_two_layer_net", None)

@@ -130,3 +130,27 @@ def test_device_map_rank_parsing():
     assert infer_sharded_data_device_id("sharding_manager.flat_shards.1") == 1
     with pytest.raises(KeyError):
         infer_sharded_data_device_id("transformer.h.0.weight")
+
+
+def test_rewrap_with_a_different_world_size_after_training_steps():
+    """The recovery path when the set of devices changes: the un-sharded checkpoint is independent of the world size, so a
+    model trained on 2 ranks (ZeRO-3 shards included) continues on 3 ranks with identical outputs."""
+    torch.manual_seed(3)
+    model = _models()["llama"]
+    ids = torch.randint(0, 90, (2, 12))
+    two = tp.tensor_parallel(model, ["cpu"] * 2, sharded=True)
+    opt = torch.optim.SGD(two.parameters(), lr=0.05)
+    for _ in range(2):
+        two(input_ids=ids, labels=ids).loss.backward()
+        opt.step()
+        opt.zero_grad()
+    with torch.no_grad():
+        want = two(input_ids=ids).logits
+    with tp.save_tensor_parallel(two):
+        state = {k: v.clone() for k, v in two.state_dict().items()}
+    fresh = LlamaForCausalLM(LlamaConfig(vocab_size=90, hidden_size=32, intermediate_size=86, num_hidden_layers=2, num_attention_heads=4))
+    fresh.load_state_dict(state)
+    three = tp.tensor_parallel(fresh, ["cpu"] * 3, sharded=True)
+    with torch.no_grad():
+        got = three(input_ids=ids).logits
+    torch.testing.assert_close(got, want, atol=1e-5, rtol=1e-5)
