@@ -1030,8 +1030,6 @@ extern "C" int tpb_gemm_plan(int tokens, int features, int k, int world, int for
   // get shorter (4096 x 4096: accumulators complete after 7 us instead of 12 us), but the partial-tile exchange - park,
   // fence, counter, batched re-read - costs more than that on every shape tried (4096 x 4096: 18.9 vs 16.4 us,
   // 1536 x 4096: 16.6 vs 15.7 us, 4096 x 11008: 27.2 vs 28.1 us).
-  const bool few_tiles = tiles * 10 <= sms * 6;
-  (void)few_tiles;
   if (plan->swapped && force_splits <= 0 && g_enable_stream_k) {
     if (force_kbox <= 0)
       while (kbox > 1 && (long long)tiles * ((kb64 + kbox - 1) / kbox) < 4LL * sms) kbox >>= 1;  // keep >= 4 units per CTA if possible
