@@ -85,6 +85,7 @@ class BloomBlock(nn.Module):
 class BloomModel(nn.Module):
     def __init__(self, config: BloomConfig):
         super().__init__()
+        self.config = config  # lets the predefined rule table be found when the bare model (no head) is wrapped
         self.num_heads = config.n_head
         self.word_embeddings = nn.Embedding(config.vocab_size, config.hidden_size)
         self.word_embeddings_layernorm = LayerNorm(config.hidden_size, eps=config.layer_norm_epsilon)

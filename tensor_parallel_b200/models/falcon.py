@@ -82,6 +82,7 @@ class FalconDecoderLayer(nn.Module):
 class FalconModel(nn.Module):
     def __init__(self, config: FalconConfig):
         super().__init__()
+        self.config = config  # lets the predefined rule table be found when the bare model (no head) is wrapped
         self.word_embeddings = nn.Embedding(config.vocab_size, config.hidden_size)
         self.h = nn.ModuleList([FalconDecoderLayer(config) for _ in range(config.n_layer)])
         self.ln_f = LayerNorm(config.hidden_size, eps=config.layer_norm_epsilon)

@@ -67,6 +67,7 @@ class GPT2Block(nn.Module):
 class GPT2Model(nn.Module):
     def __init__(self, config: GPT2Config):
         super().__init__()
+        self.config = config  # lets the predefined rule table be found when the bare model (no head) is wrapped
         self.wte = nn.Embedding(config.vocab_size, config.n_embd)
         self.wpe = nn.Embedding(config.n_positions, config.n_embd)
         self.h = nn.ModuleList([GPT2Block(config) for _ in range(config.n_layer)])

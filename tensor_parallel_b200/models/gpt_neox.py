@@ -79,6 +79,7 @@ class GPTNeoXLayer(nn.Module):
 class GPTNeoXModel(nn.Module):
     def __init__(self, config: GPTNeoXConfig):
         super().__init__()
+        self.config = config  # lets the predefined rule table be found when the bare model (no head) is wrapped
         self.embed_in = nn.Embedding(config.vocab_size, config.hidden_size)
         self.layers = nn.ModuleList([GPTNeoXLayer(config) for _ in range(config.num_hidden_layers)])
         self.final_layer_norm = LayerNorm(config.hidden_size, eps=config.layer_norm_eps)

@@ -87,6 +87,7 @@ class OPTDecoder(nn.Module):
 class OPTModel(nn.Module):
     def __init__(self, config: OPTConfig):
         super().__init__()
+        self.config = config  # lets the predefined rule table be found when the bare model (no head) is wrapped
         self.decoder = OPTDecoder(config)
 
     def forward(self, *args, **kwargs):

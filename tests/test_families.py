@@ -201,3 +201,24 @@ def test_parallel_blocks_use_a_single_all_reduce(name):
     torch.testing.assert_close(out.logits, ref.logits, atol=3e-5, rtol=1e-5)
     torch.testing.assert_close(out_plain.logits, ref.logits, atol=3e-5, rtol=1e-5)
     out.loss.backward()
+
+
+@pytest.mark.parametrize("name", list(DECODERS))
+def test_bare_model_uses_the_family_table(name):
+    """The reference's ``test_multipurpose_configs``: the same rule table serves the model with and without its head.
+    Wrapping the bare transformer must pick the predefined table (row-parallel ``"sum"`` rules), not the automatic one."""
+    torch.manual_seed(0)
+    full = DECODERS[name]()
+    base = next(m for n, m in full.named_children() if n in ("model", "transformer", "gpt_neox"))
+    ids = torch.randint(0, V, (2, 7))
+    with torch.no_grad():
+        want = base(input_ids=ids)
+    want = want["last_hidden_state"] if hasattr(want, "keys") else want[0]
+    wrapped = tp.tensor_parallel(base, ["cpu", "cpu"])
+    sums = [a for per_module in wrapped.tensor_parallel_config.output_rules.values() for a in per_module.values()
+            if a == "sum" or type(a).__name__.endswith("AllReduce")]
+    assert sums, "automatic config was used (it never sums partial outputs of attention / MLP blocks)"
+    with torch.no_grad():
+        got = wrapped(input_ids=ids)
+    got = got["last_hidden_state"] if hasattr(got, "keys") else got[0]
+    torch.testing.assert_close(got, want, atol=3e-5, rtol=1e-4)
