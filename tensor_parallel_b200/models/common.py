@@ -150,7 +150,7 @@ class CausalLMBase(nn.Module):
         logits = head(hidden)
         return logits, self.lm_loss(logits, labels)
 
-    def generate(self, input_ids, **kwargs):
+    def generate(self, input_ids=None, **kwargs):
         from tensor_parallel_b200.models.generation import generate
 
         return generate(self, input_ids, **kwargs)

@@ -26,18 +26,27 @@ def reorder_cache(past, beam_idx: torch.Tensor):
 
 
 @torch.no_grad()
-def generate(model, input_ids: torch.Tensor, max_new_tokens: int = 20, num_beams: int = 1, do_sample: bool = False,
+def generate(model, input_ids: Optional[torch.Tensor] = None, max_new_tokens: int = 20, num_beams: int = 1, do_sample: bool = False,
              top_p: float = 1.0, temperature: float = 1.0, eos_token_id: Optional[int] = None, output_scores: bool = False,
-             generator: Optional[torch.Generator] = None, **model_kwargs):
+             generator: Optional[torch.Generator] = None, inputs_embeds: Optional[torch.Tensor] = None, **model_kwargs):
     """Returns the generated ids ``[batch, prompt + new]`` (and the per-step score tensors when
-    ``output_scores``: log-probabilities the next token was chosen from)."""
+    ``output_scores``: log-probabilities the next token was chosen from).  The prompt may be given as
+    ``inputs_embeds [batch, prompt, hidden]`` instead of ids (the reference's ``test_generate_inputs_embeds`` case); the
+    result then holds the new tokens only."""
+    if (input_ids is None) == (inputs_embeds is None):
+        raise ValueError("pass exactly one of input_ids / inputs_embeds")
     if num_beams > 1:
-        return _beam_search(model, input_ids, max_new_tokens, num_beams, eos_token_id, output_scores, model_kwargs)
-    ids, past, scores = input_ids, None, []
+        return _beam_search(model, input_ids, max_new_tokens, num_beams, eos_token_id, output_scores, model_kwargs, inputs_embeds)
+    prompt = input_ids if input_ids is not None else inputs_embeds
+    ids = input_ids if input_ids is not None else torch.empty(prompt.shape[0], 0, dtype=torch.long, device=prompt.device)
+    past, scores = None, []
     step_input = input_ids
     finished = torch.zeros(ids.shape[0], dtype=torch.bool, device=ids.device)
-    for _ in range(max_new_tokens):
-        out = model(input_ids=step_input, past_key_values=past, use_cache=True, **model_kwargs)
+    for step in range(max_new_tokens):
+        if step == 0 and inputs_embeds is not None:
+            out = model(inputs_embeds=inputs_embeds, past_key_values=past, use_cache=True, **model_kwargs)
+        else:
+            out = model(input_ids=step_input, past_key_values=past, use_cache=True, **model_kwargs)
         past = out["past_key_values"]
         logits = out["logits"][:, -1].float().to(ids.device)
         if do_sample:
@@ -64,14 +73,22 @@ def generate(model, input_ids: torch.Tensor, max_new_tokens: int = 20, num_beams
     return (ids, scores) if output_scores else ids
 
 
-def _beam_search(model, input_ids, max_new_tokens, num_beams, eos_token_id, output_scores, model_kwargs):
-    batch, device = input_ids.shape[0], input_ids.device
-    ids = input_ids.repeat_interleave(num_beams, dim=0)
+def _beam_search(model, input_ids, max_new_tokens, num_beams, eos_token_id, output_scores, model_kwargs, inputs_embeds=None):
+    prompt = input_ids if input_ids is not None else inputs_embeds
+    batch, device = prompt.shape[0], prompt.device
+    if input_ids is not None:
+        ids = input_ids.repeat_interleave(num_beams, dim=0)
+    else:
+        ids = torch.empty(batch * num_beams, 0, dtype=torch.long, device=device)
+        inputs_embeds = inputs_embeds.repeat_interleave(num_beams, dim=0)
     beam_scores = torch.zeros(batch, num_beams, device=device)
     beam_scores[:, 1:] = -1e9  # all beams start identical: keep only one alive
     past, step_input, scores = None, ids, []
-    for _ in range(max_new_tokens):
-        out = model(input_ids=step_input, past_key_values=past, use_cache=True, **model_kwargs)
+    for step in range(max_new_tokens):
+        if step == 0 and inputs_embeds is not None:
+            out = model(inputs_embeds=inputs_embeds, past_key_values=past, use_cache=True, **model_kwargs)
+        else:
+            out = model(input_ids=step_input, past_key_values=past, use_cache=True, **model_kwargs)
         past = out["past_key_values"]
         logprobs = out["logits"][:, -1].float().to(device).log_softmax(-1)
         scores.append(logprobs)

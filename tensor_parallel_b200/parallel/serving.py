@@ -54,9 +54,9 @@ class ServingMixin:
         return eng
 
     @torch.no_grad()
-    def generate(self, input_ids: torch.Tensor, max_new_tokens: int = 20, **kwargs):
+    def generate(self, input_ids: Optional[torch.Tensor] = None, max_new_tokens: int = 20, **kwargs):
         greedy = not kwargs.get("do_sample", False) and kwargs.get("num_beams", 1) == 1 and not kwargs.get("output_scores", False)
-        if greedy and set(kwargs) <= {"do_sample", "num_beams", "output_scores"}:
+        if input_ids is not None and greedy and set(kwargs) <= {"do_sample", "num_beams", "output_scores"}:
             engine = self.serving_engine(input_ids.shape[0], input_ids.shape[1] + max_new_tokens + 4)
             if engine is not None:
                 return engine.generate(input_ids, max_new_tokens)

@@ -222,3 +222,26 @@ def test_bare_model_uses_the_family_table(name):
         got = wrapped(input_ids=ids)
     got = got["last_hidden_state"] if hasattr(got, "keys") else got[0]
     torch.testing.assert_close(got, want, atol=3e-5, rtol=1e-4)
+
+
+@pytest.mark.parametrize("name", ["bloom", "gpt2"])
+@pytest.mark.parametrize("beams", [1, 3])
+def test_generate_from_inputs_embeds(name, beams):
+    """The reference's ``test_generate_inputs_embeds``: the prompt is given as embeddings; the tensor-parallel wrapper must
+    produce the same step scores and tokens as the unsplit model, and the same tokens as the id prompt those embeddings
+    came from."""
+    torch.manual_seed(0)
+    model = DECODERS[name]()
+    prompt = torch.randint(0, V, (2, 5))
+    table = model.transformer.word_embeddings if name == "bloom" else model.transformer.wte
+    embeds = table(prompt).detach()
+    kwargs = {"num_beams": beams} if beams > 1 else {}
+    ref_ids, ref_scores = generate(model, inputs_embeds=embeds, max_new_tokens=3, output_scores=True, **kwargs)
+    from_ids = generate(model, prompt, max_new_tokens=3, **kwargs)
+    assert ref_ids.shape == (2, 3) and torch.equal(ref_ids, from_ids[:, 5:])
+    wrapped = tp.tensor_parallel(model, ["cpu", "cpu"], sharded=True)
+    tp_ids, tp_scores = generate(wrapped, inputs_embeds=embeds, max_new_tokens=3, output_scores=True, **kwargs)
+    for a, b in zip(ref_scores, tp_scores):
+        torch.testing.assert_close(b, a, atol=3e-4, rtol=1e-4)
+    assert torch.equal(tp_ids, ref_ids)
+    assert torch.equal(wrapped.generate(inputs_embeds=embeds, max_new_tokens=3, **kwargs), ref_ids)
