@@ -302,8 +302,8 @@ class EngineGroup:
 
     The decode step is launched kernel by kernel here, not replayed from CUDA graphs: when one thread replayed rank 0's
     graph and then rank 1's, rank 1's graph did not start before rank 0's had run to its end (every peer wait of rank 0
-    hit its time limit; measured on two B200s), whereas eager launches of the same kernels in the same order overlap
-    as expected.  One process per GPU (:class:`LlamaEngine` with a graph per process) remains the fast path."""
+    hit its time limit; measured on two B200s, and the same when each graph was replayed from a host thread of its
+    own), whereas eager launches of the same kernels in the same order overlap as expected.  One process per GPU (:class:`LlamaEngine` with a graph per process) remains the fast path."""
 
     def __init__(self, shards, comms, max_batch: int = 8, max_seq: int = 2560):
         tables = [_unwrap(_unwrap(_unwrap(s).model).embed_tokens).weight.detach() for s in shards]
