@@ -171,6 +171,24 @@ class DistributedTensorParallel(ServingMixin, nn.Module):
 
     # -- forward ---------------------------------------------------------------------------------
 
+    @torch.no_grad()
+    def reduce_replicated_gradients(self) -> int:
+        """Sums the gradients of the parameters that stayed replicated (``sharded=False``) over the ranks, see
+        ``TensorParallel.reduce_replicated_gradients``.  Every rank must call it."""
+        import torch.distributed as dist
+
+        if self.sharding_manager is not None or self.world_size < 2:
+            return 0
+        reduced = 0
+        for name, param in self.module_shards[0].named_parameters():
+            if name in self.modified_parameters_names or not param.requires_grad:
+                continue
+            if param.grad is None:  # this rank saw no gradient for it; it still has to take part in the sum
+                param.grad = torch.zeros_like(param)
+            dist.all_reduce(param.grad, group=self.process_group)
+            reduced += 1
+        return reduced
+
     def forward(self, *args, **kwargs):
         if self.sharding_manager is not None:
             self.sharding_manager.synchronize_weights(self.all_cuda)

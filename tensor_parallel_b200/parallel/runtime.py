@@ -282,6 +282,33 @@ class TensorParallel(ServingMixin, nn.Module):
             raise RuntimeError("sharding was already applied; pass sharded=False at construction to do it later")
         self.sharding_manager = Sharded(self, len(self.devices), replicated_param_names)
 
+    @torch.no_grad()
+    def reduce_replicated_gradients(self) -> int:
+        """With ``sharded=False`` the parameters that no state rule splits stay replicated on every rank, and after
+        ``backward()`` each replica only holds the part of the gradient that flowed through its own rank's slices
+        downstream (the reference has the same property and leaves it there: replicated-parameter training is only
+        correct with ZeRO-3 on).  This sums those partial gradients over the ranks and gives every replica the total,
+        so that a per-replica optimizer keeps the replicas identical.  Returns the number of parameters reduced; a
+        no-op when ZeRO-3 sharding is active (its flat shards are sum-reduced already)."""
+        if self.sharding_manager is not None or len(self.module_shards) < 2:
+            return 0
+        named = [dict(shard.named_parameters()) for shard in self.module_shards]
+        reduced = 0
+        for name, first in named[0].items():
+            if name in self.modified_parameters_names:
+                continue
+            replicas = [params.get(name) for params in named]
+            if any(p is None for p in replicas) or not first.requires_grad or all(p.grad is None for p in replicas):
+                continue
+            total = torch.zeros_like(first)
+            for p in replicas:
+                if p.grad is not None:
+                    total += p.grad.to(total.device)
+            for p in replicas:
+                p.grad = total.to(p.device).clone()
+            reduced += 1
+        return reduced
+
     # -- forward ------------------------------------------------------------------------------
 
     def prepare_args_kwargs_for_forward(self, *args, **kwargs):

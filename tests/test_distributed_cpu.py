@@ -93,3 +93,37 @@ def _worker(rank, world, port, case, result_dir):
 def test_distributed_gloo(case, world, tmp_path):
     mp.spawn(_worker, args=(world, _free_port(), case, str(tmp_path)), nprocs=world, join=True)
     assert sorted(os.listdir(tmp_path)) == [f"ok{r}" for r in range(world)]
+
+
+def _replicated_worker(rank, world, port, result_dir):
+    """``sharded=False`` under one process per rank: the replicated parameters' partial gradients are summed on request."""
+    sys.path.insert(0, REPO)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import tensor_parallel_b200 as tp
+        from tensor_parallel_b200.models.llama import LlamaConfig, LlamaForCausalLM
+
+        torch.manual_seed(0)
+        model = LlamaForCausalLM(LlamaConfig(vocab_size=80, hidden_size=32, intermediate_size=86, num_hidden_layers=2, num_attention_heads=4))
+        ids = torch.randint(0, 80, (2, 9))
+        model(input_ids=ids, labels=ids).loss.backward()
+        ref_grads = {n: p.grad.clone() for n, p in model.named_parameters()}
+        model.zero_grad()
+        wrapped = tp.tensor_parallel(model, ["cpu"], sharded=False)
+        wrapped(input_ids=ids, labels=ids).loss.backward()
+        assert wrapped.reduce_replicated_gradients() > 0
+        checked = 0
+        for name, p in wrapped.module_shards[0].named_parameters():
+            if name not in wrapped.modified_parameters_names:
+                torch.testing.assert_close(p.grad, ref_grads[name.replace("tp_wrapped_module.", "")], atol=3e-5, rtol=1e-3, msg=name)
+                checked += 1
+        assert checked >= 5  # the norm weights of two layers and the final norm
+        open(os.path.join(result_dir, f"ok{rank}"), "w").close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_distributed_replicated_gradient_reduction(tmp_path):
+    mp.spawn(_replicated_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    assert sorted(os.listdir(tmp_path)) == ["ok0", "ok1"]

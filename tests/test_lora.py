@@ -64,3 +64,27 @@ def test_lora_forward_and_gradients(world, sharded):
     pieces = [param(shard, name_b).grad for shard in wrapped.module_shards]
     assert pieces[0].shape[0] < grads[name_b].shape[0]
     torch.testing.assert_close(torch.cat(pieces, dim=0), grads[name_b], atol=2e-5, rtol=1e-3)
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_reduce_replicated_gradients_keeps_replicas_exact(world):
+    """Without ZeRO-3 a replicated parameter only receives its rank's share of the gradient; summing the shares gives every
+    replica the gradient of the unsplit model (norm weights and the replicated LoRA matrices alike)."""
+    model = _lora_llama()
+    ids = torch.randint(0, 64, (2, 9))
+    model(input_ids=ids, labels=ids).loss.backward()
+    want = {n: p.grad.clone() for n, p in model.named_parameters()}
+    model.zero_grad()
+    wrapped = tp.tensor_parallel(model, ["cpu"] * world, sharded=False)
+    wrapped(input_ids=ids, labels=ids).loss.backward()
+    reduced = wrapped.reduce_replicated_gradients()
+    assert reduced > 0
+    checked = 0
+    for shard in wrapped.module_shards:
+        for name, p in shard.named_parameters():
+            if name in wrapped.modified_parameters_names:
+                continue
+            torch.testing.assert_close(p.grad, want[name.replace("tp_wrapped_module.", "")], atol=3e-5, rtol=1e-3, msg=name)
+            checked += 1
+    assert checked >= 2 * world
+    assert tp.tensor_parallel(_lora_llama(), ["cpu"] * world, sharded=True).reduce_replicated_gradients() == 0
