@@ -17,6 +17,7 @@ from tensor_parallel_b200.parallel.checkpoint import (
     convert_state_dict,
     infer_sharded_device_map,
     load_sharded_state_dict_,
+    replicated_parameter_names,
     save_tensor_parallel,
 )
 from tensor_parallel_b200.parallel.collectives import CollectiveOperation, TPCollectiveError

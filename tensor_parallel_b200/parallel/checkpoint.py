@@ -66,19 +66,66 @@ def convert_state_dict_single_shard(state: Mapping, config: Config, world_size: 
     return out
 
 
-def convert_state_dict(input_state_dict: Mapping, tensor_parallel_config: Config, world_size: int, for_pretrained: bool = False) -> dict:
+def convert_state_dict(input_state_dict: Mapping, tensor_parallel_config: Config, world_size: int, for_pretrained: bool = False,
+                       sharded_param_names=None) -> dict:
     """Plain (possibly partial) state dict -> sharded key layout for ``world_size`` ranks.
 
     Works chunk by chunk, which is what makes memory-efficient loading possible.  Tied weights
-    present under several names are sliced under each name.  ZeRO-3 ``flat_shards`` are not
-    produced: call ``.apply_sharding()`` after loading."""
+    present under several names are sliced under each name.
+
+    ``sharded_param_names`` (the ``sharded_param_names`` of a model wrapped with ``sharded=True``, i.e. shard-side names
+    in the order of its flat shards, or the output of :func:`replicated_parameter_names`) additionally produces the
+    ZeRO-3 ``sharding_manager.flat_shards.{rank}`` entries and drops those parameters (and their tied aliases) from
+    the per-rank entries, so that the result loads straight into a model created with ``sharded=True``.  The whole set
+    of those parameters must then be present in ``input_state_dict`` (a flat shard cannot be assembled from a chunk).
+    The reference cannot emit flat shards (``src/tensor_parallel/dispatch.py:79``)."""
     out = {}
     for rank in range(world_size):
         out.update(convert_state_dict_single_shard(input_state_dict, tensor_parallel_config, world_size, rank))
         out[f"_sanity_check_params.{rank}"] = torch.empty(0)
+    if sharded_param_names:
+        from tensor_parallel_b200.parallel.actions import unit_bounds
+
+        shard_side = get_parameter_name_mapping(input_state_dict.keys(), tensor_parallel_config)
+        original_of = {v: k for k, v in shard_side.items()}
+        missing = [n for n in sharded_param_names if n not in original_of]
+        if missing:
+            raise KeyError(f"parameters of the flat shards are not in this state dict: {missing[:5]}")
+        tensors = [input_state_dict[original_of[n]] for n in sharded_param_names]
+        pieces_per_rank = [[t.detach().flatten()[slice(*unit_bounds(t.numel(), world_size, r))] for t in tensors] for r in range(world_size)]
+        flat_len = max(sum(p.numel() for p in pieces) for pieces in pieces_per_rank)
+        for r, pieces in enumerate(pieces_per_rank):
+            pad = flat_len - sum(p.numel() for p in pieces)
+            out[f"sharding_manager.flat_shards.{r}"] = torch.cat(pieces + [tensors[0].new_zeros(pad)])
+        # the sharded parameters (under every name that aliases them) no longer live in the shard modules
+        aliased = {id_: names for id_, names in _aliases_by_storage(input_state_dict).items()}
+        drop = set()
+        for n in sharded_param_names:
+            for alias in aliased.get(_storage_key(input_state_dict[original_of[n]]), [original_of[n]]):
+                drop.add(shard_side[alias])
+        out = {k: v for k, v in out.items() if not any(k == f"module_shards.{r}.{d}" for r in range(world_size) for d in drop)}
     if for_pretrained:
         out = {"wrapped_model." + key: value for key, value in out.items()}
     return out
+
+
+def _storage_key(t: torch.Tensor):
+    return (t.data_ptr(), tuple(t.shape), tuple(t.stride())) if t.numel() else ("empty", id(t))
+
+
+def _aliases_by_storage(state: Mapping):
+    groups: Dict[tuple, list] = {}
+    for name, t in state.items():
+        groups.setdefault(_storage_key(t), []).append(name)
+    return groups
+
+
+def replicated_parameter_names(module, tensor_parallel_config: Config):
+    """Shard-side names, sorted, of the parameters of ``module`` that no state rule splits - the ones ZeRO-3 puts into
+    flat shards; what ``sharded=True`` computes on its own, for use with :func:`convert_state_dict`."""
+    names = [n for n, _ in module.named_parameters()]
+    mapping = get_parameter_name_mapping(names, tensor_parallel_config)
+    return sorted(mapping[n] for n in names if not any(p.search(n) for p in tensor_parallel_config.state_rules))
 
 
 def load_sharded_state_dict_(tp_model, state: Mapping, strict: bool = True):
