@@ -355,7 +355,8 @@ def get_falcon_config(model_config, devices: Sequence[torch.device]) -> Config:
         },
         attr_rules={
             r".*self_attention$": {
-                "num_kv": partial(split_num_heads, world_size=world),
+                "num_kv": partial(split_num_heads, world_size=world),        # remote-code RWForCausalLM
+                "num_kv_heads": partial(split_num_heads, world_size=world),  # transformers' FalconAttention
                 "num_heads": _grouped_heads(q_per_kv, world),
             }
         },

@@ -49,10 +49,15 @@ def _is_stateful_cache(obj) -> bool:
 _MIRRORED_CACHE_CALLS = ("reorder_cache", "batch_select_indices", "batch_repeat_interleave", "crop", "reset")
 
 
-def _attach_cache_siblings(cache, world_size: int, keep_rank: int, devices):
+def _attach_cache_siblings(cache, world_size: int, keep_rank: int, devices, existing=None):
+    """``existing``: the caches that the other ranks already own (one per rank; the entry of ``keep_rank`` is ignored);
+    without it the siblings start as copies of ``cache``."""
     import copy
 
-    siblings = [cache if r == keep_rank else copy.deepcopy(cache) for r in range(world_size)]
+    if existing is not None:
+        siblings = [cache if r == keep_rank else existing[r] for r in range(world_size)]
+    else:
+        siblings = [cache if r == keep_rank else copy.deepcopy(cache) for r in range(world_size)]
     cache.__dict__["_tp_siblings"] = siblings
     for method_name in _MIRRORED_CACHE_CALLS:
         original = getattr(cache, method_name, None)
@@ -354,7 +359,26 @@ class TensorParallel(ServingMixin, nn.Module):
         outputs = parallel_apply_simple(
             modules, inputs, kwargs_tup, self.devices, executor=self._executor, group=getattr(self, "_rank_group", None)
         )
+        self._adopt_new_caches(outputs)
         return outputs[self.output_device_index]
+
+    def _adopt_new_caches(self, outputs):
+        """A model called with ``use_cache=True`` and no cache creates a stateful cache object on every rank, each holding
+        that rank's heads.  Only the output rank's object reaches the caller; the others are tied to it here, so that a
+        later call that passes the object back finds every rank's history."""
+        mine = outputs[self.output_device_index]
+        fields = getattr(mine, "keys", None)
+        if fields is None:
+            return
+        for key in list(fields()):
+            value = mine[key] if hasattr(mine, "__getitem__") else getattr(mine, key)
+            if _is_stateful_cache(value) and value.__dict__.get("_tp_siblings") is None:
+                others = []
+                for out in outputs:
+                    other = out[key] if hasattr(out, "__getitem__") else getattr(out, key, None)
+                    others.append(other)
+                if all(_is_stateful_cache(o) for o in others):
+                    _attach_cache_siblings(value, len(self.devices), self.output_device_index, self.devices, existing=others)
 
     def forward(self, *args, **kwargs):
         self._materialize()

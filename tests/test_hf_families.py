@@ -1,0 +1,61 @@
+"""Current Hugging Face model classes (random tiny configs, no download) under the predefined rule tables: the logits of the
+tensor-parallel wrapper equal those of the unsplit model, with and without ZeRO-3, and a chained cached call works.
+The reference's tables patch attributes of 2023-era modules and break on newer ``transformers``; here attribute rules
+skip names a module does not have, and both the remote-code and the in-library Falcon attribute names are covered."""
+import pytest
+import torch
+
+transformers = pytest.importorskip("transformers")
+from transformers import AutoConfig, AutoModelForCausalLM  # noqa: E402
+
+import tensor_parallel_b200 as tp  # noqa: E402
+
+V = 96
+CASES = {
+    "llama": dict(model_type="llama", vocab_size=V, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2),
+    "gpt2": dict(model_type="gpt2", vocab_size=V, n_embd=32, n_layer=2, n_head=4, n_positions=64),
+    "bloom": dict(model_type="bloom", vocab_size=V, hidden_size=32, n_layer=2, n_head=4),
+    "gpt_neox": dict(model_type="gpt_neox", vocab_size=V, hidden_size=32, num_hidden_layers=2, num_attention_heads=4, intermediate_size=64),
+    "opt": dict(model_type="opt", vocab_size=V, hidden_size=32, num_hidden_layers=2, num_attention_heads=4, ffn_dim=64, max_position_embeddings=64, word_embed_proj_dim=32),
+    "gptj": dict(model_type="gptj", vocab_size=V, n_embd=32, n_layer=2, n_head=4, rotary_dim=4, n_positions=64),
+    "falcon": dict(model_type="falcon", vocab_size=V, hidden_size=32, num_hidden_layers=2, num_attention_heads=4, num_kv_heads=2, new_decoder_architecture=True),
+    "codegen": dict(model_type="codegen", vocab_size=V, n_embd=64, n_layer=2, n_head=8, rotary_dim=4, n_positions=64),
+}
+
+
+def _model(name):
+    torch.manual_seed(0)
+    cfg = AutoConfig.for_model(**CASES[name])
+    return AutoModelForCausalLM.from_config(cfg, attn_implementation="eager").eval()
+
+
+@pytest.mark.parametrize("name", list(CASES))
+@pytest.mark.parametrize("sharded", [False, True])
+def test_hf_decoder_families(name, sharded):
+    model = _model(name)
+    ids = torch.randint(0, V, (2, 7))
+    with torch.no_grad():
+        want = model(input_ids=ids).logits
+    wrapped = tp.tensor_parallel(model, ["cpu", "cpu"], sharded=sharded)
+    assert isinstance(wrapped, tp.TensorParallelPreTrainedModel)
+    sums = [a for per in wrapped.tensor_parallel_config.output_rules.values() for a in per.values()
+            if a == "sum" or type(a).__name__.endswith("AllReduce")]
+    assert sums, "the automatic config was used instead of the family's rule table"
+    with torch.no_grad():
+        got = wrapped(input_ids=ids).logits
+    torch.testing.assert_close(got, want, atol=3e-5, rtol=1e-4)
+
+
+@pytest.mark.parametrize("name", ["llama", "gpt2", "falcon"])
+def test_hf_chained_cache_calls(name):
+    model = _model(name)
+    a, b = torch.randint(0, V, (2, 5)), torch.randint(0, V, (2, 1))
+    with torch.no_grad():
+        r1 = model(input_ids=a, use_cache=True)
+        r2 = model(input_ids=b, past_key_values=r1.past_key_values, use_cache=True)
+    wrapped = tp.tensor_parallel(_model(name), ["cpu", "cpu"])
+    with torch.no_grad():
+        o1 = wrapped(input_ids=a, use_cache=True)
+        o2 = wrapped(input_ids=b, past_key_values=o1.past_key_values, use_cache=True)
+    torch.testing.assert_close(o1.logits, r1.logits, atol=3e-5, rtol=1e-4)
+    torch.testing.assert_close(o2.logits, r2.logits, atol=3e-5, rtol=1e-4)
