@@ -11,12 +11,20 @@ from tensor_parallel_b200.parallel.kv import PerDeviceTensors
 from tensor_parallel_b200.utils.nested import nested_map
 
 
+def _is_cache_object(obj) -> bool:
+    return hasattr(obj, "update") and hasattr(obj, "get_seq_length")
+
+
 def gather_kv(*per_rank_kv, world_size: int):
     """Zip every rank's ``(key, value)`` into ``(PerDeviceTensors(keys), PerDeviceTensors(values))``.
 
     No data moves: the result only holds references, and the same object is handed to every rank.
     """
     if per_rank_kv[0] is None:
+        return per_rank_kv
+    if isinstance(per_rank_kv[0], torch.Tensor) or _is_cache_object(per_rank_kv[0]):
+        # not a (key, value) pair: newer attention modules keep their cache in a stateful object (handled by the
+        # runtime) and return something else at this position, e.g. T5's per-rank position bias - leave it alone
         return per_rank_kv
     zipped = tuple(PerDeviceTensors(*same_slot) for same_slot in zip(*per_rank_kv))
     return [zipped] * world_size

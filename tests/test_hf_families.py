@@ -59,3 +59,51 @@ def test_hf_chained_cache_calls(name):
         o2 = wrapped(input_ids=b, past_key_values=o1.past_key_values, use_cache=True)
     torch.testing.assert_close(o1.logits, r1.logits, atol=3e-5, rtol=1e-4)
     torch.testing.assert_close(o2.logits, r2.logits, atol=3e-5, rtol=1e-4)
+
+
+def test_hf_t5_forward_and_generate():
+    """``transformers`` 5.x T5: the attention modules return their position bias where older versions returned the
+    key / value pair, and keep the cache in a stateful object; forward, greedy and beam generation match the unsplit model."""
+    from transformers import T5ForConditionalGeneration
+
+    torch.manual_seed(0)
+    cfg = AutoConfig.for_model(model_type="t5", vocab_size=V, d_model=32, d_kv=8, d_ff=48, num_layers=2, num_heads=4, decoder_start_token_id=0)
+    model = T5ForConditionalGeneration(cfg).eval()
+    ids, dec = torch.randint(0, V, (2, 7)), torch.randint(0, V, (2, 4))
+    with torch.no_grad():
+        want = model(input_ids=ids, decoder_input_ids=dec).logits
+    greedy = model.generate(ids, max_new_tokens=5, do_sample=False)
+    beams = model.generate(ids, max_new_tokens=5, do_sample=False, num_beams=3)
+    for sharded in (False, True):
+        wrapped = tp.tensor_parallel(model, ["cpu", "cpu"], sharded=sharded)
+        with torch.no_grad():
+            got = wrapped(input_ids=ids, decoder_input_ids=dec).logits
+        torch.testing.assert_close(got, want, atol=3e-5, rtol=1e-4)
+    assert torch.equal(wrapped.generate(ids, max_new_tokens=5, do_sample=False), greedy)
+    assert torch.equal(wrapped.generate(ids, max_new_tokens=5, do_sample=False, num_beams=3), beams)
+
+
+def test_hf_bert_three_ranks_zero3():
+    from transformers import BertModel
+
+    torch.manual_seed(0)
+    cfg = AutoConfig.for_model(model_type="bert", vocab_size=V, hidden_size=32, num_hidden_layers=2, num_attention_heads=4, intermediate_size=64,
+                               max_position_embeddings=64)
+    model = BertModel(cfg).eval()
+    ids = torch.randint(0, V, (2, 7))
+    with torch.no_grad():
+        want = model(input_ids=ids).last_hidden_state
+    wrapped = tp.tensor_parallel(model, ["cpu"] * 3, sharded=True)
+    with torch.no_grad():
+        got = wrapped(input_ids=ids).last_hidden_state
+    torch.testing.assert_close(got, want, atol=3e-5, rtol=1e-4)
+
+
+@pytest.mark.parametrize("name", ["llama", "bloom"])
+@pytest.mark.parametrize("kwargs", [{}, {"num_beams": 3}])
+def test_hf_generate_matches_unsplit(name, kwargs):
+    model = _model(name)
+    ids = torch.randint(0, V, (2, 6))
+    want = model.generate(ids, max_new_tokens=5, do_sample=False, pad_token_id=0, **kwargs)
+    wrapped = tp.tensor_parallel(model, ["cpu", "cpu"])
+    assert torch.equal(wrapped.generate(ids, max_new_tokens=5, do_sample=False, pad_token_id=0, **kwargs), want)
