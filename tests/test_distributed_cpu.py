@@ -127,3 +127,41 @@ def _replicated_worker(rank, world, port, result_dir):
 def test_distributed_replicated_gradient_reduction(tmp_path):
     mp.spawn(_replicated_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
     assert sorted(os.listdir(tmp_path)) == ["ok0", "ok1"]
+
+
+def _hf_worker(rank, world, port, result_dir):
+    """A current Hugging Face Llama under one process per rank: forward and a chained cached call (the cache is a stateful
+    object that every rank keeps for its own heads)."""
+    sys.path.insert(0, REPO)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from transformers import AutoConfig, AutoModelForCausalLM
+
+        import tensor_parallel_b200 as tp
+
+        cfg = AutoConfig.for_model(model_type="llama", vocab_size=96, hidden_size=32, intermediate_size=64, num_hidden_layers=2,
+                                   num_attention_heads=4, num_key_value_heads=2)
+        torch.manual_seed(0)
+        model = AutoModelForCausalLM.from_config(cfg, attn_implementation="eager").eval()
+        a, b = torch.randint(0, 96, (2, 5)), torch.randint(0, 96, (2, 1))
+        with torch.no_grad():
+            r1 = model(input_ids=a, use_cache=True)
+            r2 = model(input_ids=b, past_key_values=r1.past_key_values, use_cache=True)
+        torch.manual_seed(0)
+        wrapped = tp.tensor_parallel(AutoModelForCausalLM.from_config(cfg, attn_implementation="eager").eval(), ["cpu"], sharded=True)
+        assert isinstance(wrapped, tp.DistributedTensorParallel)
+        with torch.no_grad():
+            o1 = wrapped(input_ids=a, use_cache=True)
+            o2 = wrapped(input_ids=b, past_key_values=o1.past_key_values, use_cache=True)
+        torch.testing.assert_close(o1.logits, r1.logits, atol=3e-5, rtol=1e-4)
+        torch.testing.assert_close(o2.logits, r2.logits, atol=3e-5, rtol=1e-4)
+        open(os.path.join(result_dir, f"ok{rank}"), "w").close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_distributed_hugging_face_llama(tmp_path):
+    pytest.importorskip("transformers")
+    mp.spawn(_hf_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    assert sorted(os.listdir(tmp_path)) == ["ok0", "ok1"]
