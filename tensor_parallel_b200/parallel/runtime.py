@@ -11,7 +11,9 @@ from __future__ import annotations
 
 import logging
 import queue
+import atexit
 import threading
+import weakref
 from typing import Any, Collection, List, Optional, Sequence, Union
 
 import torch
@@ -97,6 +99,27 @@ class _RankWorker(threading.Thread):
                 done.set()
 
 
+_live_executors: "weakref.WeakSet" = weakref.WeakSet()
+_retiring_threads: "weakref.WeakSet" = weakref.WeakSet()  # told to stop (e.g. when their model was collected), maybe still unwinding
+
+
+def _stop_rank_threads():
+    """The rank threads are daemons parked on a queue; stopping and joining them before the interpreter finalises keeps
+    the C++ runtime from tearing down thread-local state underneath a live thread (seen as ``terminate called without
+    an active exception`` and exit status 134 at the end of short scripts)."""
+    for executor in list(_live_executors):
+        try:
+            executor.shutdown(join=True)
+        except Exception:
+            pass
+    for thread in list(_retiring_threads):
+        if thread.is_alive() and thread is not threading.current_thread():
+            thread.join(timeout=5.0)
+
+
+atexit.register(_stop_rank_threads)
+
+
 class RankExecutor:
     """Runs one callable per rank concurrently on persistent threads."""
 
@@ -104,6 +127,7 @@ class RankExecutor:
         self.world_size = world_size
         self._workers: List[_RankWorker] = []
         self._lock = threading.Lock()
+        _live_executors.add(self)
 
     def _ensure(self):
         with self._lock:
@@ -136,11 +160,16 @@ class RankExecutor:
             raise (primary or secondary)[0]
         return [r for _, r in results]
 
-    def shutdown(self):
+    def shutdown(self, join: bool = False):
         with self._lock:
-            for w in self._workers:
-                w.jobs.put(None)
-            self._workers = []
+            workers, self._workers = self._workers, []
+        for w in workers:
+            w.jobs.put(None)
+            _retiring_threads.add(w)
+        if join:
+            for w in workers:
+                if w is not threading.current_thread():
+                    w.join(timeout=5.0)
 
     def __del__(self):
         try:
