@@ -107,3 +107,19 @@ def test_hf_generate_matches_unsplit(name, kwargs):
     want = model.generate(ids, max_new_tokens=5, do_sample=False, pad_token_id=0, **kwargs)
     wrapped = tp.tensor_parallel(model, ["cpu", "cpu"])
     assert torch.equal(wrapped.generate(ids, max_new_tokens=5, do_sample=False, pad_token_id=0, **kwargs), want)
+
+
+def test_hf_save_pretrained_round_trip(tmp_path):
+    """``save_pretrained`` inside ``save_tensor_parallel`` writes a checkpoint that the plain class loads (the reference's
+    README flow), here from a ZeRO-3 sharded wrapper."""
+    model = _model("llama")
+    ids = torch.randint(0, V, (2, 7))
+    with torch.no_grad():
+        want = model(input_ids=ids).logits
+    wrapped = tp.tensor_parallel(model, ["cpu", "cpu"], sharded=True)
+    with tp.save_tensor_parallel(wrapped):
+        wrapped.save_pretrained(str(tmp_path))
+    reloaded = AutoModelForCausalLM.from_pretrained(str(tmp_path), attn_implementation="eager").eval()
+    with torch.no_grad():
+        got = reloaded(input_ids=ids).logits
+    torch.testing.assert_close(got, want, atol=1e-6, rtol=1e-6)
