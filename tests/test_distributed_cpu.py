@@ -119,6 +119,16 @@ def _replicated_worker(rank, world, port, result_dir):
                 torch.testing.assert_close(p.grad, ref_grads[name.replace("tp_wrapped_module.", "")], atol=3e-5, rtol=1e-3, msg=name)
                 checked += 1
         assert checked >= 5  # the norm weights of two layers and the final norm
+        # generation in this mode: every process keeps the cache of its own heads; greedy and beam search agree with the unsplit model
+        from tensor_parallel_b200.models.generation import generate
+
+        torch.manual_seed(1)
+        plain = LlamaForCausalLM(LlamaConfig(vocab_size=80, hidden_size=32, intermediate_size=86, num_hidden_layers=2, num_attention_heads=4)).eval()
+        prompt = torch.randint(0, 80, (2, 6))
+        want_greedy, want_beam = generate(plain, prompt, max_new_tokens=5), generate(plain, prompt, max_new_tokens=5, num_beams=3)
+        served = tp.tensor_parallel(plain, ["cpu"], sharded=True)
+        assert torch.equal(served.generate(prompt, max_new_tokens=5), want_greedy)
+        assert torch.equal(served.generate(prompt, max_new_tokens=5, num_beams=3), want_beam)
         open(os.path.join(result_dir, f"ok{rank}"), "w").close()
     finally:
         dist.destroy_process_group()
