@@ -175,3 +175,44 @@ def test_distributed_hugging_face_llama(tmp_path):
     pytest.importorskip("transformers")
     mp.spawn(_hf_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
     assert sorted(os.listdir(tmp_path)) == ["ok0", "ok1"]
+
+
+def _leaver_worker(rank, world, port, result_dir):
+    """Rank 1 leaves between steps (nothing of its own in flight); rank 0's next collective must end with an error within
+    the process-group timeout instead of hanging, and rank 0 stays usable for local work."""
+    import datetime
+    import time
+
+    sys.path.insert(0, REPO)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    import tensor_parallel_b200 as tp
+    from tensor_parallel_b200.models.llama import LlamaConfig, LlamaForCausalLM
+
+    torch.manual_seed(0)
+    model = LlamaForCausalLM(LlamaConfig(vocab_size=80, hidden_size=32, intermediate_size=86, num_hidden_layers=2, num_attention_heads=4))
+    wrapped = tp.tensor_parallel(model, ["cpu"], sharded=False)
+    ids = torch.randint(0, 80, (2, 9))
+    with torch.no_grad():
+        wrapped(input_ids=ids)  # one good step on both ranks
+    dist.barrier()
+    if rank == 1:
+        open(os.path.join(result_dir, "left1"), "w").close()
+        os._exit(0)  # gone without a goodbye
+    started = time.monotonic()
+    try:
+        with torch.no_grad():
+            wrapped(input_ids=ids)
+    except Exception as exc:  # gloo reports a closed connection or a timeout
+        elapsed = time.monotonic() - started
+        assert elapsed < 60, elapsed
+        local = model.model.norm.weight.sum().item()  # the process is alive and can keep computing locally
+        with open(os.path.join(result_dir, "ok0"), "w") as f:
+            f.write(f"{type(exc).__name__} after {elapsed:.1f}s, local {local}")
+        os._exit(0)  # (a clean destroy_process_group would wait for the peer)
+    raise AssertionError("the forward pass succeeded although the peer had left")
+
+
+def test_distributed_peer_leaves_between_steps(tmp_path):
+    mp.spawn(_leaver_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    assert sorted(os.listdir(tmp_path)) == ["left1", "ok0"]
