@@ -322,6 +322,30 @@ def get_codegen_config(model_config, devices: Sequence[torch.device]) -> Config:
     )
 
 
+class SplitMultiQueryQKV(Split):
+    """Fused ``query_key_value`` of a multi-query Falcon (falcon-7b layout): ``heads`` query heads followed by ONE shared
+    key head and ONE shared value head.  The query heads are dealt out in whole heads; the shared key / value rows are
+    kept on every rank.  (For training note that those shared rows then behave like any replicated parameter: each rank
+    sees the gradient that flows through its own query heads only.)  The reference has no table for this layout."""
+
+    def __init__(self, world_size: int, head_dim: int):
+        super().__init__(world_size, dim=0)
+        self.head_dim = head_dim
+
+    def __call__(self, tensor, rank: int):
+        q_rows = tensor.shape[0] - 2 * self.head_dim
+        start, stop = unit_bounds(q_rows // self.head_dim, self.world_size, rank)
+        return torch.cat([tensor[start * self.head_dim : stop * self.head_dim], tensor[q_rows:]], dim=0)
+
+    def undo(self, tensors):
+        shared = 2 * self.head_dim
+        pieces = [t.detach().cpu() for t in tensors]
+        return torch.cat([t[: t.shape[0] - shared] for t in pieces] + [pieces[0][-shared:]], dim=0)
+
+    def __repr__(self):
+        return f"SplitMultiQueryQKV(world_size={self.world_size}, head_dim={self.head_dim})"
+
+
 def get_falcon_config(model_config, devices: Sequence[torch.device]) -> Config:
     """Falcon / RefinedWeb (new-decoder layout): fused QKV rows are ``[kv group][q_per_kv q heads | k | v]``.
     The block computes attention and MLP in parallel from the same input, so both partial
@@ -334,10 +358,21 @@ def get_falcon_config(model_config, devices: Sequence[torch.device]) -> Config:
     num_kv = _cfg(model_config, "n_head_kv", "num_kv_heads", default=heads if not getattr(model_config, "multi_query", False) else 1)
     head_dim = model_config.hidden_size // heads
     q_per_kv = heads // num_kv
+    # multi-query models of the older layout (falcon-7b): all query heads, then one shared key and one shared value head
+    new_layout = getattr(model_config, "new_decoder_architecture", hasattr(model_config, "n_head_kv"))
+    shared_kv = bool(getattr(model_config, "multi_query", False)) and not new_layout and heads > 1
+    if shared_kv:
+        num_kv, q_per_kv = 1, heads
+    elif num_kv < world:
+        raise ValueError(f"Falcon with {num_kv} key/value groups cannot be split over {world} ranks by groups "
+                         "(every rank needs at least one group)")
+    qkv_action = SplitMultiQueryQKV(world, head_dim) if shared_kv else SplitInChunks(world, dim=0, chunk_size=(q_per_kv + 2) * head_dim)
+    dense_chunk = head_dim if shared_kv else q_per_kv * head_dim
+    local_heads = partial(split_num_heads, world_size=world) if shared_kv else _grouped_heads(q_per_kv, world)
     return Config(
         state_rules={
-            r".*self_attention\.query_key_value\.weight$": SplitInChunks(world, dim=0, chunk_size=(q_per_kv + 2) * head_dim),
-            r".*self_attention\.dense\.weight$": SplitInChunks(world, dim=1, chunk_size=q_per_kv * head_dim),
+            r".*self_attention\.query_key_value\.weight$": qkv_action,
+            r".*self_attention\.dense\.weight$": SplitInChunks(world, dim=1, chunk_size=dense_chunk),
             r".*mlp\.dense_h_to_4h\.weight$": Split(world, dim=0),
             r".*mlp\.dense_4h_to_h\.weight$": Split(world, dim=1),
             r".*word_embeddings\.weight$": Split(world, dim=1),
@@ -357,7 +392,7 @@ def get_falcon_config(model_config, devices: Sequence[torch.device]) -> Config:
             r".*self_attention$": {
                 "num_kv": partial(split_num_heads, world_size=world),        # remote-code RWForCausalLM
                 "num_kv_heads": partial(split_num_heads, world_size=world),  # transformers' FalconAttention
-                "num_heads": _grouped_heads(q_per_kv, world),
+                "num_heads": local_heads,
             }
         },
     )

@@ -123,3 +123,41 @@ def test_hf_save_pretrained_round_trip(tmp_path):
     with torch.no_grad():
         got = reloaded(input_ids=ids).logits
     torch.testing.assert_close(got, want, atol=1e-6, rtol=1e-6)
+
+
+@pytest.mark.parametrize("layout", ["multi_query", "multi_query_sequential", "per_head", "grouped"])
+@pytest.mark.parametrize("world", [2, 3])
+def test_hf_falcon_layouts(layout, world):
+    """The four fused-QKV layouts of Falcon: multi-query (falcon-7b: all query heads, then one shared key and value head,
+    with the attention / MLP branches in parallel or in sequence), one (q, k, v) triple per head (falcon-rw) and key / value
+    groups (falcon-40b).  Chained cached calls and the un-sharded save must match the unsplit model."""
+    kw = {"multi_query": dict(multi_query=True, new_decoder_architecture=False, parallel_attn=True),
+          "multi_query_sequential": dict(multi_query=True, new_decoder_architecture=False, parallel_attn=False),
+          "per_head": dict(multi_query=False, new_decoder_architecture=False, parallel_attn=True),
+          "grouped": dict(num_kv_heads=3, new_decoder_architecture=True)}[layout]
+    cfg = AutoConfig.for_model(model_type="falcon", vocab_size=V, hidden_size=48, num_hidden_layers=2, num_attention_heads=6, bias=False, alibi=False, **kw)
+    torch.manual_seed(0)
+    model = AutoModelForCausalLM.from_config(cfg, attn_implementation="eager").eval()
+    a, b = torch.randint(0, V, (2, 7)), torch.randint(0, V, (2, 1))
+    with torch.no_grad():
+        r1 = model(input_ids=a, use_cache=True)
+        r2 = model(input_ids=b, past_key_values=r1.past_key_values, use_cache=True)
+    torch.manual_seed(0)
+    wrapped = tp.tensor_parallel(AutoModelForCausalLM.from_config(cfg, attn_implementation="eager").eval(), ["cpu"] * world)
+    with torch.no_grad():
+        o1 = wrapped(input_ids=a, use_cache=True)
+        o2 = wrapped(input_ids=b, past_key_values=o1.past_key_values, use_cache=True)
+    torch.testing.assert_close(o1.logits, r1.logits, atol=3e-5, rtol=1e-4)
+    torch.testing.assert_close(o2.logits, r2.logits, atol=3e-5, rtol=1e-4)
+    with tp.save_tensor_parallel(wrapped):
+        merged = wrapped.state_dict()
+    for key, value in model.state_dict().items():
+        assert torch.equal(merged[key], value), key
+
+
+def test_hf_falcon_too_few_groups_is_refused():
+    cfg = AutoConfig.for_model(model_type="falcon", vocab_size=V, hidden_size=48, num_hidden_layers=1, num_attention_heads=6, num_kv_heads=2,
+                               new_decoder_architecture=True, bias=False, alibi=False)
+    model = AutoModelForCausalLM.from_config(cfg, attn_implementation="eager")
+    with pytest.raises(ValueError, match="key/value groups"):
+        tp.tensor_parallel(model, ["cpu"] * 3)
