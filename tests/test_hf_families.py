@@ -161,3 +161,29 @@ def test_hf_falcon_too_few_groups_is_refused():
     model = AutoModelForCausalLM.from_config(cfg, attn_implementation="eager")
     with pytest.raises(ValueError, match="key/value groups"):
         tp.tensor_parallel(model, ["cpu"] * 3)
+
+
+UNEVEN = {
+    "llama_2kv_3ranks": (3, dict(model_type="llama", vocab_size=V, hidden_size=48, intermediate_size=64, num_hidden_layers=2, num_attention_heads=6, num_key_value_heads=2)),
+    "llama_mqa": (2, dict(model_type="llama", vocab_size=V, hidden_size=48, intermediate_size=64, num_hidden_layers=2, num_attention_heads=6, num_key_value_heads=1)),
+    "gpt2_4heads_3ranks": (3, CASES["gpt2"]),
+    "bloom_4heads_3ranks": (3, CASES["bloom"]),
+    "gpt_neox_4heads_3ranks": (3, CASES["gpt_neox"]),
+    "opt_4heads_3ranks": (3, CASES["opt"]),
+    "gptj_4heads_3ranks": (3, CASES["gptj"]),
+}
+
+
+@pytest.mark.parametrize("case", list(UNEVEN))
+def test_hf_uneven_head_splits(case):
+    """Head counts that do not divide by the number of ranks (some ranks own one head more; a rank may own none)."""
+    world, kw = UNEVEN[case]
+    torch.manual_seed(0)
+    model = AutoModelForCausalLM.from_config(AutoConfig.for_model(**kw), attn_implementation="eager").eval()
+    ids = torch.randint(0, V, (2, 7))
+    with torch.no_grad():
+        want = model(input_ids=ids).logits
+    wrapped = tp.tensor_parallel(model, ["cpu"] * world, sharded=True)
+    with torch.no_grad():
+        got = wrapped(input_ids=ids).logits
+    torch.testing.assert_close(got, want, atol=3e-5, rtol=1e-4)
