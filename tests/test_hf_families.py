@@ -187,3 +187,36 @@ def test_hf_uneven_head_splits(case):
     with torch.no_grad():
         got = wrapped(input_ids=ids).logits
     torch.testing.assert_close(got, want, atol=3e-5, rtol=1e-4)
+
+
+def test_hf_t5_training_step_with_zero3():
+    """Seq2seq training step on the Hugging Face T5 class (gated-GeLU, untied head - the FLAN-T5 shape): loss, gradients of
+    the tensor-parallel slices and of the ZeRO-3 flat shards equal those of the unsplit model."""
+    from transformers import T5ForConditionalGeneration
+
+    torch.manual_seed(0)
+    cfg = AutoConfig.for_model(model_type="t5", vocab_size=V, d_model=32, d_kv=8, d_ff=48, num_layers=2, num_heads=4, decoder_start_token_id=0,
+                               feed_forward_proj="gated-gelu", tie_word_embeddings=False, dropout_rate=0.0)
+    model = T5ForConditionalGeneration(cfg)
+    ids, labels = torch.randint(0, V, (2, 7)), torch.randint(0, V, (2, 4))
+    ref = model(input_ids=ids, labels=labels)
+    ref.loss.backward()
+    grads = {n: p.grad.clone() for n, p in model.named_parameters() if p.grad is not None}
+    model.zero_grad()
+    wrapped = tp.tensor_parallel(model, ["cpu", "cpu"], sharded=True)
+    out = wrapped(input_ids=ids, labels=labels)
+    torch.testing.assert_close(out.loss, ref.loss, atol=1e-5, rtol=1e-5)
+    out.loss.backward()
+    inner = wrapped.wrapped_model
+    manager = inner.sharding_manager
+    stacked = torch.stack([f.grad for f in manager.flat_shards])
+    for name, grad in zip(manager.sharded_param_names, manager._combine(stacked)):
+        torch.testing.assert_close(grad, grads[name.replace("tp_wrapped_module.", "")], atol=3e-5, rtol=1e-3, msg=name)
+    for rank, shard in enumerate(inner.module_shards):
+        for shard_name, p in shard.named_parameters():
+            original = shard_name.replace("tp_wrapped_module.", "")
+            for pattern, action in inner.tensor_parallel_config.state_rules.items():
+                if pattern.search(original):
+                    expected = grads[original] if isinstance(action, tp.Scale) else action(grads[original], rank)
+                    torch.testing.assert_close(p.grad, expected, atol=3e-5, rtol=1e-3, msg=f"{shard_name}@{rank}")
+                    break
