@@ -15,6 +15,15 @@ from tensor_parallel_b200.parallel.kv import PerDeviceTensors
 
 
 def reorder_cache(past, beam_idx: torch.Tensor):
+    if past is not None and not isinstance(past, (tuple, list)):
+        # a stateful cache object (``transformers.Cache``): it reorders itself in place; under the single-process
+        # runtime the call is mirrored to the other ranks' caches
+        for method in ("reorder_cache", "batch_select_indices"):
+            if hasattr(past, method):
+                getattr(past, method)(beam_idx)
+                return past
+        raise TypeError(f"cannot reorder a cache of type {type(past).__name__} for beam search")
+
     def pick(entry):
         if isinstance(entry, PerDeviceTensors):
             return PerDeviceTensors(*(t.index_select(0, beam_idx.to(t.device)) for t in entry.tensors))

@@ -166,6 +166,12 @@ def _hf_worker(rank, world, port, result_dir):
             o2 = wrapped(input_ids=b, past_key_values=o1.past_key_values, use_cache=True)
         torch.testing.assert_close(o1.logits, r1.logits, atol=3e-5, rtol=1e-4)
         torch.testing.assert_close(o2.logits, r2.logits, atol=3e-5, rtol=1e-4)
+        # generation through this runtime's own loop (the wrapper is a plain module here): the stateful cache reorders itself
+        prompt = torch.randint(0, 96, (2, 6))
+        want_greedy = model.generate(prompt, max_new_tokens=5, do_sample=False, pad_token_id=0)
+        want_beams = model.generate(prompt, max_new_tokens=5, do_sample=False, num_beams=3, pad_token_id=0)
+        assert torch.equal(wrapped.generate(prompt, max_new_tokens=5), want_greedy)
+        assert torch.equal(wrapped.generate(prompt, max_new_tokens=5, num_beams=3), want_beams)
         open(os.path.join(result_dir, f"ok{rank}"), "w").close()
     finally:
         dist.destroy_process_group()
