@@ -132,3 +132,59 @@ def run_ranks(world: int, calls: Sequence[Tuple[int, int]], tile_keyed: bool = T
     if failures:
         raise failures[0]
     return [max(errors[r][c] for r in range(world)) for c in range(len(calls))]
+
+
+# ---------------------------------------------------------------------------------------------------
+# stream-K work decomposition (``WorkIter`` in csrc/gemm_sm100.cu), in the kernel's integer arithmetic
+# ---------------------------------------------------------------------------------------------------
+
+
+def stream_k_items(grid: int, tiles: int, k_blocks: int):
+    """Per CTA, the list of work items ``(tile, kb0, kb1, ordinal, contributors)`` that the kernel's ``WorkIter`` yields
+    in stream-K mode: the ``tiles * k_blocks`` units are dealt out as one contiguous range per CTA
+    (``boundary(c) = c * units // grid``) and a range is cut at tile boundaries."""
+    units = tiles * k_blocks
+
+    def boundary(c):
+        return c * units // grid
+
+    def owner(unit):
+        c = unit * grid // units
+        while boundary(c + 1) <= unit:
+            c += 1
+        return c
+
+    per_cta = []
+    for cta in range(grid):
+        u, u_end, items = boundary(cta), boundary(cta + 1), []
+        while u < u_end:
+            tile, kb0 = divmod(u, k_blocks)
+            length = min(k_blocks - kb0, u_end - u)
+            if length == k_blocks:
+                ordinal, contributors = 0, 1
+            else:
+                first = owner(tile * k_blocks)
+                ordinal, contributors = cta - first, owner(tile * k_blocks + k_blocks - 1) - first + 1
+            items.append((tile, kb0, kb0 + length, ordinal, contributors))
+            u += length
+        per_cta.append(items)
+    return per_cta
+
+
+def stream_k_grid(tiles: int, kb64: int, sms: int = 148, max_contributors: int = 8):
+    """The planner's choice (``tpb_gemm_plan`` with stream-K enabled): k-blocks per stage, grid size and the bound on the
+    CTAs that share one tile; ``None`` when whole tiles are balanced already."""
+    kbox = 4
+    while kbox > 1 and tiles * ((kb64 + kbox - 1) // kbox) < 4 * sms:
+        kbox >>= 1
+    k_blocks = (kb64 + kbox - 1) // kbox
+    units = tiles * k_blocks
+    grid = min(sms, max(units // 2, 1))
+    if tiles >= grid and tiles % grid == 0:
+        return None
+    while True:
+        per = units // grid
+        contributors = (k_blocks + per - 1) // per + 1
+        if contributors <= max_contributors or grid == 1:
+            return kbox, k_blocks, grid, max(contributors, 2)
+        grid -= 1

@@ -53,3 +53,52 @@ def test_nvtx_ranges_nest_and_are_free_when_off():
         assert outer() == 7 and calls[-1] == 2 and tracing._depth == 0
     finally:
         tracing.enable(False)
+
+
+def _check_decomposition(grid, tiles, k_blocks, bound=None):
+    per_cta = pm.stream_k_items(grid, tiles, k_blocks)
+    covered = {}
+    by_tile = {}
+    for cta, items in enumerate(per_cta):
+        for tile, kb0, kb1, ordinal, contributors in items:
+            assert 0 <= kb0 < kb1 <= k_blocks
+            for kb in range(kb0, kb1):
+                assert (tile, kb) not in covered, "a unit was dealt out twice"
+                covered[(tile, kb)] = cta
+            by_tile.setdefault(tile, []).append((cta, ordinal, contributors))
+    assert len(covered) == tiles * k_blocks, "a unit was left out"
+    for tile, entries in by_tile.items():
+        ctas = sorted(c for c, _, _ in entries)
+        assert len(set(ctas)) == len(ctas), "a CTA holds two pieces of one tile"
+        assert {o for _, o, _ in entries} == set(range(len(entries))), "ordinals must number the contributors 0..n-1"
+        assert all(n == len(entries) for _, _, n in entries), "every contributor must know the same count"
+        assert [o for _, o, _ in sorted(entries)] == list(range(len(entries))), "ordinals follow the CTA order (deterministic sum)"
+        if bound is not None:
+            assert len(entries) <= bound
+    return per_cta
+
+
+def test_stream_k_decomposition_covers_every_unit_once():
+    import random
+
+    rng = random.Random(0)
+    for _ in range(300):
+        tiles, k_blocks = rng.randint(1, 300), rng.randint(1, 200)
+        grid = rng.randint(1, min(148, tiles * k_blocks))
+        _check_decomposition(grid, tiles, k_blocks)
+
+
+@pytest.mark.parametrize("features,k", [(4096, 4096), (12288, 4096), (22016, 4096), (4096, 11008), (32000, 4096), (1536, 4096),
+                                        (2752, 4096), (4096, 1376), (4096, 512), (4000, 4096), (256, 64), (65024, 8192), (128, 16384)])
+def test_stream_k_planner_bounds_the_contributors(features, k):
+    """For the shapes of the Llama / Falcon layers (whole and sharded 2- to 8-way) the planner's grid keeps the number of
+    CTAs that share one tile within the parking slots of the workspace."""
+    tiles, kb64 = (features + 127) // 128, (k + 63) // 64
+    plan = pm.stream_k_grid(tiles, kb64)
+    if plan is None:
+        return
+    kbox, k_blocks, grid, bound = plan
+    assert bound <= 8
+    per_cta = _check_decomposition(grid, tiles, k_blocks, bound=bound)
+    busy = [sum(kb1 - kb0 for _, kb0, kb1, _, _ in items) for items in per_cta]
+    assert max(busy) - min(busy) <= 1, "every CTA streams the same number of units (give or take one)"
