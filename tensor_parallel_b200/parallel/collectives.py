@@ -45,6 +45,11 @@ class RankGroup:
         with self._lock:
             self._waiters.append(rendezvous)
 
+    def __deepcopy__(self, memo):
+        # a copy of a model gets a failure domain of its own (fresh lock, no history); the copied collectives find it
+        # through the memo and register themselves again
+        return RankGroup(self.world_size, self.timeout)
+
     @property
     def failure(self) -> Optional[BaseException]:
         return self._failure
@@ -81,6 +86,11 @@ class Rendezvous:
         self._round = 0
         self._published: List[Any] = []
         group.register(self)
+
+    def __deepcopy__(self, memo):
+        import copy
+
+        return Rendezvous(copy.deepcopy(self.group, memo))
 
     def wake(self):
         with self._cond:

@@ -129,6 +129,9 @@ class RankExecutor:
         self._lock = threading.Lock()
         _live_executors.add(self)
 
+    def __deepcopy__(self, memo):
+        return RankExecutor(self.world_size)  # threads are not copied; the copy starts its own on first use
+
     def _ensure(self):
         with self._lock:
             while len(self._workers) < self.world_size:

@@ -169,3 +169,25 @@ def test_moving_wrapped_model_is_detected():
     wrapped._sanity_check_params[1] = nn.Parameter(torch.empty(0, device="meta"), requires_grad=False)
     with pytest.raises(ValueError, match="no longer on their devices"):
         wrapped(torch.randn(2, 4))
+
+
+@pytest.mark.parametrize("sharded", [False, True])
+def test_deepcopy_of_a_wrapped_model(sharded):
+    """A wrapped model can be deep-copied (the copy gets its own rank threads and failure domain) and trained without
+    touching the original."""
+    import copy
+
+    from tensor_parallel_b200.models.llama import LlamaConfig, LlamaForCausalLM
+
+    torch.manual_seed(0)
+    model = LlamaForCausalLM(LlamaConfig(vocab_size=90, hidden_size=32, intermediate_size=86, num_hidden_layers=2, num_attention_heads=4))
+    ids = torch.randint(0, 90, (2, 9))
+    wrapped = tp.tensor_parallel(model, ["cpu", "cpu"], sharded=sharded)
+    with torch.no_grad():
+        want = wrapped(input_ids=ids).logits
+    clone = copy.deepcopy(wrapped)
+    with torch.no_grad():
+        torch.testing.assert_close(clone(input_ids=ids).logits, want)
+    clone(input_ids=ids, labels=ids).loss.backward()
+    assert all(p.grad is None for p in wrapped.parameters())
+    assert any(p.grad is not None for p in clone.parameters())
