@@ -50,6 +50,9 @@ class RankGroup:
         # through the memo and register themselves again
         return RankGroup(self.world_size, self.timeout)
 
+    def __reduce__(self):  # pickling (torch.save of a whole model): locks and history are not part of the state
+        return (RankGroup, (self.world_size, self.timeout))
+
     @property
     def failure(self) -> Optional[BaseException]:
         return self._failure
@@ -91,6 +94,9 @@ class Rendezvous:
         import copy
 
         return Rendezvous(copy.deepcopy(self.group, memo))
+
+    def __reduce__(self):
+        return (Rendezvous, (self.group,))
 
     def wake(self):
         with self._cond:

@@ -132,6 +132,9 @@ class RankExecutor:
     def __deepcopy__(self, memo):
         return RankExecutor(self.world_size)  # threads are not copied; the copy starts its own on first use
 
+    def __reduce__(self):
+        return (RankExecutor, (self.world_size,))
+
     def _ensure(self):
         with self._lock:
             while len(self._workers) < self.world_size:
