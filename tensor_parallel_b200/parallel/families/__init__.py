@@ -39,6 +39,8 @@ PREDEFINED_CONFIGS: Dict[str, ConfigGetter] = {
     "gpt_neox": get_gpt_neox_config,
     "codegen": get_codegen_config,
     "llama": get_llama_config,
+    "mistral": get_llama_config,  # same module names and fused-free q / k / v / o, gate / up / down layout as Llama
+    "qwen2": get_llama_config,    # ditto, with biases on q / k / v (the rules match weight and bias)
     "opt": get_opt_config,
     "RefinedWeb": get_falcon_config,
     "RefinedWebModel": get_falcon_config,

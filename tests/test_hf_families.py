@@ -19,6 +19,8 @@ CASES = {
     "opt": dict(model_type="opt", vocab_size=V, hidden_size=32, num_hidden_layers=2, num_attention_heads=4, ffn_dim=64, max_position_embeddings=64, word_embed_proj_dim=32),
     "gptj": dict(model_type="gptj", vocab_size=V, n_embd=32, n_layer=2, n_head=4, rotary_dim=4, n_positions=64),
     "falcon": dict(model_type="falcon", vocab_size=V, hidden_size=32, num_hidden_layers=2, num_attention_heads=4, num_kv_heads=2, new_decoder_architecture=True),
+    "mistral": dict(model_type="mistral", vocab_size=V, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2),
+    "qwen2": dict(model_type="qwen2", vocab_size=V, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2),
     "codegen": dict(model_type="codegen", vocab_size=V, n_embd=64, n_layer=2, n_head=8, rotary_dim=4, n_positions=64),
 }
 
@@ -46,7 +48,7 @@ def test_hf_decoder_families(name, sharded):
     torch.testing.assert_close(got, want, atol=3e-5, rtol=1e-4)
 
 
-@pytest.mark.parametrize("name", ["llama", "gpt2", "falcon"])
+@pytest.mark.parametrize("name", ["llama", "gpt2", "falcon", "mistral", "qwen2"])
 def test_hf_chained_cache_calls(name):
     model = _model(name)
     a, b = torch.randint(0, V, (2, 5)), torch.randint(0, V, (2, 1))
