@@ -40,6 +40,9 @@ def get_llama_config(model_config, devices: Sequence[torch.device]) -> Config:
         "num_heads": _grouped_heads(q_per_kv, world),
         "num_key_value_heads": partial(split_num_heads, world_size=world),
     }
+    # a head tied to the (hidden-split) embedding table keeps that split and becomes row-parallel: it reads its slice of
+    # the hidden state and the partial logits are summed (small Llama-3.2 / Qwen2 checkpoints tie the two)
+    tied = bool(getattr(model_config, "tie_word_embeddings", False))
     return Config(
         state_rules={
             r".*self_attn\.q_proj\.(weight|bias)$": SplitInChunks(world, dim=0, chunk_size=q_per_kv * head_dim),
@@ -51,14 +54,14 @@ def get_llama_config(model_config, devices: Sequence[torch.device]) -> Config:
             r".*mlp\.up_proj\.weight$": Split(world, dim=0),
             r".*mlp\.down_proj\.weight$": Split(world, dim=1),
             r".*embed_tokens\.weight$": Split(world, dim=1),
-            r".*lm_head\.weight$": Split(world, dim=0),
+            r".*lm_head\.weight$": Split(world, dim=1 if tied else 0),
         },
-        input_rules={r".*self_attn$": {"past_key_value": select_kv_for_rank}},
+        input_rules={r".*self_attn$": {"past_key_value": select_kv_for_rank}, **({r".*lm_head$": {0: "split -1"}} if tied else {})},
         output_rules={
             r".*self_attn$": {0: "sum", 2: "gather_kv"},
             r".*mlp$": {0: "sum"},
             r".*embed_tokens$": {0: "gather -1"},
-            r".*lm_head$": {0: "gather -1"},
+            r".*lm_head$": {0: "sum" if tied else "gather -1"},
         },
         attr_rules={r".*self_attn$": attrs},
     )

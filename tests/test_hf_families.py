@@ -165,6 +165,30 @@ def test_hf_falcon_too_few_groups_is_refused():
         tp.tensor_parallel(model, ["cpu"] * 3)
 
 
+@pytest.mark.parametrize("model_type", ["llama", "qwen2"])
+@pytest.mark.parametrize("world", [2, 3])
+def test_hf_tied_head_keeps_the_tie(model_type, world):
+    """``tie_word_embeddings=True`` (small Llama-3.2 / Qwen2 checkpoints): the head shares the hidden-split embedding slice,
+    reads its slice of the hidden state and the partial logits are summed; the un-sharded save equals the original."""
+    torch.manual_seed(0)
+    cfg = AutoConfig.for_model(model_type=model_type, vocab_size=V, hidden_size=32, intermediate_size=64, num_hidden_layers=2,
+                               num_attention_heads=4, num_key_value_heads=2, tie_word_embeddings=True)
+    model = AutoModelForCausalLM.from_config(cfg, attn_implementation="eager").eval()
+    assert model.lm_head.weight is model.model.embed_tokens.weight
+    ids = torch.randint(0, V, (2, 7))
+    with torch.no_grad():
+        want = model(input_ids=ids).logits
+    wrapped = tp.tensor_parallel(model, ["cpu"] * world, sharded=True)
+    with torch.no_grad():
+        got = wrapped(input_ids=ids).logits
+    torch.testing.assert_close(got, want, atol=3e-5, rtol=1e-4)
+    with tp.save_tensor_parallel(wrapped):
+        merged = wrapped.state_dict()
+    assert set(merged) == set(model.state_dict())
+    for key, value in model.state_dict().items():
+        assert torch.equal(merged[key], value), key
+
+
 UNEVEN = {
     "llama_2kv_3ranks": (3, dict(model_type="llama", vocab_size=V, hidden_size=48, intermediate_size=64, num_hidden_layers=2, num_attention_heads=6, num_key_value_heads=2)),
     "llama_mqa": (2, dict(model_type="llama", vocab_size=V, hidden_size=48, intermediate_size=64, num_hidden_layers=2, num_attention_heads=6, num_key_value_heads=1)),
