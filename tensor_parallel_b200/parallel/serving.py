@@ -27,8 +27,10 @@ class ServingMixin:
         param = next(inner.parameters(), None)
         if getattr(cfg, "model_type", None) != "llama" or param is None or not param.is_cuda or param.dtype != torch.bfloat16:
             return None
-        if type(inner).__module__ != "tensor_parallel_b200.models.llama":
-            return None
+        if type(inner).__module__ != "tensor_parallel_b200.models.llama" or not hasattr(inner, "lm_head"):
+            return None  # (a bare LlamaModel without a head has nothing to generate from)
+        if getattr(cfg, "tie_word_embeddings", False):
+            return None  # the engine expects a vocabulary-split head; a tied head is hidden-split (the generic path serves it)
         world = getattr(self, "world_size", 1)
         eng = self._engine
         fits = eng is not None and eng.max_batch >= max_batch and eng.max_seq >= max_seq
