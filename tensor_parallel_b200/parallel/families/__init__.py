@@ -41,6 +41,9 @@ PREDEFINED_CONFIGS: Dict[str, ConfigGetter] = {
     "llama": get_llama_config,
     "mistral": get_llama_config,  # same module names and fused-free q / k / v / o, gate / up / down layout as Llama
     "qwen2": get_llama_config,    # ditto, with biases on q / k / v (the rules match weight and bias)
+    "qwen3": get_llama_config,    # per-head q / k norms act on head_dim and stay whole
+    "gemma": get_llama_config,    # head tied to the embedding table (handled by the table), explicit head_dim
+    "gemma2": get_llama_config,
     "opt": get_opt_config,
     "RefinedWeb": get_falcon_config,
     "RefinedWebModel": get_falcon_config,

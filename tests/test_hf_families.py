@@ -21,6 +21,10 @@ CASES = {
     "falcon": dict(model_type="falcon", vocab_size=V, hidden_size=32, num_hidden_layers=2, num_attention_heads=4, num_kv_heads=2, new_decoder_architecture=True),
     "mistral": dict(model_type="mistral", vocab_size=V, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2),
     "qwen2": dict(model_type="qwen2", vocab_size=V, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2),
+    "qwen3": dict(model_type="qwen3", vocab_size=V, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=8),
+    "gemma": dict(model_type="gemma", vocab_size=V, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=8),
+    "gemma2": dict(model_type="gemma2", vocab_size=V, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=8,
+                   query_pre_attn_scalar=8, sliding_window=16),
     "codegen": dict(model_type="codegen", vocab_size=V, n_embd=64, n_layer=2, n_head=8, rotary_dim=4, n_positions=64),
 }
 
@@ -48,7 +52,7 @@ def test_hf_decoder_families(name, sharded):
     torch.testing.assert_close(got, want, atol=3e-5, rtol=1e-4)
 
 
-@pytest.mark.parametrize("name", ["llama", "gpt2", "falcon", "mistral", "qwen2"])
+@pytest.mark.parametrize("name", ["llama", "gpt2", "falcon", "mistral", "qwen2", "qwen3", "gemma", "gemma2"])
 def test_hf_chained_cache_calls(name):
     model = _model(name)
     a, b = torch.randint(0, V, (2, 5)), torch.randint(0, V, (2, 1))
