@@ -37,6 +37,13 @@ class RefRMSNorm(nn.Module):
         return self.weight * x.to(dtype)
 
 
+def rotary_tables(position_ids, head_dim, theta, dtype):
+    inv_freq = 1.0 / (theta ** (torch.arange(0, head_dim, 2, device=position_ids.device, dtype=torch.float32) / head_dim))
+    ang = position_ids[:, None, :, None].float() * inv_freq
+    emb = torch.cat((ang, ang), dim=-1)
+    return emb.cos().to(dtype), emb.sin().to(dtype)
+
+
 def _rotate_half(x):
     a, b = x[..., : x.shape[-1] // 2], x[..., x.shape[-1] // 2 :]
     return torch.cat((-b, a), dim=-1)
@@ -55,15 +62,15 @@ class RefAttention(nn.Module):
         self.v_proj = nn.Linear(cfg.hidden_size, self.num_key_value_heads * self.head_dim, bias=False)
         self.o_proj = nn.Linear(self.num_heads * self.head_dim, cfg.hidden_size, bias=False)
 
-    def forward(self, hidden_states, attention_mask=None, position_ids=None, past_key_value=None, output_attentions=False, use_cache=False):
+    def forward(self, hidden_states, attention_mask=None, position_ids=None, past_key_value=None, output_attentions=False, use_cache=False,
+                position_embeddings=None):
         b, s, _ = hidden_states.shape
         q = self.q_proj(hidden_states).view(b, s, self.num_heads, self.head_dim).transpose(1, 2)
         k = self.k_proj(hidden_states).view(b, s, self.num_key_value_heads, self.head_dim).transpose(1, 2)
         v = self.v_proj(hidden_states).view(b, s, self.num_key_value_heads, self.head_dim).transpose(1, 2)
-        inv_freq = 1.0 / (self.rope_theta ** (torch.arange(0, self.head_dim, 2, device=q.device, dtype=torch.float32) / self.head_dim))
-        ang = position_ids[:, None, :, None].float() * inv_freq
-        emb = torch.cat((ang, ang), dim=-1)
-        cos, sin = emb.cos().to(q.dtype), emb.sin().to(q.dtype)
+        if position_embeddings is None:
+            position_embeddings = rotary_tables(position_ids, self.head_dim, self.rope_theta, q.dtype)
+        cos, sin = position_embeddings  # computed once per forward by the model, as Hugging Face's modelling code does
         q = q * cos + _rotate_half(q) * sin
         k = k * cos + _rotate_half(k) * sin
         if past_key_value is not None:
@@ -97,8 +104,9 @@ class RefDecoderLayer(nn.Module):
         self.input_layernorm = RefRMSNorm(cfg.hidden_size, cfg.rms_norm_eps)
         self.post_attention_layernorm = RefRMSNorm(cfg.hidden_size, cfg.rms_norm_eps)
 
-    def forward(self, h, position_ids, past_key_value=None, use_cache=False):
-        a, _, present = self.self_attn(self.input_layernorm(h), position_ids=position_ids, past_key_value=past_key_value, use_cache=use_cache)
+    def forward(self, h, position_ids, past_key_value=None, use_cache=False, position_embeddings=None):
+        a, _, present = self.self_attn(self.input_layernorm(h), position_ids=position_ids, past_key_value=past_key_value, use_cache=use_cache,
+                                       position_embeddings=position_embeddings)
         h = h + a
         return h + self.mlp(self.post_attention_layernorm(h)), present
 
@@ -109,6 +117,7 @@ class RefLlamaModel(nn.Module):
         self.embed_tokens = nn.Embedding(cfg.vocab_size, cfg.hidden_size)
         self.layers = nn.ModuleList([RefDecoderLayer(cfg) for _ in range(cfg.num_hidden_layers)])
         self.norm = RefRMSNorm(cfg.hidden_size, cfg.rms_norm_eps)
+        self.rotary_dim, self.rope_theta = cfg.hidden_size // cfg.num_attention_heads, cfg.rope_theta
 
     def forward(self, input_ids, past_key_values=None, use_cache=False):
         h = self.embed_tokens(input_ids)
@@ -116,8 +125,9 @@ class RefLlamaModel(nn.Module):
         offset = 0 if past_key_values is None else past_key_values[0][0].shape[2]
         position_ids = torch.arange(offset, offset + s, device=h.device)[None].expand(b, s)
         presents = []
+        rotary = rotary_tables(position_ids, self.rotary_dim, self.rope_theta, h.dtype)
         for i, layer in enumerate(self.layers):
-            h, present = layer(h, position_ids, None if past_key_values is None else past_key_values[i], use_cache)
+            h, present = layer(h, position_ids, None if past_key_values is None else past_key_values[i], use_cache, rotary)
             presents.append(present)
         return self.norm(h), tuple(presents)
 

@@ -1,21 +1,32 @@
-"""Headline benchmark: Llama-2-7B-shaped greedy decoding with a sharded KV cache.
+"""Headline benchmark: Llama-2-7B-shaped greedy decoding with a sharded KV cache, then a training step.
 
     python bench.py --gpus 1 --steps 256 --warmup 8
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \\
         bench.py --gpus N --steps K --warmup W [--impl reference]
 
 Config: 32 layers, d_model 4096, 32 heads (head_dim 128), SwiGLU FFN 11008, RMSNorm, vocab 32000, bf16,
-random-init weights, synthetic uniform token ids; prefill batch 8 x 2048, then greedy decode.  One *step*
-is one decode step for the whole batch (8 new tokens); the metric is decoded tokens per second of the
-whole job.  Prints ONE JSON line on rank 0.
+random-init weights, synthetic uniform token ids.
 
-Timing: CUDA events on the launching stream, barrier + synchronize on both sides, max over ranks.  Each
-step streams every weight shard and the KV cache (>= 1.7 GB per rank), far more than the 126 MB L2, so no
-explicit L2 flush is needed between steps.  `e2e` times the same steps driven from the host through the
-public API (`model.decode_step`): every step copies its input token ids from pinned host memory and reads
-the new ids back.
+Decode (``value``): prefill batch 8 x 2048, then greedy decode.  One *step* is one decode step for the whole batch
+(8 new tokens); the metric is decoded tokens per second of the whole job.  Timing: CUDA events on the launching
+stream, barrier + synchronize on both sides, max over ranks.  Each step streams every weight shard and the KV
+cache (>= 1.7 GB per rank), far more than the 126 MB L2, so no explicit L2 flush is needed between steps.  ``e2e``
+times the same steps driven from the host through the public API (``model.decode_step``): every step copies its
+input token ids from pinned host memory and reads the new ids back.
+
+Correctness of what is timed (``tokens_agree``, ``logits_rel_err``): before the model is sharded every rank holds
+the full weights, so a single-GPU engine on them produces 16 greedy tokens for two of the prompts; the N-rank
+engine is then stepped through the same 16 positions with those tokens fed in (teacher forcing, so that one
+flipped near-tie does not derail the rest) and must pick the same token at least 9 times out of 10.
+
+Training (``train_tokens_per_s``, after the decode part, same JSON line): forward + backward + AdamW step on a
+micro-batch of 4 x 2048 tokens, ``sharded=True`` (ZeRO-3) when N > 1; every step copies its batch from pinned host
+memory and reads the loss back (``bench_train.py`` holds the body).  ``--train-steps 0`` skips it.
+
+Prints ONE JSON line on rank 0.
 """
 import argparse
+import gc
 import json
 import os
 import statistics
@@ -30,51 +41,90 @@ REPO = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, REPO)
 
 BATCH, PROMPT = 8, 2048
+CHECK_SEQS, CHECK_TOKENS = 2, 16
 MODEL = dict(vocab_size=32000, hidden_size=4096, intermediate_size=11008, num_hidden_layers=32,
              num_attention_heads=32, num_key_value_heads=32, rms_norm_eps=1e-6, rope_theta=10000.0)
 
 
 class ClockSampler:
-    """Samples SM clocks / throttle reasons of the local GPUs with nvidia-smi while a region runs."""
+    """Samples SM clocks / throttle reasons of the given GPUs while a region runs: NVML from a thread every 10 ms
+    (short timed regions still get samples), ``nvidia-smi -lms`` as the fallback.  Read-only."""
 
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    # NVML clocks-event-reason bits
+    REASONS = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
 
-    def __init__(self):
-        self.lines, self.proc, self.thread = [], None, None
+    def __init__(self, gpu_indices):
+        self.gpus = list(gpu_indices)
+        self.sm, self.sm_max, self.reasons, self.power = [], [], set(), []
+        self.lines, self.proc, self.thread, self._stop, self.how = [], None, None, threading.Event(), None
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+            import pynvml
+
+            pynvml.nvmlInit()
+            handles = [pynvml.nvmlDeviceGetHandleByIndex(i) for i in self.gpus]
+            self.sm_max = [float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)) for h in handles]
+            read_reasons = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
+
+            def loop():
+                while not self._stop.is_set():
+                    for h in handles:
+                        try:
+                            self.sm.append(float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)))
+                            self.power.append(pynvml.nvmlDeviceGetPowerUsage(h) / 1000.0)
+                            bits = int(read_reasons(h))
+                            for name, bit in self.REASONS.items():
+                                if bits & bit:
+                                    self.reasons.add(name)
+                        except pynvml.NVMLError:
+                            pass
+                    self._stop.wait(0.01)
+
+            self.how = "nvml"
+            self.thread = threading.Thread(target=loop, daemon=True)
+            self.thread.start()
+            return
+        except Exception:  # noqa: BLE001 - NVML missing or refused: fall back to the command-line tool
+            pass
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             return
+        self.how = "nvidia-smi"
         self.thread = threading.Thread(target=lambda: [self.lines.append(l) for l in self.proc.stdout], daemon=True)
         self.thread.start()
 
-    def stop(self, gpu_indices):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, sm_max, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
-            f = [x.strip() for x in line.split(",")]
-            if len(f) < 9 or not f[0].isdigit() or int(f[0]) not in gpu_indices:
-                continue
+    def stop(self):
+        if self.how is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvml and nvidia-smi unavailable"]}
+        if self.how == "nvml":
+            self._stop.set()
+            self.thread.join(timeout=2)
+        else:
+            self.proc.terminate()
             try:
-                sm.append(float(f[1])); sm_max.append(float(f[2]))
-            except ValueError:
-                continue
-            for name, val in zip(names, f[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(sm_max) if sm_max else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+            names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+            for line in self.lines:
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 9 or not f[0].isdigit() or int(f[0]) not in self.gpus:
+                    continue
+                try:
+                    self.sm.append(float(f[1])); self.sm_max.append(float(f[2])); self.power.append(float(f[3]))
+                except ValueError:
+                    continue
+                for name, val in zip(names, f[5:9]):
+                    if val.lower().startswith("active"):
+                        self.reasons.add(name)
+        return {"sm_mhz": statistics.median(self.sm) if self.sm else None, "sm_max_mhz": max(self.sm_max) if self.sm_max else None,
+                "reasons": sorted(self.reasons), "samples": len(self.sm), "power_w_max": max(self.power) if self.power else None,
+                "source": self.how}
 
 
 def emit(payload):
@@ -98,8 +148,15 @@ def base_record(args, impl):
         "data": "synthetic uniform token ids, random-init weights (seed 0, N(0,0.02))", "impl": impl,
         "config": {"model": "Llama-2-7B-shaped (32L, d4096, 32h x 128, ffn 11008, vocab 32000)", "global_batch": BATCH,
                    "seq_len": PROMPT, "prefill": f"{BATCH}x{PROMPT}", "decode": "greedy, sharded KV cache",
-                   "parallelism": f"tp{args.gpus}", "l2": "per-step working set (weights + KV, >= 1.7 GB/rank) exceeds the 126 MB L2; no flush"},
+                   "parallelism": f"tp{args.gpus}", "l2": "per-step working set (weights + KV, >= 1.7 GB/rank) exceeds the 126 MB L2; no flush",
+                   "train": "micro-batch 4 x 2048, AdamW, sharded=True (ZeRO-3) when N > 1"},
     }
+
+
+def add_training(rec, train):
+    rec["train"] = train
+    if train and "value" in train:
+        rec["train_tokens_per_s"], rec["train_ms_per_step"], rec["train_loss"] = train["value"], train["ms_per_step"], train["loss"]
 
 
 # ------------------------------------------------------------------------------------------------
@@ -109,9 +166,10 @@ def base_record(args, impl):
 def run_ours(args):
     import torch.distributed as dist
 
+    import bench_train
     import tensor_parallel_b200 as tp
+    from tensor_parallel_b200.engine import DecoderEngine
     from tensor_parallel_b200.models.llama import LlamaConfig, LlamaForCausalLM
-    from tensor_parallel_b200.ops import native
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -129,13 +187,22 @@ def run_ours(args):
         model = LlamaForCausalLM(LlamaConfig(**MODEL))
     torch.set_default_dtype(torch.float32)
     model.eval()
-    tp_model = tp.tensor_parallel(model, [device])  # distributed mode when a process group exists
-    del model
-    torch.cuda.empty_cache()
-
     gen = torch.Generator().manual_seed(1)
     prompt = torch.randint(0, MODEL["vocab_size"], (BATCH, PROMPT), generator=gen)
-    max_new = 2 * (args.steps + args.warmup) + 16
+
+    # oracle for the correctness check: the full model on this GPU alone (every rank builds the same weights)
+    oracle = DecoderEngine(model, None, max_batch=CHECK_SEQS, max_seq=PROMPT + CHECK_TOKENS + 8)
+    ref_logits = oracle.prefill(prompt[:CHECK_SEQS])
+    ref_tokens = oracle.generate(prompt[:CHECK_SEQS], CHECK_TOKENS)[:, PROMPT:]  # [seqs, CHECK_TOKENS]
+    del oracle
+    gc.collect()
+    torch.cuda.empty_cache()
+
+    tp_model = tp.tensor_parallel(model, [device])  # distributed mode when a process group exists
+    del model
+    gc.collect()
+    torch.cuda.empty_cache()
+    max_new = 2 * (args.steps + args.warmup) + CHECK_TOKENS + 16
 
     def sync_all():
         torch.cuda.synchronize(device)
@@ -154,17 +221,29 @@ def run_ours(args):
     prefill_ms = t0.elapsed_time(t1)
     engine = tp_model._engine
     first = logits.argmax(-1)
+
+    # correctness: logits of the prompt pass and 15 teacher-forced decode steps against the single-GPU oracle
+    got, want = logits[:CHECK_SEQS].float(), ref_logits.float()
+    logits_rel_err = float(((got - want).norm() / want.norm()).item())
+    agree = int((first[:CHECK_SEQS] == ref_tokens[:, 0]).sum())
     engine.ids[:BATCH].copy_(first)
+    for i in range(1, CHECK_TOKENS):
+        engine.ids[:CHECK_SEQS].copy_(ref_tokens[:, i - 1])
+        engine.decode_step(BATCH)
+        agree += int((engine.next_ids[:CHECK_SEQS] == ref_tokens[:, i]).sum())
+    tokens_agree = agree / float(CHECK_SEQS * CHECK_TOKENS)
+    torch.cuda.synchronize(device)
+    engine.check_status()
 
     for _ in range(args.warmup):
         engine.decode_step(BATCH)
-    engine.comm.check_status() if engine.comm is not None else native.device_state(device).check_status()
+    engine.check_status()
 
-    sampler = ClockSampler()
-    sampler.start()
+    sampler = ClockSampler(visible_gpu_indices(world) if world > 1 else [visible_gpu_indices(max(local_rank + 1, 1))[local_rank]])
+    if rank == 0:
+        sampler.start()
     # ---- device-timed region: K graph replays ----
     sync_all()
-    launches_before = native.launch_count
     e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
@@ -185,13 +264,28 @@ def run_ours(args):
     h1.record()
     sync_all()
     e2e_ms = h0.elapsed_time(h1)
-    clocks = sampler.stop(visible_gpu_indices(world) if world > 1 else [visible_gpu_indices(max(local_rank + 1, 1))[local_rank]])
-    engine.comm.check_status() if engine.comm is not None else native.device_state(device).check_status()
+    engine.check_status()
+    kernels_per_step = engine.kernels_per_step
 
-    times = torch.tensor([ms, e2e_ms, prefill_ms], device=device, dtype=torch.float64)
+    times = torch.tensor([ms, e2e_ms, prefill_ms, tokens_agree, -logits_rel_err], device=device, dtype=torch.float64)
     if world > 1:
+        worst = times.clone()
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    ms, e2e_ms, prefill_ms = (float(t) for t in times.tolist())
+        dist.all_reduce(worst, op=dist.ReduceOp.MIN)  # agreement / error: the worst rank counts
+        times[3:] = worst[3:]
+    ms, e2e_ms, prefill_ms, tokens_agree, neg_err = (float(t) for t in times.tolist())
+    logits_rel_err = -neg_err
+
+    # ---- training step (frees the serving state first) ----
+    tp_model._engine = None
+    del engine, tp_model
+    gc.collect()
+    torch.cuda.empty_cache()
+    train = None
+    if args.train_steps > 0:
+        train = bench_train.train_ours("llama7b", args.train_steps, 3)
+    clocks = sampler.stop() if rank == 0 else None
+
     if rank == 0:
         rec = base_record(args, "tensor_parallel_b200")
         rec.update({
@@ -199,14 +293,20 @@ def run_ours(args):
             "e2e": {"value": BATCH * args.steps / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
                     "h2d_bytes_per_step": BATCH * 8, "d2h_bytes_per_step": BATCH * 8,
                     "api": "tensor_parallel(...).decode_step(pinned ids) -> pinned next ids"},
-            "gpu_launches": engine.kernels_per_step * args.steps, "kernels_per_step": engine.kernels_per_step,
+            "gpu_launches": kernels_per_step * args.steps, "kernels_per_step": kernels_per_step,
             "prefill_tokens_per_s": BATCH * PROMPT / (prefill_ms / 1e3), "prefill_ms": prefill_ms,
+            "tokens_agree": tokens_agree, "logits_rel_err": logits_rel_err,
+            "check": f"{CHECK_SEQS} prompts x {CHECK_TOKENS} tokens against a single-GPU engine on the unsharded weights, teacher-forced",
             "clocks": clocks,
         })
+        add_training(rec, train)
         emit(rec)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if tokens_agree < 0.9:
+        raise SystemExit(f"the {world}-rank engine agrees with the single-GPU engine on only {tokens_agree:.2f} of the checked tokens "
+                         f"(logits relative error {logits_rel_err:.3f}): the timed computation is wrong")
 
 
 # ------------------------------------------------------------------------------------------------
@@ -218,7 +318,7 @@ def run_reference(args):
     ref_dir = os.path.join(REPO, "baseline", "_ref")
     if not os.path.isdir(os.path.join(ref_dir, "tensor_parallel")):
         if rank == 0:
-            emit({"impl": "reference", "unavailable": "baseline/_ref/tensor_parallel is not installed (pip --target baseline/_ref /root/reference)"})
+            emit({"impl": "reference", "unavailable": "baseline/_ref/tensor_parallel is not installed (pip install --target baseline/_ref <reference checkout>)"})
         return
     if rank != 0:
         return  # the reference's multi-GPU mode is one process driving all GPUs from threads
@@ -234,6 +334,8 @@ def run_reference(args):
     except Exception as exc:  # noqa: BLE001
         emit({"impl": "reference", "unavailable": f"import failed: {exc!r}"[:300]})
         return
+    import bench_train
+
     if torch.cuda.device_count() < args.gpus:
         emit({"impl": "reference", "unavailable": f"needs {args.gpus} visible GPUs in one process, found {torch.cuda.device_count()}"})
         return
@@ -261,21 +363,25 @@ def run_reference(args):
         for d in devices:
             torch.cuda.synchronize(d)
 
+    sampler = ClockSampler(visible_gpu_indices(args.gpus))
     with torch.no_grad():
+        # one untimed prompt pass (library / allocator warm-up), then the timed one: the same schedule as this framework's arm
+        tp_model(prompt, past_key_values=None, use_cache=True, last_only=True)
         sync_all()
-        t0 = time.perf_counter()
+        torch.cuda.set_device(devices[0])
+        p0 = torch.cuda.Event(enable_timing=True); p1 = torch.cuda.Event(enable_timing=True)
+        p0.record()
         logits, past = tp_model(prompt, past_key_values=None, use_cache=True, last_only=True)
+        p1.record()
         sync_all()
-        prefill_ms = (time.perf_counter() - t0) * 1e3
+        prefill_ms = p0.elapsed_time(p1)
         nxt = logits[:, -1].argmax(-1, keepdim=True)
         for _ in range(args.warmup):
             logits, past = tp_model(nxt, past_key_values=past, use_cache=True, last_only=True)
             nxt = logits[:, -1].argmax(-1, keepdim=True)
-        sampler = ClockSampler()
         sampler.start()
         sync_all()
         e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
-        torch.cuda.set_device(devices[0])
         e0.record()
         for _ in range(args.steps):
             logits, past = tp_model(nxt, past_key_values=past, use_cache=True, last_only=True)
@@ -296,7 +402,20 @@ def run_reference(args):
         h1.record()
         sync_all()
         e2e_ms = h0.elapsed_time(h1)
-        clocks = sampler.stop(visible_gpu_indices(args.gpus))
+    del tp_model, past, logits, nxt
+    if args.gpus == 1:
+        del model
+    gc.collect()
+    for d in devices:
+        with torch.cuda.device(d):
+            torch.cuda.empty_cache()
+    train = None
+    if args.train_steps > 0:
+        try:
+            train = bench_train.train_reference("llama7b", args.gpus, args.train_steps, 3)
+        except Exception as exc:  # noqa: BLE001 - the decode numbers above stay valid
+            train = {"impl": "reference", "unavailable": f"training step failed: {exc!r}"[:300]}
+    clocks = sampler.stop()
     rec = base_record(args, "reference")
     rec.update({
         "value": BATCH * args.steps / (ms / 1e3), "ms_per_step": ms / args.steps,
@@ -305,6 +424,7 @@ def run_reference(args):
         "gpu_launches": 0, "prefill_tokens_per_s": BATCH * PROMPT / (prefill_ms / 1e3), "prefill_ms": prefill_ms, "clocks": clocks,
         "reference_mode": "tensor_parallel.TensorParallel, threaded single process, torch.cuda.nccl collectives, cuBLAS GEMMs, SDPA attention",
     })
+    add_training(rec, train)
     emit(rec)
 
 
@@ -313,6 +433,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--train-steps", type=int, default=4, help="optimizer steps timed after the decode part (0: skip training)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     args = ap.parse_args()
     if args.warmup < 3:

@@ -4,8 +4,11 @@
         -m tensor_parallel_b200.bench_comm
 
 For every case the kernel is launched ``iters`` times back to back between two CUDA events (weights rotate through
-a ring so they are not L2-resident); the reported time is the max over ranks.  Fused paths are compared with their
-un-fused composition and with the roofline ``max(FLOPs / measured GEMM peak, NVLink bytes / link bandwidth)``.
+a ring so they are not L2-resident); the reported time is the max over ranks.  The decode-sized cases are also
+replayed from one CUDA graph (``graph_us``: device time without host launch gaps, which is how the serving engine
+runs them).  Fused paths are compared with their un-fused composition and with the roofline
+``max(FLOPs / measured GEMM peak, NVLink bytes / link bandwidth)``; the stand-alone all-reduce with its variants
+(peer loads / stores, NVSwitch multimem) and with NCCL.
 """
 from __future__ import annotations
 
@@ -38,6 +41,35 @@ def timed(fn, iters=20, warm=3):
     return float(t.item())
 
 
+def graph_timed(fn, iters=32, replays=5):
+    """Device time per launch when ``iters`` launches are replayed from one CUDA graph (max over ranks)."""
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        for i in range(4):
+            fn(i)
+    torch.cuda.current_stream().wait_stream(stream)
+    torch.cuda.synchronize()
+    dist.barrier()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(iters):
+            fn(i)
+    graph.replay()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(replays):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) * 1e3 / (iters * replays)], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
 def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", rank)))
@@ -58,11 +90,14 @@ def main():
         src = rc.staging_view("in", (n,), torch.bfloat16)
         src.copy_(x)
         t_dev = timed(lambda i: rc.all_reduce(src))
+        t_peer = timed(lambda i: rc.all_reduce(src, force_algo=1))
+        t_nvls = timed(lambda i: rc.all_reduce(src, force_algo=4)) if rc.mc_base else None
         y = x.clone()
         t_nccl = timed(lambda i: dist.all_reduce(y))
         bus = 2 * (world - 1) / world * nbytes
-        report(case="all_reduce", bytes=nbytes, world=world, device_us=t_dev, nccl_us=t_nccl, device_busbw_gbs=bus / t_dev / 1e3,
-               nccl_busbw_gbs=bus / t_nccl / 1e3)
+        report(case="all_reduce", bytes=nbytes, world=world, device_us=t_dev, peer_two_shot_us=t_peer, nvls_two_shot_us=t_nvls,
+               nccl_us=t_nccl, device_busbw_gbs=bus / t_dev / 1e3, nccl_busbw_gbs=bus / t_nccl / 1e3,
+               link_roofline_us=nbytes / (LINK_GBS * 1e3))
 
     # row-parallel GEMM + all-reduce, decode shapes (per-rank K = full K / world)
     for name, feats, k_full in (("o_proj", 4096, 4096), ("down_proj", 4096, 11008)):
@@ -74,6 +109,13 @@ def main():
         o = torch.empty(8, feats, device=dev, dtype=torch.bfloat16)
         t_local = timed(lambda i: native.gemm_nt(x, ws[i % ring], out=o))
         t_fused = timed(lambda i: rc.gemm_allreduce(x, ws[i % ring], residual=res, out=o))
+        g_local = graph_timed(lambda i: native.gemm_nt(x, ws[i % ring], out=o))
+        by_protocol = {}
+        for label, flag in (("flagged_words", -1), ("arrival_counters", 1)):
+            native.LIB.tpb_gemm_disable_flagged_exchange(flag)
+            by_protocol[label] = graph_timed(lambda i: rc.gemm_allreduce(x, ws[i % ring], residual=res, out=o))
+        native.LIB.tpb_gemm_disable_flagged_exchange(0)
+        g_fused = graph_timed(lambda i: rc.gemm_allreduce(x, ws[i % ring], residual=res, out=o))
         stage = rc.staging_view("in", (8, feats), torch.bfloat16)
 
         def unfused(i):
@@ -91,7 +133,8 @@ def main():
         roof = max(2 * 8 * feats * k / (GEMM_PEAK_TFLOPS * 1e6), feats * k * 2 / (HBM_GBS * 1e3), 8 * feats * 4 * (world - 1) / (LINK_GBS * 1e3))
         report(case="gemm_allreduce_decode", layer=name, world=world, tokens=8, features=feats, k_local=k, local_gemm_us=t_local,
                fused_us=t_fused, gemm_then_device_allreduce_us=t_unfused, gemm_then_nccl_us=t_nccl, roofline_us=roof,
-               fraction_of_roofline=roof / t_fused)
+               graph_local_gemm_us=g_local, graph_fused_us=g_fused, graph_fused_by_protocol_us=by_protocol,
+               fraction_of_roofline=roof / g_fused)
 
     # all-gather + column-parallel GEMM (prefill shape): fused vs device all-gather + GEMM
     tokens, hidden, feats = 4096, 4096, 4096
@@ -114,6 +157,8 @@ def main():
            allgather_then_gemm_us=t_unfused, gemm_only_us=t_gemm, roofline_us=roof, fraction_of_roofline=roof / t_fused)
     torch.cuda.synchronize()
     rc.check_status()
+    dist.barrier()
+    C.close_all_heaps()  # (every rank unmaps its multicast view before anyone exits)
     dist.barrier()
     dist.destroy_process_group()
 

@@ -22,7 +22,7 @@ OBJ_DIR = PKG / "build" / "obj"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-    "-Xcompiler", "-fPIC", "--use_fast_math=false",
+    "-Xcompiler", "-fPIC",
 ]
 
 
@@ -47,7 +47,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     OBJ_DIR.mkdir(parents=True, exist_ok=True)
     LIB_DIR.mkdir(parents=True, exist_ok=True)
     header_time = _newest_header_mtime()
-    flags = [f for f in NVCC_FLAGS if not f.startswith("--use_fast_math")]
+    flags = list(NVCC_FLAGS) + os.environ.get("TPB_NVCC_FLAGS", "").split()  # e.g. -DTPB_GEMM_TRACE, -DTPB_BOUNDS
     jobs = []
     for src in sources():
         obj = OBJ_DIR / (src.stem + ".o")

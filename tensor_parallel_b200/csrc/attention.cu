@@ -11,6 +11,8 @@
 #include <math.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "attn_common.cuh"
 #include "launch.cuh"
 #include "ptx_sm100.cuh"
@@ -377,7 +379,7 @@ attn_decode_fused_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k,
                          float* __restrict__ part_o, float* __restrict__ part_ml, uint32_t* __restrict__ counters,
                          const int* __restrict__ pos_ptr, int q_heads, int kv_heads, int g_total, int g_offset, int max_seq,
                          int splits, float scale_log2e, int rotary_dim, float log2_theta, int interleaved, long long q_ld,
-                         long long k_ld, long long v_ld, const float2* __restrict__ rope_table) {
+                         long long k_ld, long long v_ld, const float2* __restrict__ rope_table, long long out_ld) {
   constexpr int EPL = D / 8;
   pdl_trigger();
   pdl_wait();
@@ -522,7 +524,7 @@ attn_decode_fused_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k,
     const int qh = kvh * g_total + g_offset + g;
     const long long row = (long long)b * q_heads + qh;
     if (splits == 1) {
-      out[row * D + d] = __float2bfloat16(ll > 0.f ? oo / ll : 0.f);
+      out[(long long)b * out_ld + (long long)qh * D + d] = __float2bfloat16(ll > 0.f ? oo / ll : 0.f);
     } else {
       part_o[(row * splits + split) * D + d] = oo;
       if (d == 0) { part_ml[(row * splits + split) * 2] = mm; part_ml[(row * splits + split) * 2 + 1] = ll; }
@@ -571,7 +573,7 @@ attn_decode_fused_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k,
       }
       mm = m_new;
     }
-    out[row * D + d] = __float2bfloat16(ll > 0.f ? oo / ll : 0.f);
+    out[(long long)b * out_ld + (long long)(kvh * g_total + g_offset + g) * D + d] = __float2bfloat16(ll > 0.f ? oo / ll : 0.f);
   }
 }
 
@@ -792,15 +794,19 @@ extern "C" int tpb_qkv_rope_append(const void* q, const void* k, const void* v, 
   return cudaGetLastError() == cudaSuccess ? TPB_OK : TPB_ERR_CUDA;
 }
 
+// Kernels launched by the most recent tpb_attn_decode / tpb_attn_decode_fused call of this thread.
+static thread_local int g_last_launches = 0;
+extern "C" int tpb_last_launches(void) { return g_last_launches; }
+
 // Opts a decode kernel instantiation in to its dynamic shared memory (once per kernel and device).
 template <auto Kernel>
 static bool dec_smem_ready(size_t bytes) {
-  static bool done[64] = {false};  // one array per kernel instantiation
+  static std::atomic<bool> done[64];  // one array per kernel instantiation; rank threads of one process may race here
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
-  if (!done[dev]) {
+  if (!done[dev].load(std::memory_order_acquire)) {
     if (cudaFuncSetAttribute(Kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes)) != cudaSuccess) return false;
-    done[dev] = true;
+    done[dev].store(true, std::memory_order_release);
   }
   return true;
 }
@@ -816,7 +822,7 @@ extern "C" int tpb_attn_decode(const void* q, const void* kcache, const void* vc
   const int g_total = q_heads / kv_heads;
   const float sl2 = scale * 1.4426950408889634f;
   dim3 grid(batch * kv_heads, splits);
-  int done = 0;
+  int done = 0, launches = 0;
   while (done < g_total) {
     const int left = g_total - done;
     const int gmax = head_dim == 128 ? 4 : 8;
@@ -834,13 +840,16 @@ extern "C" int tpb_attn_decode(const void* q, const void* kcache, const void* vc
     }
 #undef DEC
     done += gnow;
+    ++launches;
   }
   if (splits > 1) {
     if (head_dim == 128)
       attn_decode_combine_kernel<128><<<batch * q_heads, 128, 0, s>>>(part_o, part_ml, (bf16*)out, splits);
     else
       attn_decode_combine_kernel<64><<<batch * q_heads, 64, 0, s>>>(part_o, part_ml, (bf16*)out, splits);
+    ++launches;
   }
+  g_last_launches = launches;
   return cudaGetLastError() == cudaSuccess ? TPB_OK : TPB_ERR_CUDA;
 }
 
@@ -904,21 +913,23 @@ extern "C" int tpb_rope_table(void* table, int positions, int rotary_dim, float 
 // q_ld / k_ld / v_ld); pos_ptr[0] = position of the new token = number of tokens already cached.
 // part_o / part_ml as for tpb_attn_decode; counters: uint32 [batch * kv_heads], zeroed once by the caller.
 // rope_table: optional output of tpb_rope_table covering every position < max_seq (null: angles are computed in place).
+// out: [batch][q_heads * head_dim] with a row pitch of out_ld elements (<= 0: dense).
 extern "C" int tpb_attn_decode_fused(const void* q, const void* k, const void* v, void* kcache, void* vcache, void* out,
                                      float* part_o, float* part_ml, void* counters, const int* pos_ptr, int batch, int q_heads,
                                      int kv_heads, int head_dim, int max_seq, int splits, float scale, int rotary_dim, float theta,
                                      int interleaved, long long q_ld, long long k_ld, long long v_ld, const void* rope_table,
-                                     void* stream_) {
+                                     long long out_ld, void* stream_) {
   if (!q || !k || !v || !kcache || !vcache || !out || !pos_ptr || batch <= 0 || splits < 1 || q_heads % kv_heads) return TPB_ERR_ARG;
   if (splits > 1 && (!part_o || !part_ml || !counters)) return TPB_ERR_ARG;
   if (head_dim != 64 && head_dim != 128) return TPB_ERR_SIZE;
   if ((rotary_dim & 1) || rotary_dim > head_dim) return TPB_ERR_ARG;
+  if (out_ld <= 0) out_ld = (long long)q_heads * head_dim;  // (rows of `out` may be column slices of a wider buffer)
   cudaStream_t s = static_cast<cudaStream_t>(stream_);
   const int g_total = q_heads / kv_heads;
   const float sl2 = scale * 1.4426950408889634f;
   const float l2t = log2f(theta);
   dim3 grid(batch * kv_heads, splits);
-  int done = 0;
+  int done = 0, launches = 0;
   while (done < g_total) {
     const int left = g_total - done;
     const int gmax = head_dim == 128 ? 4 : 8;
@@ -928,7 +939,7 @@ extern "C" int tpb_attn_decode_fused(const void* q, const void* k, const void* v
   if (!dec_smem_ready<attn_decode_fused_kernel<D, G>>(dec_ring_bytes<D>())) return TPB_ERR_CUDA;                               \
   launch_kernel(attn_decode_fused_kernel<D, G>, grid, dim3(DEC_THREADS), dec_ring_bytes<D>(), s, (const bf16*)q, (const bf16*)k, (const bf16*)v, \
                 (bf16*)kcache, (bf16*)vcache, (bf16*)out, part_o, part_ml, (uint32_t*)counters, pos_ptr, q_heads, kv_heads, g_total, \
-                done, max_seq, splits, sl2, rotary_dim, l2t, interleaved, q_ld, k_ld, v_ld, (const float2*)rope_table)
+                done, max_seq, splits, sl2, rotary_dim, l2t, interleaved, q_ld, k_ld, v_ld, (const float2*)rope_table, out_ld)
     if (head_dim == 128) {
       if (gnow == 1) { DECF(128, 1); } else if (gnow == 2) { DECF(128, 2); } else { DECF(128, 4); }
     } else {
@@ -936,7 +947,9 @@ extern "C" int tpb_attn_decode_fused(const void* q, const void* k, const void* v
     }
 #undef DECF
     done += gnow;
+    ++launches;
   }
+  g_last_launches = launches;
   return cudaGetLastError() == cudaSuccess ? TPB_OK : TPB_ERR_CUDA;
 }
 

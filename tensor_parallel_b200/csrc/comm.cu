@@ -17,6 +17,12 @@
 //                two-shot : rank r reduces slice r from all peers and pushes it to every rank's output
 //   all-gather            : rank r pushes its slice to offset r of every rank's output
 //   reduce-scatter        : rank r reduces slice r from all peers into its local output
+// With an NVLink multicast (NVLS) view of the heap (symm.cu) the large-message variants let the NVSwitch do the work:
+//   all-reduce   two-shot : rank r fetches the switch-reduced slice r (multimem.ld_reduce, fp32 accumulation) and writes it
+//                           to every rank's output with one multimem.st: about S bytes per direction per GPU instead of
+//                           2 S (N - 1) / N through peer loads and stores
+//   all-gather            : one multimem.st per packet instead of N peer stores
+//   reduce-scatter        : multimem.ld_reduce of the own slice
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -27,7 +33,7 @@
 
 namespace tpb {
 
-constexpr int COMM_MAX_BLOCKS = 64;
+constexpr int COMM_MAX_BLOCKS = TPB_COMM_MAX_BLOCKS;
 constexpr int COMM_THREADS = 512;
 
 struct CommParams {
@@ -39,6 +45,8 @@ struct CommParams {
   uint32_t* status;                // local status word
   long long n;                     // elements (all-reduce: total; all-gather / reduce-scatter: per-rank slice)
   uint64_t wait_ns;
+  const void* mc_in;               // multicast view of the input buffers (null: no NVLS)
+  void* mc_out;                    // multicast view of the output buffers
 };
 
 __device__ __forceinline__ bool block_barrier(const CommParams& p, int phase, uint32_t epoch) {
@@ -94,6 +102,26 @@ __device__ __forceinline__ uint4 ld_peer(const void* base, long long packet) {
   return v;
 }
 
+// NVLS: one instruction returns the element-wise sum of the 16-byte packet over every rank's copy, reduced inside the
+// NVSwitch (bf16 pairs are accumulated in fp32); the store writes the packet to every rank's copy.
+template <typename T> __device__ __forceinline__ uint4 multimem_ld_reduce(const void* mc_addr);
+template <> __device__ __forceinline__ uint4 multimem_ld_reduce<__nv_bfloat16>(const void* mc_addr) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc_addr) : "memory");
+  return v;
+}
+template <> __device__ __forceinline__ uint4 multimem_ld_reduce<float>(const void* mc_addr) {
+  float4 f;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=f"(f.x), "=f"(f.y), "=f"(f.z), "=f"(f.w) : "l"(mc_addr) : "memory");
+  return make_uint4(__float_as_uint(f.x), __float_as_uint(f.y), __float_as_uint(f.z), __float_as_uint(f.w));
+}
+__device__ __forceinline__ void multimem_st(void* mc_addr, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc_addr), "f"(__uint_as_float(v.x)),
+               "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w)) : "memory");
+}
+
 template <typename T>
 __device__ __forceinline__ uint4 reduce_packet(const CommParams& p, long long packet) {
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -109,7 +137,7 @@ __device__ __forceinline__ uint4 reduce_packet(const CommParams& p, long long pa
   return Pack<T>::pack(acc);
 }
 
-// mode: 0 all-reduce one-shot, 1 all-reduce two-shot, 2 all-gather, 3 reduce-scatter
+// mode: 0 all-reduce one-shot, 1 all-reduce two-shot, 2 all-gather, 3 reduce-scatter; 4, 5, 6 = 1, 2, 3 through the multicast view
 template <typename T, int MODE>
 __global__ void __launch_bounds__(COMM_THREADS) collective_kernel(const CommParams p) {
   const uint32_t epoch = p.epochs[blockIdx.x] + 1;
@@ -141,10 +169,36 @@ __global__ void __launch_bounds__(COMM_THREADS) collective_kernel(const CommPara
         for (int r = 0; r < TPB_MAX_WORLD; ++r)
           if (r < p.world) static_cast<uint4*>(p.out[r])[p.rank * packets + i] = v;
       }
-    } else {
+    } else if (MODE == 3) {
       const long long packets = p.n / N;
       for (long long i = tid; i < packets; i += stride)
         static_cast<uint4*>(p.out[p.rank])[i] = reduce_packet<T>(p, p.rank * packets + i);
+    } else if (MODE == 4) {
+      const long long packets = p.n / N;
+      const long long per = (packets + p.world - 1) / p.world;
+      const long long lo = per * p.rank, hi = min(packets, lo + per);
+      const uint4* src = static_cast<const uint4*>(p.mc_in);
+      uint4* dst = static_cast<uint4*>(p.mc_out);
+      long long i = lo + tid;
+      for (; i + 3 * stride < hi; i += 4 * stride) {  // four reductions in flight per thread
+        const uint4 a = multimem_ld_reduce<T>(src + i), b = multimem_ld_reduce<T>(src + i + stride);
+        const uint4 c = multimem_ld_reduce<T>(src + i + 2 * stride), d = multimem_ld_reduce<T>(src + i + 3 * stride);
+        multimem_st(dst + i, a);
+        multimem_st(dst + i + stride, b);
+        multimem_st(dst + i + 2 * stride, c);
+        multimem_st(dst + i + 3 * stride, d);
+      }
+      for (; i < hi; i += stride) multimem_st(dst + i, multimem_ld_reduce<T>(src + i));
+    } else if (MODE == 5) {
+      const long long packets = p.n / N;
+      uint4* dst = static_cast<uint4*>(p.mc_out);
+      for (long long i = tid; i < packets; i += stride)
+        multimem_st(dst + p.rank * packets + i, static_cast<const uint4*>(p.in[p.rank])[i]);
+    } else {
+      const long long packets = p.n / N;
+      const uint4* src = static_cast<const uint4*>(p.mc_in);
+      for (long long i = tid; i < packets; i += stride)
+        static_cast<uint4*>(p.out[p.rank])[i] = multimem_ld_reduce<T>(src + p.rank * packets + i);
     }
     __threadfence_system();
   }
@@ -202,9 +256,11 @@ extern "C" int tpb_last_cuda_error(char* buf, int len) {
 // kind: 0 all-reduce (algorithm chosen by size), 2 all-gather, 3 reduce-scatter.  dtype: 0 bf16, 1 fp32.
 // `n` = total elements for all-reduce, per-rank slice elements otherwise.  Buffers must be 16-byte aligned
 // and n * sizeof(T) a multiple of 16.
+// mc_in / mc_out: multicast views of the input / output buffers (null: plain peer loads and stores).  With them, all-reduces
+// above 512 KiB, all-gathers and reduce-scatters go through the NVSwitch (force_algo 4 / 1 picks the two-shot variant by hand).
 extern "C" int tpb_collective(int kind, int dtype, int world, int rank, void* const* in, void* const* out,
                               void* const* sig, void* epochs, void* status, long long n, int force_algo,
-                              double wait_seconds, void* stream_) {
+                              double wait_seconds, const void* mc_in, void* mc_out, void* stream_) {
   if (world < 1 || world > TPB_MAX_WORLD || rank < 0 || rank >= world || !in || !out || !sig || !epochs || !status || n <= 0)
     return TPB_ERR_ARG;
   const int per_packet = dtype == 0 ? 8 : 4;
@@ -218,22 +274,32 @@ extern "C" int tpb_collective(int kind, int dtype, int world, int rank, void* co
   p.status = static_cast<uint32_t*>(status);
   p.n = n;
   p.wait_ns = wait_seconds > 0 ? uint64_t(wait_seconds * 1e9) : TPB_WAIT_LIMIT_NS;
+  const bool nvls = mc_in && mc_out && world > 1;
+  p.mc_in = nvls ? mc_in : nullptr;
+  p.mc_out = nvls ? mc_out : nullptr;
   cudaStream_t s = static_cast<cudaStream_t>(stream_);
   const long long bytes = n * (dtype == 0 ? 2 : 4);
   int mode = kind;
-  if (kind == 0) mode = force_algo >= 0 ? force_algo : (bytes <= 512 * 1024 ? 0 : 1);
+  if (kind == 0) mode = force_algo >= 0 ? force_algo : (bytes <= 512 * 1024 ? 0 : (nvls ? 4 : 1));
+  if (kind == 2 && nvls && force_algo != 2) mode = 5;
+  if (kind == 3 && nvls && force_algo != 3) mode = 6;
+  if (mode >= 4 && !nvls) return TPB_ERR_ARG;
   const long long packets = n / per_packet;
-  long long work = mode == 1 ? (packets + world - 1) / world : packets;
+  long long work = (mode == 1 || mode == 4) ? (packets + world - 1) / world : packets;
   int blocks = int((work + COMM_THREADS - 1) / COMM_THREADS);
   if (blocks < 1) blocks = 1;
   if (blocks > COMM_MAX_BLOCKS) blocks = COMM_MAX_BLOCKS;
 #define RUN(T, M) collective_kernel<T, M><<<blocks, COMM_THREADS, 0, s>>>(p)
   if (dtype == 0) {
     switch (mode) { case 0: RUN(__nv_bfloat16, 0); break; case 1: RUN(__nv_bfloat16, 1); break;
-                    case 2: RUN(__nv_bfloat16, 2); break; case 3: RUN(__nv_bfloat16, 3); break; default: return TPB_ERR_ARG; }
+                    case 2: RUN(__nv_bfloat16, 2); break; case 3: RUN(__nv_bfloat16, 3); break;
+                    case 4: RUN(__nv_bfloat16, 4); break; case 5: RUN(__nv_bfloat16, 5); break;
+                    case 6: RUN(__nv_bfloat16, 6); break; default: return TPB_ERR_ARG; }
   } else {
     switch (mode) { case 0: RUN(float, 0); break; case 1: RUN(float, 1); break;
-                    case 2: RUN(float, 2); break; case 3: RUN(float, 3); break; default: return TPB_ERR_ARG; }
+                    case 2: RUN(float, 2); break; case 3: RUN(float, 3); break;
+                    case 4: RUN(float, 4); break; case 5: RUN(float, 5); break;
+                    case 6: RUN(float, 6); break; default: return TPB_ERR_ARG; }
   }
 #undef RUN
   return cudaGetLastError() == cudaSuccess ? TPB_OK : TPB_ERR_CUDA;
@@ -247,7 +313,8 @@ extern "C" int tpb_comm_preload(void) {
   cudaError_t e = cudaSuccess;
 #define LOAD(T, M) if (e == cudaSuccess) e = cudaFuncGetAttributes(&attr, collective_kernel<T, M>)
   LOAD(__nv_bfloat16, 0); LOAD(__nv_bfloat16, 1); LOAD(__nv_bfloat16, 2); LOAD(__nv_bfloat16, 3);
-  LOAD(float, 0); LOAD(float, 1); LOAD(float, 2); LOAD(float, 3);
+  LOAD(__nv_bfloat16, 4); LOAD(__nv_bfloat16, 5); LOAD(__nv_bfloat16, 6);
+  LOAD(float, 0); LOAD(float, 1); LOAD(float, 2); LOAD(float, 3); LOAD(float, 4); LOAD(float, 5); LOAD(float, 6);
 #undef LOAD
   return e == cudaSuccess ? TPB_OK : TPB_ERR_CUDA;
 }

@@ -57,7 +57,7 @@ constexpr int NUM_THREADS = 192;
 constexpr int EPI_THREADS = 128;
 constexpr int MAX_WORLD = 8;
 constexpr int LL_FIRST_SLOT = 32;  // first fp32 slot of the flagged-word area (slots below hold plain partials)
-constexpr int LL_TILE_WORDS = 128 * 32;  // 16-byte flagged words owned by one tile: 128 feature rows x up to 32 token pairs
+constexpr int LL_TILE_WORDS = 128 * 16;  // 16-byte flagged words owned by one tile: 128 feature rows x up to 16 token quads
 
 struct GemmParams {
   int m_extent;   // rows of A (lanes side)
@@ -99,8 +99,25 @@ struct GemmParams {
   uint32_t* ag_flags[MAX_WORLD];              // every rank's arrival words [ag_world], indexed by source rank
   uint32_t* ag_push_counter;                  // local: CTAs done pushing (self re-arming)
   int stream_k;                   // 1: every CTA owns one contiguous range of (tile, k-block) units (see WorkIter)
+  uint64_t wait_ns;               // wall-time bound of every wait inside the kernel
+  // MN-major operands (normal orientation only): the operand is stored [K rows][MN columns] in memory, i.e. it is the
+  // transpose of what the K-major path expects.  Lets the backward GEMMs (dX = dY W, dW = dY^T X) read W, dY and X as
+  // they lie in memory, without a transpose kernel in front.
+  int a_mn, b_mn;
+  // normalisation of the token operand folded into the GEMM (swapped orientation only): the caller multiplies the norm
+  // weight into the GEMM weight once (W'[f, k] = W[f, k] g[k]); the epilogue warps compute every token's statistics from
+  // norm_x while the weights stream and the epilogue applies  out = rstd (acc - mean rowsum[f]) + bias.
+  int norm_mode;                  // 0 none, 1 RMSNorm, 2 LayerNorm
+  float norm_eps;
+  const __nv_bfloat16* norm_x;    // [tokens, norm_k]: the rows the statistics are taken over (row pitch norm_ld); usually
+                                  // the token operand itself, a superset of its columns when the GEMM contracts a slice
+  long long norm_ld;
+  int norm_k;
+  const float* norm_rowsum;       // LayerNorm only: [features] sums of the rows of W'
+#ifdef TPB_GEMM_TRACE
   int debug_skip_mma;             // measurement aid: stream the operands through the smem ring without issuing MMAs
   int trace_block;                // measurement aid: CTA (index + 1) that records %globaltimer stamps into g_gemm_trace; 0 = off
+#endif
 };
 
 // %globaltimer stamps of one CTA of the most recent traced launch (see tpb_gemm_trace):
@@ -108,11 +125,16 @@ struct GemmParams {
 // 5 arrival counters bumped, 6 reduce phase entered, 7 all arrivals seen, 8 reduced tile written; partial-tile path
 // (last item of the CTA): 9 partial parked, 10 fence + barrier passed, 11 counter bumped, 12 last contributor starts
 // the sum; 13 teardown; whole-tile path: 14 accumulators read, 15 tile written.
+// Compiled in only with -DTPB_GEMM_TRACE: the product build carries neither the stamps nor their parameters.
+#ifdef TPB_GEMM_TRACE
 __device__ unsigned long long g_gemm_trace[32];
 #define TPB_TRACE(i)                                                                         \
   do {                                                                                       \
     if (p.trace_block && int(blockIdx.x) == p.trace_block - 1) g_gemm_trace[i] = globaltimer_ns(); \
   } while (0)
+#else
+#define TPB_TRACE(i) do { } while (0)
+#endif
 
 
 __device__ __forceinline__ float apply_act(float x, int act) {
@@ -134,7 +156,7 @@ __device__ __forceinline__ float apply_act(float x, int act) {
 __device__ __noinline__ float apply_act_call(float x, int act) { return apply_act(x, act); }
 
 // Retry loop of the flagged exchange (out of line: it is inlined 16 times otherwise).  Bounded by wall time.
-__device__ __noinline__ uint4 poll_flagged_word(const uint4* ptr, uint32_t flag, bool* ok) {
+__device__ __noinline__ uint4 poll_flagged_word(const uint4* ptr, uint32_t flag, uint64_t limit_ns, bool* ok) {
   const uint64_t start = globaltimer_ns();
   uint4 w;
   for (uint32_t i = 0;; ++i) {
@@ -144,7 +166,7 @@ __device__ __noinline__ uint4 poll_flagged_word(const uint4* ptr, uint32_t flag,
       return w;
     }
     if (i > 64) __nanosleep(20);
-    if ((i & 63) == 63 && globaltimer_ns() - start > TPB_WAIT_LIMIT_NS) {
+    if ((i & 63) == 63 && globaltimer_ns() - start > limit_ns) {
       *ok = false;
       return w;
     }
@@ -226,7 +248,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   constexpr uint32_t ACC_COLS = NACC * BN;                                  // columns of one accumulator set
   constexpr uint32_t TMEM_COLS = (2 * ACC_COLS < 32) ? 32 : 2 * ACC_COLS;   // two sets; power of two by construction
   static_assert(TMEM_COLS <= 512 && (TMEM_COLS & (TMEM_COLS - 1)) == 0, "TMEM allocation must be a power of two <= 512");
-  constexpr uint32_t IDESC = make_idesc_bf16(BM, BN);
+  constexpr uint32_t MN_BLOCK_BYTES = 64 * BK * 2;  // one [BK k-rows][64 MN elements] block of an MN-major operand
   constexpr int MMAS_PER_STAGE = KBOX * (BK / UMMA_K);
 
   extern __shared__ uint8_t smem_raw[];
@@ -239,6 +261,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   volatile uint32_t* abort_flag = tmem_slot + 1;
   volatile uint32_t* epi_ok = tmem_slot + 2;
   volatile uint32_t* epi_last = tmem_slot + 3;
+  float* norm_stats = reinterpret_cast<float*>(tmem_slot + 4);  // [64 tokens][rstd, mean * rstd]
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -314,7 +337,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             kb = (kb_seq + p.ag_rank * p.ag_kb_per_rank) % p.k_blocks;
             const int src = kb / p.ag_kb_per_rank;
             if (src != ag_ready_src) {
-              if (!wait_flag_ge(p.ag_flags[p.ag_rank] + src, p.ag_epoch)) {
+              if (!wait_flag_ge(p.ag_flags[p.ag_rank] + src, p.ag_epoch, p.wait_ns)) {
                 atomicMax(p.status, STATUS_TIMEOUT_FLAG);
                 *abort_flag = 1;
                 break;
@@ -333,12 +356,26 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           uint8_t* a_dst = smem + size_t(s) * STAGE_BYTES;
           uint8_t* b_dst = a_dst + KBOX * A_BYTES;
           mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+          if (p.a_mn) {  // (KBOX == 1) 64-wide MN blocks of BK k-rows each, stacked along MN
 #pragma unroll
-          for (int j = 0; j < KBOX; ++j)  // columns past K are filled with zeros by TMA and cost no DRAM traffic
-            tma_load_2d(a_dst + j * A_BYTES, &tmap_a, &full_bar[s], (kb * KBOX + j) * BK, mt * BM);
+            for (int b = 0; b < BM / 64; ++b)
+              tma_load_2d(a_dst + b * MN_BLOCK_BYTES, &tmap_a, &full_bar[s], mt * BM + b * 64, kb * BK);
+          } else {
 #pragma unroll
-          for (int j = 0; j < KBOX; ++j)
-            tma_load_2d(b_dst + j * B_BYTES, &tmap_b, &full_bar[s], (kb * KBOX + j) * BK, nt * BN);
+            for (int j = 0; j < KBOX; ++j)  // columns past K are filled with zeros by TMA and cost no DRAM traffic
+              tma_load_2d(a_dst + j * A_BYTES, &tmap_a, &full_bar[s], (kb * KBOX + j) * BK, mt * BM);
+          }
+          if (p.b_mn) {
+            if constexpr (BN >= 64) {
+#pragma unroll
+              for (int b = 0; b < BN / 64; ++b)
+                tma_load_2d(b_dst + b * MN_BLOCK_BYTES, &tmap_b, &full_bar[s], nt * BN + b * 64, kb * BK);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < KBOX; ++j)
+              tma_load_2d(b_dst + j * B_BYTES, &tmap_b, &full_bar[s], (kb * KBOX + j) * BK, nt * BN);
+          }
         }
       }
     }
@@ -347,6 +384,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     if (elect_one()) {
       uint32_t it = 0;
       uint32_t local = 0;
+      const uint32_t idesc = make_idesc_bf16(BM, BN, p.a_mn != 0, p.b_mn != 0);
       WorkIter work(p);
       WorkItem item;
       for (; !*abort_flag && work.next(p, item); ++local) {
@@ -372,17 +410,23 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           tc_fence_after();
           const uint32_t a_addr = smem_u32(smem + size_t(s) * STAGE_BYTES);
           const uint32_t b_addr = a_addr + KBOX * A_BYTES;
+#ifdef TPB_GEMM_TRACE
           if (p.debug_skip_mma) {
             issued += MMAS_PER_STAGE;
             if (kb + 1 < kb1) { mbar_arrive(&empty_bar[s]); continue; }
           }
+#endif
 #pragma unroll
           for (int j = 0; j < KBOX; ++j) {
 #pragma unroll
             for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-              const uint64_t adesc = make_desc_kmajor_sw128(a_addr + j * A_BYTES + kk * UMMA_K * 2);
-              const uint64_t bdesc = make_desc_kmajor_sw128(b_addr + j * B_BYTES + kk * UMMA_K * 2);
-              umma_bf16(d_tmem + (issued % NACC) * BN, adesc, bdesc, IDESC, issued >= NACC ? 1u : 0u);
+              // K-major: a k-step of 16 elements is 32 bytes further along the swizzled 128-byte rows;
+              // MN-major: it is 16 k-rows (two 8-row swizzle atoms) further down the block
+              const uint64_t adesc = p.a_mn ? make_desc_mnmajor_sw128(a_addr + kk * UMMA_K * 128, MN_BLOCK_BYTES)
+                                            : make_desc_kmajor_sw128(a_addr + j * A_BYTES + kk * UMMA_K * 2);
+              const uint64_t bdesc = p.b_mn ? make_desc_mnmajor_sw128(b_addr + kk * UMMA_K * 128, MN_BLOCK_BYTES)
+                                            : make_desc_kmajor_sw128(b_addr + j * B_BYTES + kk * UMMA_K * 2);
+              umma_bf16(d_tmem + (issued % NACC) * BN, adesc, bdesc, idesc, issued >= NACC ? 1u : 0u);
               ++issued;
             }
           }
@@ -405,6 +449,40 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     float hot_bias_scale = p.bias_scale;
     asm volatile("" : "+l"(hot_out), "+l"(hot_bias), "+l"(hot_residual), "+r"(hot_ld_out), "+r"(hot_act), "+r"(hot_n_extent),
                  "+r"(hot_m_extent), "+f"(hot_bias_scale));
+    if (p.norm_mode) {
+      // statistics of every token row of the unnormalised operand (swapped orientation: at most 64 tokens, all of them
+      // in this CTA's tile), computed by the otherwise idle epilogue warps while the weights stream in
+      const int chunks = p.norm_k >> 3;
+      const float inv_k = 1.f / float(p.norm_k);
+      for (int t = warp - 2; t < p.n_extent; t += EPI_THREADS / 32) {
+        const uint4* xrow = reinterpret_cast<const uint4*>(p.norm_x + size_t(t) * p.norm_ld);
+        float s1 = 0.f, s2 = 0.f;
+        for (int c = lane; c < chunks; c += 32) {
+          const uint4 u = xrow[c];
+          const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float lo = bf16_bits_to_float(w4[i] & 0xFFFF), hi = bf16_bits_to_float(w4[i] >> 16);
+            s1 += lo + hi;
+            s2 += lo * lo + hi * hi;
+          }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+          s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+        }
+        if (lane == 0) {
+          const float mean = p.norm_mode == 2 ? s1 * inv_k : 0.f;
+          const float rstd = rsqrtf(fmaxf(s2 * inv_k - mean * mean, 0.f) + p.norm_eps);
+          norm_stats[2 * t] = rstd;
+          norm_stats[2 * t + 1] = mean * rstd;
+        }
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
+    }
+    const bool hot_norm = p.norm_mode != 0;
+    const float* hot_rowsum = p.norm_rowsum;
     uint32_t local = 0;
     WorkIter work(p);
     WorkItem item;
@@ -544,6 +622,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           // tokens are the accumulator columns, a lane owns one feature: neighbouring lanes pair up so that every
           // store carries two features (4 bytes); rows past the feature count only take part in the shuffle
           const float b = (m_ok && hot_bias) ? hot_bias_scale * __bfloat162float(hot_bias[m]) : 0.f;
+          const float rowsum = (hot_norm && hot_rowsum && m_ok) ? hot_rowsum[m] : 0.f;
           const bool pitch_even = (hot_ld_out & 1) == 0 && (reinterpret_cast<uintptr_t>(hot_out) & 3) == 0;
           const bool writes_pair = pitch_even && !(lane & 1) && m + 1 < hot_m_extent;
           const bool covered = pitch_even && (lane & 1);  // the even neighbour stores this lane's value
@@ -551,7 +630,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           for (int j = 0; j < 16; ++j) {
             if (n0 + j >= hot_n_extent) break;  // (uniform) the code of the remaining iterations is never fetched
             const size_t idx = size_t(n0 + j) * hot_ld_out + m;
-            float x = v[j] + b;
+            float x = v[j];
+            if (hot_norm) x = x * norm_stats[2 * (n0 + j)] - norm_stats[2 * (n0 + j) + 1] * rowsum;
+            x += b;
             if (hot_act) x = apply_act_call(x, hot_act);
             if (hot_residual && m_ok) x += __bfloat162float(hot_residual[idx]);
             const float up = __shfl_down_sync(0xffffffffu, x, 1);
@@ -566,10 +647,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         if (p.act == 5) {
           // gated silu, swapped orientation: lanes 0-15 of a warp hold gate rows, lanes 16-31 the matching up rows
           const float b = p.bias ? p.bias_scale * __bfloat162float(p.bias[m]) : 0.f;
+          const float rowsum = (hot_norm && hot_rowsum) ? hot_rowsum[m] : 0.f;
           const int f_out = (m >> 5) * 16 + (m & 15);
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            const float x = v[j] + b;
+            float x = v[j];
+            if (hot_norm && n0 + j < p.n_extent) x = x * norm_stats[2 * (n0 + j)] - norm_stats[2 * (n0 + j) + 1] * rowsum;
+            x += b;
             const float partner = __shfl_xor_sync(0xffffffffu, x, 16);
             if ((lane & 16) == 0 && n0 + j < p.n_extent)
               p.out[size_t(n0 + j) * p.ld_out + f_out] = __float2bfloat16(x / (1.f + __expf(-x)) * partner);
@@ -622,87 +706,66 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         }
       };
       // flagged-word variant (swapped orientation only: all tokens sit in one tile): slot k of rank d's flagged area
-      // holds rank k's partial as 16-byte words {value(t), epoch, value(t + 1), epoch} laid out
-      // [tile][token pair][feature row]: the 32 lanes of a warp touch 512 contiguous bytes per access (whole sectors;
-      // a [row][pair] order was measured 2x slower at 8 ranks because every lane then touches its own sector).
-      // A tile always owns the same LL_TILE_WORDS words whatever the shape of the call, and its epoch only
-      // grows, so a word left behind by an earlier call (of any shape) can never carry the epoch a later call waits
-      // for.  The area starts LL_FIRST_SLOT slots into the workspace and a flagged slot spans two fp32 slots.
+      // holds rank k's partial, rounded to bf16 (what an all-reduce of bf16 activations sums as well), as 16-byte words
+      // {bf16x2(t, t+1), epoch, bf16x2(t+2, t+3), epoch} laid out [tile][token quad][feature row]: the 32 lanes of a warp
+      // touch 512 contiguous bytes per access.  Each 8-byte half carries its own epoch, so only 8-byte single-copy
+      // atomicity is relied upon.  A tile always owns the same LL_TILE_WORDS words whatever the shape of the call, and its
+      // epoch only grows, so a word left behind by an earlier call (of any shape) can never carry the epoch a later call
+      // waits for.  The area starts LL_FIRST_SLOT slots into the workspace and a flagged slot spans two fp32 slots.
       bool ll_gave_up = false;
-      const size_t ll_row = size_t(tile) * LL_TILE_WORDS + size_t(row);  // this thread's word of token pair 0; pair q is 128 q words on
+      const size_t ll_row = size_t(tile) * LL_TILE_WORDS + size_t(row);  // this thread's word of token quad 0; quad q is 128 q words on
       auto push_ll = [&](int n0, const float (&v)[16]) {
         if (!chunk_valid(n0)) return;
 #pragma unroll 1  // (rolled: small code, see read_acc)
         for (int d = 0; d < p.world; ++d) {
-          uint4* dst = reinterpret_cast<uint4*>(p.slots[d] + size_t(LL_FIRST_SLOT + 2 * p.rank) * p.slot_stride) + ll_row + size_t(n0 >> 1) * BM;
+          uint4* dst = reinterpret_cast<uint4*>(p.slots[d] + size_t(LL_FIRST_SLOT + 2 * p.rank) * p.slot_stride) + ll_row + size_t(n0 >> 2) * BM;
 #pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            if (n0 + 2 * q >= p.n_extent) break;
-            st_relaxed_sys_v4(dst + q * BM, __float_as_uint(v[2 * q]), ll_flag,
-                              n0 + 2 * q + 1 < p.n_extent ? __float_as_uint(v[2 * q + 1]) : 0u, ll_flag);
+          for (int q = 0; q < 4; ++q) {
+            if (n0 + 4 * q >= p.n_extent) break;
+            st_relaxed_sys_v4(dst + q * BM, pack_bf16x2(v[4 * q], v[4 * q + 1]), ll_flag, pack_bf16x2(v[4 * q + 2], v[4 * q + 3]), ll_flag);
           }
         }
       };
       auto wait_ll = [&](const uint4* ptr, uint4 first) -> uint4 {
         if ((first.y == ll_flag && first.w == ll_flag) || ll_gave_up) return first;
         bool ok;
-        first = poll_flagged_word(ptr, ll_flag, &ok);
+        first = poll_flagged_word(ptr, ll_flag, p.wait_ns, &ok);
         if (!ok) {
           atomicMax(p.status, STATUS_TIMEOUT_FLAG);
           ll_gave_up = true;
         }
         return first;
       };
-      auto reduce_ll = [&](int n0) {  // sum the ranks' partials in rank order (identical on every rank), then the usual epilogue
+      // sum the ranks' partials in rank order (identical on every rank); the caller runs the usual epilogue on the sums
+      auto reduce_ll = [&](int n0, float (&sum)[16]) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) sum[j] = 0.f;
         if (!chunk_valid(n0)) return;
         const uint4* area = reinterpret_cast<const uint4*>(p.slots[p.rank] + size_t(LL_FIRST_SLOT) * p.slot_stride);
         const size_t slot_words = p.slot_stride >> 1;  // 16-byte words per flagged slot (= 2 fp32 slots)
-        const float b = p.bias ? p.bias_scale * __bfloat162float(p.bias[m]) : 0.f;
-        constexpr int G = 4, KH = 4;  // G token pairs x KH ranks of flagged words are in flight before the first one is examined
+        constexpr int KH = 4;  // 4 token quads x KH ranks of flagged words are in flight before the first one is examined
 #pragma unroll 1
-        for (int q0 = 0; q0 < 8 && n0 + 2 * q0 < p.n_extent; q0 += G) {
-          float s0[G], s1[G];
+        for (int k0 = 0; k0 < p.world; k0 += KH) {  // ranks in ascending order: the sum is bitwise identical on every rank
+          uint4 a[4][KH];
 #pragma unroll
-          for (int g = 0; g < G; ++g) s0[g] = s1[g] = 0.f;
-#pragma unroll 1
-          for (int k0 = 0; k0 < p.world; k0 += KH) {  // ranks in ascending order: the sum is bitwise identical on every rank
-            uint4 a[G][KH];
+          for (int q = 0; q < 4; ++q) {
 #pragma unroll
-            for (int g = 0; g < G; ++g) {
-              const bool live = q0 + g < 8 && n0 + 2 * (q0 + g) < p.n_extent;
-#pragma unroll
-              for (int k = 0; k < KH; ++k)
-                if (live && k0 + k < p.world)
-                  a[g][k] = ld_relaxed_sys_v4(area + size_t(k0 + k) * slot_words + ll_row + size_t((n0 >> 1) + q0 + g) * BM);
-            }
-#pragma unroll
-            for (int g = 0; g < G; ++g) {
-              if (q0 + g < 8 && n0 + 2 * (q0 + g) < p.n_extent) {
-#pragma unroll
-                for (int k = 0; k < KH; ++k) {
-                  if (k0 + k < p.world) {
-                    const uint4 w4 = wait_ll(area + size_t(k0 + k) * slot_words + ll_row + size_t((n0 >> 1) + q0 + g) * BM, a[g][k]);
-                    s0[g] += __uint_as_float(w4.x);
-                    s1[g] += __uint_as_float(w4.z);
-                  }
-                }
-              }
-            }
+            for (int k = 0; k < KH; ++k)
+              if (n0 + 4 * q < p.n_extent && k0 + k < p.world)
+                a[q][k] = ld_relaxed_sys_v4(area + size_t(k0 + k) * slot_words + ll_row + size_t((n0 >> 2) + q) * BM);
           }
 #pragma unroll
-          for (int g = 0; g < G; ++g) {
-            const int t = n0 + 2 * (q0 + g);
-            if (q0 + g < 8 && t < p.n_extent) {
-              const size_t o0 = size_t(t) * p.ld_out + m;
-              float x0 = s0[g] + b;
-              if (p.act) x0 = apply_act_call(x0, p.act);
-              if (p.residual) x0 += __bfloat162float(p.residual[o0]);
-              p.out[o0] = __float2bfloat16(x0);
-              if (t + 1 < p.n_extent) {
-                float x1 = s1[g] + b;
-                if (p.act) x1 = apply_act_call(x1, p.act);
-                if (p.residual) x1 += __bfloat162float(p.residual[o0 + p.ld_out]);
-                p.out[o0 + p.ld_out] = __float2bfloat16(x1);
+          for (int q = 0; q < 4; ++q) {
+            if (n0 + 4 * q < p.n_extent) {
+#pragma unroll
+              for (int k = 0; k < KH; ++k) {
+                if (k0 + k < p.world) {
+                  const uint4 w4 = wait_ll(area + size_t(k0 + k) * slot_words + ll_row + size_t((n0 >> 2) + q) * BM, a[q][k]);
+                  sum[4 * q] += bf16_bits_to_float(w4.x & 0xFFFF);
+                  sum[4 * q + 1] += bf16_bits_to_float(w4.x >> 16);
+                  sum[4 * q + 2] += bf16_bits_to_float(w4.z & 0xFFFF);
+                  sum[4 * q + 3] += bf16_bits_to_float(w4.z >> 16);
+                }
               }
             }
           }
@@ -748,7 +811,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             TPB_TRACE(3);
           }
 #pragma unroll 1
-          for (int c0 = 0; c0 < BN; c0 += 16) reduce_ll(nt * BN + c0);
+          for (int c0 = 0; c0 < BN; c0 += 16) {
+            float v[16];
+            reduce_ll(nt * BN + c0, v);
+            finalize(nt * BN + c0, v);
+          }
           if (threadIdx.x == 64) TPB_TRACE(8);
         }
       } else {
@@ -801,7 +868,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             if (p.ll) {
               if (threadIdx.x == 64) p.ll_epochs[tile] = ll_flag;
 #pragma unroll 1
-              for (int c0 = 0; c0 < BN; c0 += 16) reduce_ll(nt * BN + c0);
+              for (int c0 = 0; c0 < BN; c0 += 16) {
+                float v[16];
+                reduce_ll(nt * BN + c0, v);
+                finalize(nt * BN + c0, v);
+              }
             }
           }
         }
@@ -839,7 +910,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       if (threadIdx.x == 0) {
         TPB_TRACE(6);
         const uint32_t target = p.expected[tile] + contributions;
-        bool ok = !*abort_flag && wait_flag_ge(p.arrivals[p.rank] + tile, target);
+        bool ok = !*abort_flag && wait_flag_ge(p.arrivals[p.rank] + tile, target, p.wait_ns);
         TPB_TRACE(7);
         if (!ok) atomicMax(p.status, STATUS_TIMEOUT_FLAG);
         p.expected[tile] = target;
@@ -926,7 +997,14 @@ static int make_tmap_2d(CUtensorMap* map, const void* ptr, uint64_t rows, uint64
   return r == CUDA_SUCCESS ? TPB_OK : TPB_ERR_TMAP;
 }
 
-static int g_debug_stages = 0, g_debug_skip_mma = 0, g_trace_block = 0, g_disable_ll = 0, g_enable_stream_k = 0;  // measurement aids, see tpb_gemm_debug
+static int g_debug_stages = 0, g_disable_ll = 0, g_enable_stream_k = 0;  // measurement aids, see tpb_gemm_debug
+#ifdef TPB_GEMM_TRACE
+static int g_debug_skip_mma = 0, g_trace_block = 0;
+#endif
+// split-K of few-tile weight-streaming GEMMs (see tpb_gemm_plan): a tile is split when it streams at least
+// g_split_min_kb KiB of weights, into pieces of about g_split_target_kb KiB
+static int g_split_min_kb = 512, g_split_target_kb = 128;
+static uint64_t g_wait_ns = TPB_WAIT_LIMIT_NS;  // bound of the waits for peer GPUs, see tpb_set_wait_limit
 
 template <int BN, int KBOX, int NACC>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, int grid, cudaStream_t stream) {
@@ -937,9 +1015,11 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams&
   if (stages > p.kb_per_split + 1 && (p.stream_k || p.m_tiles * p.n_tiles * p.k_splits <= grid)) stages = max(2, p.kb_per_split + 1);
   if (g_debug_stages > 0 && g_debug_stages < stages) stages = g_debug_stages;
   p.stages = stages;
+#ifdef TPB_GEMM_TRACE
   p.debug_skip_mma = g_debug_skip_mma;
   p.trace_block = g_trace_block;
-  size_t smem = stages * stage_bytes + 1024 /*align*/ + (2 * MAX_STAGES + 4) * 8 + 16;
+#endif
+  size_t smem = stages * stage_bytes + 1024 /*align*/ + (2 * MAX_STAGES + 4) * 8 + 16 + 64 * 2 * sizeof(float) /*norm statistics*/;
   // opt in to large dynamic shared memory (per device); static + dynamic must stay within 227 KB
   static size_t configured[64] = {0};
   int dev = 0;
@@ -970,7 +1050,24 @@ using namespace tpb;
 // Measurement aids (0 restores the defaults): cap the smem ring depth, skip the MMAs.
 extern "C" int tpb_gemm_debug(int stages, int skip_mma) {
   g_debug_stages = stages;
+#ifdef TPB_GEMM_TRACE
   g_debug_skip_mma = skip_mma;
+#else
+  if (skip_mma) return TPB_ERR_ARG;  // compiled out of the product build
+#endif
+  return TPB_OK;
+}
+// Thresholds of the automatic split-K of few-tile weight-streaming GEMMs (KiB of weights per tile; <= 0 keeps a value).
+extern "C" int tpb_gemm_tune_split(int min_tile_kb, int target_kb) {
+  if (min_tile_kb > 0) g_split_min_kb = min_tile_kb;
+  if (target_kb > 0) g_split_target_kb = target_kb;
+  return TPB_OK;
+}
+// Bound, in seconds, of every wait for a peer GPU inside the GEMM kernels (a kernel that runs into it records a status
+// code and returns).  Applies to launches made after the call.
+extern "C" int tpb_set_wait_limit(double seconds) {
+  if (!(seconds > 0)) return TPB_ERR_ARG;
+  g_wait_ns = uint64_t(seconds * 1e9);
   return TPB_OK;
 }
 
@@ -988,6 +1085,7 @@ extern "C" int tpb_gemm_enable_stream_k(int enable) {
   g_enable_stream_k = enable;
   return TPB_OK;
 }
+#ifdef TPB_GEMM_TRACE
 extern "C" int tpb_gemm_trace(int block) {
   g_trace_block = block < 0 ? 0 : block + 1;
   return TPB_OK;
@@ -995,14 +1093,24 @@ extern "C" int tpb_gemm_trace(int block) {
 extern "C" int tpb_gemm_trace_read(unsigned long long* out32) {
   return cudaMemcpyFromSymbol(out32, g_gemm_trace, sizeof(unsigned long long) * 32) == cudaSuccess ? TPB_OK : TPB_ERR_CUDA;
 }
+#else
+extern "C" int tpb_gemm_trace(int) { return TPB_ERR_ARG; }
+extern "C" int tpb_gemm_trace_read(unsigned long long*) { return TPB_ERR_ARG; }
+#endif
 
 // Plan of a linear layer out[tokens, features] = x[tokens, K] @ w[features, K]^T.
 // force_splits > 0 fixes the split-K factor; force_kbox > 0 fixes the k-blocks per stage (1, 2 or 4).
 extern "C" int tpb_gemm_plan(int tokens, int features, int k, int world, int force_splits, int force_kbox,
                              tpb_gemm_plan_t* plan) {
+  return tpb_gemm_plan_ex(tokens, features, k, world, force_splits, force_kbox, 0, plan);
+}
+
+// flags bit 0: keep the tokens on the tensor-core rows whatever their number (needed by MN-major operands).
+extern "C" int tpb_gemm_plan_ex(int tokens, int features, int k, int world, int force_splits, int force_kbox, int flags,
+                                tpb_gemm_plan_t* plan) {
   if (!plan || tokens <= 0 || features <= 0 || k <= 0) return TPB_ERR_ARG;
   const int sms = sm_count();
-  plan->swapped = tokens <= 64 ? 1 : 0;
+  plan->swapped = (tokens <= 64 && !(flags & 1)) ? 1 : 0;
   int bn;
   if (plan->swapped) {
     bn = tokens <= 16 ? 16 : (tokens <= 32 ? 32 : 64);
@@ -1060,8 +1168,23 @@ extern "C" int tpb_gemm_plan(int tokens, int features, int k, int world, int for
     plan->kbox = kbox;
     plan->k_blocks = (kb64 + kbox - 1) / kbox;  // in units of one pipeline stage (kbox * 64 columns)
     int splits = 1;
+    const long long tile_kb = (long long)BM * k * 2 / 1024;  // weights one 128-row tile streams
     if (force_splits > 0) {
       splits = force_splits;
+    } else if (plan->swapped && tiles * 2 <= sms && tile_kb >= g_split_min_kb) {
+      // Few weight tiles (a tensor-parallel shard of a projection): the GEMM is a pure weight stream and takes
+      // bytes / (CTAs x per-CTA stream rate), so a handful of CTAs streaming 1 MB each is slow however little data
+      // there is.  Split K so that most SMs stream a share of about g_split_target_kb; the partials meet in the slot
+      // workspace and the last CTA of a tile to arrive sums them (one fence + one atomic, nobody waits).
+      splits = sms / tiles;
+      const int by_bytes = int((tile_kb + g_split_target_kb - 1) / g_split_target_kb);
+      if (splits > by_bytes) splits = by_bytes;
+      if (splits > 16) splits = 16;
+      if (force_kbox <= 0)
+        while (kbox > 1 && (kb64 + kbox - 1) / kbox < splits) kbox >>= 1;  // enough pipeline stages to deal out
+      plan->kbox = kbox;
+      plan->k_blocks = (kb64 + kbox - 1) / kbox;
+      if (splits < 1) splits = 1;
     } else if (tiles * 2 <= sms && plan->k_blocks * kbox >= 128) {
       // few output tiles and a long K (>= 8192): split K so that more SMs work on the problem
       splits = sms / tiles;
@@ -1087,8 +1210,16 @@ extern "C" int tpb_gemm_plan(int tokens, int features, int k, int world, int for
 
 static int gemm_impl(const void* x, const void* w, void* out, const void* bias, const void* residual, int tokens,
                      int features, int k, int ldx, int ldw, int ld_out, int act, float bias_scale,
-                     const tpb_gemm_plan_t* plan, const tpb_reduce_ctx_t* rc, const tpb_allgather_ctx_t* ag, void* stream_) {
+                     const tpb_gemm_plan_t* plan, const tpb_reduce_ctx_t* rc, const tpb_allgather_ctx_t* ag,
+                     const tpb_gemm_opts_t* opts, void* stream_) {
   if (!x || !w || !out || !plan) return TPB_ERR_ARG;
+  const bool x_mn = opts && opts->x_mn, w_mn = opts && opts->w_mn;
+  if ((x_mn || w_mn) && (plan->swapped || plan->kbox != 1 || plan->bn < 64 || ag)) return TPB_ERR_ARG;
+  if (opts && opts->norm_mode) {
+    if (!plan->swapped || !opts->norm_x || ((opts->norm_k > 0 ? opts->norm_k : k) & 7) || (opts->norm_ld & 7) || ((uintptr_t)opts->norm_x & 15) || tokens > 64 ||
+        opts->norm_mode < 0 || opts->norm_mode > 2 || (rc && rc->world > 1 && plan->reduce) || ag)
+      return TPB_ERR_ARG;
+  }
   if (act == 5 && ((features & 31) || residual || (rc && rc->world > 1 && plan->reduce && rc->world != 1))) return TPB_ERR_ARG;
   if ((ldx & 7) || (ldw & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return TPB_ERR_ALIGN;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
@@ -1104,6 +1235,17 @@ static int gemm_impl(const void* x, const void* w, void* out, const void* bias, 
   p.k_splits = plan->k_splits;
   p.kb_per_split = plan->kb_per_split;
   p.stream_k = plan->stream_k;
+  p.wait_ns = (opts && opts->wait_seconds > 0) ? uint64_t(opts->wait_seconds * 1e9) : g_wait_ns;
+  p.a_mn = x_mn ? 1 : 0;  // (MN-major operands only exist in the normal orientation: A = tokens, B = features)
+  p.b_mn = w_mn ? 1 : 0;
+  if (opts && opts->norm_mode) {
+    p.norm_mode = opts->norm_mode;
+    p.norm_eps = opts->norm_eps;
+    p.norm_x = static_cast<const __nv_bfloat16*>(opts->norm_x);
+    p.norm_ld = opts->norm_ld;
+    p.norm_k = opts->norm_k > 0 ? opts->norm_k : k;
+    p.norm_rowsum = opts->norm_rowsum;
+  }
   p.ld_out = ld_out;
   p.ld_slot = act == 5 ? features : ld_out;
   p.out = static_cast<__nv_bfloat16*>(out);
@@ -1166,9 +1308,10 @@ static int gemm_impl(const void* x, const void* w, void* out, const void* bias, 
   const int a_rows = p.m_extent, b_rows = p.n_extent;
   const int lda = plan->swapped ? ldw : ldx, ldb = plan->swapped ? ldx : ldw;
   CUtensorMap ta, tb;
-  int rcode = make_tmap_2d(&ta, a_ptr, a_rows, k, lda, BM);
+  // K-major operand: [rows, k] with boxes of [box rows][64 k]; MN-major operand: [k, rows] with boxes of [64 k][64 rows]
+  int rcode = p.a_mn ? make_tmap_2d(&ta, a_ptr, k, a_rows, lda, BK) : make_tmap_2d(&ta, a_ptr, a_rows, k, lda, BM);
   if (rcode != TPB_OK) return rcode;
-  rcode = make_tmap_2d(&tb, b_ptr, b_rows, k, ldb, plan->bn);
+  rcode = p.b_mn ? make_tmap_2d(&tb, b_ptr, k, b_rows, ldb, BK) : make_tmap_2d(&tb, b_ptr, b_rows, k, ldb, plan->bn);
   if (rcode != TPB_OK) return rcode;
 
   switch (plan->bn * 10 + plan->kbox) {
@@ -1188,7 +1331,16 @@ static int gemm_impl(const void* x, const void* w, void* out, const void* bias, 
 extern "C" int tpb_gemm_bf16(const void* x, const void* w, void* out, const void* bias, const void* residual, int tokens,
                              int features, int k, int ldx, int ldw, int ld_out, int act, float bias_scale,
                              const tpb_gemm_plan_t* plan, const tpb_reduce_ctx_t* rc, void* stream_) {
-  return gemm_impl(x, w, out, bias, residual, tokens, features, k, ldx, ldw, ld_out, act, bias_scale, plan, rc, nullptr, stream_);
+  return gemm_impl(x, w, out, bias, residual, tokens, features, k, ldx, ldw, ld_out, act, bias_scale, plan, rc, nullptr, nullptr, stream_);
+}
+
+// tpb_gemm_bf16 with options: operands given transposed in memory (x as [k, tokens], w as [k, features]: the backward
+// GEMMs of a linear layer need no transpose kernel), a normalisation of x folded into the kernel, a wait bound.
+extern "C" int tpb_gemm_bf16_ex(const void* x, const void* w, void* out, const void* bias, const void* residual, int tokens,
+                                int features, int k, int ldx, int ldw, int ld_out, int act, float bias_scale,
+                                const tpb_gemm_plan_t* plan, const tpb_reduce_ctx_t* rc, const tpb_gemm_opts_t* opts,
+                                void* stream_) {
+  return gemm_impl(x, w, out, bias, residual, tokens, features, k, ldx, ldw, ld_out, act, bias_scale, plan, rc, nullptr, opts, stream_);
 }
 
 // All-gather fused with the GEMM that consumes it: x is split by columns over the ranks; every rank passes its
@@ -1202,5 +1354,5 @@ extern "C" int tpb_gemm_allgather_bf16(const void* w, void* out, const void* bia
                                        const tpb_reduce_ctx_t* rc, const tpb_allgather_ctx_t* ag, void* stream_) {
   if (!ag) return TPB_ERR_ARG;
   return gemm_impl(ag->gathered[ag->rank], w, out, bias, nullptr, tokens, features, k, ld_gathered, ldw, ld_out, act, 1.0f, plan, rc,
-                   ag, stream_);
+                   ag, nullptr, stream_);
 }

@@ -20,6 +20,7 @@ enum {
 };
 
 #define TPB_MAX_WORLD 8
+#define TPB_COMM_MAX_BLOCKS 160  // largest grid of a stand-alone collective = rows of its signal arrays (one CTA per SM and more)
 
 typedef struct {
   int swapped;  // 1: weight rows fill the 128 tensor-core rows (few tokens), 0: tokens do
@@ -61,8 +62,28 @@ typedef struct {
   unsigned epoch;                     // number of fused all-gather calls issued on these flags, this one included
 } tpb_allgather_ctx_t;
 
+// Options of tpb_gemm_bf16_ex.
+typedef struct {
+  int x_mn, w_mn;            // the operand lies transposed in memory: x as [k, tokens] (row pitch ldx), w as [k, features]
+                             // (row pitch ldw).  Needs a plan made with flag bit 0 (tokens on the tensor-core rows).
+  int norm_mode;             // 0 none, 1 RMSNorm, 2 LayerNorm of the rows of x, folded into the kernel (<= 64 tokens):
+                             // x must be the UNNORMALISED rows, w must already carry the norm weight (w'[f, k] = w[f, k] g[k])
+                             // and the result is rstd (x w'^T - mean rowsum) + bias_scale * bias
+  float norm_eps;
+  const void* norm_x;        // rows the statistics are taken over: x itself, or (norm_k > k) the full rows x is a column
+                             // slice of (a row-parallel projection of a normalised state)
+  long long norm_ld;
+  int norm_k;                // columns of norm_x; <= 0: k
+  const float* norm_rowsum;  // LayerNorm: fp32 [features], sum over k of w'[f, k]; the caller folds W beta into the bias
+  double wait_seconds;       // bound of the waits for peer GPUs; <= 0: the library default (tpb_set_wait_limit)
+} tpb_gemm_opts_t;
+
 int tpb_gemm_plan(int tokens, int features, int k, int world, int force_splits, int force_kbox,
                   tpb_gemm_plan_t* plan);
+int tpb_gemm_plan_ex(int tokens, int features, int k, int world, int force_splits, int force_kbox, int flags,
+                     tpb_gemm_plan_t* plan);
+int tpb_gemm_tune_split(int min_tile_kb, int target_kb);
+int tpb_set_wait_limit(double seconds);
 
 // out[tokens, features] = act(x[tokens, k] @ w[features, k]^T + bias_scale * bias) + residual
 // (bf16 operands, fp32 accumulation).  With rc->world > 1 the product is additionally summed over all ranks
@@ -71,13 +92,17 @@ int tpb_gemm_bf16(const void* x, const void* w, void* out, const void* bias, con
                   int features, int k, int ldx, int ldw, int ld_out, int act, float bias_scale,
                   const tpb_gemm_plan_t* plan, const tpb_reduce_ctx_t* rc, void* stream);
 
+int tpb_gemm_bf16_ex(const void* x, const void* w, void* out, const void* bias, const void* residual, int tokens,
+                     int features, int k, int ldx, int ldw, int ld_out, int act, float bias_scale,
+                     const tpb_gemm_plan_t* plan, const tpb_reduce_ctx_t* rc, const tpb_gemm_opts_t* opts, void* stream);
+
 int tpb_gemm_allgather_bf16(const void* w, void* out, const void* bias, int tokens, int features, int k, int ld_gathered,
                             int ldw, int ld_out, int act, const tpb_gemm_plan_t* plan, const tpb_reduce_ctx_t* rc,
                             const tpb_allgather_ctx_t* ag, void* stream);
 
-// Measurement aids.  tpb_gemm_debug caps the smem ring depth / skips the MMAs (0, 0 restores the defaults).
-// tpb_gemm_trace makes CTA `block` of every following GEMM launch record %globaltimer stamps of its phases
-// (block < 0: off); tpb_gemm_trace_read copies the 32 stamps of the current device to the host.
+// Measurement aids.  tpb_gemm_debug caps the smem ring depth (0 restores the default).  Skipping the MMAs and the
+// kernel-internal %globaltimer trace (tpb_gemm_trace / tpb_gemm_trace_read) exist only in a library built with
+// -DTPB_GEMM_TRACE; in the product build they return TPB_ERR_ARG and the kernels carry no trace code.
 int tpb_gemm_debug(int stages, int skip_mma);
 int tpb_gemm_trace(int block);
 int tpb_gemm_disable_flagged_exchange(int disable);

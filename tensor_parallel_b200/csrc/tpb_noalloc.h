@@ -34,7 +34,8 @@ extern "C" {
 // workspace of your own).
 //
 // First call on each device: the library looks up the device address of its workspace with
-// cudaGetSymbolAddress while that device is current.  This one-time step is not a stream operation, so make
+// cudaGetSymbolAddress while that device is current, and opts the attention kernels in to their dynamic shared
+// memory (cudaFuncSetAttribute, once per kernel and device).  Neither one-time step is a stream operation, so make
 // the first call on every device you use BEFORE starting any stream capture; later calls only launch kernels.
 //
 // Sharing: all calls on one device use the same workspace.  Nothing in it has to be zero at entry - every word

@@ -1,13 +1,17 @@
-"""Symmetric heap and device-side collectives (Python side of ``csrc/comm.cu``).
+"""Symmetric heap and device-side collectives (Python side of ``csrc/comm.cu`` and ``csrc/symm.cu``).
 
-Every rank owns one ``cudaMalloc``'ed region of identical layout that all ranks map:
-``cudaDeviceEnablePeerAccess`` + plain pointers when all ranks live in one process (threaded
-mode), CUDA IPC handles exchanged through ``torch.distributed`` when there is one process per
-GPU.  Kernels address peers' regions directly over NVLink; no NCCL call is on these paths.
+Every rank owns one region of identical layout that all ranks map.  Preferred form: a physical allocation
+from the virtual-memory-management API, shared between rank processes as a POSIX file descriptor (passed over a
+Unix-domain socket) or simply by handle inside one process, mapped by every rank for plain peer loads / stores
+AND bound into one NVLink multicast object, so that kernels can also issue ``multimem`` instructions that the
+NVSwitch executes on all ranks' copies at once (``RankComm.mc_base``).  Fallback when the driver offers
+neither: ``cudaMalloc`` + ``cudaDeviceEnablePeerAccess`` (one process) or CUDA IPC handles (one process per
+GPU).  ``TPB_VMM=0`` forces the fallback, ``TPB_NVLS=0`` keeps the VMM heap but creates no multicast view.
+Kernels address peers' regions directly over NVLink; no NCCL call is on these paths.
 
 Layout of a region (offsets identical on all ranks)::
 
-    signals   : uint32 [2][64][8]            start / end barrier words of the collectives
+    signals   : uint32 [2][160][8]           start / end barrier words of the collectives
     arrivals  : uint32 [2 regions][MAX_TILES] per-tile arrival counters of the fused GEMM epilogue
     slots     : fp32   [2 regions][max_slots][slot_stride]  partial tiles pushed by peers
     staging   : two payload buffers for the stand-alone collectives (input side / output side)
@@ -17,9 +21,13 @@ into the other half than the one a slower peer may still be reducing from.
 """
 from __future__ import annotations
 
+import atexit
 import ctypes
 import logging
+import os
+import socket
 import threading
+import uuid
 from typing import Dict, List, Optional, Sequence
 
 import torch
@@ -32,7 +40,7 @@ from tensor_parallel_b200.ops.native import LIB, ReduceCtx, c_int, c_ll, c_void_
 logger = logging.getLogger(__name__)
 
 MAX_WORLD = 8
-COMM_MAX_BLOCKS = 64
+COMM_MAX_BLOCKS = 160  # = TPB_COMM_MAX_BLOCKS of csrc/tpb_api.h
 SIGNAL_BYTES = 2 * COMM_MAX_BLOCKS * MAX_WORLD * 4
 MAX_TILES = native.MAX_TILES
 
@@ -43,7 +51,19 @@ LIB.tpb_ipc_get_handle.argtypes = [c_void_p, c_void_p]
 LIB.tpb_ipc_open_handle.argtypes = [c_void_p, ctypes.POINTER(c_void_p)]
 LIB.tpb_ipc_close_handle.argtypes = [c_void_p]
 LIB.tpb_collective.argtypes = [c_int, c_int, c_int, c_int, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p),
-                               ctypes.POINTER(c_void_p), c_void_p, c_void_p, c_ll, c_int, ctypes.c_double, c_void_p]
+                               ctypes.POINTER(c_void_p), c_void_p, c_void_p, c_ll, c_int, ctypes.c_double, c_void_p, c_void_p, c_void_p]
+_ull, _size_t = ctypes.c_ulonglong, ctypes.c_size_t
+LIB.tpb_symm_support.argtypes = [c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int)]
+LIB.tpb_symm_round_size.argtypes = [c_int, c_int, _size_t, ctypes.POINTER(_size_t)]
+LIB.tpb_symm_create.argtypes = [c_int, _size_t, ctypes.POINTER(_ull), ctypes.POINTER(c_int)]
+LIB.tpb_symm_import.argtypes = [c_int, ctypes.POINTER(_ull)]
+LIB.tpb_symm_map.argtypes = [_ull, _size_t, ctypes.POINTER(c_int), c_int, ctypes.POINTER(c_void_p)]
+LIB.tpb_symm_unmap.argtypes = [c_void_p, _size_t]
+LIB.tpb_symm_release.argtypes = [_ull]
+LIB.tpb_mc_create.argtypes = [c_int, _size_t, ctypes.POINTER(_ull), ctypes.POINTER(c_int)]
+LIB.tpb_mc_add_device.argtypes = [_ull, c_int]
+LIB.tpb_mc_bind.argtypes = [_ull, _ull, _size_t]
+LIB.tpb_mc_unbind.argtypes = [_ull, c_int, _size_t]
 
 
 class AllGatherCtx(ctypes.Structure):
@@ -98,9 +118,12 @@ class HeapLayout:
 class RankComm:
     """One rank's view of the symmetric heap: its own region plus peer-mapped pointers."""
 
-    def __init__(self, world: int, rank: int, device: torch.device, layout: HeapLayout, base_ptrs: Sequence[int]):
+    def __init__(self, world: int, rank: int, device: torch.device, layout: HeapLayout, base_ptrs: Sequence[int],
+                 mc_base: int = 0, heap=None):
         self.world, self.rank, self.device, self.layout = world, rank, device, layout
         self.base = list(base_ptrs)
+        self.mc_base = mc_base  # multicast (NVLS) view of all ranks' regions, same offsets; 0: none
+        self.heap = heap        # owner of the mappings (None: cudaMalloc'ed region, freed with the process)
         with torch.cuda.device(device):
             self.epochs = torch.zeros(COMM_MAX_BLOCKS, dtype=torch.int32, device=device)
             self.expected = torch.zeros(2 * MAX_TILES, dtype=torch.int32, device=device)
@@ -120,7 +143,9 @@ class RankComm:
             for r in range(world):
                 arr[r] = self.base[r] + off
             self._ptr_arrays[name] = arr
-        self.wait_seconds = 2.0
+        self.wait_seconds = native.device_wait_seconds()
+        self._status_host = torch.zeros(4, dtype=torch.int32).pin_memory()
+        self._status_event: Optional[torch.cuda.Event] = None
         with torch.cuda.device(device):
             self.ag_push_counter = torch.zeros(4, dtype=torch.int32, device=device)
         self._ag_calls = [0, 0]
@@ -208,9 +233,11 @@ class RankComm:
 
     def _collective(self, kind: int, dtype: torch.dtype, n: int, force_algo: int = -1):
         code = 0 if dtype == torch.bfloat16 else 1
+        mc_in = self.mc_base + self.layout.off_staging_in if self.mc_base else 0
+        mc_out = self.mc_base + self.layout.off_staging_out if self.mc_base else 0
         check(LIB.tpb_collective(kind, code, self.world, self.rank, self._ptr_arrays["in"], self._ptr_arrays["out"],
                                  self._ptr_arrays["sig"], c_void_p(self.epochs.data_ptr()), c_void_p(self.status.data_ptr()), n,
-                                 force_algo, self.wait_seconds, native._stream()), "tpb_collective")
+                                 force_algo, self.wait_seconds, c_void_p(mc_in), c_void_p(mc_out), native._stream()), "tpb_collective")
         native.launch_count += 1
 
     def _capacity(self, dtype: torch.dtype, in_copies: int, out_copies: int) -> int:
@@ -293,13 +320,41 @@ class RankComm:
             if not bool((band == GUARD_PATTERN).all().item()):
                 raise RuntimeError(f"guard band {i} of rank {self.rank}'s symmetric heap was overwritten")
 
+    def _raise(self, code: int):
+        self.status.zero_()
+        from tensor_parallel_b200.parallel.collectives import TPCollectiveError
+
+        what = {1: "an mbarrier wait", 2: "a wait for a peer GPU"}.get(code, f"status {code}")
+        raise TPCollectiveError(f"{what} timed out inside a kernel on rank {self.rank}: the collective did not complete and "
+                                "its result must not be used (a peer is late by more than the device wait limit, or gone)")
+
     def check_status(self):
+        """Raises if a kernel of this rank gave up on a wait.  Synchronises the device."""
         code = int(self.status[0].item())
         if code:
-            self.status.zero_()
-            from tensor_parallel_b200.parallel.collectives import TPCollectiveError
+            self._raise(code)
 
-            raise TPCollectiveError({1: "an mbarrier wait", 2: "a wait for a peer GPU"}.get(code, f"status {code}") + " timed out inside a kernel")
+    def poll_status(self):
+        """Non-blocking form for hot loops: reads the host copy of the status word that the previous call queued behind
+        the kernels then in flight, raises if it is set, and queues the next copy.  A timeout therefore surfaces one call
+        late at the latest, without the host ever waiting for the GPU."""
+        if self._status_event is not None and self._status_event.query():
+            code = int(self._status_host[0])
+            self._status_event = None
+            if code:
+                self._raise(code)
+        if self._status_event is None:
+            with torch.cuda.device(self.device):
+                self._status_host.copy_(self.status, non_blocking=True)
+                self._status_event = torch.cuda.Event()
+                self._status_event.record()
+
+    def close(self):
+        """Unmaps this rank's views of the heap (multicast first).  Every rank calls it before any rank exits."""
+        if self.heap is not None:
+            self.heap.close()
+            self.heap = None
+            self.mc_base = 0
 
 
 def _alloc_region(device: torch.device, nbytes: int) -> int:
@@ -313,13 +368,195 @@ DEFAULT_SLOT_STRIDE = 64 * 16384       # fp32 elements per partial slot: 64 toke
 DEFAULT_STAGING = 288 * 1024 * 1024    # bytes per staging buffer (16384 x 8192 bf16 fits)
 
 
+class VmmHeap:
+    """One rank's (or, inside one process, all ranks') mappings of a VMM symmetric heap; see ``csrc/symm.cu``."""
+
+    _open: List["VmmHeap"] = []
+
+    def __init__(self, size: int):
+        VmmHeap._open.append(self)
+        self.size = size
+        self.handles: List[int] = []      # allocation handles held by this process (own and imported)
+        self.mappings: List[int] = []     # unicast virtual addresses
+        self.mc_handle = 0
+        self.mc_ptr = 0
+        self.bound: List[int] = []        # device indices whose memory this process bound to the multicast object
+        self._closed = False
+        atexit.register(self.close)
+
+    def close(self):
+        if self._closed:
+            return
+        self._closed = True
+        try:
+            torch.cuda.synchronize()
+        except Exception:  # noqa: BLE001 - interpreter shutdown
+            pass
+        if self.mc_ptr:
+            LIB.tpb_symm_unmap(c_void_p(self.mc_ptr), self.size)
+        for dev in self.bound:
+            LIB.tpb_mc_unbind(self.mc_handle, dev, self.size)
+        if self.mc_handle:
+            LIB.tpb_symm_release(self.mc_handle)
+        for ptr in self.mappings:
+            LIB.tpb_symm_unmap(c_void_p(ptr), self.size)
+        for handle in self.handles:
+            LIB.tpb_symm_release(handle)
+        self.mc_ptr = self.mc_handle = 0
+        self.mappings, self.handles, self.bound = [], [], []
+
+
+def close_all_heaps():
+    """Tears down every VMM heap of this process (multicast views first).  For an orderly exit of a multi-rank job:
+    every rank stops launching, the ranks meet at a barrier, every rank calls this, and only then do they exit."""
+    for heap in list(VmmHeap._open):
+        heap.close()
+    VmmHeap._open.clear()
+    _process_backends.clear()
+    _thread_backends.clear()
+
+
+def _vmm_wanted() -> bool:
+    return os.environ.get("TPB_VMM", "1") != "0"
+
+
+def _nvls_wanted() -> bool:
+    return os.environ.get("TPB_NVLS", "1") != "0"
+
+
+def _symm_support(device: torch.device):
+    vmm, mc = c_int(0), c_int(0)
+    with torch.cuda.device(device):
+        if LIB.tpb_symm_support(device.index, ctypes.byref(vmm), ctypes.byref(mc)) != 0:
+            return False, False
+    return bool(vmm.value), bool(mc.value)
+
+
+def _map(handle: int, size: int, devices: Sequence[int]) -> int:
+    arr = (c_int * len(devices))(*devices)
+    ptr = c_void_p()
+    check(LIB.tpb_symm_map(handle, size, arr, len(devices), ctypes.byref(ptr)), "tpb_symm_map")
+    return ptr.value
+
+
+def _exchange_fds(fd: Optional[int], rank: int, world: int, process_group, only_from: Optional[int] = None) -> List[Optional[int]]:
+    """Every rank hands its descriptor ``fd`` to every other rank (``only_from``: just that rank sends) over Unix-domain
+    sockets in the abstract namespace; returns the received descriptors by source rank (own slot: ``fd``)."""
+    name = f"\0tpb-{uuid.uuid4().hex}-{rank}"
+    server = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+    server.bind(name)
+    server.listen(world)
+    names: List[Optional[str]] = [None] * world
+    dist.all_gather_object(names, name, group=process_group)  # also orders "everyone listens" before the first connect
+    senders = range(world) if only_from is None else [only_from]
+    if rank in senders:
+        for peer in range(world):
+            if peer == rank:
+                continue
+            with socket.socket(socket.AF_UNIX, socket.SOCK_STREAM) as conn:
+                conn.connect(names[peer])
+                socket.send_fds(conn, [rank.to_bytes(4, "little")], [fd])
+    received: List[Optional[int]] = [None] * world
+    received[rank] = fd
+    expect = sum(1 for r in senders if r != rank)
+    server.settimeout(60.0)
+    for _ in range(expect):
+        conn, _addr = server.accept()
+        with conn:
+            msg, fds, _flags, _a = socket.recv_fds(conn, 4, 1)
+            received[int.from_bytes(msg, "little")] = fds[0]
+    server.close()
+    dist.barrier(group=process_group)
+    return received
+
+
+def _all_ok(ok: bool, process_group) -> bool:
+    flags: List[Optional[bool]] = [None] * dist.get_world_size(process_group)
+    dist.all_gather_object(flags, bool(ok), group=process_group)
+    return all(flags)
+
+
+def _vmm_process_heap(device: torch.device, layout: HeapLayout, process_group):
+    """``(base pointers, multicast pointer or 0, VmmHeap)`` or ``None`` when any rank cannot take part."""
+    world, rank = dist.get_world_size(process_group), dist.get_rank(process_group)
+    vmm, mc = _symm_support(device)
+    if not _all_ok(vmm and _vmm_wanted(), process_group):
+        return None
+    use_mc = _all_ok(mc and _nvls_wanted(), process_group)
+    size = _size_t(0)
+    with torch.cuda.device(device):
+        ok = LIB.tpb_symm_round_size(device.index, world if use_mc else 1, layout.total, ctypes.byref(size)) == 0
+        handle, fd = _ull(0), c_int(-1)
+        ok = ok and LIB.tpb_symm_create(device.index, size.value, ctypes.byref(handle), ctypes.byref(fd)) == 0
+    if not _all_ok(ok, process_group):
+        if ok:
+            os.close(fd.value)
+            LIB.tpb_symm_release(handle.value)
+        return None
+    heap = VmmHeap(size.value)
+    heap.handles.append(handle.value)
+    fds = _exchange_fds(fd.value, rank, world, process_group)
+    ptrs = []
+    with torch.cuda.device(device):
+        for r in range(world):
+            h = handle.value
+            if r != rank:
+                imported = _ull(0)
+                check(LIB.tpb_symm_import(fds[r], ctypes.byref(imported)), "tpb_symm_import")
+                os.close(fds[r])
+                h = imported.value
+                heap.handles.append(h)
+            ptrs.append(_map(h, size.value, [device.index]))
+        os.close(fd.value)
+        heap.mappings = list(ptrs)
+        torch.cuda.synchronize(device)
+        tensor_from_ptr(ptrs[rank], size.value, device).zero_()
+        torch.cuda.synchronize(device)
+    mc_ptr = 0
+    if use_mc:
+        mc_handle, mc_fd = _ull(0), c_int(-1)
+        ok = True
+        with torch.cuda.device(device):
+            if rank == 0:
+                ok = LIB.tpb_mc_create(world, size.value, ctypes.byref(mc_handle), ctypes.byref(mc_fd)) == 0
+        if _all_ok(ok, process_group):
+            mc_fds = _exchange_fds(mc_fd.value if rank == 0 else None, rank, world, process_group, only_from=0)
+            with torch.cuda.device(device):
+                if rank != 0:
+                    ok = LIB.tpb_symm_import(mc_fds[0], ctypes.byref(mc_handle)) == 0
+                    os.close(mc_fds[0])
+                else:
+                    os.close(mc_fd.value)
+                ok = ok and LIB.tpb_mc_add_device(mc_handle.value, device.index) == 0
+            if _all_ok(ok, process_group):  # every device is added before anyone binds
+                with torch.cuda.device(device):
+                    ok = LIB.tpb_mc_bind(mc_handle.value, handle.value, size.value) == 0
+                    if ok:
+                        heap.mc_handle = mc_handle.value
+                        heap.bound.append(device.index)
+                if _all_ok(ok, process_group):
+                    with torch.cuda.device(device):
+                        mc_ptr = _map(mc_handle.value, size.value, [device.index])
+                    heap.mc_ptr = mc_ptr
+        if not mc_ptr:
+            logger.warning("NVLink multicast set-up failed; collectives use plain peer loads and stores")
+    dist.barrier(group=process_group)
+    return ptrs, mc_ptr, heap
+
+
 def make_process_comm(device: torch.device, process_group=None, slot_stride: int = DEFAULT_SLOT_STRIDE,
                       max_slots: int = 64, staging_bytes: int = DEFAULT_STAGING) -> RankComm:
-    """One process per GPU: allocate the local region, exchange CUDA IPC handles, map the peers."""
+    """One process per GPU: allocate the local region, share it with the peers, map theirs."""
     world, rank = dist.get_world_size(process_group), dist.get_rank(process_group)
     if world > MAX_WORLD:
         raise ValueError(f"at most {MAX_WORLD} ranks are supported by the device collectives")
     layout = HeapLayout(slot_stride, max(max_slots, world), staging_bytes)
+    vmm = _vmm_process_heap(device, layout, process_group)
+    if vmm is not None:
+        ptrs, mc_ptr, heap = vmm
+        comm = RankComm(world, rank, device, layout, ptrs, mc_base=mc_ptr, heap=heap)
+        dist.barrier(group=process_group)
+        return comm
     base = _alloc_region(device, layout.total)
     handle = ctypes.create_string_buffer(64)
     with torch.cuda.device(device):
@@ -340,9 +577,58 @@ def make_process_comm(device: torch.device, process_group=None, slot_stride: int
     return comm
 
 
+def _vmm_thread_heap(devices: Sequence[torch.device], layout: HeapLayout):
+    """All ranks in one process: every region is mapped once with access for every device; one multicast view."""
+    if not _vmm_wanted():
+        return None
+    support = [_symm_support(d) for d in devices]
+    if not all(v for v, _ in support):
+        return None
+    use_mc = all(m for _, m in support) and _nvls_wanted() and len(devices) > 1
+    indices = [d.index for d in devices]
+    size = _size_t(0)
+    with torch.cuda.device(devices[0]):
+        if LIB.tpb_symm_round_size(indices[0], len(devices) if use_mc else 1, layout.total, ctypes.byref(size)) != 0:
+            return None
+    heap = VmmHeap(size.value)
+    try:
+        for d in devices:
+            handle = _ull(0)
+            with torch.cuda.device(d):
+                check(LIB.tpb_symm_create(d.index, size.value, ctypes.byref(handle), None), "tpb_symm_create")
+                heap.handles.append(handle.value)
+                heap.mappings.append(_map(handle.value, size.value, indices))
+                tensor_from_ptr(heap.mappings[-1], size.value, d).zero_()
+                torch.cuda.synchronize(d)
+    except RuntimeError as exc:
+        logger.warning("VMM symmetric heap unavailable (%s); using cudaMalloc + peer access", exc)
+        heap.close()
+        return None
+    mc_ptr = 0
+    if use_mc:
+        mc_handle = _ull(0)
+        with torch.cuda.device(devices[0]):
+            ok = LIB.tpb_mc_create(len(devices), size.value, ctypes.byref(mc_handle), None) == 0
+        ok = ok and all(LIB.tpb_mc_add_device(mc_handle.value, i) == 0 for i in indices)
+        if ok:
+            heap.mc_handle = mc_handle.value
+            for d, handle in zip(devices, heap.handles):
+                with torch.cuda.device(d):
+                    if LIB.tpb_mc_bind(mc_handle.value, handle, size.value) == 0:
+                        heap.bound.append(d.index)
+                    else:
+                        ok = False
+        if ok:
+            with torch.cuda.device(devices[0]):
+                mc_ptr = heap.mc_ptr = _map(mc_handle.value, size.value, indices)
+        else:
+            logger.warning("NVLink multicast set-up failed; collectives use plain peer loads and stores")
+    return list(heap.mappings), mc_ptr, heap
+
+
 def make_thread_comms(devices: Sequence[torch.device], slot_stride: int = DEFAULT_SLOT_STRIDE, max_slots: int = 64,
                       staging_bytes: int = DEFAULT_STAGING) -> Optional[List[RankComm]]:
-    """All ranks in one process: enable peer access pairwise and share plain pointers."""
+    """All ranks in one process: share plain pointers (VMM mappings, or cudaMalloc + pairwise peer access)."""
     world = len(devices)
     if world > MAX_WORLD or len({d.index for d in devices}) != world:
         return None
@@ -353,6 +639,10 @@ def make_thread_comms(devices: Sequence[torch.device], slot_stride: int = DEFAUL
                     logger.warning("no peer access between %s and %s; device collectives disabled", d, peer)
                     return None
     layout = HeapLayout(slot_stride, max(max_slots, world), staging_bytes)
+    vmm = _vmm_thread_heap(devices, layout)
+    if vmm is not None:
+        bases, mc_ptr, heap = vmm
+        return [RankComm(world, r, devices[r], layout, bases, mc_base=mc_ptr, heap=heap) for r in range(world)]
     bases = [_alloc_region(d, layout.total) for d in devices]
     return [RankComm(world, r, devices[r], layout, bases) for r in range(world)]
 
@@ -388,21 +678,28 @@ class _AllGatherFn(torch.autograd.Function):
 
 
 class DeviceAllReduce:
-    """``"sum"`` on the symmetric heap (one process per rank)."""
+    """``"sum"`` on the symmetric heap (one process per rank).  The kernels sum bf16 and fp32; any other dtype (fp16,
+    integers ...) goes to ``fallback`` - the process-group all-reduce - so that the result keeps the input's dtype."""
 
-    def __init__(self, comm: RankComm):
-        self.comm = comm
+    def __init__(self, comm: RankComm, fallback=None):
+        self.comm, self.fallback = comm, fallback
 
     def __call__(self, x: torch.Tensor, rank: int = 0):
+        if x.dtype not in (torch.bfloat16, torch.float32) or not x.is_cuda:
+            if self.fallback is None:
+                raise TypeError(f"the device all-reduce sums bf16 and fp32 tensors, got {x.dtype} and no fallback collective")
+            return self.fallback(x, rank)
+        self.comm.poll_status()
         return _AllReduceFn.apply(x, self.comm)
 
 
 class DeviceAllGather:
     """``"gather d"`` on the symmetric heap; falls back to the process group for uneven slices."""
 
-    def __init__(self, comm: RankComm, dim: int, fallback):
-        self.comm, self.dim, self.fallback = comm, dim, fallback
+    def __init__(self, comm: RankComm, dim: int, fallback, process_group=None):
+        self.comm, self.dim, self.fallback, self.pg = comm, dim, fallback, process_group
         self._even: Dict[tuple, bool] = {}
+        self._warned = False
 
     def __call__(self, x: torch.Tensor, rank: int = 0):
         dim = self.dim % x.ndim
@@ -411,11 +708,16 @@ class DeviceAllGather:
         if even is None:
             sizes = torch.tensor([x.shape[dim]], device=x.device)
             gathered = [torch.zeros_like(sizes) for _ in range(self.comm.world)]
-            dist.all_gather(gathered, sizes)
+            dist.all_gather(gathered, sizes, group=self.pg)
             even = self._even[key] = len({int(t.item()) for t in gathered}) == 1
         per = 8 if x.dtype == torch.bfloat16 else 4
         if not even or x.numel() % per or x.dtype not in (torch.bfloat16, torch.float32):
+            if not self._warned:
+                self._warned = True
+                logger.info("gather of %s %s along dim %d goes through the process group: the device all-gather takes equal "
+                            "bf16 / fp32 slices whose size is a multiple of 16 bytes", tuple(x.shape), x.dtype, dim)
             return self.fallback(x, rank)
+        self.comm.poll_status()
         return _AllGatherFn.apply(x, dim, self.comm)
 
 
@@ -451,12 +753,14 @@ class ProcessBackend:
         self.comm, self.pg = comm, process_group
 
     def all_reduce_op(self, group):
-        return DeviceAllReduce(self.comm)
+        from tensor_parallel_b200.parallel.collectives import DistributedAllReduce
+
+        return DeviceAllReduce(self.comm, DistributedAllReduce(self.comm.world, self.pg))
 
     def all_gather_op(self, group, dim):
         from tensor_parallel_b200.parallel.collectives import DistributedAllGather
 
-        return DeviceAllGather(self.comm, dim, DistributedAllGather(self.comm.world, dim, self.pg))
+        return DeviceAllGather(self.comm, dim, DistributedAllGather(self.comm.world, dim, self.pg), self.pg)
 
     def flat_gather(self):
         from tensor_parallel_b200.parallel.distributed import ProcessGroupFlatGather

@@ -58,13 +58,13 @@ class _RowParallelFn(torch.autograd.Function):
         x2d, weight = ctx.saved_tensors
         g = grad.reshape(-1, grad.shape[-1]).to(torch.bfloat16).contiguous()
         g = ctx.comm.all_reduce(g).clone()  # adjoint of the forward all-reduce
-        gx = native.gemm_nt(g, native.transpose(weight)).view(ctx.shape) if ctx.needs_input_grad[0] else None
-        gw = native.gemm_nt(native.transpose(g), native.transpose(x2d)) if ctx.needs_input_grad[1] else None
+        gx = native.linear_dgrad(g, weight).view(ctx.shape) if ctx.needs_input_grad[0] else None
+        gw = native.linear_wgrad(g, x2d) if ctx.needs_input_grad[1] else None
         gb = g.float().sum(0).to(grad.dtype) if ctx.has_bias and ctx.needs_input_grad[2] else None
         return gx, gw, gb, None
 
 
-def _fused_row_parallel_forward(linear: nn.Linear, comm):
+def _fused_row_parallel_forward(linear: nn.Linear, comm, process_group=None):
     plain_forward = linear.forward
 
     def forward(x):
@@ -74,8 +74,9 @@ def _fused_row_parallel_forward(linear: nn.Linear, comm):
         return _RowParallelFn.apply(x, linear.weight, linear.bias, comm)
 
     from tensor_parallel_b200.ops.comm import DeviceAllReduce
+    from tensor_parallel_b200.parallel.collectives import DistributedAllReduce
 
-    comm_sum = DeviceAllReduce(comm)
+    comm_sum = DeviceAllReduce(comm, DistributedAllReduce(comm.world, process_group))
     return forward
 
 
@@ -121,7 +122,7 @@ def rewrite(tp_module) -> int:
         linear = linears[0]
         if getattr(linear, "_tp_fused_row_parallel", False):
             continue
-        linear.forward = _fused_row_parallel_forward(linear, comm)
+        linear.forward = _fused_row_parallel_forward(linear, comm, getattr(tp_module, "process_group", None))
         linear._tp_fused_row_parallel = True
         sub.output_actions = {k: v for k, v in sub.output_actions.items() if k != 0}
         sites += 1

@@ -65,9 +65,9 @@ class _VocabParallelCE(torch.autograd.Function):
             # this rank's share of d loss / d hidden (through its vocabulary slice).  It is NOT summed over ranks
             # here: the replicated hidden state receives partial cotangents on every rank, and the adjoint of the
             # collective that produced it (the previous row-parallel all-reduce, the embedding gather) adds them up.
-            gx = native.gemm_nt(dlogits, native.transpose(weight)).view(hidden_shape)
+            gx = native.linear_dgrad(dlogits, weight).view(hidden_shape)
         if ctx.needs_input_grad[1]:
-            gw = native.gemm_nt(native.transpose(dlogits), native.transpose(x2d))
+            gw = native.linear_wgrad(dlogits, x2d)
         return gx, gw, None, None, None, None, None
 
 

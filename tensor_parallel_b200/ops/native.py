@@ -45,6 +45,21 @@ class ReduceCtx(ctypes.Structure):
                 ("max_tiles", c_int), ("ll_epochs", c_void_p)]
 
 
+class GemmOpts(ctypes.Structure):
+    _fields_ = [("x_mn", c_int), ("w_mn", c_int), ("norm_mode", c_int), ("norm_eps", c_float), ("norm_x", c_void_p),
+                ("norm_ld", c_ll), ("norm_k", c_int), ("norm_rowsum", c_void_p), ("wait_seconds", ctypes.c_double)]
+
+
+def device_wait_seconds() -> float:
+    """Bound of every wait for a peer GPU inside a kernel.  ``TPB_DEVICE_WAIT_S`` if set, else the host-side
+    collective timeout ``TENSOR_PARALLEL_TIMEOUT`` capped at 30 s: ranks may legitimately drift apart by seconds
+    (a checkpoint written by one rank, a slow data loader), but a kernel should not spin for minutes on a dead peer."""
+    explicit = os.environ.get("TPB_DEVICE_WAIT_S")
+    if explicit:
+        return float(explicit)
+    return min(float(os.environ.get("TENSOR_PARALLEL_TIMEOUT", "600")), 30.0)
+
+
 def check(code: int, what: str):
     if code != 0:
         detail = ""
@@ -136,20 +151,39 @@ def device_state(device: torch.device) -> DeviceState:
 # ------------------------------------------------------------------------------------------------
 
 LIB.tpb_gemm_plan.argtypes = [c_int, c_int, c_int, c_int, c_int, c_int, ctypes.POINTER(GemmPlan)]
+LIB.tpb_gemm_plan_ex.argtypes = [c_int, c_int, c_int, c_int, c_int, c_int, c_int, ctypes.POINTER(GemmPlan)]
+LIB.tpb_gemm_bf16_ex.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                 c_int, c_float, ctypes.POINTER(GemmPlan), ctypes.POINTER(ReduceCtx), ctypes.POINTER(GemmOpts), c_void_p]
+LIB.tpb_gemm_tune_split.argtypes = [c_int, c_int]
+LIB.tpb_set_wait_limit.argtypes = [ctypes.c_double]
+LIB.tpb_set_wait_limit(device_wait_seconds())
+LIB.tpb_gemm_disable_flagged_exchange.argtypes = [c_int]
+# TPB_FLAGGED_EXCHANGE = always | never: fixes the cross-rank protocol of the fused few-token GEMM + all-reduce
+# (default: chosen by rank count, see csrc/gemm_sm100.cu)
+_exchange = os.environ.get("TPB_FLAGGED_EXCHANGE", "")
+if _exchange in ("always", "never"):
+    LIB.tpb_gemm_disable_flagged_exchange(-1 if _exchange == "always" else 1)
 LIB.tpb_gemm_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                               c_int, c_float, ctypes.POINTER(GemmPlan), ctypes.POINTER(ReduceCtx), c_void_p]
 ACT_CODES = {None: 0, "none": 0, "relu": 1, "gelu": 2, "gelu_tanh": 3, "silu": 4, "swiglu16": 5}
 _plan_cache: Dict[Tuple, GemmPlan] = {}
 
 
-def gemm_plan(tokens: int, features: int, k: int, world: int = 1, force_splits: int = 0, force_kbox: int = 0) -> GemmPlan:
-    key = (tokens, features, k, world, force_splits, force_kbox, torch.cuda.current_device())
+def gemm_plan(tokens: int, features: int, k: int, world: int = 1, force_splits: int = 0, force_kbox: int = 0,
+              no_swap: bool = False) -> GemmPlan:
+    key = (tokens, features, k, world, force_splits, force_kbox, no_swap, torch.cuda.current_device())
     plan = _plan_cache.get(key)
     if plan is None:
         plan = GemmPlan()
-        check(LIB.tpb_gemm_plan(tokens, features, k, world, force_splits, force_kbox, ctypes.byref(plan)), "gemm_plan")
+        check(LIB.tpb_gemm_plan_ex(tokens, features, k, world, force_splits, force_kbox, int(no_swap), ctypes.byref(plan)), "gemm_plan")
         _plan_cache[key] = plan
     return plan
+
+
+def tune_split(min_tile_kb: int = 0, target_kb: int = 0):
+    """Thresholds of the automatic split-K of few-tile decode GEMMs; cached plans are dropped."""
+    LIB.tpb_gemm_tune_split(min_tile_kb, target_kb)
+    _plan_cache.clear()
 
 
 def gemm_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
@@ -160,24 +194,44 @@ def gemm_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
 
 
 def gemm_nt(x2d: torch.Tensor, w: torch.Tensor, bias=None, residual=None, act=None, out=None, force_splits: int = 0,
-            reduce_ctx: Optional[ReduceCtx] = None, world: int = 1, bias_scale: float = 1.0, force_kbox: int = 0) -> torch.Tensor:
-    """``out[tokens, features] = act(x2d @ w.T + bias) + residual`` on the tcgen05 kernel."""
+            reduce_ctx: Optional[ReduceCtx] = None, world: int = 1, bias_scale: float = 1.0, force_kbox: int = 0,
+            x_t: bool = False, w_t: bool = False, norm: Optional[Tuple] = None, norm_rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[tokens, features] = act(x2d @ w.T + bias) + residual`` on the tcgen05 kernel.
+
+    ``x_t`` / ``w_t``: the operand is passed transposed, ``x2d`` as ``[k, tokens]`` / ``w`` as ``[k, features]`` (row
+    major), and is read as it lies in memory (MN-major tensor-core operand) - what the backward GEMMs of a linear
+    layer need.  ``norm = (mode, eps, rowsum)`` folds an RMSNorm (``mode`` 1) or LayerNorm (2) of the rows of ``x2d``
+    into the kernel (at most 64 tokens): ``w`` must already be multiplied by the norm weight along k.  ``norm_rows``
+    ``[tokens, n]`` are the rows the statistics are taken over when ``x2d`` is only a column slice of them."""
     global launch_count
-    tokens, k = x2d.shape
-    features = w.shape[0]
+    if x_t:
+        k, tokens = x2d.shape
+    else:
+        tokens, k = x2d.shape
+    features = w.shape[1] if w_t else w.shape[0]
     x2d, w = _tma_ready(x2d), _tma_ready(w)
     if out is None:
         out = torch.empty(tokens, features // 2 if act == "swiglu16" else features, dtype=torch.bfloat16, device=x2d.device)
-    plan = gemm_plan(tokens, features, k, world, force_splits, force_kbox)
+    plan = gemm_plan(tokens, features, k, world, force_splits, force_kbox, no_swap=x_t or w_t)
     state = device_state(x2d.device)
     ctx = reduce_ctx
     if ctx is None:
         if plan.reduce:
             state.ensure_slots(tokens * (features if act == "swiglu16" else out.stride(0)))
         ctx = state.ctx
-    check(LIB.tpb_gemm_bf16(_ptr(x2d), _ptr(w), _ptr(out), _ptr(bias), _ptr(residual), tokens, features, k, x2d.stride(0),
-                            w.stride(0), out.stride(0), ACT_CODES[act], bias_scale, ctypes.byref(plan), ctypes.byref(ctx), _stream()),
-          "tpb_gemm_bf16")
+    opts = None
+    if x_t or w_t or norm is not None:
+        opts = GemmOpts()
+        opts.x_mn, opts.w_mn = int(x_t), int(w_t)
+        if norm is not None:
+            mode, eps, rowsum = norm
+            opts.norm_mode, opts.norm_eps = int(mode), float(eps)
+            rows = x2d if norm_rows is None else norm_rows
+            opts.norm_x, opts.norm_ld, opts.norm_k = rows.data_ptr(), rows.stride(0), rows.shape[1]
+            opts.norm_rowsum = rowsum.data_ptr() if rowsum is not None else 0
+    check(LIB.tpb_gemm_bf16_ex(_ptr(x2d), _ptr(w), _ptr(out), _ptr(bias), _ptr(residual), tokens, features, k, x2d.stride(0),
+                               w.stride(0), out.stride(0), ACT_CODES[act], bias_scale, ctypes.byref(plan), ctypes.byref(ctx),
+                               ctypes.byref(opts) if opts is not None else None, _stream()), "tpb_gemm_bf16")
     launch_count += 1
     return out
 
@@ -240,14 +294,24 @@ class _LinearFn(torch.autograd.Function):
             g2d = g2d.contiguous()
         gx = gw = gb = None
         if ctx.needs_input_grad[0]:
-            # dX[m, k] = sum_n dY[m, n] W[n, k]  ==  dY @ (W^T)^T  with W^T [k, n] K-major over n
-            gx = gemm_nt(g2d, transpose(weight)).view(ctx.x_shape)
+            gx = linear_dgrad(g2d, weight).view(ctx.x_shape)
         if ctx.needs_input_grad[1]:
-            # dW[n, k] = sum_m dY[m, n] X[m, k]  ==  dY^T @ (X^T)^T
-            gw = gemm_nt(transpose(g2d), transpose(x2d))
+            gw = linear_wgrad(g2d, x2d)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             gb = g2d.float().sum(0).to(grad.dtype)
         return gx, gw, gb
+
+
+def linear_dgrad(g2d: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """``dX[m, k] = sum_n dY[m, n] W[n, k]``: the contraction runs over W's rows, so W ``[n, k]`` is read as it lies in
+    memory as an MN-major operand (no transposed copy of the weight)."""
+    return gemm_nt(g2d, weight, w_t=True)
+
+
+def linear_wgrad(g2d: torch.Tensor, x2d: torch.Tensor) -> torch.Tensor:
+    """``dW[n, k] = sum_m dY[m, n] X[m, k]``: both operands are contracted over their rows and are read in place as
+    MN-major operands (no transposed copies of the gradient and the activation)."""
+    return gemm_nt(g2d, x2d, x_t=True, w_t=True)
 
 
 def linear(x, weight, bias=None):
@@ -454,7 +518,7 @@ def _strided_ok(t: torch.Tensor) -> bool:
     return t.stride(3) == 1 and all(s % 8 == 0 for s in t.stride()[:3]) and t.data_ptr() % 16 == 0
 
 
-def attention_forward(q, k, v, causal, scale, want_lse=False, bias=None):
+def attention_forward(q, k, v, causal, scale, want_lse=False, bias=None, out=None):
     """q ``[B,Sq,Hq,D]``, k / v ``[B,Sk,Hkv,D]`` (any strides with contiguous head_dim) -> ``[B,Sq,Hq,D]``.
     ``bias`` (bf16 / fp32, broadcastable to ``[B,Hq,Sq,Sk]``) is added to the scaled scores; ``-inf`` masks a key."""
     global launch_count
@@ -463,7 +527,8 @@ def attention_forward(q, k, v, causal, scale, want_lse=False, bias=None):
     v = v if _strided_ok(v) else v.contiguous()
     b, sq, hq, d = q.shape
     sk, hkv = k.shape[1], k.shape[2]
-    out = torch.empty(b, sq, hq, d, dtype=q.dtype, device=q.device)
+    if out is None:  # (a caller's `out` may be a strided [b, sq, hq, d] view with contiguous head_dim)
+        out = torch.empty(b, sq, hq, d, dtype=q.dtype, device=q.device)
     lse = torch.empty(b, hq, sq, dtype=torch.float32, device=q.device) if want_lse else None
     scale = 1.0 / math.sqrt(d) if scale is None else scale
     if bias is None:
@@ -543,11 +608,11 @@ def attn_decode(q, kcache, vcache, len_ptr, len_add, scale=None, splits=1, works
     scale = 1.0 / math.sqrt(d) if scale is None else scale
     check(LIB.tpb_attn_decode(_ptr(q), _ptr(kcache), _ptr(vcache), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(len_ptr), len_add,
                               b, hq, hkv, d, smax, splits, scale, _stream()), "tpb_attn_decode")
-    launch_count += 1 + (1 if splits > 1 else 0) + max(0, (hq // hkv) // (4 if d == 128 else 8) - 1)
+    launch_count += LIB.tpb_last_launches()
     return out
 
 
-LIB.tpb_attn_decode_fused.argtypes = [c_void_p] * 10 + [c_int] * 6 + [c_float, c_int, c_float, c_int, c_ll, c_ll, c_ll, c_void_p, c_void_p]
+LIB.tpb_attn_decode_fused.argtypes = [c_void_p] * 10 + [c_int] * 6 + [c_float, c_int, c_float, c_int, c_ll, c_ll, c_ll, c_void_p, c_ll, c_void_p]
 LIB.tpb_rope_table.argtypes = [c_void_p, c_int, c_int, c_float, c_void_p]
 
 
@@ -569,7 +634,7 @@ def attn_decode_fused(q, k, v, kcache, vcache, pos_ptr, rotary_dim, theta, inter
     global launch_count
     d = kcache.shape[3]
     b, hq, hkv, smax = q.shape[0], q.shape[1] // d, kcache.shape[1], kcache.shape[2]
-    out = torch.empty(b, hq, d, dtype=q.dtype, device=q.device) if out is None else out
+    out = torch.empty(b, hq, d, dtype=q.dtype, device=q.device) if out is None else out  # (rows may be column slices of a wider buffer)
     part_o = part_ml = counters = None
     if splits > 1:
         if workspace is None:
@@ -580,9 +645,10 @@ def attn_decode_fused(q, k, v, kcache, vcache, pos_ptr, rotary_dim, theta, inter
     scale = 1.0 / math.sqrt(d) if scale is None else scale
     check(LIB.tpb_attn_decode_fused(_ptr(q), _ptr(k), _ptr(v), _ptr(kcache), _ptr(vcache), _ptr(out), _ptr(part_o), _ptr(part_ml),
                                     _ptr(counters), _ptr(pos_ptr), b, hq, hkv, d, smax, splits, scale, rotary_dim, theta,
-                                    int(interleaved), q.stride(0), k.stride(0), v.stride(0), _ptr(rope_angles), _stream()),
+                                    int(interleaved), q.stride(0), k.stride(0), v.stride(0), _ptr(rope_angles),
+                                    out.stride(0) if out.stride(0) != hq * d else 0, _stream()),
           "tpb_attn_decode_fused")
-    launch_count += max(1, (hq // hkv) // (4 if d == 128 else 8))
+    launch_count += LIB.tpb_last_launches()
     return out
 
 

@@ -48,8 +48,9 @@ class AdamW(torch.optim.Optimizer):
                     with torch.cuda.device(p.device):
                         native.adamw_step(p, grad, state["exp_avg"], state["exp_avg_sq"], state["step"], group["lr"], beta1, beta2,
                                           group["eps"], group["weight_decay"], master=state.get("master"))
-                    p._version  # noqa: B018  (the kernel writes through data_ptr; bump below so ZeRO-3 re-gathers)
-                    p.add_(0)
+                    # the kernel wrote through data_ptr: bump the version counter (no kernel) so that ZeRO-3 re-gathers
+                    # and a serving engine built from these weights notices
+                    torch.autograd.graph.increment_version(p)
                     continue
                 g = grad.float()
                 m, v = state["exp_avg"], state["exp_avg_sq"]

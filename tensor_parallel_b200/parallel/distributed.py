@@ -189,7 +189,16 @@ class DistributedTensorParallel(ServingMixin, nn.Module):
             reduced += 1
         return reduced
 
+    def check_status(self):
+        """Raises ``TPCollectiveError`` if a kernel of this rank gave up waiting for a peer (synchronises the device)."""
+        comm = getattr(self._device_backend, "comm", None)
+        if comm is not None:
+            comm.check_status()
+
     def forward(self, *args, **kwargs):
+        comm = getattr(self._device_backend, "comm", None)
+        if comm is not None:
+            comm.poll_status()  # a device-side wait that gave up during an earlier call raises here, without a sync
         if self.sharding_manager is not None:
             self.sharding_manager.synchronize_weights(self.all_cuda)
         device = self.devices[0]

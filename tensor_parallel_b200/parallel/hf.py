@@ -92,6 +92,50 @@ class TensorParallelPreTrainedModel(*_BASES):
             state[prefix + key[len(head):]] = state.pop(key)
         return state
 
+    # -- generation: plain greedy decoding of a served family runs on the kernel-level engine ----------
+
+    _ENGINE_KWARGS = {"max_new_tokens", "max_length", "do_sample", "num_beams", "attention_mask", "use_cache", "pad_token_id",
+                      "eos_token_id", "input_ids"}
+
+    @torch.no_grad()
+    def generate(self, inputs: Optional[torch.Tensor] = None, generation_config=None, **kwargs):
+        """``GenerationMixin.generate`` with one shortcut: greedy decoding of a full-attention prompt on CUDA bf16 shards
+        of a family the serving engine describes (``tensor_parallel_b200.engine_spec``) runs there - hand-written
+        kernels, fused GEMM + all-reduce, no Python per layer - and returns what the Hugging Face loop would return
+        (tokens after an end-of-sequence token are replaced by the pad token).  Everything else (sampling, beams,
+        logits processors, padded prompts, streamers ...) takes the stock path through ``forward``."""
+        ids = inputs if inputs is not None else kwargs.get("input_ids")
+        engine_ok = (
+            generation_config is None and isinstance(ids, torch.Tensor) and ids.ndim == 2 and ids.dtype in (torch.int64, torch.int32)
+            and set(kwargs) <= self._ENGINE_KWARGS and not kwargs.get("do_sample", getattr(self.generation_config, "do_sample", False))
+            and kwargs.get("num_beams", getattr(self.generation_config, "num_beams", 1)) == 1
+            and kwargs.get("use_cache", True)
+            and (kwargs.get("attention_mask") is None or bool(kwargs["attention_mask"].all()))
+            and getattr(self.generation_config, "repetition_penalty", None) in (None, 1.0)
+        )
+        if engine_ok:
+            new = kwargs.get("max_new_tokens")
+            if new is None:
+                total = kwargs.get("max_length", getattr(self.generation_config, "max_length", None))
+                new = None if total is None else total - ids.shape[1]
+            engine = self.wrapped_model.serving_engine(ids.shape[0], ids.shape[1] + (new or 0) + 4) if new and new > 0 else None
+            if engine is not None:
+                out = engine.generate(ids, new)
+                eos = kwargs.get("eos_token_id", getattr(self.generation_config, "eos_token_id", None))
+                if eos is not None:
+                    pad = kwargs.get("pad_token_id", getattr(self.generation_config, "pad_token_id", None))
+                    eos_ids = torch.as_tensor(eos if isinstance(eos, (list, tuple)) else [eos], device=out.device)
+                    pad = int(eos_ids[0]) if pad is None else pad
+                    gen = out[:, ids.shape[1]:]
+                    ended = torch.isin(gen, eos_ids).cumsum(1)
+                    after = (ended - torch.isin(gen, eos_ids).long()) > 0  # strictly after the first end-of-sequence token
+                    gen.masked_fill_(after, pad)
+                    alive = (~(ended > 0)).any(0).nonzero()
+                    keep = int(alive.max()) + 2 if alive.numel() else 1   # the step at which the last sequence ended
+                    out = out[:, : ids.shape[1] + min(keep, gen.shape[1])]
+                return out
+        return super().generate(inputs, generation_config=generation_config, **kwargs)
+
     # -- generation plumbing: questions about the architecture go to shard 0 -------------------------
 
     def _shard0(self):

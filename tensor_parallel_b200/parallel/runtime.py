@@ -415,8 +415,15 @@ class TensorParallel(ServingMixin, nn.Module):
                 if all(_is_stateful_cache(o) for o in others):
                     _attach_cache_siblings(value, len(self.devices), self.output_device_index, self.devices, existing=others)
 
+    def check_status(self):
+        """Raises ``TPCollectiveError`` if a kernel gave up waiting for a peer GPU (synchronises the devices)."""
+        for comm in getattr(getattr(self, "_device_backend", None), "comms", None) or ():
+            comm.check_status()
+
     def forward(self, *args, **kwargs):
         self._materialize()
+        for comm in getattr(getattr(self, "_device_backend", None), "comms", None) or ():
+            comm.poll_status()  # a device-side wait that gave up during an earlier call raises here, without a sync
         if self.sharding_manager is not None:
             self.sharding_manager.synchronize_weights(self.all_cuda)
         if len(self.module_shards) <= 1:

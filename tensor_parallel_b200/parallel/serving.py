@@ -1,8 +1,9 @@
 """``generate()`` / ``decode_step()`` for tensor-parallel models.
 
-On CUDA, Llama-shaped shards are served by :class:`tensor_parallel_b200.engine.LlamaEngine`
-(hand-written kernels, fused GEMM + all-reduce, CUDA-graph decode).  Everything else — other
-families, CPU shards, beam search, sampling — goes through the generic loop in
+On CUDA, bf16 shards of the families that ``tensor_parallel_b200.engine_spec`` describes (Llama / Mistral /
+Qwen2, OPT, Falcon; the self-contained models and the Hugging Face classes) are served by
+:class:`tensor_parallel_b200.engine.DecoderEngine` (hand-written kernels, fused GEMM + all-reduce, CUDA-graph
+decode).  Everything else — other families, CPU shards, beam search, sampling — goes through the generic loop in
 ``tensor_parallel_b200.models.generation`` with the head-sharded ``PerDeviceTensors`` cache.
 """
 from __future__ import annotations
@@ -20,40 +21,57 @@ class ServingMixin:
         return getattr(backend, "comm", None)
 
     def serving_engine(self, max_batch: int = 8, max_seq: int = 2560):
-        """The kernel-level engine of this model, or ``None`` when it does not apply."""
+        """The kernel-level engine of this model, or ``None`` when it does not apply: the shards must be CUDA bf16
+        causal LMs of a family that ``tensor_parallel_b200.engine_spec`` can describe (Llama / Mistral / Qwen2, OPT,
+        Falcon - self-contained or Hugging Face classes).
+
+        The engine keeps its own serving-layout copies of the projection weights.  It notices through the tensors'
+        version counters when the shard's parameters have been written to since it was built (an optimizer step,
+        ``load_state_dict``, a merged adapter) and is rebuilt then; with ZeRO-3 the flat shards are gathered first."""
+        from tensor_parallel_b200 import engine_spec
+
         shard = self.module_shards[0]
-        inner = shard.__dict__.get("tp_wrapped_module", shard)
-        cfg = getattr(inner, "config", None)
-        param = next(inner.parameters(), None)
-        if getattr(cfg, "model_type", None) != "llama" or param is None or not param.is_cuda or param.dtype != torch.bfloat16:
+        param = next(engine_spec.unwrap(shard).parameters(), None)
+        if param is None or not param.is_cuda or param.dtype != torch.bfloat16:
             return None
-        if type(inner).__module__ != "tensor_parallel_b200.models.llama" or not hasattr(inner, "lm_head"):
-            return None  # (a bare LlamaModel without a head has nothing to generate from)
-        if getattr(cfg, "tie_word_embeddings", False):
-            return None  # the engine expects a vocabulary-split head; a tied head is hidden-split (the generic path serves it)
-        world = getattr(self, "world_size", 1)
+        manager = getattr(self, "sharding_manager", None)
+        if manager is not None:
+            with torch.no_grad():
+                manager.synchronize_weights(getattr(self, "all_cuda", True))
         eng = self._engine
+        if eng is not None and eng.stale():
+            self._engine = eng = None
         fits = eng is not None and eng.max_batch >= max_batch and eng.max_seq >= max_seq
-        if eng is not None and not fits:
+        if fits:
+            return eng
+        if eng is not None:
             max_batch, max_seq = max(max_batch, eng.max_batch), max(max_seq, eng.max_seq)
+        spec = engine_spec.describe(shard, max_seq)
+        if spec is None:
+            return None
+        world = getattr(self, "world_size", 1)
         if len(self.module_shards) > 1:
             # single process, one shard per GPU: one engine per rank on the shared symmetric heaps, one driving thread
             comms = getattr(getattr(self, "_device_backend", None), "comms", None)
             if comms is None or len(comms) != len(self.module_shards):
                 return None
-            if not fits:
-                from tensor_parallel_b200.engine import EngineGroup
+            from tensor_parallel_b200.engine import EngineGroup
 
-                self._engine = eng = EngineGroup(list(self.module_shards), comms, max_batch=max_batch, max_seq=max_seq)
-            return eng
+            self._engine = None  # (frees the old caches before the new ones are allocated)
+            try:
+                self._engine = EngineGroup(list(self.module_shards), comms, max_batch=max_batch, max_seq=max_seq)
+            except ValueError:
+                return None
+            return self._engine
         comm = self._engine_comm()
         if world > 1 and comm is None:
             return None
-        if not fits:
-            from tensor_parallel_b200.engine import LlamaEngine
+        from tensor_parallel_b200.engine import DecoderEngine
 
-            self._engine = eng = LlamaEngine(shard, comm if world > 1 else None, max_batch=max_batch, max_seq=max_seq)
-        return eng
+        self._engine = None
+        self._engine = DecoderEngine(shard, comm if world > 1 else None, max_batch=max_batch, max_seq=max_seq, spec=spec,
+                                     process_group=getattr(self, "process_group", None))
+        return self._engine
 
     @torch.no_grad()
     def generate(self, input_ids: Optional[torch.Tensor] = None, max_new_tokens: int = 20, **kwargs):
@@ -71,7 +89,7 @@ class ServingMixin:
         """Engine-backed prompt pass; returns last-position logits ``[batch, vocab]``."""
         engine = self.serving_engine(input_ids.shape[0], input_ids.shape[1] + max_new_tokens + 4)
         if engine is None:
-            raise RuntimeError("prefill()/decode_step() need the CUDA serving engine (Llama-shaped bf16 shards)")
+            raise RuntimeError("prefill()/decode_step() need the CUDA serving engine (bf16 shards of a served family)")
         return engine.prefill(input_ids)
 
     @torch.no_grad()

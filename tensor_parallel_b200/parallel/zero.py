@@ -11,8 +11,11 @@ replica only sees the partial gradient that flowed through its own weight slices
 
 The gather is skipped while no flat shard changed (``_version`` check), e.g. across
 gradient-accumulation micro-steps.  Parameter order is ``sorted(names)`` unless the caller
-passes an explicit sequence, and the layout is saved alongside the shards
-(``shard_layout`` buffer-free metadata via ``get_extra_state``).
+passes an explicit sequence, and the layout (names, shapes, per-rank piece sizes) is saved alongside
+the shards as the module's extra state (key ``sharding_manager._extra_state``): loading flat shards
+into a model whose layout differs raises instead of silently scrambling parameters - the reference
+keeps the order of a Python ``set`` and saves nothing (``src/tensor_parallel/sharding.py:41-44``).
+A checkpoint without that key (one written by the reference) still loads.
 Reference: ``src/tensor_parallel/sharding.py:18-180``.
 """
 from __future__ import annotations
@@ -159,6 +162,29 @@ class Sharded(nn.Module):
             "shapes": [list(s) for s in getattr(self, "_shapes", [])],
             "sizes_with_pad": getattr(self, "_sizes_with_pad", []),
         }
+
+    def get_extra_state(self):
+        return self.layout()
+
+    def set_extra_state(self, state):
+        """Refuses flat shards that were cut from a different parameter list or with different piece sizes."""
+        if not state or not state.get("names"):
+            return
+        mine = self.layout()
+        for key in ("names", "shapes", "sizes_with_pad"):
+            if [list(x) if isinstance(x, (list, tuple)) else x for x in state.get(key, [])] != \
+                    [list(x) if isinstance(x, (list, tuple)) else x for x in mine[key]]:
+                raise RuntimeError(
+                    f"the checkpoint's ZeRO-3 flat shards were built with a different layout ({key} differ): "
+                    f"checkpoint has {len(state.get('names', []))} parameters starting with {state.get('names', [])[:3]}, this model "
+                    f"{len(mine['names'])} starting with {mine['names'][:3]}.  Pass sharded_param_names=<the checkpoint's names> when "
+                    "wrapping, or load an un-sharded checkpoint (save_tensor_parallel) instead."
+                )
+
+    def _load_from_state_dict(self, state_dict, prefix, *args, **kwargs):
+        if prefix + "_extra_state" not in state_dict:  # a checkpoint written without layout metadata: trust the caller
+            state_dict[prefix + "_extra_state"] = self.layout()
+        return super()._load_from_state_dict(state_dict, prefix, *args, **kwargs)
 
     def state_dict(self, *args, **kwargs):
         if self.preserve_shards_when_saving:

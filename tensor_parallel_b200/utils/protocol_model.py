@@ -5,8 +5,9 @@ What is modelled, word for word:
 
 * every rank owns two workspace halves; consecutive calls alternate between them;
 * half ``h`` of rank ``d`` holds one slot per source rank; a slot is an array of 16-byte words
-  ``(value(t), flag, value(t + 1), flag)`` addressed ``tile * TILE_WORDS + pair * ROWS + row``
-  (or, with ``tile_keyed=False``, the shape-dependent ``(tile * ROWS + row) * pairs + pair`` order that an earlier
+  ``(values(t, t + 1), flag, values(t + 2, t + 3), flag)`` (each half is one 8-byte unit: two bf16 values and the
+  flag) addressed ``tile * TILE_WORDS + quad * ROWS + row``
+  (or, with ``tile_keyed=False``, the shape-dependent ``(tile * ROWS + row) * quads + quad`` order that an earlier
   version of the kernel used and that this model shows to be unsafe when shapes are interleaved);
 * a call on tile ``t`` uses flag ``epoch[h][t] + 1`` and stores it back; epochs live with the rank and only grow;
 * the sender stores its words into every rank's slot (in any order, a word at a time); the receiver polls the words of
@@ -23,11 +24,11 @@ import time
 from typing import Dict, List, Sequence, Tuple
 
 ROWS = 128                    # feature rows per tile
-TILE_WORDS = ROWS * 32        # words one tile owns (up to 32 token pairs)
+TILE_WORDS = ROWS * 16        # words one tile owns (up to 16 token quads)
 
 
 class Heap:
-    """Flagged areas of all ranks: ``mem[dest][half][src]`` maps a word index to ``(v0, f0, v1, f1)``."""
+    """Flagged areas of all ranks: ``mem[dest][half][src]`` maps a word index to ``((a, b), f0, (c, d), f1)``."""
 
     def __init__(self, world: int):
         self.world = world
@@ -57,7 +58,7 @@ class Rank:
     def all_reduce(self, partial: Sequence[Sequence[float]], features: int, timeout: float = 5.0) -> List[List[float]]:
         """``partial[token][feature]`` of this rank; returns the sum over ranks (every rank gets the same lists)."""
         tokens = len(partial)
-        pairs = (tokens + 1) // 2
+        pairs = (tokens + 3) // 4  # token quads: one 16-byte word each
         half = self.calls & 1
         self.calls += 1
         tiles = (features + ROWS - 1) // ROWS
@@ -69,8 +70,8 @@ class Rank:
         self.rng.shuffle(words)
         for n, (t, r, p) in enumerate(words):
             f = t * ROWS + r
-            v0 = partial[2 * p][f]
-            v1 = partial[2 * p + 1][f] if 2 * p + 1 < tokens else 0.0
+            tok = [partial[4 * p + j][f] if 4 * p + j < tokens else 0.0 for j in range(4)]
+            v0, v1 = (tok[0], tok[1]), (tok[2], tok[3])
             idx = _word_index(t, r, p, pairs, self.tile_keyed)
             for dest in range(self.heap.world):
                 self.heap.mem[dest][half][self.rank][idx] = (v0, flags[t], v1, flags[t])
@@ -92,9 +93,9 @@ class Rank:
                     if time.monotonic() > deadline:
                         raise TimeoutError(f"rank {self.rank}: word {idx} of rank {src} never arrived")
                     time.sleep(0)
-                out[2 * p][f] += w[0]
-                if 2 * p + 1 < tokens:
-                    out[2 * p + 1][f] += w[2]
+                for j, value in enumerate(w[0] + w[2]):
+                    if 4 * p + j < tokens:
+                        out[4 * p + j][f] += value
         return out
 
 

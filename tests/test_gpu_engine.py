@@ -66,3 +66,102 @@ def test_generate_uses_engine_and_host_driven_steps():
         tok = wrapped.decode_step(tok).clone().pin_memory()
         seq.append(tok.clone())
     assert torch.equal(torch.stack(seq, 1), out[:, 33:].cpu())
+
+
+def _agreement(engine_tokens, generic_tokens, prompt_len):
+    a, b = engine_tokens[:, prompt_len:].cpu(), generic_tokens[:, prompt_len:].cpu()
+    return (a == b).float().mean().item()
+
+
+def _bf16_rounded(model):
+    """fp32 oracle (CPU) and bf16 CUDA copy holding exactly the same (bf16-representable) weights."""
+    import copy
+
+    served = copy.deepcopy(model).to(device="cuda", dtype=torch.bfloat16).eval()
+    oracle = copy.deepcopy(model).float().eval()
+    oracle.load_state_dict({k: v.float().cpu() for k, v in served.state_dict().items()})
+    return oracle, served
+
+
+def test_engine_serves_falcon_shaped_model():
+    """Parallel attention + MLP block with two LayerNorms, grouped fused QKV, GeLU, tied head: the engine runs four
+    kernels per layer and must track the fp32 module-level forward."""
+    from tensor_parallel_b200.models.falcon import FalconConfig, FalconForCausalLM
+    from tensor_parallel_b200.models.generation import generate
+
+    torch.manual_seed(0)
+    cfg = FalconConfig(vocab_size=1024, hidden_size=512, n_layer=3, n_head=8, n_head_kv=2)
+    oracle, served = _bf16_rounded(FalconForCausalLM(cfg))
+    wrapped = tp.tensor_parallel(served, ["cuda:0"])
+    ids = torch.randint(0, 1024, (3, 70), generator=torch.Generator().manual_seed(1))
+    logits = wrapped.prefill(ids, max_new_tokens=12)
+    with torch.no_grad():
+        want = oracle(input_ids=ids)
+    torch.testing.assert_close(logits.cpu(), want.logits[:, -1], atol=0.08, rtol=0.05)
+    got = wrapped.generate(ids, max_new_tokens=10)
+    assert wrapped._engine is not None and wrapped._engine.parallel
+    assert wrapped._engine.kernels_per_step <= 4 * cfg.n_layer + 8
+    ref = generate(oracle, ids, max_new_tokens=10)
+    assert _agreement(got, ref, 70) >= 0.9
+    wrapped._engine.check_status()
+
+
+def test_engine_serves_opt_shaped_model():
+    """Learned positions, LayerNorm with bias, biased projections, ReLU, tied head."""
+    from tensor_parallel_b200.models.generation import generate
+    from tensor_parallel_b200.models.opt import OPTConfig, OPTForCausalLM
+
+    torch.manual_seed(0)
+    cfg = OPTConfig(vocab_size=1024, hidden_size=512, num_hidden_layers=3, ffn_dim=1024, num_attention_heads=8, max_position_embeddings=256)
+    model = OPTForCausalLM(cfg)
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            if name.endswith("bias"):
+                p.normal_(0.0, 0.05)
+            if "layer_norm.weight" in name:
+                p.add_(0.1 * torch.randn_like(p))
+    oracle, served = _bf16_rounded(model)
+    wrapped = tp.tensor_parallel(served, ["cuda:0"])
+    ids = torch.randint(0, 1024, (2, 70), generator=torch.Generator().manual_seed(1))
+    logits = wrapped.prefill(ids, max_new_tokens=12)
+    with torch.no_grad():
+        want = oracle(input_ids=ids)
+    torch.testing.assert_close(logits.cpu(), want.logits[:, -1], atol=0.08, rtol=0.05)
+    got = wrapped.generate(ids, max_new_tokens=10)
+    assert wrapped._engine is not None and not wrapped._engine.parallel
+    assert _agreement(got, generate(oracle, ids, max_new_tokens=10), 70) >= 0.9
+    wrapped._engine.check_status()
+
+
+def test_engine_serves_hugging_face_llama():
+    """``transformers`` ``LlamaForCausalLM`` (GQA) wrapped by the HF-aware wrapper: greedy ``generate()`` runs on the engine
+    and agrees with the stock Hugging Face loop on the fp32 model."""
+    transformers = pytest.importorskip("transformers")
+    from tensor_parallel_b200.ops import native
+
+    torch.manual_seed(0)
+    cfg = transformers.LlamaConfig(vocab_size=1024, hidden_size=512, intermediate_size=1376, num_hidden_layers=3,
+                                   num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=512)
+    hf = transformers.LlamaForCausalLM(cfg).eval()
+    oracle, served = _bf16_rounded(hf)
+    wrapped = tp.tensor_parallel(served, ["cuda:0"])
+    ids = torch.randint(0, 1024, (2, 40), generator=torch.Generator().manual_seed(1))
+    before = native.launch_count
+    got = wrapped.generate(ids.cuda(), max_new_tokens=10, do_sample=False)
+    assert native.launch_count - before > 50, "greedy generate() of a Hugging Face Llama did not reach the native engine"
+    ref = oracle.generate(ids, max_new_tokens=10, do_sample=False)
+    assert got.shape == ref.shape and _agreement(got, ref, 40) >= 0.9
+
+
+def test_engine_is_rebuilt_after_a_weight_update():
+    """The engine owns serving-layout copies; writing to the shard's parameters must invalidate them."""
+    ref, model = _models(4)
+    wrapped = tp.tensor_parallel(model, ["cuda:0"])
+    ids = torch.randint(0, 1024, (2, 20), generator=torch.Generator().manual_seed(3))
+    first = wrapped.prefill(ids, max_new_tokens=4)
+    engine = wrapped._engine
+    with torch.no_grad():
+        wrapped.module_shards[0].model.layers[0].mlp.gate_proj.weight.mul_(-1.0)
+    second = wrapped.prefill(ids, max_new_tokens=4)
+    assert wrapped._engine is not engine
+    assert (first - second).abs().max().item() > 1e-3

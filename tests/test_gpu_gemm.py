@@ -177,3 +177,92 @@ def test_transpose():
     nat = _native()
     x = torch.randn(300, 136, device="cuda", dtype=torch.bfloat16)
     assert torch.equal(nat.transpose(x), x.t().contiguous())
+
+
+@pytest.mark.parametrize("tokens,features,k", [(128, 256, 512), (300, 1000, 520), (2048, 4096, 1024), (8, 192, 136), (1000, 136, 72), (520, 1376, 264)])
+@pytest.mark.parametrize("x_t,w_t", [(False, True), (True, True), (True, False)])
+def test_gemm_operands_transposed_in_memory(tokens, features, k, x_t, w_t):
+    """MN-major tensor-core operands: x handed over as [k, tokens] and / or w as [k, features], read in place."""
+    nat = _native()
+    torch.manual_seed(5)
+    x = torch.randn(tokens, k, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(features, k, device="cuda", dtype=torch.bfloat16) * 0.05
+    bias = torch.randn(features, device="cuda", dtype=torch.bfloat16)
+    out = nat.gemm_nt(x.t().contiguous() if x_t else x, w.t().contiguous() if w_t else w, bias=bias, x_t=x_t, w_t=w_t)
+    torch.cuda.synchronize()
+    nat.device_state(x.device).check_status()
+    _check(out, _ref(x, w, bias), k)
+
+
+def test_linear_backward_reads_operands_in_place():
+    """dX and dW of the autograd linear against fp32 autograd; no transpose kernel is launched."""
+    nat = _native()
+    torch.manual_seed(6)
+    x = torch.randn(3, 100, 264, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(520, 264, device="cuda", dtype=torch.bfloat16) * 0.05).requires_grad_()
+    b = torch.randn(520, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    g = torch.randn(3, 100, 520, device="cuda", dtype=torch.bfloat16)
+    before = nat.launch_count
+    nat.linear(x, w, b).backward(g)
+    torch.cuda.synchronize()
+    assert nat.launch_count - before == 3  # forward, dgrad, wgrad
+    xr, wr, br = (t.detach().float().requires_grad_() for t in (x, w, b))
+    torch.nn.functional.linear(xr, wr, br).backward(g.float())
+    for got, want in ((x.grad, xr.grad), (w.grad, wr.grad), (b.grad, br.grad)):
+        err = (got.float() - want).abs().max().item()
+        assert err <= 0.02 * want.abs().max().item() + 0.05, err
+
+
+@pytest.mark.parametrize("mode", [1, 2])
+@pytest.mark.parametrize("tokens,features,k,act", [(8, 1536, 4096, None), (8, 2752, 4096, "swiglu16"), (3, 256, 512, "gelu"), (40, 1000, 1024, None)])
+def test_gemm_with_folded_norm(mode, tokens, features, k, act):
+    """RMSNorm / LayerNorm of the token rows folded into the GEMM: statistics in the epilogue warps, norm weight
+    multiplied into the GEMM weight beforehand.  Reference: fp32 norm followed by an fp32 matmul."""
+    nat = _native()
+    torch.manual_seed(7)
+    x = torch.randn(tokens, k, device="cuda", dtype=torch.bfloat16) * 2 + (0.5 if mode == 2 else 0.0)
+    w = torch.randn(features, k, device="cuda", dtype=torch.bfloat16) * 0.05
+    gamma = 1 + 0.1 * torch.randn(k, device="cuda")
+    beta = 0.1 * torch.randn(k, device="cuda") if mode == 2 else None
+    bias = torch.randn(features, device="cuda", dtype=torch.bfloat16)
+    xf = x.float()
+    if mode == 1:
+        normed = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5) * gamma
+    else:
+        normed = torch.nn.functional.layer_norm(xf, (k,), gamma, beta, 1e-5)
+    ref = normed @ w.float().t() + bias.float()
+    w_folded = (w.float() * gamma).to(torch.bfloat16)
+    rowsum = w_folded.float().sum(1) if mode == 2 else None
+    fused_bias = (bias.float() + (w.float() @ beta if beta is not None else 0)).to(torch.bfloat16)
+    if act == "swiglu16":
+        ref = torch.nn.functional.silu(ref[:, : features // 2]) * ref[:, features // 2 :]
+        half = features // 2
+        w_folded = nat.interleave_gate_up(w_folded[:half].contiguous(), w_folded[half:].contiguous())
+        fused_bias = torch.stack((fused_bias[:half].reshape(-1, 16), fused_bias[half:].reshape(-1, 16)), dim=1).reshape(-1).contiguous()
+        if rowsum is not None:
+            rowsum = w_folded.float().sum(1)
+    elif act == "gelu":
+        ref = torch.nn.functional.gelu(ref)
+    for _ in range(2):
+        out = nat.gemm_nt(x, w_folded, bias=fused_bias, act=act, norm=(mode, 1e-5, rowsum))
+    torch.cuda.synchronize()
+    nat.device_state(x.device).check_status()
+    err = (out.float() - ref).abs().max().item()
+    assert err <= 0.03 * ref.abs().max().item() + 0.05, err
+
+
+@pytest.mark.parametrize("tokens,features,k", [(8, 1536, 4096), (8, 2752, 4096), (8, 4000, 4096), (16, 768, 8192)])
+def test_gemm_splits_k_when_few_tiles_stream_much(tokens, features, k):
+    """Shard-sized decode GEMMs (few 128-row tiles, a long K) are split over K automatically."""
+    nat = _native()
+    torch.manual_seed(8)
+    plan = nat.gemm_plan(tokens, features, k)
+    assert plan.swapped and plan.k_splits > 1 and plan.grid <= 148
+    x = torch.randn(tokens, k, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(features, k, device="cuda", dtype=torch.bfloat16) * 0.05
+    res = torch.randn(tokens, features, device="cuda", dtype=torch.bfloat16)
+    for _ in range(3):
+        out = nat.gemm_nt(x, w, residual=res)
+    torch.cuda.synchronize()
+    nat.device_state(x.device).check_status()
+    _check(out, _ref(x, w, None, res), k)

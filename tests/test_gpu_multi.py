@@ -1,7 +1,9 @@
-"""Two-GPU tests of the device-side communication path (one process per GPU, NCCL only as the
-oracle): stand-alone collectives on the symmetric heap, the fused GEMM + all-reduce kernel, the
-distributed tensor-parallel wrapper (training parity incl. ZeRO-3) and the serving engine at TP=2.
-Child processes run with NVLS disabled; every device-side wait is time-bounded."""
+"""Multi-GPU tests of the device-side communication path (one process per GPU, NCCL only as the
+oracle) at 2, 4 and 8 ranks where the machine has them: stand-alone collectives on the symmetric heap
+(peer loads / stores and the NVLink-multicast variants), the fused GEMM + all-reduce kernel with both
+exchange protocols, the distributed tensor-parallel wrapper (training parity incl. ZeRO-3) and the serving
+engine.  NCCL's own NVLS is off in the children; every device-side wait is time-bounded (5 s here).  A rank
+whose body raises still meets the others at a barrier and unmaps its multicast view before any process exits."""
 import itertools
 import os
 import socket
@@ -24,236 +26,318 @@ def _free_port():
 
 def _setup(rank, world, port):
     sys.path.insert(0, REPO)
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0", TPB_DEVICE_WAIT_S="5")
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
 
 
-def _collectives_worker(rank, world, port, out_dir):
-    _setup(rank, world, port)
-    try:
-        from tensor_parallel_b200.ops import comm as C
+def _run(body_name, rank, world, port, out_dir):
+    """Child entry: runs one body; whatever happens, all ranks stop issuing traffic, meet, and tear their heaps down
+    (multicast view first) before any of them exits."""
+    import traceback
 
-        dev = torch.device("cuda", rank)
-        rc = C.make_process_comm(dev, staging_bytes=64 << 20)
-        torch.manual_seed(100 + rank)
-        for dtype in (torch.bfloat16, torch.float32):
-            for n, algo in ((4096, 0), (4096, 1), (1 << 20, -1), (1000 * 8, 1)):
-                x = torch.randn(n, device=dev, dtype=dtype)
-                want = x.float().clone()
-                dist.all_reduce(want)
-                for _ in range(3):  # repeated calls: epochs only grow
-                    got = rc.all_reduce(x, force_algo=algo).clone()
-                tol = dict(atol=3e-2, rtol=3e-2) if dtype == torch.bfloat16 else dict(atol=1e-5, rtol=1e-5)
-                torch.testing.assert_close(got.float(), want, **tol)
-            x = torch.randn(3, 1000, device=dev, dtype=dtype)
-            parts = [torch.empty_like(x) for _ in range(world)]
-            dist.all_gather(parts, x)
-            torch.testing.assert_close(rc.all_gather(x).clone(), torch.stack(parts))
-            y = torch.randn(world, 5, 1000, device=dev, dtype=dtype)
-            want = y.float().clone()
-            dist.all_reduce(want)
-            tol = dict(atol=3e-2, rtol=3e-2) if dtype == torch.bfloat16 else dict(atol=1e-5, rtol=1e-5)
-            torch.testing.assert_close(rc.reduce_scatter(y).clone().float(), want[rank], **tol)
-        # payloads larger than the staging buffers go through in pieces
-        full_in, full_out = rc.staging_in, rc.staging_out
-        rc.staging_in, rc.staging_out = full_in[: 256 << 10], full_out[: 256 << 10]
+    _setup(rank, world, port)
+    error = None
+    try:
+        globals()[body_name](rank, world, out_dir)
+        open(os.path.join(out_dir, f"ok{rank}"), "w").close()
+    except BaseException as exc:  # noqa: BLE001
+        error = exc
+        with open(os.path.join(out_dir, f"error{rank}.txt"), "w") as fh:
+            traceback.print_exc(file=fh)
+    finally:
         try:
-            x = torch.randn(300_001, device=dev, dtype=torch.bfloat16)
+            torch.cuda.synchronize()
+            dist.barrier()
+            from tensor_parallel_b200.ops import comm as C
+
+            C.close_all_heaps()
+            dist.barrier()
+        finally:
+            dist.destroy_process_group()
+    if error is not None:
+        raise error
+
+
+def _collectives_worker(rank, world, out_dir):
+    from tensor_parallel_b200.ops import comm as C
+
+    dev = torch.device("cuda", rank)
+    rc = C.make_process_comm(dev, staging_bytes=64 << 20)
+    with open(os.path.join(out_dir, f"heap{rank}.txt"), "w") as fh:
+        fh.write(f"vmm={int(rc.heap is not None)} nvls={int(bool(rc.mc_base))}\n")
+    if os.environ.get("TPB_EXPECT_NVLS"):
+        assert rc.mc_base, "the NVLink multicast view was not set up"
+    torch.manual_seed(100 + rank)
+    # algorithms: 0 one-shot, 1 two-shot over peer loads / stores, 4 two-shot through the NVSwitch (multimem), -1 by size
+    nvls_cases = ((4096, 4), (1 << 20, 4), (1000 * 8, 4), (3 << 20, -1)) if rc.mc_base else ()
+    for dtype in (torch.bfloat16, torch.float32):
+        for n, algo in ((4096, 0), (4096, 1), (1 << 20, -1), (1 << 20, 1), (1000 * 8, 1)) + nvls_cases:
+            x = torch.randn(n, device=dev, dtype=dtype)
             want = x.float().clone()
             dist.all_reduce(want)
-            torch.testing.assert_close(rc.all_reduce(x).float(), want, atol=3e-2, rtol=3e-2)
-            parts = [torch.empty_like(x) for _ in range(world)]
-            dist.all_gather(parts, x)
-            torch.testing.assert_close(rc.all_gather(x), torch.stack(parts))
-            y = torch.randn(world, 200_000, device=dev, dtype=torch.float32)
-            want = y.clone()
-            dist.all_reduce(want)
-            torch.testing.assert_close(rc.reduce_scatter(y), want[rank], atol=1e-5, rtol=1e-5)
-        finally:
-            rc.staging_in, rc.staging_out = full_in, full_out
-        torch.cuda.synchronize()
-        rc.check_status()
-
-        # fused GEMM + all-reduce (row-parallel linear): decode shapes with and without split-K, with bias / residual
-        from tensor_parallel_b200.ops import native
-
-        # both cross-rank protocols: flagged words (default for these shapes) and arrival counters
-        for flagged, (tokens, features, k) in itertools.product(
-                (True, False), ((8, 4096, 512), (8, 4096, 1376), (16, 1024, 2048), (1, 256, 64), (40, 1000, 512), (8, 1024, 16384))):
-            native.LIB.tpb_gemm_disable_flagged_exchange(0 if flagged else 1)
-            x = torch.randn(tokens, k, device=dev, dtype=torch.bfloat16)
-            w = torch.randn(features, k, device=dev, dtype=torch.bfloat16) * 0.05
-            bias = torch.randn(features, device=dev, dtype=torch.bfloat16)
-            dist.broadcast(bias, 0)
-            res = torch.randn(tokens, features, device=dev, dtype=torch.bfloat16)
-            dist.broadcast(res, 0)
-            want = x.float() @ w.float().t()
-            dist.all_reduce(want)
-            want = want + bias.float() + res.float()
-            for _ in range(4):  # alternates the two workspace halves
-                got = rc.gemm_allreduce(x, w, bias=bias, residual=res, bias_scale=1.0)
-            torch.cuda.synchronize()
-            rc.check_status()
-            err = (got.float() - want).abs().max().item()
-            assert err <= 0.02 * want.abs().max().item() + 0.05, (flagged, tokens, features, k, err)
-        native.LIB.tpb_gemm_disable_flagged_exchange(0)
-        # shapes interleaved on the same workspace: words left behind by one shape must never satisfy another one
-        mixed = [(64, 1024, 256), (8, 4096, 512), (64, 1024, 256), (64, 1024, 256), (8, 4096, 512), (5, 2048, 512), (8, 4096, 512)]
-        for step, (tokens, features, k) in enumerate(mixed * 2):
-            x = torch.randn(tokens, k, device=dev, dtype=torch.bfloat16)
-            w = torch.randn(features, k, device=dev, dtype=torch.bfloat16) * 0.05
-            want = x.float() @ w.float().t()
-            dist.all_reduce(want)
-            got = rc.gemm_allreduce(x, w)
-            err = (got.float() - want).abs().max().item()
-            assert err <= 0.02 * want.abs().max().item() + 0.05, ("mixed", step, tokens, features, k, err)
-        torch.cuda.synchronize()
-        rc.check_status()
-        # fused all-gather + GEMM (column-parallel linear fed by a hidden-split activation)
-        for tokens, cols, features in ((8, 256, 1536), (300, 128, 1000), (2048, 512, 4096)):
-            xl = torch.randn(tokens, cols, device=dev, dtype=torch.bfloat16)
-            w = torch.randn(features, cols * world, device=dev, dtype=torch.bfloat16) * 0.05
-            parts = [torch.empty_like(xl) for _ in range(world)]
-            dist.all_gather(parts, xl)
-            want = torch.cat(parts, dim=1).float() @ w.float().t()
-            for _ in range(3):
-                got = rc.allgather_gemm(xl, w)
-            torch.cuda.synchronize()
-            rc.check_status()
-            err = (got.float() - want).abs().max().item()
-            assert err <= 0.02 * want.abs().max().item() + 0.05, (tokens, cols, features, err)
-        dist.barrier()
-        rc.check_guards()  # nobody (this rank or a peer) wrote outside the areas of the symmetric heap
-        open(os.path.join(out_dir, f"ok{rank}"), "w").close()
-    finally:
-        dist.destroy_process_group()
-
-
-def _model_worker(rank, world, port, out_dir):
-    _setup(rank, world, port)
+            for _ in range(3):  # repeated calls: epochs only grow
+                got = rc.all_reduce(x, force_algo=algo).clone()
+            tol = dict(atol=3e-2, rtol=3e-2) if dtype == torch.bfloat16 else dict(atol=1e-5, rtol=1e-5)
+            torch.testing.assert_close(got.float(), want, **tol)
+        x = torch.randn(3, 1000, device=dev, dtype=dtype)
+        parts = [torch.empty_like(x) for _ in range(world)]
+        dist.all_gather(parts, x)
+        torch.testing.assert_close(rc.all_gather(x).clone(), torch.stack(parts))
+        y = torch.randn(world, 5, 1000, device=dev, dtype=dtype)
+        want = y.float().clone()
+        dist.all_reduce(want)
+        tol = dict(atol=3e-2, rtol=3e-2) if dtype == torch.bfloat16 else dict(atol=1e-5, rtol=1e-5)
+        torch.testing.assert_close(rc.reduce_scatter(y).clone().float(), want[rank], **tol)
+    # payloads larger than the staging buffers go through in pieces
+    full_in, full_out = rc.staging_in, rc.staging_out
+    rc.staging_in, rc.staging_out = full_in[: 256 << 10], full_out[: 256 << 10]
     try:
-        import tensor_parallel_b200 as tp
-        from tensor_parallel_b200.models.llama import LlamaConfig, LlamaForCausalLM
-
-        dev = torch.device("cuda", rank)
-        torch.manual_seed(0)
-        cfg = LlamaConfig(vocab_size=512, hidden_size=256, intermediate_size=688, num_hidden_layers=2, num_attention_heads=4,
-                          num_key_value_heads=2)
-        # fp32 training parity (stock torch compute, device-side collectives with autograd)
-        model = LlamaForCausalLM(cfg).to(dev)
-        ids = torch.randint(0, 512, (2, 24), device=dev)
-        dist.broadcast(ids, 0)
-        ref = model(input_ids=ids, labels=ids)
-        ref.loss.backward()
-        ref_grads = {n: p.grad.clone() for n, p in model.named_parameters()}
-        model.zero_grad()
-        wrapped = tp.tensor_parallel(model, [dev], sharded=True)
-        assert wrapped._device_backend is not None, "device collectives were not selected"
-        out = wrapped(input_ids=ids, labels=ids)
-        torch.testing.assert_close(out.logits, ref.logits, atol=2e-3, rtol=1e-3)
-        out.loss.backward()
-        gate = wrapped.module_shards[0].model.layers[0].mlp.tp_wrapped_module.gate_proj.weight.grad
-        want = torch.tensor_split(ref_grads["model.layers.0.mlp.gate_proj.weight"], world, dim=0)[rank]
-        torch.testing.assert_close(gate, want, atol=2e-3, rtol=1e-2)
-        mgr = wrapped.sharding_manager
-        flats = [torch.zeros_like(mgr.flat_shards[0].grad) for _ in range(world)]
-        dist.all_gather(flats, mgr.flat_shards[0].grad)
-        for name, grad in zip(mgr.sharded_param_names, mgr._combine(torch.stack(flats))):
-            torch.testing.assert_close(grad, ref_grads[name.replace("tp_wrapped_module.", "")], atol=2e-3, rtol=1e-2, msg=name)
-
-        # bf16 serving engine at TP=2 vs the single-GPU engine on the same weights
-        torch.manual_seed(1)
-        full = LlamaForCausalLM(cfg).to(device=dev, dtype=torch.bfloat16).eval()
-        for p in full.parameters():
-            dist.broadcast(p.data, 0)
-        prompt = torch.randint(0, 512, (3, 40), device=dev)
-        dist.broadcast(prompt, 0)
-        single = tp.TensorParallel(full, [dev])  # one device: the module itself
-        want_logits = single.prefill(prompt.cpu(), max_new_tokens=8)
-        want_tokens = single.generate(prompt.cpu(), max_new_tokens=8)
-        import copy
-
-        tp2 = tp.tensor_parallel(copy.deepcopy(full), [dev])
-        got_logits = tp2.prefill(prompt.cpu(), max_new_tokens=8)
-        torch.testing.assert_close(got_logits, want_logits, atol=0.1, rtol=0.05)
-        got_tokens = tp2.generate(prompt.cpu(), max_new_tokens=8)
-        assert tp2._engine.world == world and tp2._engine.graph is not None
-        agree = (got_tokens == want_tokens).float().mean().item()
-        assert agree > 0.9, agree  # bf16 summation order differs between 1 and 2 ranks; near-ties may flip
-        torch.cuda.synchronize()
-        tp2._engine.comm.check_status()
-        dist.barrier()
-        tp2._engine.comm.check_guards()
-        open(os.path.join(out_dir, f"ok{rank}"), "w").close()
+        x = torch.randn(300_001, device=dev, dtype=torch.bfloat16)
+        want = x.float().clone()
+        dist.all_reduce(want)
+        torch.testing.assert_close(rc.all_reduce(x).float(), want, atol=3e-2, rtol=3e-2)
+        parts = [torch.empty_like(x) for _ in range(world)]
+        dist.all_gather(parts, x)
+        torch.testing.assert_close(rc.all_gather(x), torch.stack(parts))
+        y = torch.randn(world, 200_000, device=dev, dtype=torch.float32)
+        want = y.clone()
+        dist.all_reduce(want)
+        torch.testing.assert_close(rc.reduce_scatter(y), want[rank], atol=1e-5, rtol=1e-5)
     finally:
-        dist.destroy_process_group()
+        rc.staging_in, rc.staging_out = full_in, full_out
+    torch.cuda.synchronize()
+    rc.check_status()
+
+    # fused GEMM + all-reduce (row-parallel linear): decode shapes with and without split-K, with bias / residual
+    from tensor_parallel_b200.ops import native
+
+    # both cross-rank protocols: flagged words (default for these shapes) and arrival counters
+    for flagged, (tokens, features, k) in itertools.product(
+            (True, False), ((8, 4096, 512), (8, 4096, 1376), (16, 1024, 2048), (1, 256, 64), (40, 1000, 512), (8, 1024, 16384))):
+        native.LIB.tpb_gemm_disable_flagged_exchange(0 if flagged else 1)
+        x = torch.randn(tokens, k, device=dev, dtype=torch.bfloat16)
+        w = torch.randn(features, k, device=dev, dtype=torch.bfloat16) * 0.05
+        bias = torch.randn(features, device=dev, dtype=torch.bfloat16)
+        dist.broadcast(bias, 0)
+        res = torch.randn(tokens, features, device=dev, dtype=torch.bfloat16)
+        dist.broadcast(res, 0)
+        want = x.float() @ w.float().t()
+        dist.all_reduce(want)
+        want = want + bias.float() + res.float()
+        for _ in range(4):  # alternates the two workspace halves
+            got = rc.gemm_allreduce(x, w, bias=bias, residual=res, bias_scale=1.0)
+        torch.cuda.synchronize()
+        rc.check_status()
+        err = (got.float() - want).abs().max().item()
+        assert err <= 0.02 * want.abs().max().item() + 0.05, (flagged, tokens, features, k, err)
+    native.LIB.tpb_gemm_disable_flagged_exchange(0)
+    # shapes interleaved on the same workspace: words left behind by one shape must never satisfy another one
+    mixed = [(64, 1024, 256), (8, 4096, 512), (64, 1024, 256), (64, 1024, 256), (8, 4096, 512), (5, 2048, 512), (8, 4096, 512)]
+    for step, (tokens, features, k) in enumerate(mixed * 2):
+        x = torch.randn(tokens, k, device=dev, dtype=torch.bfloat16)
+        w = torch.randn(features, k, device=dev, dtype=torch.bfloat16) * 0.05
+        want = x.float() @ w.float().t()
+        dist.all_reduce(want)
+        got = rc.gemm_allreduce(x, w)
+        err = (got.float() - want).abs().max().item()
+        assert err <= 0.02 * want.abs().max().item() + 0.05, ("mixed", step, tokens, features, k, err)
+    torch.cuda.synchronize()
+    rc.check_status()
+    # fused all-gather + GEMM (column-parallel linear fed by a hidden-split activation)
+    for tokens, cols, features in ((8, 256, 1536), (300, 128, 1000), (2048, 512, 4096)):
+        xl = torch.randn(tokens, cols, device=dev, dtype=torch.bfloat16)
+        w = torch.randn(features, cols * world, device=dev, dtype=torch.bfloat16) * 0.05
+        parts = [torch.empty_like(xl) for _ in range(world)]
+        dist.all_gather(parts, xl)
+        want = torch.cat(parts, dim=1).float() @ w.float().t()
+        for _ in range(3):
+            got = rc.allgather_gemm(xl, w)
+        torch.cuda.synchronize()
+        rc.check_status()
+        err = (got.float() - want).abs().max().item()
+        assert err <= 0.02 * want.abs().max().item() + 0.05, (tokens, cols, features, err)
+    dist.barrier()
+    rc.check_guards()  # nobody (this rank or a peer) wrote outside the areas of the symmetric heap
 
 
-def _fused_training_worker(rank, world, port, out_dir):
+def _model_worker(rank, world, out_dir):
+    import tensor_parallel_b200 as tp
+    from tensor_parallel_b200.models.llama import LlamaConfig, LlamaForCausalLM
+
+    dev = torch.device("cuda", rank)
+    torch.manual_seed(0)
+    heads, kv_heads = max(4, world), max(2, world)
+    cfg = LlamaConfig(vocab_size=512, hidden_size=64 * heads, intermediate_size=688, num_hidden_layers=2, num_attention_heads=heads,
+                      num_key_value_heads=kv_heads)
+    # fp32 training parity (stock torch compute, device-side collectives with autograd)
+    model = LlamaForCausalLM(cfg).to(dev)
+    ids = torch.randint(0, 512, (2, 24), device=dev)
+    dist.broadcast(ids, 0)
+    ref = model(input_ids=ids, labels=ids)
+    ref.loss.backward()
+    ref_grads = {n: p.grad.clone() for n, p in model.named_parameters()}
+    model.zero_grad()
+    wrapped = tp.tensor_parallel(model, [dev], sharded=True)
+    assert wrapped._device_backend is not None, "device collectives were not selected"
+    out = wrapped(input_ids=ids, labels=ids)
+    torch.testing.assert_close(out.logits, ref.logits, atol=2e-3, rtol=1e-3)
+    out.loss.backward()
+    gate = wrapped.module_shards[0].model.layers[0].mlp.tp_wrapped_module.gate_proj.weight.grad
+    want = torch.tensor_split(ref_grads["model.layers.0.mlp.gate_proj.weight"], world, dim=0)[rank]
+    torch.testing.assert_close(gate, want, atol=2e-3, rtol=1e-2)
+    mgr = wrapped.sharding_manager
+    flats = [torch.zeros_like(mgr.flat_shards[0].grad) for _ in range(world)]
+    dist.all_gather(flats, mgr.flat_shards[0].grad)
+    for name, grad in zip(mgr.sharded_param_names, mgr._combine(torch.stack(flats))):
+        torch.testing.assert_close(grad, ref_grads[name.replace("tp_wrapped_module.", "")], atol=2e-3, rtol=1e-2, msg=name)
+
+    # bf16 serving engine at TP=2 vs the single-GPU engine on the same weights
+    torch.manual_seed(1)
+    full = LlamaForCausalLM(cfg).to(device=dev, dtype=torch.bfloat16).eval()
+    for p in full.parameters():
+        dist.broadcast(p.data, 0)
+    prompt = torch.randint(0, 512, (3, 40), device=dev)
+    dist.broadcast(prompt, 0)
+    single = tp.TensorParallel(full, [dev])  # one device: the module itself
+    want_logits = single.prefill(prompt.cpu(), max_new_tokens=8)
+    want_tokens = single.generate(prompt.cpu(), max_new_tokens=8)
+    import copy
+
+    tp2 = tp.tensor_parallel(copy.deepcopy(full), [dev])
+    got_logits = tp2.prefill(prompt.cpu(), max_new_tokens=8)
+    torch.testing.assert_close(got_logits, want_logits, atol=0.1, rtol=0.05)
+    got_tokens = tp2.generate(prompt.cpu(), max_new_tokens=8)
+    assert tp2._engine.world == world and tp2._engine.graph is not None
+    agree = (got_tokens == want_tokens).float().mean().item()
+    assert agree > 0.9, agree  # bf16 summation order differs between 1 and 2 ranks; near-ties may flip
+    torch.cuda.synchronize()
+    tp2._engine.comm.check_status()
+    dist.barrier()
+    tp2._engine.comm.check_guards()
+
+
+def _fused_training_worker(rank, world, out_dir):
     """bf16 shards: the planner swaps row-parallel linears for GEMM + all-reduce and the head for the
     vocab-parallel cross-entropy; loss and gradients must track the fp32 unsplit model."""
-    _setup(rank, world, port)
-    try:
-        import tensor_parallel_b200 as tp
-        from tensor_parallel_b200.models.llama import LlamaConfig, LlamaForCausalLM
-        from tensor_parallel_b200.ops import native
+    import tensor_parallel_b200 as tp
+    from tensor_parallel_b200.models.llama import LlamaConfig, LlamaForCausalLM
+    from tensor_parallel_b200.ops import native
 
-        dev = torch.device("cuda", rank)
-        torch.manual_seed(0)
-        cfg = LlamaConfig(vocab_size=1024, hidden_size=256, intermediate_size=688, num_hidden_layers=2, num_attention_heads=4,
-                          fused_lm_loss=True)
-        ref = LlamaForCausalLM(cfg)
-        for p in ref.parameters():
-            p.data = p.data.to(torch.bfloat16).float()  # bf16-representable weights, fp32 maths
-        model = LlamaForCausalLM(cfg)
-        model.load_state_dict(ref.state_dict())
-        model = model.to(device=dev, dtype=torch.bfloat16)
-        ids = torch.randint(0, 1024, (4, 80), generator=torch.Generator().manual_seed(3))
-        cfg.fused_lm_loss = False
-        want = ref(input_ids=ids, labels=ids)
-        want.loss.backward()
-        cfg.fused_lm_loss = True
-        wrapped = tp.tensor_parallel(model, [dev], sharded=True)
-        o_proj = wrapped.module_shards[0].model.layers[0].self_attn.tp_wrapped_module.o_proj
-        assert getattr(o_proj, "_tp_fused_row_parallel", False), "planner did not fuse the row-parallel linear"
-        before = native.launch_count
-        out = wrapped(input_ids=ids.to(dev), labels=ids.to(dev))
-        assert out.logits is None  # fused head + loss: logits are never materialised
-        out.loss.backward()
+    dev = torch.device("cuda", rank)
+    torch.manual_seed(0)
+    heads = max(4, world)
+    cfg = LlamaConfig(vocab_size=1024, hidden_size=64 * heads, intermediate_size=688, num_hidden_layers=2, num_attention_heads=heads,
+                      fused_lm_loss=True)
+    ref = LlamaForCausalLM(cfg)
+    for p in ref.parameters():
+        p.data = p.data.to(torch.bfloat16).float()  # bf16-representable weights, fp32 maths
+    model = LlamaForCausalLM(cfg)
+    model.load_state_dict(ref.state_dict())
+    model = model.to(device=dev, dtype=torch.bfloat16)
+    ids = torch.randint(0, 1024, (4, 80), generator=torch.Generator().manual_seed(3))
+    cfg.fused_lm_loss = False
+    want = ref(input_ids=ids, labels=ids)
+    want.loss.backward()
+    cfg.fused_lm_loss = True
+    wrapped = tp.tensor_parallel(model, [dev], sharded=True)
+    o_proj = wrapped.module_shards[0].model.layers[0].self_attn.tp_wrapped_module.o_proj
+    assert getattr(o_proj, "_tp_fused_row_parallel", False), "planner did not fuse the row-parallel linear"
+    before = native.launch_count
+    out = wrapped(input_ids=ids.to(dev), labels=ids.to(dev))
+    assert out.logits is None  # fused head + loss: logits are never materialised
+    out.loss.backward()
+    torch.cuda.synchronize()
+    wrapped._device_backend.comm.check_status()
+    assert native.launch_count - before > 40
+    torch.testing.assert_close(out.loss.float().cpu(), want.loss, atol=3e-2, rtol=2e-2)
+    ref_grads = {n: p.grad for n, p in ref.named_parameters()}
+    cfgr = wrapped.tensor_parallel_config
+    checked = 0
+    for shard_name, p in wrapped.module_shards[0].named_parameters():
+        original = shard_name.replace("tp_wrapped_module.", "")
+        for pattern, action in cfgr.state_rules.items():
+            if pattern.search(original):
+                expected = action(ref_grads[original], rank)
+                got = p.grad.float().cpu()
+                rel = (got - expected).norm().item() / (expected.norm().item() + 1e-9)
+                with open(os.path.join(out_dir, f"grad_errors_{rank}.txt"), "a") as fh:
+                    fh.write(f"{rel:.4f} {shard_name}\n")
+                assert (got - expected).norm().item() <= 0.1 * expected.norm().item() + 2e-5 * expected.numel() ** 0.5, (shard_name, rank, rel)
+                checked += 1
+                break
+    assert checked >= 10
+    opt = tp.optim.AdamW(wrapped.parameters(), lr=1e-3)
+    opt.step()
+    out2 = wrapped(input_ids=ids.to(dev), labels=ids.to(dev))
+    assert out2.loss.item() < out.loss.item()
+
+
+def _status_worker(rank, world, out_dir):
+    """No kernel is made to time out here: the status word a timed-out wait would set is written from the host, and the
+    runtime has to turn it into ``TPCollectiveError`` at its next calls instead of handing stale data on.  Also: a
+    ``"sum"`` of a dtype the kernels do not add (fp16, int64) takes the process-group path and keeps its dtype."""
+    import tensor_parallel_b200 as tp
+    from tensor_parallel_b200.models.llama import LlamaConfig, LlamaForCausalLM
+    from tensor_parallel_b200.ops import comm as C
+    from tensor_parallel_b200.parallel.collectives import TPCollectiveError
+
+    dev = torch.device("cuda", rank)
+    torch.manual_seed(0)
+    heads = max(4, world)
+    cfg = LlamaConfig(vocab_size=512, hidden_size=64 * heads, intermediate_size=688, num_hidden_layers=2, num_attention_heads=heads)
+    model = LlamaForCausalLM(cfg).to(device=dev, dtype=torch.bfloat16).eval()
+    wrapped = tp.tensor_parallel(model, [dev])
+    comm = wrapped._device_backend.comm
+    ids = torch.randint(0, 512, (2, 16), device=dev)
+    dist.broadcast(ids, 0)
+    with torch.no_grad():
+        wrapped(input_ids=ids)
         torch.cuda.synchronize()
-        wrapped._device_backend.comm.check_status()
-        assert native.launch_count - before > 40
-        torch.testing.assert_close(out.loss.float().cpu(), want.loss, atol=3e-2, rtol=2e-2)
-        ref_grads = {n: p.grad for n, p in ref.named_parameters()}
-        cfgr = wrapped.tensor_parallel_config
-        checked = 0
-        for shard_name, p in wrapped.module_shards[0].named_parameters():
-            original = shard_name.replace("tp_wrapped_module.", "")
-            for pattern, action in cfgr.state_rules.items():
-                if pattern.search(original):
-                    expected = action(ref_grads[original], rank)
-                    got = p.grad.float().cpu()
-                    rel = (got - expected).norm().item() / (expected.norm().item() + 1e-9)
-                    with open(os.path.join(out_dir, f"grad_errors_{rank}.txt"), "a") as fh:
-                        fh.write(f"{rel:.4f} {shard_name}\n")
-                    assert (got - expected).norm().item() <= 0.1 * expected.norm().item() + 2e-5 * expected.numel() ** 0.5, (shard_name, rank, rel)
-                    checked += 1
-                    break
-        assert checked >= 10
-        opt = tp.optim.AdamW(wrapped.parameters(), lr=1e-3)
-        opt.step()
-        out2 = wrapped(input_ids=ids.to(dev), labels=ids.to(dev))
-        assert out2.loss.item() < out.loss.item()
-        open(os.path.join(out_dir, f"ok{rank}"), "w").close()
+        dist.barrier()
+        comm.status[0] = 2  # what a wait for a peer that ran out of time leaves behind
+        torch.cuda.synchronize()
+        raised = False
+        try:
+            for _ in range(3):  # the poll is asynchronous: the second or third call at the latest sees it
+                wrapped(input_ids=ids)
+                torch.cuda.synchronize()
+        except TPCollectiveError:
+            raised = True
+        assert raised, "forward() ignored a timed-out device wait"
+        assert int(comm.status[0].item()) == 0  # cleared by the raise
+        dist.barrier()
+        # all ranks raised at the same call (same status, same schedule), so the collectives still pair up
+        comm.status[0] = 2
+        torch.cuda.synchronize()
+        raised = False
+        try:
+            wrapped.generate(ids.cpu(), max_new_tokens=4)
+        except TPCollectiveError:
+            raised = True
+        assert raised, "generate() ignored a timed-out device wait"
+    dist.barrier()
+    reduce_op = C.ProcessBackend(comm).all_reduce_op(None)
+    half = torch.full((5, 3), float(rank + 1), device=dev, dtype=torch.float16)
+    out = reduce_op(half, rank)
+    assert out.dtype == torch.float16 and torch.equal(out.float(), torch.full((5, 3), world * (world + 1) / 2.0, device=dev))
+    counts = torch.full((4,), rank + 1, device=dev, dtype=torch.int64)
+    out = reduce_op(counts, rank)
+    assert out.dtype == torch.int64 and int(out[0]) == world * (world + 1) // 2
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("worker", ["_collectives_worker", "_model_worker", "_fused_training_worker", "_status_worker"])
+def test_ranks_as_processes(worker, world, tmp_path):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    try:
+        mp.spawn(_run, args=(worker, world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     finally:
-        dist.destroy_process_group()
-
-
-@pytest.mark.parametrize("worker", [_collectives_worker, _model_worker, _fused_training_worker])
-def test_two_gpus(worker, tmp_path):
-    mp.spawn(worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
-    assert sorted(f for f in os.listdir(tmp_path) if f.startswith("ok")) == ["ok0", "ok1"]
+        for name in sorted(os.listdir(tmp_path)):
+            if name.startswith("error"):
+                print(name, open(os.path.join(tmp_path, name)).read())
+    assert sorted(f for f in os.listdir(tmp_path) if f.startswith("ok")) == [f"ok{r}" for r in range(world)]
 
 
 def test_threaded_mode_on_two_gpus():

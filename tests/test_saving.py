@@ -178,3 +178,31 @@ def test_convert_state_dict_emits_flat_shards(name, world):
     ids = torch.randint(0, 90, (2, 6))
     with torch.no_grad():
         torch.testing.assert_close(other(input_ids=ids).logits, model(input_ids=ids).logits, atol=3e-5, rtol=1e-5)
+
+
+def test_flat_shard_layout_is_saved_and_checked():
+    """The sharded layout's state dict carries the ZeRO-3 layout (names, shapes, piece sizes); a model whose flat shards
+    are cut differently refuses it, and a checkpoint without the metadata (reference-written) still loads."""
+    import torch
+    from torch import nn
+
+    import tensor_parallel_b200 as tp
+
+    def make():
+        torch.manual_seed(0)
+        return nn.Sequential(nn.Linear(16, 32), nn.LayerNorm(32), nn.Linear(32, 8), nn.LayerNorm(8))
+
+    model = tp.TensorParallel(make(), ["cpu", "cpu"], sharded=True)
+    state = model.state_dict()
+    layout = state["sharding_manager._extra_state"]
+    assert layout["names"] == list(model.sharding_manager.sharded_param_names) and len(layout["sizes_with_pad"]) == 2
+    same = tp.TensorParallel(make(), ["cpu", "cpu"], sharded=True)
+    same.load_state_dict(state)
+    names = list(model.sharding_manager.sharded_param_names)
+    other = tp.TensorParallel(make(), ["cpu", "cpu"], sharded=True, sharded_param_names=names[::-1])
+    import pytest
+
+    with pytest.raises(RuntimeError, match="different layout"):
+        other.load_state_dict(state)
+    legacy = {k: v for k, v in state.items() if not k.endswith("_extra_state")}
+    same.load_state_dict(legacy)
