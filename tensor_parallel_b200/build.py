@@ -42,15 +42,20 @@ def _newest_header_mtime() -> float:
     return max((h.stat().st_mtime for h in headers), default=0.0)
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
+def build(force: bool = False, verbose: bool = False, lib_path: Path = None, extra_flags=()) -> Path:
+    """Builds what is out of date.  ``lib_path`` / ``extra_flags`` make a variant of the library somewhere else (its
+    objects live beside it), e.g. ``-DTPB_GEMM_TRACE`` for the kernel-internal phase trace or ``-DTPB_BOUNDS`` for the
+    in-kernel bounds checks; ``TPB_LIB_PATH`` makes ``ops.native`` load such a variant."""
     nvcc = _nvcc()
-    OBJ_DIR.mkdir(parents=True, exist_ok=True)
-    LIB_DIR.mkdir(parents=True, exist_ok=True)
+    lib_path = Path(lib_path) if lib_path is not None else LIB_PATH
+    obj_dir = OBJ_DIR if lib_path == LIB_PATH else lib_path.parent / (lib_path.stem + "_obj")
+    obj_dir.mkdir(parents=True, exist_ok=True)
+    lib_path.parent.mkdir(parents=True, exist_ok=True)
     header_time = _newest_header_mtime()
-    flags = list(NVCC_FLAGS) + os.environ.get("TPB_NVCC_FLAGS", "").split()  # e.g. -DTPB_GEMM_TRACE, -DTPB_BOUNDS
+    flags = list(NVCC_FLAGS) + list(extra_flags) + os.environ.get("TPB_NVCC_FLAGS", "").split()
     jobs = []
     for src in sources():
-        obj = OBJ_DIR / (src.stem + ".o")
+        obj = obj_dir / (src.stem + ".o")
         stale = force or not obj.exists() or obj.stat().st_mtime < max(src.stat().st_mtime, header_time)
         if stale:
             jobs.append([nvcc, *flags, *( ["-Xptxas", "-v"] if verbose else []), "-c", str(src), "-o", str(obj)])
@@ -66,11 +71,11 @@ def build(force: bool = False, verbose: bool = False) -> Path:
             for log in pool.map(run, jobs):
                 if verbose and log:
                     print(log, file=sys.stderr)
-    objs = [str(OBJ_DIR / (src.stem + ".o")) for src in sources()]
+    objs = [str(obj_dir / (src.stem + ".o")) for src in sources()]
     newest_obj = max(os.path.getmtime(o) for o in objs)
-    if force or jobs or not LIB_PATH.exists() or LIB_PATH.stat().st_mtime < newest_obj:
-        run([nvcc, "-shared", "-o", str(LIB_PATH), *objs, "-gencode", "arch=compute_100a,code=sm_100a"])
-    return LIB_PATH
+    if force or jobs or not lib_path.exists() or lib_path.stat().st_mtime < newest_obj:
+        run([nvcc, "-shared", "-o", str(lib_path), *objs, "-gencode", "arch=compute_100a,code=sm_100a"])
+    return lib_path
 
 
 if __name__ == "__main__":

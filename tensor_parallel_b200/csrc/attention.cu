@@ -381,7 +381,6 @@ attn_decode_fused_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k,
                          int splits, float scale_log2e, int rotary_dim, float log2_theta, int interleaved, long long q_ld,
                          long long k_ld, long long v_ld, const float2* __restrict__ rope_table, long long out_ld) {
   constexpr int EPL = D / 8;
-  pdl_trigger();
   pdl_wait();
   const int bh = blockIdx.x;
   const int b = bh / kv_heads, kvh = bh % kv_heads;

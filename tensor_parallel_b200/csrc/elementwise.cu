@@ -91,7 +91,6 @@ __global__ void __launch_bounds__(NORM_THREADS)
 norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ residual, const T* __restrict__ weight,
                 const T* __restrict__ bias, T* __restrict__ out, T* __restrict__ sum_out, float* __restrict__ rstd_out,
                 float* __restrict__ mean_out, int cols, float eps) {
-  pdl_trigger();
   pdl_wait();
   const size_t row = blockIdx.x;
   const T* xr = x + row * cols;
@@ -390,7 +389,6 @@ __global__ void act_bwd_kernel(const T* __restrict__ dout, const T* __restrict__
 template <typename T>
 __global__ void embedding_kernel(const int64_t* __restrict__ ids, const T* __restrict__ table, T* __restrict__ out,
                                  int tokens, int cols, long long table_ld, long long out_ld) {
-  pdl_trigger();
   pdl_wait();
   const int vec_per_row = cols >> 3;
   const long long total = (long long)tokens * vec_per_row;

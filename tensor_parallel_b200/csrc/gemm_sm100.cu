@@ -285,12 +285,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
   }
-  pdl_trigger();  // the next kernel in the stream may start its own prologue now
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   pdl_wait();     // everything below reads what earlier kernels wrote
+  pdl_trigger();  // the next kernel in the stream may be scheduled and run its own prologue (see launch.cuh)
   if (threadIdx.x == 0) TPB_TRACE(1);
 
   const int tiles = p.m_tiles * p.n_tiles;
@@ -385,6 +385,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       uint32_t it = 0;
       uint32_t local = 0;
       const uint32_t idesc = make_idesc_bf16(BM, BN, p.a_mn != 0, p.b_mn != 0);
+      const bool any_mn = (p.a_mn | p.b_mn) != 0;
       WorkIter work(p);
       WorkItem item;
       for (; !*abort_flag && work.next(p, item); ++local) {
@@ -416,16 +417,26 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             if (kb + 1 < kb1) { mbar_arrive(&empty_bar[s]); continue; }
           }
 #endif
+          if (!any_mn) {  // (the issue loop of the few-token shapes is latency-critical: no per-instruction branches)
 #pragma unroll
-          for (int j = 0; j < KBOX; ++j) {
+            for (int j = 0; j < KBOX; ++j) {
+#pragma unroll
+              for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                // K-major: a k-step of 16 elements is 32 bytes further along the swizzled 128-byte rows
+                const uint64_t adesc = make_desc_kmajor_sw128(a_addr + j * A_BYTES + kk * UMMA_K * 2);
+                const uint64_t bdesc = make_desc_kmajor_sw128(b_addr + j * B_BYTES + kk * UMMA_K * 2);
+                umma_bf16(d_tmem + (issued % NACC) * BN, adesc, bdesc, idesc, issued >= NACC ? 1u : 0u);
+                ++issued;
+              }
+            }
+          } else {
 #pragma unroll
             for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-              // K-major: a k-step of 16 elements is 32 bytes further along the swizzled 128-byte rows;
-              // MN-major: it is 16 k-rows (two 8-row swizzle atoms) further down the block
+              // MN-major (KBOX == 1): a k-step is 16 k-rows (two 8-row swizzle atoms) further down the block
               const uint64_t adesc = p.a_mn ? make_desc_mnmajor_sw128(a_addr + kk * UMMA_K * 128, MN_BLOCK_BYTES)
-                                            : make_desc_kmajor_sw128(a_addr + j * A_BYTES + kk * UMMA_K * 2);
+                                            : make_desc_kmajor_sw128(a_addr + kk * UMMA_K * 2);
               const uint64_t bdesc = p.b_mn ? make_desc_mnmajor_sw128(b_addr + kk * UMMA_K * 128, MN_BLOCK_BYTES)
-                                            : make_desc_kmajor_sw128(b_addr + j * B_BYTES + kk * UMMA_K * 2);
+                                            : make_desc_kmajor_sw128(b_addr + kk * UMMA_K * 2);
               umma_bf16(d_tmem + (issued % NACC) * BN, adesc, bdesc, idesc, issued >= NACC ? 1u : 0u);
               ++issued;
             }
@@ -492,6 +503,24 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       const int nt = tile / p.m_tiles;
       const int acc = local & 1;
       const uint32_t acc_ph = (local >> 1) & 1;
+      const int m = mt * BM + row;
+      const bool m_ok = m < p.m_extent;
+      // Few-token tiles: fetch this row's residual values and bias NOW, while the weights are still streaming - loaded
+      // after the accumulators are ready they would add a full memory round trip to the critical path of the kernel.
+      float res_pre[16];
+      float bias_pre = 0.f;
+      bool prefetched = false;
+      if constexpr (BN == 16) {
+        if (p.swapped && hot_act != 5 && nt == 0) {
+          prefetched = true;
+          if (m_ok) {
+            if (hot_bias) bias_pre = hot_bias_scale * __bfloat162float(hot_bias[m]);
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              res_pre[j] = (hot_residual && j < hot_n_extent) ? __bfloat162float(hot_residual[size_t(j) * hot_ld_out + m]) : 0.f;
+          }
+        }
+      }
       // one thread waits, the group agrees on the outcome (so that nobody is left at a named barrier)
       if (threadIdx.x == 64) {
         bool ok = !*abort_flag && mbar_wait(&acc_full[acc], acc_ph);
@@ -510,8 +539,6 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       if (!*epi_ok) break;
       tc_fence_after();
       if (threadIdx.x == 64) TPB_TRACE(2);
-      const int m = mt * BM + row;
-      const bool m_ok = m < p.m_extent;
       const uint32_t t_lane = tmem_base + (uint32_t(quarter * 32) << 16) + acc * ACC_COLS;
       const int n_mma = (item.kb1 - item.kb0) * MMAS_PER_STAGE;
       const int n_acc = n_mma < NACC ? n_mma : NACC;  // accumulators that were written for this item
@@ -621,7 +648,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         if (p.swapped && hot_act != 5) {
           // tokens are the accumulator columns, a lane owns one feature: neighbouring lanes pair up so that every
           // store carries two features (4 bytes); rows past the feature count only take part in the shuffle
-          const float b = (m_ok && hot_bias) ? hot_bias_scale * __bfloat162float(hot_bias[m]) : 0.f;
+          const float b = prefetched ? bias_pre : ((m_ok && hot_bias) ? hot_bias_scale * __bfloat162float(hot_bias[m]) : 0.f);
           const float rowsum = (hot_norm && hot_rowsum && m_ok) ? hot_rowsum[m] : 0.f;
           const bool pitch_even = (hot_ld_out & 1) == 0 && (reinterpret_cast<uintptr_t>(hot_out) & 3) == 0;
           const bool writes_pair = pitch_even && !(lane & 1) && m + 1 < hot_m_extent;
@@ -634,7 +661,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             if (hot_norm) x = x * norm_stats[2 * (n0 + j)] - norm_stats[2 * (n0 + j) + 1] * rowsum;
             x += b;
             if (hot_act) x = apply_act_call(x, hot_act);
-            if (hot_residual && m_ok) x += __bfloat162float(hot_residual[idx]);
+            if (hot_residual && m_ok) x += prefetched ? res_pre[j] : __bfloat162float(hot_residual[idx]);
             const float up = __shfl_down_sync(0xffffffffu, x, 1);
             if (m_ok) {
               if (writes_pair) *reinterpret_cast<uint32_t*>(hot_out + idx) = pack_bf16x2(x, up);
@@ -994,6 +1021,9 @@ static int make_tmap_2d(CUtensorMap* map, const void* ptr, uint64_t rows, uint64
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    fprintf(stderr, "tpb: cuTensorMapEncodeTiled failed (%d): base %p, %llu rows x %llu cols, pitch %llu elements, box %u x %u\n", int(r), ptr,
+            (unsigned long long)rows, (unsigned long long)cols, (unsigned long long)ld, box_rows, unsigned(BK));
   return r == CUDA_SUCCESS ? TPB_OK : TPB_ERR_TMAP;
 }
 
@@ -1213,6 +1243,18 @@ static int gemm_impl(const void* x, const void* w, void* out, const void* bias, 
                      const tpb_gemm_plan_t* plan, const tpb_reduce_ctx_t* rc, const tpb_allgather_ctx_t* ag,
                      const tpb_gemm_opts_t* opts, void* stream_) {
   if (!x || !w || !out || !plan) return TPB_ERR_ARG;
+  {
+    // cuTensorMapEncodeTiled is a driver call and needs a context bound to THIS thread.  A thread that has made no
+    // context-binding runtime call yet (an autograd worker whose first native call is this GEMM) has none:
+    // cudaSetDevice binds the primary context of the device the runtime considers current.
+    static thread_local int bound_device = -1;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return TPB_ERR_CUDA;
+    if (bound_device != dev) {
+      if (cudaSetDevice(dev) != cudaSuccess) return TPB_ERR_CUDA;
+      bound_device = dev;
+    }
+  }
   const bool x_mn = opts && opts->x_mn, w_mn = opts && opts->w_mn;
   if ((x_mn || w_mn) && (plan->swapped || plan->kbox != 1 || plan->bn < 64 || ag)) return TPB_ERR_ARG;
   if (opts && opts->norm_mode) {

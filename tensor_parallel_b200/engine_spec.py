@@ -93,15 +93,17 @@ class DecoderSpec:
 
 
 def _rope_theta(cfg) -> float:
+    """Base of the rotary frequencies; raises for scaled / extrapolated variants (linear, NTK, YaRN, llama3 ...).
+    Newer ``transformers`` keep everything in ``rope_parameters`` (``rope_scaling`` is then an alias of it)."""
+    params = getattr(cfg, "rope_parameters", None) or getattr(cfg, "rope_scaling", None) or {}
+    if isinstance(params, dict):
+        kind = params.get("rope_type", params.get("type", "default"))
+        if kind not in ("default", None):
+            raise ValueError(f"scaled rotary embeddings ({kind})")
     theta = getattr(cfg, "rope_theta", None)
-    if theta is None:
-        params = getattr(cfg, "rope_parameters", None) or {}
-        theta = params.get("rope_theta", 10000.0)
-        if params.get("rope_type", "default") not in ("default", None):
-            raise ValueError("scaled rotary embeddings")
-    if getattr(cfg, "rope_scaling", None):
-        raise ValueError("scaled rotary embeddings")
-    return float(theta)
+    if theta is None and isinstance(params, dict):
+        theta = params.get("rope_theta")
+    return float(10000.0 if theta is None else theta)
 
 
 def _llama_like(lm, cfg, max_seq: int) -> Optional[DecoderSpec]:

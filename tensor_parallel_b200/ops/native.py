@@ -21,6 +21,9 @@ _ERRORS = {1: "bad argument", 2: "alignment rule violated", 3: "CUDA runtime err
 
 
 def _load() -> ctypes.CDLL:
+    variant = os.environ.get("TPB_LIB_PATH")  # a variant built with build(lib_path=..., extra_flags=...)
+    if variant:
+        return ctypes.CDLL(variant)
     path = _build.LIB_PATH
     if not path.exists() or os.environ.get("TPB_REBUILD"):
         _build.build()  # explicit rebuilds otherwise: python -m tensor_parallel_b200.build

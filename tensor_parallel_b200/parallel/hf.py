@@ -107,9 +107,10 @@ class TensorParallelPreTrainedModel(*_BASES):
         ids = inputs if inputs is not None else kwargs.get("input_ids")
         engine_ok = (
             generation_config is None and isinstance(ids, torch.Tensor) and ids.ndim == 2 and ids.dtype in (torch.int64, torch.int32)
-            and set(kwargs) <= self._ENGINE_KWARGS and not kwargs.get("do_sample", getattr(self.generation_config, "do_sample", False))
-            and kwargs.get("num_beams", getattr(self.generation_config, "num_beams", 1)) == 1
-            and kwargs.get("use_cache", True)
+            and set(kwargs) <= self._ENGINE_KWARGS
+            and not (kwargs.get("do_sample") if kwargs.get("do_sample") is not None else getattr(self.generation_config, "do_sample", None))
+            and (kwargs.get("num_beams") or getattr(self.generation_config, "num_beams", None) or 1) == 1
+            and kwargs.get("use_cache", True) is not False
             and (kwargs.get("attention_mask") is None or bool(kwargs["attention_mask"].all()))
             and getattr(self.generation_config, "repetition_penalty", None) in (None, 1.0)
         )
