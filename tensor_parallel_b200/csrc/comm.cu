@@ -280,9 +280,12 @@ extern "C" int tpb_collective(int kind, int dtype, int world, int rank, void* co
   cudaStream_t s = static_cast<cudaStream_t>(stream_);
   const long long bytes = n * (dtype == 0 ? 2 : 4);
   int mode = kind;
-  if (kind == 0) mode = force_algo >= 0 ? force_algo : (bytes <= 512 * 1024 ? 0 : (nvls ? 4 : 1));
-  if (kind == 2 && nvls && force_algo != 2) mode = 5;
-  if (kind == 3 && nvls && force_algo != 3) mode = 6;
+  // through the switch from 4 ranks on: at 2 ranks the peer two-shot moves the same bytes with less latency
+  // (128 MiB: 234 us against 377 us with multimem, NCCL 280 us; measured on B200)
+  const bool nvls_auto = nvls && world >= 4;
+  if (kind == 0) mode = force_algo >= 0 ? force_algo : (bytes <= 512 * 1024 ? 0 : (nvls_auto ? 4 : 1));
+  if (kind == 2 && nvls_auto && force_algo != 2) mode = 5;
+  if (kind == 3 && nvls_auto && force_algo != 3) mode = 6;
   if (mode >= 4 && !nvls) return TPB_ERR_ARG;
   const long long packets = n / per_packet;
   long long work = (mode == 1 || mode == 4) ? (packets + world - 1) / world : packets;

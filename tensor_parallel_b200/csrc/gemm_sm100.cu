@@ -249,6 +249,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   constexpr uint32_t TMEM_COLS = (2 * ACC_COLS < 32) ? 32 : 2 * ACC_COLS;   // two sets; power of two by construction
   static_assert(TMEM_COLS <= 512 && (TMEM_COLS & (TMEM_COLS - 1)) == 0, "TMEM allocation must be a power of two <= 512");
   constexpr uint32_t MN_BLOCK_BYTES = 64 * BK * 2;  // one [BK k-rows][64 MN elements] block of an MN-major operand
+  constexpr bool MN_CAPABLE = BN >= 128;            // instantiations that may get MN-major operands (see tpb_gemm_plan_ex)
+  constexpr bool FEW_TOKENS = BN <= 64;             // instantiations of the swapped orientation: norm folding, flagged words
   constexpr int MMAS_PER_STAGE = KBOX * (BK / UMMA_K);
 
   extern __shared__ uint8_t smem_raw[];
@@ -356,7 +358,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           uint8_t* a_dst = smem + size_t(s) * STAGE_BYTES;
           uint8_t* b_dst = a_dst + KBOX * A_BYTES;
           mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-          if (p.a_mn) {  // (KBOX == 1) 64-wide MN blocks of BK k-rows each, stacked along MN
+          // (MN-major operands only exist in the many-token instantiations: the few-token kernels stay small)
+          if (MN_CAPABLE && p.a_mn) {  // (KBOX == 1) 64-wide MN blocks of BK k-rows each, stacked along MN
 #pragma unroll
             for (int b = 0; b < BM / 64; ++b)
               tma_load_2d(a_dst + b * MN_BLOCK_BYTES, &tmap_a, &full_bar[s], mt * BM + b * 64, kb * BK);
@@ -365,12 +368,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             for (int j = 0; j < KBOX; ++j)  // columns past K are filled with zeros by TMA and cost no DRAM traffic
               tma_load_2d(a_dst + j * A_BYTES, &tmap_a, &full_bar[s], (kb * KBOX + j) * BK, mt * BM);
           }
-          if (p.b_mn) {
-            if constexpr (BN >= 64) {
+          if (MN_CAPABLE && p.b_mn) {
 #pragma unroll
-              for (int b = 0; b < BN / 64; ++b)
-                tma_load_2d(b_dst + b * MN_BLOCK_BYTES, &tmap_b, &full_bar[s], nt * BN + b * 64, kb * BK);
-            }
+            for (int b = 0; b < BN / 64; ++b)
+              tma_load_2d(b_dst + b * MN_BLOCK_BYTES, &tmap_b, &full_bar[s], nt * BN + b * 64, kb * BK);
           } else {
 #pragma unroll
             for (int j = 0; j < KBOX; ++j)
@@ -385,7 +386,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       uint32_t it = 0;
       uint32_t local = 0;
       const uint32_t idesc = make_idesc_bf16(BM, BN, p.a_mn != 0, p.b_mn != 0);
-      const bool any_mn = (p.a_mn | p.b_mn) != 0;
+      const bool any_mn = MN_CAPABLE && (p.a_mn | p.b_mn) != 0;
       WorkIter work(p);
       WorkItem item;
       for (; !*abort_flag && work.next(p, item); ++local) {
@@ -460,7 +461,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     float hot_bias_scale = p.bias_scale;
     asm volatile("" : "+l"(hot_out), "+l"(hot_bias), "+l"(hot_residual), "+r"(hot_ld_out), "+r"(hot_act), "+r"(hot_n_extent),
                  "+r"(hot_m_extent), "+f"(hot_bias_scale));
-    if (p.norm_mode) {
+    if (FEW_TOKENS && p.norm_mode) {
       // statistics of every token row of the unnormalised operand (swapped orientation: at most 64 tokens, all of them
       // in this CTA's tile), computed by the otherwise idle epilogue warps while the weights stream in
       const int chunks = p.norm_k >> 3;
@@ -492,7 +493,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       }
       asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
     }
-    const bool hot_norm = p.norm_mode != 0;
+    const bool hot_norm = FEW_TOKENS && p.norm_mode != 0;
     const float* hot_rowsum = p.norm_rowsum;
     uint32_t local = 0;
     WorkIter work(p);
@@ -1033,7 +1034,7 @@ static int g_debug_skip_mma = 0, g_trace_block = 0;
 #endif
 // split-K of few-tile weight-streaming GEMMs (see tpb_gemm_plan): a tile is split when it streams at least
 // g_split_min_kb KiB of weights, into pieces of about g_split_target_kb KiB
-static int g_split_min_kb = 512, g_split_target_kb = 128;
+static int g_split_min_kb = 1024, g_split_target_kb = 256;
 static uint64_t g_wait_ns = TPB_WAIT_LIMIT_NS;  // bound of the waits for peer GPUs, see tpb_set_wait_limit
 
 template <int BN, int KBOX, int NACC>
@@ -1147,7 +1148,7 @@ extern "C" int tpb_gemm_plan_ex(int tokens, int features, int k, int world, int 
     plan->m_tiles = (features + BM - 1) / BM;
     plan->n_tiles = (tokens + bn - 1) / bn;
   } else {
-    bn = features >= 256 ? 256 : (features > 64 ? 128 : 64);
+    bn = features >= 256 ? 256 : ((features > 64 || (flags & 1)) ? 128 : 64);  // (MN-major operands: 128-wide tiles at least)
     // prefer 128-wide tiles when 256-wide ones would leave most SMs idle
     if (bn == 256 && ((tokens + BM - 1) / BM) * ((features + 255) / 256) < sms) bn = 128;
     plan->m_tiles = (tokens + BM - 1) / BM;
@@ -1201,11 +1202,14 @@ extern "C" int tpb_gemm_plan_ex(int tokens, int features, int k, int world, int 
     const long long tile_kb = (long long)BM * k * 2 / 1024;  // weights one 128-row tile streams
     if (force_splits > 0) {
       splits = force_splits;
-    } else if (plan->swapped && tiles * 2 <= sms && tile_kb >= g_split_min_kb) {
+    } else if (plan->swapped && tiles * 4 <= sms && tile_kb >= g_split_min_kb) {
       // Few weight tiles (a tensor-parallel shard of a projection): the GEMM is a pure weight stream and takes
-      // bytes / (CTAs x per-CTA stream rate), so a handful of CTAs streaming 1 MB each is slow however little data
-      // there is.  Split K so that most SMs stream a share of about g_split_target_kb; the partials meet in the slot
-      // workspace and the last CTA of a tile to arrive sums them (one fence + one atomic, nobody waits).
+      // bytes / (CTAs x per-CTA stream rate) - one CTA pulls about 120 GB/s - so a handful of CTAs streaming 1 MB each
+      // is slow however little data there is.  Split K so that most SMs stream a share of about g_split_target_kb; the
+      // partials meet in the slot workspace and the last CTA of a tile to arrive sums them (one fence + one atomic,
+      // nobody waits).  The exchange costs 3 to 4 us, which is why tiles under 1 MB and grids of more than a quarter of
+      // the SMs are left whole (measured on B200 with the shard shapes of a Llama-2-7B layer at 1, 2, 4 and 8 ranks:
+      // 8-way qkv 16.9 -> 13.7 us, gate|up 17.8 -> 15.7 us, head 17.0 -> 15.8 us; 2-way o_proj 13.1 -> 15.2 us if split).
       splits = sms / tiles;
       const int by_bytes = int((tile_kb + g_split_target_kb - 1) / g_split_target_kb);
       if (splits > by_bytes) splits = by_bytes;
@@ -1256,7 +1260,7 @@ static int gemm_impl(const void* x, const void* w, void* out, const void* bias, 
     }
   }
   const bool x_mn = opts && opts->x_mn, w_mn = opts && opts->w_mn;
-  if ((x_mn || w_mn) && (plan->swapped || plan->kbox != 1 || plan->bn < 64 || ag)) return TPB_ERR_ARG;
+  if ((x_mn || w_mn) && (plan->swapped || plan->kbox != 1 || plan->bn < 128 || ag)) return TPB_ERR_ARG;
   if (opts && opts->norm_mode) {
     if (!plan->swapped || !opts->norm_x || ((opts->norm_k > 0 ? opts->norm_k : k) & 7) || (opts->norm_ld & 7) || ((uintptr_t)opts->norm_x & 15) || tokens > 64 ||
         opts->norm_mode < 0 || opts->norm_mode > 2 || (rc && rc->world > 1 && plan->reduce) || ag)

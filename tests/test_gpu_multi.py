@@ -31,7 +31,7 @@ def _setup(rank, world, port):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
 
 
-def _run(body_name, rank, world, port, out_dir):
+def _run(rank, body_name, world, port, out_dir):
     """Child entry: runs one body; whatever happens, all ranks stop issuing traffic, meet, and tear their heaps down
     (multicast view first) before any of them exits."""
     import traceback
