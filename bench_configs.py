@@ -1,10 +1,15 @@
 """The other model configurations of the benchmark plan, through the public API (one process per GPU):
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port P \\
-        bench_configs.py --config falcon40b_infer|flan_t5_xl_train|opt13b_train [--layers L]
+        bench_configs.py --config falcon40b_infer|flan_t5_xl_train|opt13b_train [--layers L] [--impl reference]
+
+``--impl reference`` (``falcon40b_infer`` only) runs the unmodified reference from ``baseline/_ref`` with its own
+``get_refined_web_config`` rule table on a plain-PyTorch model of the same shape (``baseline/ref_models.py``): rank 0 drives all
+GPUs from threads, which is the reference's multi-GPU mode.
 
 * ``falcon40b_infer``  : Falcon-40B-shaped (60 layers, d 8192, 128 query / 8 KV heads of 64, parallel block, FFN 32768
-  GeLU, vocab 65024), bf16; prefill batch 16 x 1024 then 128 greedy tokens with the head-sharded KV cache.
+  GeLU, vocab 65024), bf16; prefill batch 16 x 1024 then 128 greedy tokens with the head-sharded KV cache, served by the
+  kernel-level engine (four kernels per layer and decode step, one fused GEMM + all-reduce per layer).
 * ``flan_t5_xl_train`` : FLAN-T5-XL-shaped (24+24 layers, d 2048, 32 heads of 64, gated-GeLU FFN 5120, vocab 32128), bf16,
   seq2seq training step with ``sharded=True`` (ZeRO-3 inside the TP group); encoder batch 16 x 512, targets 16 x 128.
 * ``opt13b_train``     : OPT-13B-shaped training step, micro-batch 4 x 2048, ``sharded=True``, AdamW.
@@ -24,13 +29,83 @@ REPO = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, REPO)
 
 
+def falcon_reference(args):
+    """Falcon-40B-shaped inference on the reference (threaded mode, its RefinedWeb rule table, cuBLAS + SDPA + torch.cuda.nccl)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    ref_dir = os.path.join(REPO, "baseline", "_ref")
+    sys.path.insert(0, ref_dir)
+    sys.path.insert(0, os.path.join(REPO, "baseline"))
+    import warnings
+
+    warnings.filterwarnings("ignore")
+    try:
+        import tensor_parallel as ref_tp
+        from ref_models import RefFalconConfig, RefFalconForCausalLM
+        from tensor_parallel.slicing_configs import get_refined_web_config
+    except Exception as exc:  # noqa: BLE001
+        print(json.dumps({"config": args.config, "impl": "reference", "unavailable": repr(exc)[:200]}), flush=True)
+        return
+    gpus = args.gpus or torch.cuda.device_count()
+    devices = [torch.device("cuda", i) for i in range(gpus)]
+    torch.manual_seed(0)
+    cfg = RefFalconConfig(n_layer=args.layers or 60)
+    torch.set_default_dtype(torch.bfloat16)
+    with torch.device(devices[0]):
+        model = RefFalconForCausalLM(cfg).eval()
+        for p in model.parameters():
+            if p.ndim >= 2:
+                torch.nn.init.normal_(p, 0.0, 0.02)
+    torch.set_default_dtype(torch.float32)
+    tp_model = ref_tp.TensorParallel(model, device_ids=devices, tensor_parallel_config=get_refined_web_config(cfg, devices) if gpus > 1 else None,
+                                     sharded=False)
+    if gpus > 1:
+        del model
+        torch.cuda.empty_cache()
+    gen = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, cfg.vocab_size, (16, 1024), generator=gen).to(devices[0])
+    new_tokens = args.decode_steps
+
+    def sync():
+        for d in devices:
+            torch.cuda.synchronize(d)
+
+    with torch.no_grad():
+        tp_model(prompt[:, :64], past_key_values=None, use_cache=True, last_only=True)  # warm-up
+        sync()
+        torch.cuda.set_device(devices[0])
+        e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        e0.record()
+        logits, past = tp_model(prompt, past_key_values=None, use_cache=True, last_only=True)
+        e1.record()
+        nxt = logits[:, -1].argmax(-1, keepdim=True)
+        for _ in range(new_tokens):
+            logits, past = tp_model(nxt, past_key_values=past, use_cache=True, last_only=True)
+            nxt = logits[:, -1].argmax(-1, keepdim=True)
+        e2.record()
+        sync()
+    print(json.dumps({"config": args.config, "impl": "reference", "n_gpus": gpus, "layers": args.layers or "full", "dtype": "bf16",
+                      "data": "synthetic", "prefill_ms": e0.elapsed_time(e1), "prefill_tokens_per_s": 16 * 1024 / (e0.elapsed_time(e1) / 1e3),
+                      "decode_steps": new_tokens, "decode_ms_per_step": e1.elapsed_time(e2) / new_tokens,
+                      "decode_tokens_per_s": 16 * new_tokens / (e1.elapsed_time(e2) / 1e3),
+                      "reference_mode": "tensor_parallel.TensorParallel, threaded, get_refined_web_config"}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--config", required=True, choices=["falcon40b_infer", "flan_t5_xl_train", "opt13b_train"])
     ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=2)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--gpus", type=int, default=0, help="reference arm: GPUs driven by rank 0 (default: all visible)")
+    ap.add_argument("--decode-steps", type=int, default=127)
     args = ap.parse_args()
+    if args.impl == "reference":
+        if args.config != "falcon40b_infer":
+            raise SystemExit("the reference arm of bench_configs.py covers falcon40b_infer (bench.py holds the Llama arms)")
+        return falcon_reference(args)
     import tensor_parallel_b200 as tp
     from tensor_parallel_b200.ops import native
 
@@ -81,28 +156,34 @@ def main():
            "impl": "tensor_parallel_b200", "data": "synthetic"}
     before = native.launch_count
     if args.config == "falcon40b_infer":
-        from tensor_parallel_b200.models.generation import generate
-
-        prompt = torch.randint(0, cfg.vocab_size, (16, 1024), generator=gen).to(device)
+        if world == 1:
+            tp_model = tp.TensorParallel(tp_model, [device])  # one device: the module itself, plus the serving API
+        prompt = torch.randint(0, cfg.vocab_size, (16, 1024), generator=gen)
+        new_tokens = args.decode_steps
         with torch.no_grad():
-            generate(tp_model, prompt[:, :64], max_new_tokens=2)  # warm-up
+            tp_model.prefill(prompt, max_new_tokens=new_tokens + 8)  # builds the engine; library / allocation warm-up
+            engine = tp_model._engine
             sync()
             e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
             e0.record()
-            out = tp_model(input_ids=prompt, use_cache=True)
+            logits = tp_model.prefill(prompt, max_new_tokens=new_tokens + 8)
             e1.record()
-            past, nxt = out["past_key_values"], out["logits"][:, -1].argmax(-1, keepdim=True)
-            new_tokens = 127
-            for _ in range(new_tokens):
-                out = tp_model(input_ids=nxt, past_key_values=past, use_cache=True)
-                past, nxt = out["past_key_values"], out["logits"][:, -1].argmax(-1, keepdim=True)
+            engine.ids[:16].copy_(logits.argmax(-1))
+            engine.decode_step(16)  # captures the graph (untimed)
+            sync()
+            e1b = torch.cuda.Event(enable_timing=True)
+            e1b.record()
+            for _ in range(new_tokens - 1):
+                engine.decode_step(16)
             e2.record()
             sync()
-        t = torch.tensor([e0.elapsed_time(e1), e1.elapsed_time(e2)], device=device, dtype=torch.float64)
+            engine.check_status()
+        t = torch.tensor([e0.elapsed_time(e1), e1b.elapsed_time(e2)], device=device, dtype=torch.float64)
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        rec.update(prefill_ms=float(t[0]), prefill_tokens_per_s=16 * 1024 / (float(t[0]) / 1e3), decode_ms_per_step=float(t[1]) / new_tokens,
-                   decode_tokens_per_s=16 * new_tokens / (float(t[1]) / 1e3))
+        rec.update(prefill_ms=float(t[0]), prefill_tokens_per_s=16 * 1024 / (float(t[0]) / 1e3), decode_ms_per_step=float(t[1]) / (new_tokens - 1),
+                   decode_tokens_per_s=16 * (new_tokens - 1) / (float(t[1]) / 1e3), kernels_per_step=engine.kernels_per_step,
+                   served_by="DecoderEngine (CUDA graph)")
     else:
         opt = tp.optim.AdamW(tp_model.parameters(), lr=1e-5, weight_decay=0.1)
         if args.config == "flan_t5_xl_train":

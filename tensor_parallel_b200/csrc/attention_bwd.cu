@@ -5,6 +5,9 @@
 //   dV = P^T dO                        dP = dO V^T
 //   dS = P * (dP - delta) * scale
 //   dQ = dS K                          dK = dS^T Q
+// With an additive score bias (relative positions, ALiBi, padding masks) the scores are S * scale + bias, and the gradient
+// of the bias is d(bias) = P * (dP - delta), summed over whatever dimensions the bias broadcasts over: the dQ kernel,
+// which visits every (query, key) pair exactly once, adds it into an fp32 buffer with the bias' own (broadcast) strides.
 //
 // Two kernels, both free of atomics and therefore deterministic:
 //   attn_bwd_dq_kernel  : one CTA per 64 query rows of one head, loops over key tiles (like the forward)
@@ -23,6 +26,19 @@
 namespace tpb {
 
 constexpr float LOG2E = 1.4426950408889634f;
+
+// Additive score bias in natural-log units (kind 0 none, 1 fp32, 2 bf16) addressed with element strides over
+// (batch, head, query, key), a stride of 0 broadcasting; dbias (optional, fp32, zero-initialised) uses the same strides.
+struct BiasArgs {
+  const void* bias;
+  int kind;
+  long long sb, sh, sq, sk;
+  float* dbias;
+};
+
+__device__ __forceinline__ float bias_at(const BiasArgs& ba, long long idx) {
+  return ba.kind == 1 ? __ldg(static_cast<const float*>(ba.bias) + idx) : __bfloat162float(static_cast<const bf16*>(ba.bias)[idx]);
+}
 
 __global__ void attn_bwd_delta_kernel(const bf16* __restrict__ out, const bf16* __restrict__ dout, float* __restrict__ delta,
                                       int sq, int heads, int d, long long o_sb, long long o_ss, long long o_sh,
@@ -57,7 +73,7 @@ attn_bwd_dq_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const
                    bf16* __restrict__ dq, int sq, int sk, int q_heads, int kv_heads, long long q_sb, long long q_ss,
                    long long q_sh, long long k_sb, long long k_ss, long long k_sh, long long v_sb, long long v_ss,
                    long long v_sh, long long do_sb, long long do_ss, long long do_sh, long long dq_sb, long long dq_ss,
-                   long long dq_sh, int causal, float scale) {
+                   long long dq_sh, int causal, float scale, const BiasArgs ba) {
   extern __shared__ __align__(128) uint8_t bw_smem[];
   bf16* q_s = reinterpret_cast<bf16*>(bw_smem);
   bf16* do_s = q_s + PF_M * D;
@@ -143,8 +159,16 @@ attn_bwd_dq_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const
         const int r2 = j >> 1;
         const int qi = qi0 + r2 * 8;
         const bool dead = key >= sk || qi >= sq || (causal && key > qi + shift) || lse2[r2] == -INFINITY;
-        const float p = dead ? 0.f : exp2f(s_acc[nt][j] * scale_log2e - lse2[r2]);
-        ds[j] = p * (dp_acc[nt][j] - dl[r2]) * scale;
+        float sv = s_acc[nt][j] * scale_log2e;
+        long long bi = 0;
+        if (ba.kind && !dead) {
+          bi = b * ba.sb + h * ba.sh + (long long)qi * ba.sq + (long long)key * ba.sk;
+          sv += bias_at(ba, bi) * LOG2E;
+        }
+        const float p = dead ? 0.f : exp2f(sv - lse2[r2]);
+        const float dscore = p * (dp_acc[nt][j] - dl[r2]);  // gradient of the biased score
+        if (ba.dbias && !dead && dscore != 0.f) atomicAdd(ba.dbias + bi, dscore);
+        ds[j] = dscore * scale;
       }
       dsf[nt >> 1][(nt & 1) * 2] = pack2(ds[0], ds[1]);
       dsf[nt >> 1][(nt & 1) * 2 + 1] = pack2(ds[2], ds[3]);
@@ -185,7 +209,7 @@ attn_bwd_dkv_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, cons
                     bf16* __restrict__ dk, bf16* __restrict__ dv, int sq, int sk, int q_heads, int kv_heads,
                     long long q_sb, long long q_ss, long long q_sh, long long k_sb, long long k_ss, long long k_sh,
                     long long v_sb, long long v_ss, long long v_sh, long long do_sb, long long do_ss, long long do_sh,
-                    long long dk_sb, long long dk_ss, long long dk_sh, int causal, float scale) {
+                    long long dk_sb, long long dk_ss, long long dk_sh, int causal, float scale, const BiasArgs ba) {
   extern __shared__ __align__(128) uint8_t bw_smem[];
   bf16* k_s = reinterpret_cast<bf16*>(bw_smem);
   bf16* v_s = k_s + PF_N * D;
@@ -271,7 +295,9 @@ attn_bwd_dkv_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, cons
           const int key = key0 + (j >> 1) * 8;
           const float l2 = lse_s[col];
           const bool dead = key >= sk || qi >= sq || (causal && key > qi + shift) || l2 == -INFINITY;
-          pv[j] = dead ? 0.f : exp2f(st[nt][j] * scale_log2e - l2);
+          float sv = st[nt][j] * scale_log2e;
+          if (ba.kind && !dead) sv += bias_at(ba, b * ba.sb + hq * ba.sh + (long long)qi * ba.sq + (long long)key * ba.sk) * LOG2E;
+          pv[j] = dead ? 0.f : exp2f(sv - l2);
           ds[j] = pv[j] * (dpt[nt][j] - dl_s[col]) * scale;
         }
         pf[nt >> 1][(nt & 1) * 2] = pack2(pv[0], pv[1]);
@@ -317,15 +343,27 @@ using namespace tpb;
 // q, dout, out, dq: [batch, sq, q_heads, d]; k, v, dk, dv: [batch, sk, kv_heads, d]; strides in elements with a
 // contiguous head_dim; dq uses its own strides, dk and dv share (dk_sb, dk_ss, dk_sh).  lse [batch, q_heads, sq]
 // is the log-sum-exp written by tpb_attn_prefill; delta is a caller-provided fp32 scratch of the same shape.
-extern "C" int tpb_attn_backward(const void* q, const void* k, const void* v, const void* out, const void* dout,
-                                 const float* lse, float* delta, void* dq, void* dk, void* dv, int batch, int sq, int sk,
-                                 int q_heads, int kv_heads, int head_dim, long long q_sb, long long q_ss, long long q_sh,
-                                 long long k_sb, long long k_ss, long long k_sh, long long v_sb, long long v_ss,
-                                 long long v_sh, long long o_sb, long long o_ss, long long o_sh, long long do_sb,
-                                 long long do_ss, long long do_sh, long long dq_sb, long long dq_ss, long long dq_sh,
-                                 long long dk_sb, long long dk_ss, long long dk_sh, int causal, float scale, void* stream_) {
+//
+// bias (may be null): the additive score bias the forward pass was given, dtype bias_dtype (0 bf16, 1 fp32), element strides
+// over (batch, head, query, key) with 0 broadcasting.  dbias (may be null): fp32 buffer addressed with the same strides,
+// zero-initialised by the caller; receives the gradient of the bias (added with atomics where the bias broadcasts).
+extern "C" int tpb_attn_backward_bias(const void* q, const void* k, const void* v, const void* out, const void* dout,
+                                      const float* lse, float* delta, void* dq, void* dk, void* dv, int batch, int sq, int sk,
+                                      int q_heads, int kv_heads, int head_dim, long long q_sb, long long q_ss, long long q_sh,
+                                      long long k_sb, long long k_ss, long long k_sh, long long v_sb, long long v_ss,
+                                      long long v_sh, long long o_sb, long long o_ss, long long o_sh, long long do_sb,
+                                      long long do_ss, long long do_sh, long long dq_sb, long long dq_ss, long long dq_sh,
+                                      long long dk_sb, long long dk_ss, long long dk_sh, int causal, float scale, const void* bias,
+                                      int bias_dtype, long long bias_sb, long long bias_sh, long long bias_sq, long long bias_sk,
+                                      float* dbias, void* stream_) {
   if (!q || !k || !v || !out || !dout || !lse || !delta || !dq || !dk || !dv || batch <= 0 || sq <= 0 || sk <= 0 || q_heads % kv_heads)
     return TPB_ERR_ARG;
+  if ((bias && bias_dtype != 0 && bias_dtype != 1) || (dbias && !bias)) return TPB_ERR_ARG;
+  BiasArgs ba;
+  ba.bias = bias;
+  ba.kind = !bias ? 0 : (bias_dtype == 1 ? 1 : 2);
+  ba.sb = bias_sb; ba.sh = bias_sh; ba.sq = bias_sq; ba.sk = bias_sk;
+  ba.dbias = dbias;
   if (head_dim != 64 && head_dim != 128) return TPB_ERR_SIZE;
   const long long strides[] = {q_sb, q_ss, q_sh, k_sb, k_ss, k_sh, v_sb, v_ss, v_sh, do_sb, do_ss, do_sh};
   for (long long s : strides)
@@ -349,9 +387,9 @@ extern "C" int tpb_attn_backward(const void* q, const void* k, const void* v, co
   }
   dim3 grid_q((sq + PF_M - 1) / PF_M, q_heads, batch), grid_kv((sk + PF_N - 1) / PF_N, kv_heads, batch);
 #define ARGS_DQ (const bf16*)q, (const bf16*)k, (const bf16*)v, (const bf16*)dout, lse, delta, (bf16*)dq, sq, sk, q_heads, kv_heads, q_sb, \
-                q_ss, q_sh, k_sb, k_ss, k_sh, v_sb, v_ss, v_sh, do_sb, do_ss, do_sh, dq_sb, dq_ss, dq_sh, causal, scale
+                q_ss, q_sh, k_sb, k_ss, k_sh, v_sb, v_ss, v_sh, do_sb, do_ss, do_sh, dq_sb, dq_ss, dq_sh, causal, scale, ba
 #define ARGS_DKV (const bf16*)q, (const bf16*)k, (const bf16*)v, (const bf16*)dout, lse, delta, (bf16*)dk, (bf16*)dv, sq, sk, q_heads,   \
-                 kv_heads, q_sb, q_ss, q_sh, k_sb, k_ss, k_sh, v_sb, v_ss, v_sh, do_sb, do_ss, do_sh, dk_sb, dk_ss, dk_sh, causal, scale
+                 kv_heads, q_sb, q_ss, q_sh, k_sb, k_ss, k_sh, v_sb, v_ss, v_sh, do_sb, do_ss, do_sh, dk_sb, dk_ss, dk_sh, causal, scale, ba
   if (head_dim == 128) {
     attn_bwd_dq_kernel<128><<<grid_q, PF_THREADS, smem_dq, s>>>(ARGS_DQ);
     attn_bwd_dkv_kernel<128><<<grid_kv, PF_THREADS, smem_dkv, s>>>(ARGS_DKV);
@@ -362,4 +400,16 @@ extern "C" int tpb_attn_backward(const void* q, const void* k, const void* v, co
 #undef ARGS_DQ
 #undef ARGS_DKV
   return cudaGetLastError() == cudaSuccess ? TPB_OK : TPB_ERR_CUDA;
+}
+
+extern "C" int tpb_attn_backward(const void* q, const void* k, const void* v, const void* out, const void* dout,
+                                 const float* lse, float* delta, void* dq, void* dk, void* dv, int batch, int sq, int sk,
+                                 int q_heads, int kv_heads, int head_dim, long long q_sb, long long q_ss, long long q_sh,
+                                 long long k_sb, long long k_ss, long long k_sh, long long v_sb, long long v_ss,
+                                 long long v_sh, long long o_sb, long long o_ss, long long o_sh, long long do_sb,
+                                 long long do_ss, long long do_sh, long long dq_sb, long long dq_ss, long long dq_sh,
+                                 long long dk_sb, long long dk_ss, long long dk_sh, int causal, float scale, void* stream_) {
+  return tpb_attn_backward_bias(q, k, v, out, dout, lse, delta, dq, dk, dv, batch, sq, sk, q_heads, kv_heads, head_dim, q_sb, q_ss, q_sh,
+                                k_sb, k_ss, k_sh, v_sb, v_ss, v_sh, o_sb, o_ss, o_sh, do_sb, do_ss, do_sh, dq_sb, dq_ss, dq_sh, dk_sb,
+                                dk_ss, dk_sh, causal, scale, nullptr, 0, 0, 0, 0, 0, nullptr, stream_);
 }

@@ -1,0 +1,431 @@
+// Flash-style attention forward for sm_100a on tcgen05 tensor cores.
+//
+// One CTA per (batch, query head, 128-query tile); keys / values stream through in tiles of 128:
+//
+//   warp 0   : TMA producer  - Q once, then K / V tiles into a 2-deep shared-memory ring (4-D tensor maps over the
+//                              caller's strided [batch, seq, head, head_dim] views; no multicast)
+//   warp 1   : MMA issuer    - S = Q K^T  (tcgen05.mma, M = 128 queries, N = 128 keys, both operands K-major) into one of
+//                              two TMEM score buffers, and O_tile = P V (A = P from shared memory, B = V read MN-major as it
+//                              lies in memory) into a TMEM output tile; QK of tile j + 1 is issued BEFORE the wait for the
+//                              probabilities of tile j, so the tensor core works on the next scores while the softmax
+//                              warps are busy
+//   warps 2-5: softmax       - thread r owns query row r (= TMEM lane r): pass 1 reads the scores from TMEM, applies
+//                              scale / bias / masks, writes them back and takes the row maximum; then the previous tile's
+//                              P V product is folded into the fp32 output registers (o = o * alpha + O_tile: the running
+//                              output never lives in TMEM, so nothing there is ever rescaled); pass 2 exponentiates,
+//                              sums, and stores the bf16 probabilities into shared memory in the 128-byte-swizzled K-major
+//                              layout the tensor core reads.
+//
+// TMEM: scores 2 x 128 columns, output tile head_dim columns (512 allocated).  Shared memory at head_dim 128:
+// Q 32 KB + 2 x (K 32 KB + V 32 KB) + P 32 KB = 192 KB.  Every mbarrier wait is bounded; on expiry the CTA records a
+// status code and drains.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <atomic>
+
+#include "ptx_sm100.cuh"
+#include "tpb_api.h"
+
+namespace tpb {
+
+typedef __nv_bfloat16 bf16;
+
+constexpr int FA_M = 128;        // queries per CTA
+constexpr int FA_N = 128;        // keys per tile
+constexpr int FA_THREADS = 192;  // producer warp, MMA warp, four softmax warps
+constexpr int FA_BLOCK_BYTES = 128 * 128;  // one [128 rows][64 elements] swizzled block
+
+struct FaParams {
+  int sq, sk, q_heads, kv_heads, causal;
+  float scale_log2e;
+  bf16* out;
+  long long o_sb, o_ss, o_sh;
+  float* lse;
+  const void* bias;  // additive score bias in natural-log units, -inf masks a key; element strides, 0 broadcasts
+  int bias_kind;     // 0 none, 1 fp32, 2 bf16
+  long long bias_sb, bias_sh, bias_sq, bias_sk;
+  uint32_t* status;
+};
+
+template <int D>
+__global__ void __launch_bounds__(FA_THREADS, 1)
+attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                        const __grid_constant__ CUtensorMap tmap_v, const FaParams p) {
+  constexpr int DB = D / 64;                          // 64-wide blocks of the head dimension
+  constexpr uint32_t Q_BYTES = DB * FA_BLOCK_BYTES;   // Q tile = K tile = V tile
+  constexpr uint32_t P_BYTES = 2 * FA_BLOCK_BYTES;    // 128 x 128 probabilities
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr uint32_t S_COLS = FA_N, O_COL0 = 2 * FA_N;
+  constexpr uint32_t IDESC_QK = make_idesc_bf16(FA_M, FA_N, false, false);
+  constexpr uint32_t IDESC_PV = make_idesc_bf16(FA_M, D, false, true);
+
+  extern __shared__ uint8_t fa_smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(fa_smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* q_s = smem;
+  uint8_t* k_s = q_s + Q_BYTES;          // [2 stages]
+  uint8_t* v_s = k_s + 2 * Q_BYTES;      // [2 stages]
+  uint8_t* p_s = v_s + 2 * Q_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + P_BYTES);
+  uint64_t* q_full = bars;
+  uint64_t* kv_full = bars + 1;    // [2]
+  uint64_t* kv_empty = bars + 3;   // [2]
+  uint64_t* s_full = bars + 5;     // [2]
+  uint64_t* p_full = bars + 7;
+  uint64_t* o_full = bars + 8;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qblk = gridDim.x - 1 - blockIdx.x;  // heavy (late) causal tiles first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int kvh = h / (p.q_heads / p.kv_heads);
+  const int q0 = qblk * FA_M;
+  const int shift = p.sk - p.sq;  // query i may see keys j <= i + shift when causal
+  int kv_end = p.sk;
+  if (p.causal) kv_end = min(p.sk, q0 + FA_M + shift);
+  const int n_tiles = kv_end > 0 ? (kv_end + FA_N - 1) / FA_N : 0;
+
+  if (threadIdx.x == 0) {
+    prefetch_tmap(&tmap_q);
+    prefetch_tmap(&tmap_k);
+    prefetch_tmap(&tmap_v);
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+      mbar_init(&s_full[s], 1);
+    }
+    mbar_init(p_full, 4);  // one arrival per softmax warp
+    mbar_init(o_full, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  auto give_up = [&](uint32_t code) {
+    atomicMax(p.status, code);
+    *abort_flag = 1;
+  };
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (elect_one() && n_tiles > 0) {
+      mbar_expect_tx(q_full, Q_BYTES);
+#pragma unroll
+      for (int d = 0; d < DB; ++d) tma_load_4d(q_s + d * FA_BLOCK_BYTES, &tmap_q, q_full, d * 64, q0, h, b);
+      for (int j = 0; j < n_tiles && !*abort_flag; ++j) {
+        const int s = j & 1;
+        if (!mbar_wait(&kv_empty[s], ((j >> 1) & 1) ^ 1)) { give_up(STATUS_TIMEOUT_MBAR); break; }
+        mbar_expect_tx(&kv_full[s], 2 * Q_BYTES);
+#pragma unroll
+        for (int d = 0; d < DB; ++d) {
+          tma_load_4d(k_s + s * Q_BYTES + d * FA_BLOCK_BYTES, &tmap_k, &kv_full[s], d * 64, j * FA_N, kvh, b);
+          tma_load_4d(v_s + s * Q_BYTES + d * FA_BLOCK_BYTES, &tmap_v, &kv_full[s], d * 64, j * FA_N, kvh, b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (elect_one() && n_tiles > 0) {
+      const uint32_t q_addr = smem_u32(q_s), p_addr = smem_u32(p_s);
+      auto issue_qk = [&](int j) {  // S[j & 1] = Q K(j)^T
+        const uint32_t k_addr = smem_u32(k_s + (j & 1) * Q_BYTES);
+        const uint32_t d_tmem = tmem_base + (j & 1) * S_COLS;
+#pragma unroll
+        for (int d = 0; d < DB; ++d) {
+#pragma unroll
+          for (int kk = 0; kk < 64 / 16; ++kk) {
+            const uint64_t adesc = make_desc_kmajor_sw128(q_addr + d * FA_BLOCK_BYTES + kk * 32);
+            const uint64_t bdesc = make_desc_kmajor_sw128(k_addr + d * FA_BLOCK_BYTES + kk * 32);
+            umma_bf16(d_tmem, adesc, bdesc, IDESC_QK, (d | kk) ? 1u : 0u);
+          }
+        }
+        umma_commit(&s_full[j & 1]);
+      };
+      bool ok = mbar_wait(q_full, 0) && mbar_wait(&kv_full[0], 0);
+      if (!ok) give_up(STATUS_TIMEOUT_MBAR);
+      if (ok) {
+        tc_fence_after();
+        issue_qk(0);
+      }
+      for (int j = 0; ok && j < n_tiles && !*abort_flag; ++j) {
+        if (j + 1 < n_tiles) {
+          // scores of the next tile: the softmax warps finished with this TMEM buffer when they delivered P(j - 1),
+          // which PV(j - 1) below waited for
+          if (!mbar_wait(&kv_full[(j + 1) & 1], ((j + 1) >> 1) & 1)) { give_up(STATUS_TIMEOUT_MBAR); break; }
+          tc_fence_after();
+          issue_qk(j + 1);
+        }
+        if (!mbar_wait(p_full, j & 1)) { give_up(STATUS_TIMEOUT_MBAR); break; }
+        tc_fence_after();
+        // O_tile = P(j) V(j): V tile [128 keys][D] is the MN-major B operand (N = head_dim contiguous)
+        const uint32_t v_addr = smem_u32(v_s + (j & 1) * Q_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < FA_N / 16; ++kk) {
+          const uint64_t adesc = make_desc_kmajor_sw128(p_addr + (kk >> 2) * FA_BLOCK_BYTES + (kk & 3) * 32);
+          const uint64_t bdesc = make_desc_mnmajor_sw128(v_addr + kk * 16 * 128, FA_BLOCK_BYTES);
+          umma_bf16(tmem_base + O_COL0, adesc, bdesc, IDESC_PV, kk ? 1u : 0u);
+        }
+        umma_commit(o_full);
+        umma_commit(&kv_empty[j & 1]);  // K(j) and V(j) may be overwritten once these MMAs retire
+      }
+    }
+  } else {
+    // ---------------- softmax warps ----------------
+    const int quarter = warp & 3;  // TMEM lane quarter this warp may access
+    const int row = quarter * 32 + lane;
+    const int qi = q0 + row;
+    const uint32_t t_lane = tmem_base + (uint32_t(quarter * 32) << 16);
+    float o_reg[D];
+#pragma unroll
+    for (int i = 0; i < D; ++i) o_reg[i] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f, alpha_prev = 1.f;
+    const float* bias_f = static_cast<const float*>(p.bias);
+    const bf16* bias_h = static_cast<const bf16*>(p.bias);
+    const long long bias_row = p.bias_kind ? (b * p.bias_sb + h * p.bias_sh + (long long)min(qi, p.sq - 1) * p.bias_sq) : 0;
+    bool alive = true;
+
+    auto fold_output = [&](float alpha) {  // o = o * alpha + O_tile
+#pragma unroll
+      for (int c = 0; c < D; c += 32) {
+        uint32_t r[32];
+        tmem_ld_x32(t_lane + O_COL0 + c, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o_reg[c + i] = o_reg[c + i] * alpha + __uint_as_float(r[i]);
+      }
+    };
+
+    for (int j = 0; j < n_tiles; ++j) {
+      if (*abort_flag || !mbar_wait(&s_full[j & 1], (j >> 1) & 1)) {
+        if (!*abort_flag) give_up(STATUS_TIMEOUT_MBAR);
+        alive = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t s_addr = t_lane + (j & 1) * S_COLS;
+      const int key0 = j * FA_N;
+      // only tiles that touch the diagonal, the end of the keys or a bias need per-element work in pass 1
+      const bool plain = !p.bias_kind && key0 + FA_N <= p.sk && (!p.causal || key0 + FA_N - 1 <= q0 + shift);
+      // ---- pass 1: final scores (log2 units) back into TMEM, row maximum ----
+      float m_new = m_run;
+#pragma unroll 1
+      for (int c = 0; c < FA_N; c += 32) {
+        uint32_t r[32];
+        tmem_ld_x32(s_addr + c, r);
+        tmem_ld_wait();
+        if (plain) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float sv = __uint_as_float(r[i]) * p.scale_log2e;
+            r[i] = __float_as_uint(sv);
+            m_new = fmaxf(m_new, sv);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int key = key0 + c + i;
+            const bool dead = key >= p.sk || (p.causal && key > qi + shift);
+            float sv = dead ? -INFINITY : __uint_as_float(r[i]) * p.scale_log2e;
+            if (p.bias_kind && !dead) {
+              const long long bi = bias_row + (long long)key * p.bias_sk;
+              const float bv = p.bias_kind == 1 ? __ldg(bias_f + bi) : __bfloat162float(bias_h[bi]);
+              sv += bv * 1.4426950408889634f;
+            }
+            r[i] = __float_as_uint(sv);
+            m_new = fmaxf(m_new, sv);
+          }
+        }
+        tmem_st_x32(s_addr + c, r);
+      }
+      tmem_st_wait();
+      const float base = m_new == -INFINITY ? 0.f : m_new;
+      const float alpha = m_run == -INFINITY ? 0.f : exp2f(m_run - base);
+      // ---- fold the previous tile's P V into the output registers (also: P(j - 1) has been consumed) ----
+      if (j > 0) {
+        if (!mbar_wait(o_full, (j - 1) & 1)) {
+          give_up(STATUS_TIMEOUT_MBAR);
+          alive = false;
+          break;
+        }
+        tc_fence_after();
+        fold_output(alpha_prev);
+      }
+      // ---- pass 2: probabilities -> shared memory (K-major, 128-byte swizzle: chunk c of row r sits at c ^ (r & 7)) ----
+      float row_sum = 0.f;
+      uint8_t* p_row = p_s + row * 128;
+#pragma unroll 1
+      for (int c = 0; c < FA_N; c += 32) {
+        uint32_t r[32];
+        tmem_ld_x32(s_addr + c, r);
+        tmem_ld_wait();
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float p0 = exp2f(__uint_as_float(r[2 * i]) - base), p1 = exp2f(__uint_as_float(r[2 * i + 1]) - base);
+          row_sum += p0 + p1;
+          packed[i] = pack_bf16x2(p0, p1);
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int chunk = (c >> 3) + q;  // 16-byte chunk (8 keys) within the 128-key row: block chunk / 8, position chunk % 8
+          uint8_t* dst = p_row + (chunk >> 3) * FA_BLOCK_BYTES + (((chunk & 7) ^ (row & 7)) << 4);
+          *reinterpret_cast<uint4*>(dst) = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+        }
+      }
+      l_run = l_run * alpha + row_sum;
+      m_run = m_new;
+      alpha_prev = alpha;
+      tc_fence_before();
+      fence_proxy_async_smem();  // the probabilities must be visible to the tensor core's shared-memory reads
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+    }
+    if (alive && n_tiles > 0) {
+      if (mbar_wait(o_full, (n_tiles - 1) & 1)) {
+        tc_fence_after();
+        fold_output(alpha_prev);
+      } else {
+        give_up(STATUS_TIMEOUT_MBAR);
+        alive = false;
+      }
+    }
+    if (alive && qi < p.sq) {
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      bf16* orow = p.out + b * p.o_sb + (long long)qi * p.o_ss + (long long)h * p.o_sh;
+      if ((reinterpret_cast<uintptr_t>(orow) & 15) == 0) {
+#pragma unroll
+        for (int c = 0; c < D; c += 8) {
+          uint4 v;
+          v.x = pack_bf16x2(o_reg[c] * inv, o_reg[c + 1] * inv);
+          v.y = pack_bf16x2(o_reg[c + 2] * inv, o_reg[c + 3] * inv);
+          v.z = pack_bf16x2(o_reg[c + 4] * inv, o_reg[c + 5] * inv);
+          v.w = pack_bf16x2(o_reg[c + 6] * inv, o_reg[c + 7] * inv);
+          *reinterpret_cast<uint4*>(orow + c) = v;
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < D; c += 2)
+          *reinterpret_cast<uint32_t*>(orow + c) = pack_bf16x2(o_reg[c] * inv, o_reg[c + 1] * inv);
+      }
+      if (p.lse)
+        p.lse[((long long)b * p.q_heads + h) * p.sq + qi] = l_run > 0.f ? (m_run * 0.6931471805599453f + logf(l_run)) : -INFINITY;
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn fa_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// bf16 [batch][seq][heads][head_dim] view with element strides (head_dim contiguous); box = [64 head_dim][128 rows of seq].
+static int fa_tmap(CUtensorMap* map, const void* ptr, int head_dim, long long seq, int heads, int batch, long long s_seq,
+                   long long s_head, long long s_batch) {
+  EncodeTiledFn fn = fa_encode_fn();
+  if (!fn) return TPB_ERR_DRIVER;
+  cuuint64_t dims[4] = {cuuint64_t(head_dim), cuuint64_t(seq), cuuint64_t(heads), cuuint64_t(batch)};
+  // a dimension of extent 1 may come with any stride (even 0): give it a legal one
+  cuuint64_t strides[3] = {cuuint64_t(s_seq) * 2, cuuint64_t(heads > 1 ? s_head : head_dim) * 2, cuuint64_t(batch > 1 ? s_batch : head_dim) * 2};
+  if (seq == 1) strides[0] = cuuint64_t(head_dim) * 2;
+  cuuint32_t box[4] = {64, FA_N, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    fprintf(stderr, "tpb: attention tensor map rejected (%d): base %p, seq %lld, heads %d, batch %d, strides %lld / %lld / %lld\n", int(r), ptr,
+            seq, heads, batch, s_seq, s_head, s_batch);
+  return r == CUDA_SUCCESS ? TPB_OK : TPB_ERR_TMAP;
+}
+
+template <int D>
+static int fa_launch(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FaParams& p, dim3 grid, cudaStream_t stream) {
+  constexpr size_t smem = size_t(D / 64) * FA_BLOCK_BYTES * 5 + 2 * FA_BLOCK_BYTES + 1024 + 128;
+  static std::atomic<bool> configured[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return TPB_ERR_CUDA;
+  if (!configured[dev].load(std::memory_order_acquire)) {
+    if (cudaFuncSetAttribute(attn_fwd_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return TPB_ERR_CUDA;
+    configured[dev].store(true, std::memory_order_release);
+  }
+  attn_fwd_tcgen05_kernel<D><<<grid, FA_THREADS, smem, stream>>>(tq, tk, tv, p);
+  return cudaGetLastError() == cudaSuccess ? TPB_OK : TPB_ERR_CUDA;
+}
+
+}  // namespace tpb
+
+using namespace tpb;
+
+// Same contract as tpb_attn_prefill_bias (strides in elements, head_dim contiguous, bias strides of 0 broadcast) plus:
+// every stride of q / k / v must be a multiple of 8 elements and the bases 16-byte aligned (TMA), `status` is a device word
+// that receives a non-zero code if a wait inside the kernel ran out of time.
+extern "C" int tpb_attn_prefill_sm100(const void* q, const void* k, const void* v, void* out, float* lse, int batch, int sq, int sk,
+                                      int q_heads, int kv_heads, int head_dim, long long q_sb, long long q_ss, long long q_sh,
+                                      long long k_sb, long long k_ss, long long k_sh, long long v_sb, long long v_ss, long long v_sh,
+                                      long long o_sb, long long o_ss, long long o_sh, int causal, float scale, const void* bias,
+                                      int bias_dtype, long long bias_sb, long long bias_sh, long long bias_sq, long long bias_sk,
+                                      void* status, void* stream_) {
+  if (!q || !k || !v || !out || !status || batch <= 0 || sq <= 0 || sk <= 0 || q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads) return TPB_ERR_ARG;
+  if (head_dim != 64 && head_dim != 128) return TPB_ERR_SIZE;
+  if ((q_ss & 7) || (k_ss & 7) || (v_ss & 7) || (q_heads > 1 && (q_sh & 7)) || (kv_heads > 1 && ((k_sh & 7) || (v_sh & 7))) ||
+      (batch > 1 && ((q_sb & 7) || (k_sb & 7) || (v_sb & 7))) || ((uintptr_t)q & 15) || ((uintptr_t)k & 15) || ((uintptr_t)v & 15) ||
+      (o_ss & 1) || (o_sh & 1) || (o_sb & 1) || ((uintptr_t)out & 3))
+    return TPB_ERR_ALIGN;
+  if (bias && bias_dtype != 0 && bias_dtype != 1) return TPB_ERR_ARG;
+  {
+    static thread_local int bound_device = -1;  // the tensor-map encoder needs a context bound to this thread
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return TPB_ERR_CUDA;
+    if (bound_device != dev) {
+      if (cudaSetDevice(dev) != cudaSuccess) return TPB_ERR_CUDA;
+      bound_device = dev;
+    }
+  }
+  CUtensorMap tq, tk, tv;
+  int rc = fa_tmap(&tq, q, head_dim, sq, q_heads, batch, q_ss, q_sh, q_sb);
+  if (rc == TPB_OK) rc = fa_tmap(&tk, k, head_dim, sk, kv_heads, batch, k_ss, k_sh, k_sb);
+  if (rc == TPB_OK) rc = fa_tmap(&tv, v, head_dim, sk, kv_heads, batch, v_ss, v_sh, v_sb);
+  if (rc != TPB_OK) return rc;
+  FaParams p;
+  memset(&p, 0, sizeof(p));
+  p.sq = sq; p.sk = sk; p.q_heads = q_heads; p.kv_heads = kv_heads; p.causal = causal;
+  p.scale_log2e = scale * 1.4426950408889634f;
+  p.out = static_cast<bf16*>(out);
+  p.o_sb = o_sb; p.o_ss = o_ss; p.o_sh = o_sh;
+  p.lse = lse;
+  p.bias = bias;
+  p.bias_kind = !bias ? 0 : (bias_dtype == 1 ? 1 : 2);
+  p.bias_sb = bias_sb; p.bias_sh = bias_sh; p.bias_sq = bias_sq; p.bias_sk = bias_sk;
+  p.status = static_cast<uint32_t*>(status);
+  dim3 grid((sq + FA_M - 1) / FA_M, q_heads, batch);
+  cudaStream_t s = static_cast<cudaStream_t>(stream_);
+  return head_dim == 128 ? fa_launch<128>(tq, tk, tv, p, grid, s) : fa_launch<64>(tq, tk, tv, p, grid, s);
+}

@@ -117,10 +117,6 @@ template <> __device__ __forceinline__ uint4 multimem_ld_reduce<float>(const voi
                : "=f"(f.x), "=f"(f.y), "=f"(f.z), "=f"(f.w) : "l"(mc_addr) : "memory");
   return make_uint4(__float_as_uint(f.x), __float_as_uint(f.y), __float_as_uint(f.z), __float_as_uint(f.w));
 }
-__device__ __forceinline__ void multimem_st(void* mc_addr, const uint4& v) {
-  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc_addr), "f"(__uint_as_float(v.x)),
-               "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w)) : "memory");
-}
 
 template <typename T>
 __device__ __forceinline__ uint4 reduce_packet(const CommParams& p, long long packet) {

@@ -96,10 +96,12 @@ struct GemmParams {
   const __nv_bfloat16* ag_src;                // local slice
   long long ag_src_ld, ag_dst_ld;
   __nv_bfloat16* ag_dst[MAX_WORLD];           // every rank's gathered buffer [rows, ag_world * ag_cols]
+  __nv_bfloat16* ag_mc_dst;                   // multicast view of the gathered buffers (null: one peer store per rank)
   uint32_t* ag_flags[MAX_WORLD];              // every rank's arrival words [ag_world], indexed by source rank
   uint32_t* ag_push_counter;                  // local: CTAs done pushing (self re-arming)
   int stream_k;                   // 1: every CTA owns one contiguous range of (tile, k-block) units (see WorkIter)
   uint64_t wait_ns;               // wall-time bound of every wait inside the kernel
+  size_t out_elems;               // extent of `out` in elements (checked before every store in a -DTPB_BOUNDS build)
   // MN-major operands (normal orientation only): the operand is stored [K rows][MN columns] in memory, i.e. it is the
   // transpose of what the K-major path expects.  Lets the backward GEMMs (dX = dY W, dW = dY^T X) read W, dY and X as
   // they lie in memory, without a transpose kernel in front.
@@ -305,9 +307,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       const long long r = i / vec_per_row;
       const int c = int(i % vec_per_row) * 8;
       const uint4 val = *reinterpret_cast<const uint4*>(p.ag_src + r * p.ag_src_ld + c);
+      if (p.ag_mc_dst) {
+        // one store, replicated to every rank by the NVSwitch: this GPU sends its slice once instead of once per peer
+        multimem_st(p.ag_mc_dst + r * p.ag_dst_ld + p.ag_rank * p.ag_cols + c, val);
+      } else {
 #pragma unroll
-      for (int d = 0; d < MAX_WORLD; ++d)
-        if (d < p.ag_world) *reinterpret_cast<uint4*>(p.ag_dst[d] + r * p.ag_dst_ld + p.ag_rank * p.ag_cols + c) = val;
+        for (int d = 0; d < MAX_WORLD; ++d)
+          if (d < p.ag_world) *reinterpret_cast<uint4*>(p.ag_dst[d] + r * p.ag_dst_ld + p.ag_rank * p.ag_cols + c) = val;
+      }
     }
     __threadfence_system();
     __syncthreads();
@@ -561,6 +568,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       };
       auto store_partial = [&](float* slot, int n0, const float (&v)[16]) {
         if (!chunk_valid(n0)) return;
+        // (largest index this call touches in the slot: checked in a -DTPB_BOUNDS build, where it skips the whole chunk)
+        if (!TPB_IN_BOUNDS((p.swapped ? size_t(min(n0 + 15, p.n_extent - 1)) * p.ld_slot + m : size_t(m) * p.ld_slot + min(n0 + 15, p.n_extent - 1)) <
+                               p.slot_stride, p.status))
+          return;
         if (!p.swapped) {
           const size_t base = size_t(m) * p.ld_slot + n0;
           if (n0 + 16 <= p.n_extent && (p.ld_slot & 3) == 0) {
@@ -636,12 +647,15 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           o0.z = pack_bf16x2(o[4], o[5]);   o0.w = pack_bf16x2(o[6], o[7]);
           o1.x = pack_bf16x2(o[8], o[9]);   o1.y = pack_bf16x2(o[10], o[11]);
           o1.z = pack_bf16x2(o[12], o[13]); o1.w = pack_bf16x2(o[14], o[15]);
-          uint4* op = reinterpret_cast<uint4*>(p.out + base);
-          op[0] = o0;
-          op[1] = o1;
+          if (TPB_IN_BOUNDS(base + 16 <= p.out_elems, p.status)) {
+            uint4* op = reinterpret_cast<uint4*>(p.out + base);
+            op[0] = o0;
+            op[1] = o1;
+          }
         } else {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) p.out[base + j] = __float2bfloat16(o[j]);
+          for (int j = 0; j < 16; ++j)
+            if (TPB_IN_BOUNDS(base + j < p.out_elems, p.status)) p.out[base + j] = __float2bfloat16(o[j]);
         }
       };
       auto finalize = [&](int n0, float (&v)[16]) {  // bias, activation, residual, bf16 store
@@ -664,7 +678,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             if (hot_act) x = apply_act_call(x, hot_act);
             if (hot_residual && m_ok) x += prefetched ? res_pre[j] : __bfloat162float(hot_residual[idx]);
             const float up = __shfl_down_sync(0xffffffffu, x, 1);
-            if (m_ok) {
+            if (m_ok && TPB_IN_BOUNDS(idx + (writes_pair ? 1 : 0) < p.out_elems, p.status)) {
               if (writes_pair) *reinterpret_cast<uint32_t*>(hot_out + idx) = pack_bf16x2(x, up);
               else if (!covered) hot_out[idx] = __float2bfloat16(x);
             }
@@ -683,7 +697,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             if (hot_norm && n0 + j < p.n_extent) x = x * norm_stats[2 * (n0 + j)] - norm_stats[2 * (n0 + j) + 1] * rowsum;
             x += b;
             const float partner = __shfl_xor_sync(0xffffffffu, x, 16);
-            if ((lane & 16) == 0 && n0 + j < p.n_extent)
+            if ((lane & 16) == 0 && n0 + j < p.n_extent && TPB_IN_BOUNDS(size_t(n0 + j) * p.ld_out + f_out < p.out_elems, p.status))
               p.out[size_t(n0 + j) * p.ld_out + f_out] = __float2bfloat16(x / (1.f + __expf(-x)) * partner);
           }
           return;
@@ -720,15 +734,17 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             o0.z = pack_bf16x2(v[4], v[5]);   o0.w = pack_bf16x2(v[6], v[7]);
             o1.x = pack_bf16x2(v[8], v[9]);   o1.y = pack_bf16x2(v[10], v[11]);
             o1.z = pack_bf16x2(v[12], v[13]); o1.w = pack_bf16x2(v[14], v[15]);
-            uint4* op = reinterpret_cast<uint4*>(p.out + base);
-            op[0] = o0;
-            op[1] = o1;
+            if (TPB_IN_BOUNDS(base + 16 <= p.out_elems, p.status)) {
+              uint4* op = reinterpret_cast<uint4*>(p.out + base);
+              op[0] = o0;
+              op[1] = o1;
+            }
           } else {
             for (int j = 0; j < 16 && n0 + j < p.n_extent; ++j) {
               float x = v[j] + (p.bias ? p.bias_scale * __bfloat162float(p.bias[n0 + j]) : 0.f);
               if (p.act) x = apply_act_call(x, p.act);
               if (p.residual) x += __bfloat162float(p.residual[base + j]);
-              p.out[base + j] = __float2bfloat16(x);
+              if (TPB_IN_BOUNDS(base + j < p.out_elems, p.status)) p.out[base + j] = __float2bfloat16(x);
             }
           }
         }
@@ -747,6 +763,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
 #pragma unroll 1  // (rolled: small code, see read_acc)
         for (int d = 0; d < p.world; ++d) {
           uint4* dst = reinterpret_cast<uint4*>(p.slots[d] + size_t(LL_FIRST_SLOT + 2 * p.rank) * p.slot_stride) + ll_row + size_t(n0 >> 2) * BM;
+          if (!TPB_IN_BOUNDS(ll_row + size_t((n0 >> 2) + 3) * BM < (p.slot_stride >> 1), p.status)) break;
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             if (n0 + 4 * q >= p.n_extent) break;
@@ -974,7 +991,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
               float x = o[j] + (p.bias ? p.bias_scale * __bfloat162float(p.bias[f + j]) : 0.f);
               if (p.act) x = apply_act_call(x, p.act);
               if (p.residual) x += __bfloat162float(p.residual[idx + j]);
-              p.out[idx + j] = __float2bfloat16(x);
+              if (TPB_IN_BOUNDS(idx + j < p.out_elems, p.status)) p.out[idx + j] = __float2bfloat16(x);
             }
           }
         }
@@ -1089,6 +1106,13 @@ extern "C" int tpb_gemm_debug(int stages, int skip_mma) {
   return TPB_OK;
 }
 // Thresholds of the automatic split-K of few-tile weight-streaming GEMMs (KiB of weights per tile; <= 0 keeps a value).
+extern "C" int tpb_bounds_checked(void) {
+#ifdef TPB_BOUNDS
+  return 1;
+#else
+  return 0;
+#endif
+}
 extern "C" int tpb_gemm_tune_split(int min_tile_kb, int target_kb) {
   if (min_tile_kb > 0) g_split_min_kb = min_tile_kb;
   if (target_kb > 0) g_split_target_kb = target_kb;
@@ -1128,6 +1152,19 @@ extern "C" int tpb_gemm_trace_read(unsigned long long* out32) {
 extern "C" int tpb_gemm_trace(int) { return TPB_ERR_ARG; }
 extern "C" int tpb_gemm_trace_read(unsigned long long*) { return TPB_ERR_ARG; }
 #endif
+
+// Loads every GEMM kernel on the current device.  With lazy module loading the first launch of a kernel may have to
+// synchronise; host threads that each drive one GPU of a process call this before their kernels start waiting for
+// one another.
+extern "C" int tpb_gemm_preload(void) {
+  cudaFuncAttributes attr;
+  cudaError_t e = cudaSuccess;
+#define LOAD(BN, KBOX, NACC) if (e == cudaSuccess) e = cudaFuncGetAttributes(&attr, gemm_bf16_tcgen05_kernel<BN, KBOX, NACC>)
+  LOAD(16, 1, 8); LOAD(16, 2, 8); LOAD(16, 4, 8); LOAD(32, 1, 8); LOAD(32, 2, 8); LOAD(32, 4, 8);
+  LOAD(64, 1, 2); LOAD(128, 1, 1); LOAD(256, 1, 1);
+#undef LOAD
+  return e == cudaSuccess ? TPB_OK : TPB_ERR_CUDA;
+}
 
 // Plan of a linear layer out[tokens, features] = x[tokens, K] @ w[features, K]^T.
 // force_splits > 0 fixes the split-K factor; force_kbox > 0 fixes the k-blocks per stage (1, 2 or 4).
@@ -1282,6 +1319,7 @@ static int gemm_impl(const void* x, const void* w, void* out, const void* bias, 
   p.kb_per_split = plan->kb_per_split;
   p.stream_k = plan->stream_k;
   p.wait_ns = (opts && opts->wait_seconds > 0) ? uint64_t(opts->wait_seconds * 1e9) : g_wait_ns;
+  p.out_elems = (opts && opts->out_elems > 0) ? opts->out_elems : size_t(tokens - 1) * size_t(ld_out) + size_t(act == 5 ? features / 2 : features);
   p.a_mn = x_mn ? 1 : 0;  // (MN-major operands only exist in the normal orientation: A = tokens, B = features)
   p.b_mn = w_mn ? 1 : 0;
   if (opts && opts->norm_mode) {
@@ -1347,6 +1385,7 @@ static int gemm_impl(const void* x, const void* w, void* out, const void* bias, 
       p.ag_flags[d] = static_cast<uint32_t*>(ag->flags[d]);
     }
     p.ag_push_counter = static_cast<uint32_t*>(ag->push_counter);
+    p.ag_mc_dst = static_cast<__nv_bfloat16*>(ag->mc_gathered);
   }
 
   const void* a_ptr = plan->swapped ? w : x;

@@ -60,6 +60,8 @@ typedef struct {
   void* flags[TPB_MAX_WORLD];         // every rank's arrival words, uint32 [world], indexed by source rank
   void* push_counter;                 // local uint32, zero-initialised
   unsigned epoch;                     // number of fused all-gather calls issued on these flags, this one included
+  void* mc_gathered;                  // multicast (NVLS) view of the gathered buffers, or null: the slice is then pushed with
+                                      // one plain store per peer instead of one multimem.st
 } tpb_allgather_ctx_t;
 
 // Options of tpb_gemm_bf16_ex.
@@ -76,7 +78,12 @@ typedef struct {
   int norm_k;                // columns of norm_x; <= 0: k
   const float* norm_rowsum;  // LayerNorm: fp32 [features], sum over k of w'[f, k]; the caller folds W beta into the bias
   double wait_seconds;       // bound of the waits for peer GPUs; <= 0: the library default (tpb_set_wait_limit)
+  size_t out_elems;          // extent of `out` in elements, for the index checks of a -DTPB_BOUNDS build; 0: derived from the shape
 } tpb_gemm_opts_t;
+
+// 1 if this library was built with -DTPB_BOUNDS (kernels check their store indices and report STATUS_BAD_ARG = 3 in the
+// status word instead of touching memory outside the extents they were given).
+int tpb_bounds_checked(void);
 
 int tpb_gemm_plan(int tokens, int features, int k, int world, int force_splits, int force_kbox,
                   tpb_gemm_plan_t* plan);

@@ -68,7 +68,8 @@ LIB.tpb_mc_unbind.argtypes = [_ull, c_int, _size_t]
 
 class AllGatherCtx(ctypes.Structure):
     _fields_ = [("world", c_int), ("rank", c_int), ("local", c_void_p), ("local_ld", c_int), ("cols_local", c_int),
-                ("gathered", c_void_p * 8), ("flags", c_void_p * 8), ("push_counter", c_void_p), ("epoch", ctypes.c_uint)]
+                ("gathered", c_void_p * 8), ("flags", c_void_p * 8), ("push_counter", c_void_p), ("epoch", ctypes.c_uint),
+                ("mc_gathered", c_void_p)]
 
 
 LIB.tpb_gemm_allgather_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -192,7 +193,7 @@ class RankComm:
     # -- fused all-gather + GEMM ------------------------------------------------------------------
 
     @traced("tpb.allgather_gemm")
-    def allgather_gemm(self, x_local: torch.Tensor, weight: torch.Tensor, bias=None, act=None, out=None):
+    def allgather_gemm(self, x_local: torch.Tensor, weight: torch.Tensor, bias=None, act=None, out=None, force_peer_stores: bool = False):
         """``concat_over_ranks(x_local, dim=1) @ weight.T`` in ONE kernel: every rank pushes its column slice
         ``x_local [tokens, k / world]`` into all peers' gathered buffers from the kernel's prologue, and the GEMM
         main loop consumes the k-blocks of a slice as soon as that slice has arrived (own slice first), so the
@@ -219,6 +220,8 @@ class RankComm:
             ctx.flags[r] = self.base[r] + self.layout.off_ag_flags + region * MAX_WORLD * 4
         ctx.push_counter = self.ag_push_counter.data_ptr()
         ctx.epoch = self._ag_calls[region]
+        if self.mc_base and self.world >= 4 and not force_peer_stores:  # (2 ranks: a peer store moves the same bytes)
+            ctx.mc_gathered = self.mc_base + self.layout.off_gather + region * _align(self.layout.gather_bytes)
         if out is None:
             out = torch.empty(tokens, features, dtype=torch.bfloat16, device=x_local.device)
         rctx = self._ctxs[0]
@@ -837,8 +840,14 @@ class _MultiRankAllGather(torch.autograd.Function):
 
 
 class ThreadDeviceAllReduce:
-    """``"sum"`` for the threaded mode on CUDA: ranks meet at a host rendezvous, then the authoritative thread
-    launches the device all-reduce for every rank on that rank's stream (no NCCL, no host-side reduction)."""
+    """``"sum"`` for the threaded mode on CUDA.
+
+    Without gradients (inference) every rank thread launches its own all-reduce kernel on its own GPU and moves on:
+    the kernels meet on the GPUs through flags in the shared symmetric heaps (bounded waits), the host threads never
+    wait for each other - the reference puts two host barriers around every collective
+    (``src/tensor_parallel/communications.py:34-52``).  With gradients the ranks still meet once on the host, because
+    the backward pass is driven by ONE autograd graph that spans all devices: the authoritative thread then launches the
+    kernel of every rank from one autograd node (no NCCL, no host-side reduction)."""
 
     def __init__(self, group, comms, fallback):
         from tensor_parallel_b200.parallel.collectives import CollectiveOperation
@@ -849,6 +858,11 @@ class ThreadDeviceAllReduce:
     def __call__(self, x: torch.Tensor, rank: int):
         if not x.is_cuda or x.dtype not in (torch.bfloat16, torch.float32) or x.numel() * x.element_size() > self.comms[0].layout.staging_bytes:
             return self.fallback(x, rank)
+        if not (torch.is_grad_enabled() and x.requires_grad):
+            comm = self.comms[rank]
+            comm.poll_status()
+            with torch.cuda.device(comm.device):
+                return comm.all_reduce(x.contiguous()).clone()
         return self._op(x, rank)
 
 
@@ -858,16 +872,27 @@ class ThreadDeviceAllGather:
 
         self.comms, self.dim, self.fallback = comms, dim, fallback
         self._shapes = Rendezvous(group)
+        self._even: List[Dict[tuple, bool]] = [dict() for _ in comms]  # per rank: (shape, dtype, device kind) -> all ranks alike
         self._op = CollectiveOperation(len(comms), lambda *xs: _MultiRankAllGather.apply(comms, self.dim % xs[0].ndim, *xs), group=group)
 
     def __call__(self, x: torch.Tensor, rank: int):
-        shapes = self._shapes.exchange(rank, (tuple(x.shape), x.dtype, x.is_cuda))
+        key = (tuple(x.shape), x.dtype, x.is_cuda)
+        even = self._even[rank].get(key)
+        if even is None:  # the ranks compare shapes on the host once per shape; later calls go straight to the GPU
+            shapes = self._shapes.exchange(rank, key)
+            even = self._even[rank][key] = len(set(shapes)) == 1
         per = 8 if x.dtype == torch.bfloat16 else 4
         world = len(self.comms)
-        ok = (len(set(shapes)) == 1 and x.is_cuda and x.dtype in (torch.bfloat16, torch.float32) and x.numel() % per == 0
+        ok = (even and x.is_cuda and x.dtype in (torch.bfloat16, torch.float32) and x.numel() % per == 0
               and world * x.numel() * x.element_size() <= self.comms[0].layout.staging_bytes)
         if not ok:
             return self.fallback(x, rank)
+        if not (torch.is_grad_enabled() and x.requires_grad):
+            comm = self.comms[rank]
+            comm.poll_status()
+            with torch.cuda.device(comm.device):
+                stacked = comm.all_gather(x.contiguous())
+                return torch.cat(list(stacked.unbind(0)), dim=self.dim % x.ndim)
         return self._op(x, rank)
 
 

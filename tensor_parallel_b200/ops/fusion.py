@@ -80,6 +80,39 @@ def _fused_row_parallel_forward(linear: nn.Linear, comm, process_group=None):
     return forward
 
 
+def _fused_row_parallel_forward_threaded(linear: nn.Linear, comm, rule_sum, rank: int):
+    """Single-process mode (one shard per GPU, one host thread per rank).  Without gradients the linear runs the fused
+    GEMM + all-reduce kernel on this rank's symmetric heap - the rank threads never meet on the host.  With gradients it
+    keeps the rule's own ``"sum"`` (whose autograd node spans all devices, as one backward pass has to)."""
+    plain_forward = linear.forward
+
+    def forward(x):
+        fused = (not (torch.is_grad_enabled() and (x.requires_grad or linear.weight.requires_grad)) and x.is_cuda
+                 and x.dtype == torch.bfloat16 and linear.weight.dtype == torch.bfloat16 and linear.weight.shape[1] % 8 == 0)
+        if not fused:
+            return rule_sum(plain_forward(x), rank)
+        from tensor_parallel_b200.ops import native
+
+        x2d = x.reshape(-1, x.shape[-1])
+        tokens, features = x2d.shape[0], linear.weight.shape[0]
+        comm.poll_status()
+        with torch.cuda.device(comm.device):
+            if tokens <= 64 and comm.fits_fused(tokens, features, linear.weight.shape[1]):
+                out = comm.gemm_allreduce(x2d, linear.weight, bias=linear.bias, bias_scale=float(comm.world))
+            else:
+                if tokens * features <= comm._capacity(torch.bfloat16, 1, 1):
+                    staged = comm.staging_view("in", (tokens, features), torch.bfloat16)
+                    native.gemm_nt(x2d, linear.weight, out=staged)
+                    out = comm.all_reduce(staged).clone()
+                else:
+                    out = comm.all_reduce(native.gemm_nt(x2d, linear.weight))
+                if linear.bias is not None:
+                    out += linear.bias * comm.world
+        return out.view(*x.shape[:-1], features)
+
+    return forward
+
+
 def _row_parallel_linears(wrapped: nn.Module, prefix: str, config) -> list:
     found = []
     for name, sub in wrapped.named_modules():
@@ -94,11 +127,50 @@ def _row_parallel_linears(wrapped: nn.Module, prefix: str, config) -> list:
     return found
 
 
+def _rewrite_threaded(tp_module, comms, config) -> int:
+    """Row-parallel linear + ``"sum"`` sites of every shard of a single-process model (see
+    :func:`_fused_row_parallel_forward_threaded`).  Returns the number of sites per shard."""
+    from tensor_parallel_b200.ops.comm import ThreadDeviceAllReduce
+
+    from tensor_parallel_b200.ops import native
+
+    per_shard = []
+    for rank, (shard, comm) in enumerate(zip(tp_module.module_shards, comms)):
+        with torch.cuda.device(comm.device):  # every kernel the rank threads may launch concurrently is loaded up front
+            native.check(native.LIB.tpb_gemm_preload(), "tpb_gemm_preload")
+            native.check(native.LIB.tpb_comm_preload(), "tpb_comm_preload")
+        sites = 0
+        original_names = {}
+        for name, sub in shard.named_modules():
+            original_names[id(sub)] = name.replace("tp_wrapped_module.", "").replace(".tp_wrapped_module", "")
+        for name, sub in list(shard.named_modules()):
+            if not isinstance(sub, TensorParallelWrapper):
+                continue
+            action = sub.output_actions.get(0)
+            if not isinstance(action, ThreadDeviceAllReduce):
+                continue
+            inner = sub.__dict__["tp_wrapped_module"]
+            linears = _row_parallel_linears(inner, original_names[id(inner)], config)
+            if len(linears) != 1 or getattr(linears[0], "_tp_fused_row_parallel", False):
+                continue
+            linears[0].forward = _fused_row_parallel_forward_threaded(linears[0], comm, action, rank)
+            linears[0]._tp_fused_row_parallel = True
+            sub.output_actions = {k: v for k, v in sub.output_actions.items() if k != 0}
+            sites += 1
+        per_shard.append(sites)
+    if per_shard and per_shard[0]:
+        logger.info("fusion planner rewrote %d site(s) per shard (single-process mode)", per_shard[0])
+    return per_shard[0] if per_shard else 0
+
+
 def rewrite(tp_module) -> int:
     """Apply the plan to ``tp_module`` (a ``DistributedTensorParallel``); returns the number of rewritten sites."""
     backend = getattr(tp_module, "_device_backend", None)
     comm = getattr(backend, "comm", None)
     config = getattr(tp_module, "_live_config", None)
+    comms = getattr(backend, "comms", None)
+    if config is not None and comms is not None and len(comms) == len(tp_module.module_shards) > 1:
+        return _rewrite_threaded(tp_module, comms, config)
     if comm is None or config is None or len(tp_module.module_shards) != 1:
         return 0
     from tensor_parallel_b200.ops.comm import DeviceAllReduce

@@ -50,7 +50,8 @@ class ReduceCtx(ctypes.Structure):
 
 class GemmOpts(ctypes.Structure):
     _fields_ = [("x_mn", c_int), ("w_mn", c_int), ("norm_mode", c_int), ("norm_eps", c_float), ("norm_x", c_void_p),
-                ("norm_ld", c_ll), ("norm_k", c_int), ("norm_rowsum", c_void_p), ("wait_seconds", ctypes.c_double)]
+                ("norm_ld", c_ll), ("norm_k", c_int), ("norm_rowsum", c_void_p), ("wait_seconds", ctypes.c_double),
+                ("out_elems", c_size_t)]
 
 
 def device_wait_seconds() -> float:
@@ -198,14 +199,17 @@ def gemm_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
 
 def gemm_nt(x2d: torch.Tensor, w: torch.Tensor, bias=None, residual=None, act=None, out=None, force_splits: int = 0,
             reduce_ctx: Optional[ReduceCtx] = None, world: int = 1, bias_scale: float = 1.0, force_kbox: int = 0,
-            x_t: bool = False, w_t: bool = False, norm: Optional[Tuple] = None, norm_rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+            x_t: bool = False, w_t: bool = False, norm: Optional[Tuple] = None, norm_rows: Optional[torch.Tensor] = None,
+            out_elems: int = 0) -> torch.Tensor:
     """``out[tokens, features] = act(x2d @ w.T + bias) + residual`` on the tcgen05 kernel.
 
     ``x_t`` / ``w_t``: the operand is passed transposed, ``x2d`` as ``[k, tokens]`` / ``w`` as ``[k, features]`` (row
     major), and is read as it lies in memory (MN-major tensor-core operand) - what the backward GEMMs of a linear
     layer need.  ``norm = (mode, eps, rowsum)`` folds an RMSNorm (``mode`` 1) or LayerNorm (2) of the rows of ``x2d``
     into the kernel (at most 64 tokens): ``w`` must already be multiplied by the norm weight along k.  ``norm_rows``
-    ``[tokens, n]`` are the rows the statistics are taken over when ``x2d`` is only a column slice of them."""
+    ``[tokens, n]`` are the rows the statistics are taken over when ``x2d`` is only a column slice of them.
+    ``out_elems`` (a library built with ``-DTPB_BOUNDS`` only): extent of ``out`` that the kernel checks its store
+    indices against; 0 derives it from the shape."""
     global launch_count
     if x_t:
         k, tokens = x2d.shape
@@ -223,9 +227,9 @@ def gemm_nt(x2d: torch.Tensor, w: torch.Tensor, bias=None, residual=None, act=No
             state.ensure_slots(tokens * (features if act == "swiglu16" else out.stride(0)))
         ctx = state.ctx
     opts = None
-    if x_t or w_t or norm is not None:
+    if x_t or w_t or norm is not None or out_elems:
         opts = GemmOpts()
-        opts.x_mn, opts.w_mn = int(x_t), int(w_t)
+        opts.x_mn, opts.w_mn, opts.out_elems = int(x_t), int(w_t), int(out_elems)
         if norm is not None:
             mode, eps, rowsum = norm
             opts.norm_mode, opts.norm_eps = int(mode), float(eps)
@@ -497,7 +501,9 @@ def geglu(gate, up, approximate="tanh"):
 
 LIB.tpb_attn_prefill.argtypes = [c_void_p] * 5 + [c_int] * 6 + [c_ll] * 12 + [c_int, c_float, c_void_p]
 LIB.tpb_attn_prefill_bias.argtypes = [c_void_p] * 5 + [c_int] * 6 + [c_ll] * 12 + [c_int, c_float, c_void_p, c_int] + [c_ll] * 4 + [c_void_p]
+LIB.tpb_attn_prefill_sm100.argtypes = [c_void_p] * 5 + [c_int] * 6 + [c_ll] * 12 + [c_int, c_float, c_void_p, c_int] + [c_ll] * 4 + [c_void_p, c_void_p]
 LIB.tpb_attn_decode.argtypes = [c_void_p] * 7 + [c_int] * 7 + [c_float, c_void_p]
+_LEGACY_ATTENTION = bool(os.environ.get("TPB_ATTN_LEGACY"))  # the mma.sync forward kernel instead of the tcgen05 one
 LIB.tpb_qkv_rope_append.argtypes = [c_void_p] * 7 + [c_int] * 6 + [c_float, c_int, c_int, c_ll, c_ll, c_ll, c_void_p]
 
 
@@ -506,9 +512,8 @@ def attention_supported(q, k, v, bias) -> bool:
         return False
     if bias is None:
         return True
-    # additive bias: forward only (the backward kernels do not produce a bias gradient and do not re-add the bias)
-    needs_grad = torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad or bias.requires_grad)
-    return (not needs_grad and bias.is_cuda and bias.dtype in (torch.bfloat16, torch.float32) and bias.ndim <= 4
+    # additive score bias (relative positions, ALiBi, padding masks): forward and backward, bias gradient included
+    return (bias.is_cuda and bias.dtype in (torch.bfloat16, torch.float32) and bias.ndim <= 4
             and _broadcastable(bias.shape, (q.shape[0], q.shape[2], q.shape[1], k.shape[1])))
 
 
@@ -534,7 +539,17 @@ def attention_forward(q, k, v, causal, scale, want_lse=False, bias=None, out=Non
         out = torch.empty(b, sq, hq, d, dtype=q.dtype, device=q.device)
     lse = torch.empty(b, hq, sq, dtype=torch.float32, device=q.device) if want_lse else None
     scale = 1.0 / math.sqrt(d) if scale is None else scale
-    if bias is None:
+    if not _LEGACY_ATTENTION:
+        # tcgen05 / TMEM kernel: Q, K, V tiles by TMA straight from the strided views, scores and P V on the tensor cores
+        bias4 = None if bias is None else bias.reshape((1,) * (4 - bias.ndim) + tuple(bias.shape))
+        strides = [0, 0, 0, 0] if bias4 is None else [0 if bias4.shape[i] == 1 else bias4.stride(i) for i in range(4)]
+        status = device_state(q.device).status
+        check(LIB.tpb_attn_prefill_sm100(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(lse), b, sq, sk, hq, hkv, d,
+                                         q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
+                                         v.stride(0), v.stride(1), v.stride(2), out.stride(0), out.stride(1), out.stride(2),
+                                         int(causal), scale, _ptr(bias4), 1 if (bias4 is not None and bias4.dtype == torch.float32) else 0,
+                                         strides[0], strides[1], strides[2], strides[3], _ptr(status), _stream()), "tpb_attn_prefill_sm100")
+    elif bias is None:
         check(LIB.tpb_attn_prefill(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(lse), b, sq, sk, hq, hkv, d,
                                    q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
                                    v.stride(0), v.stride(1), v.stride(2), out.stride(0), out.stride(1), out.stride(2),
@@ -552,10 +567,18 @@ def attention_forward(q, k, v, causal, scale, want_lse=False, bias=None, out=Non
 
 
 LIB.tpb_attn_backward.argtypes = [c_void_p] * 10 + [c_int] * 6 + [c_ll] * 21 + [c_int, c_float, c_void_p]
+LIB.tpb_attn_backward_bias.argtypes = [c_void_p] * 10 + [c_int] * 6 + [c_ll] * 21 + [c_int, c_float, c_void_p, c_int] + [c_ll] * 4 + [c_void_p, c_void_p]
 
 
-def attention_backward(q, k, v, out, dout, lse, causal, scale):
-    """Gradients of :func:`attention_forward` (scores are recomputed tile by tile)."""
+def _bias_view(bias):
+    """``bias`` as a 4-D tensor over (batch, head, query, key) and its element strides with broadcast dimensions at 0."""
+    bias4 = bias.reshape((1,) * (4 - bias.ndim) + tuple(bias.shape))
+    return bias4, [0 if bias4.shape[i] == 1 else bias4.stride(i) for i in range(4)]
+
+
+def attention_backward(q, k, v, out, dout, lse, causal, scale, bias=None, want_dbias=False):
+    """Gradients of :func:`attention_forward` (scores are recomputed tile by tile).  With ``bias`` the scores are
+    re-biased; ``want_dbias`` also returns the gradient of the bias (fp32, in the bias' own shape)."""
     global launch_count
     q, k, v, dout = (t if _strided_ok(t) else t.contiguous() for t in (q, k, v, dout))
     b, sq, hq, d = q.shape
@@ -565,34 +588,51 @@ def attention_backward(q, k, v, out, dout, lse, causal, scale):
     dv = torch.empty(b, sk, hkv, d, dtype=q.dtype, device=q.device)
     delta = torch.empty(b, hq, sq, dtype=torch.float32, device=q.device)
     scale = 1.0 / math.sqrt(d) if scale is None else scale
-    check(LIB.tpb_attn_backward(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(dout), _ptr(lse), _ptr(delta), _ptr(dq), _ptr(dk), _ptr(dv),
-                                b, sq, sk, hq, hkv, d,
-                                q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
-                                v.stride(0), v.stride(1), v.stride(2), out.stride(0), out.stride(1), out.stride(2),
-                                dout.stride(0), dout.stride(1), dout.stride(2), dq.stride(0), dq.stride(1), dq.stride(2),
-                                dk.stride(0), dk.stride(1), dk.stride(2), int(causal), scale, _stream()), "tpb_attn_backward")
+    bias4, bstr, dbias = None, [0, 0, 0, 0], None
+    if bias is not None:
+        bias4, bstr = _bias_view(bias)
+        if want_dbias:  # dense fp32 buffer in the bias' shape: the kernel addresses it with the bias' broadcast pattern
+            dbias = torch.zeros(bias4.shape, dtype=torch.float32, device=q.device)
+            dstr = [0 if dbias.shape[i] == 1 else dbias.stride(i) for i in range(4)]
+            if dstr != bstr:  # a non-contiguous bias view: keep one addressing for both
+                bias4 = bias4.contiguous()
+                bstr = dstr
+    check(LIB.tpb_attn_backward_bias(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(dout), _ptr(lse), _ptr(delta), _ptr(dq), _ptr(dk), _ptr(dv),
+                                     b, sq, sk, hq, hkv, d,
+                                     q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
+                                     v.stride(0), v.stride(1), v.stride(2), out.stride(0), out.stride(1), out.stride(2),
+                                     dout.stride(0), dout.stride(1), dout.stride(2), dq.stride(0), dq.stride(1), dq.stride(2),
+                                     dk.stride(0), dk.stride(1), dk.stride(2), int(causal), scale, _ptr(bias4),
+                                     1 if (bias4 is not None and bias4.dtype == torch.float32) else 0, bstr[0], bstr[1], bstr[2], bstr[3],
+                                     _ptr(dbias), _stream()), "tpb_attn_backward")
     launch_count += 3
+    if want_dbias:
+        return dq, dk, dv, dbias.reshape(bias.shape)
     return dq, dk, dv
 
 
 class _AttentionFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, causal, scale):
-        out, lse = attention_forward(q, k, v, causal, scale, want_lse=True)
-        ctx.save_for_backward(q, k, v, out, lse)
-        ctx.causal, ctx.scale = causal, scale
+    def forward(ctx, q, k, v, causal, scale, bias):
+        out, lse = attention_forward(q, k, v, causal, scale, want_lse=True, bias=bias)
+        ctx.save_for_backward(q, k, v, out, lse, *([bias] if bias is not None else []))
+        ctx.causal, ctx.scale, ctx.has_bias = causal, scale, bias is not None
         return out
 
     @staticmethod
     def backward(ctx, grad):
-        q, k, v, out, lse = ctx.saved_tensors
-        dq, dk, dv = attention_backward(q, k, v, out, grad.to(q.dtype), lse, ctx.causal, ctx.scale)
-        return dq, dk, dv, None, None
+        q, k, v, out, lse = ctx.saved_tensors[:5]
+        bias = ctx.saved_tensors[5] if ctx.has_bias else None
+        want_dbias = ctx.has_bias and ctx.needs_input_grad[5]
+        grads = attention_backward(q, k, v, out, grad.to(q.dtype), lse, ctx.causal, ctx.scale, bias=bias, want_dbias=want_dbias)
+        dbias = grads[3].to(bias.dtype) if want_dbias else None
+        return grads[0], grads[1], grads[2], None, None, dbias
 
 
 def attention(q, k, v, causal, bias=None, scale=None):
-    if bias is None and torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad):
-        return _AttentionFn.apply(q, k, v, bool(causal), scale)
+    needs_grad = torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad or (bias is not None and bias.requires_grad))
+    if needs_grad:
+        return _AttentionFn.apply(q, k, v, bool(causal), scale, bias)
     return attention_forward(q, k, v, causal, scale, bias=bias)[0]
 
 

@@ -222,6 +222,8 @@ class ThreadGatherKV(CollectiveBase):
     def __call__(self, kv, rank: int):
         from tensor_parallel_b200.parallel.aux import gather_kv
 
+        if kv is None:  # no cache was asked for: every rank sees None at this site, nothing to zip, no need to meet
+            return None
         everyone = self._rv.exchange(rank, kv)
         return gather_kv(*everyone, world_size=self.group.world_size)[rank]
 

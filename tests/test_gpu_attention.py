@@ -186,3 +186,44 @@ def test_fused_decode_step_matches_separate_kernels(hq, hkv, d, splits, angle_ta
         torch.testing.assert_close(kc2, kc)
         torch.testing.assert_close(vc2, vc)
         pos += 1
+
+
+BIAS_BWD_CASES = [
+    # b, sq, sk, hq, hkv, d, causal, bias shape
+    (2, 96, 96, 4, 4, 64, False, (1, 4, 96, 96)),     # T5 relative-position bias: broadcast over the batch, trainable
+    (2, 130, 130, 4, 2, 64, True, (1, 4, 1, 130)),    # ALiBi-like: broadcast over batch and queries
+    (3, 64, 200, 2, 2, 128, False, (3, 1, 1, 200)),   # padding mask per sequence (with -inf entries), cross attention
+    (1, 200, 200, 4, 4, 128, True, (1, 4, 200, 200)),
+]
+
+
+@pytest.mark.parametrize("b,sq,sk,hq,hkv,d,causal,bias_shape", BIAS_BWD_CASES)
+def test_attention_backward_with_score_bias(b, sq, sk, hq, hkv, d, causal, bias_shape):
+    """Forward and backward with an additive score bias, bias gradient included, against fp32 autograd of the same math."""
+    nat = _native()
+    torch.manual_seed(9)
+    q = torch.randn(b, sq, hq, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn(b, sk, hkv, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn(b, sk, hkv, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    bias = torch.randn(bias_shape, device="cuda", dtype=torch.float32)
+    masked = bias_shape[0] == b and bias_shape[2] == 1 and b > 1
+    if masked:  # the last keys of every sequence but the first are padding
+        bias = torch.zeros(bias_shape, device="cuda")
+        for i in range(1, b):
+            bias[i, :, :, sk - 17 * i:] = float("-inf")
+    else:
+        bias.requires_grad_(True)
+    g = torch.randn(b, sq, hq, d, device="cuda", dtype=torch.bfloat16)
+    out = nat.attention(q, k, v, causal, bias=bias)
+    out.backward(g)
+    qr, kr, vr = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    br = bias.detach().clone().requires_grad_(not masked)
+    ref = OF.attention_ref(qr, kr, vr, causal, bias=br)
+    ref.backward(g.float())
+    torch.testing.assert_close(out.float(), ref.detach(), atol=3e-2, rtol=3e-2)
+    checks = [("dq", q.grad, qr.grad), ("dk", k.grad, kr.grad), ("dv", v.grad, vr.grad)]
+    if not masked:
+        checks.append(("dbias", bias.grad, br.grad))
+    for name, got, want in checks:
+        err = (got.float() - want).norm().item() / (want.norm().item() + 1e-9)
+        assert err < 0.03, (name, err)

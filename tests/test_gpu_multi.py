@@ -386,6 +386,41 @@ def test_threaded_mode_on_two_gpus():
     assert {t.device.index for t in o2.past_key_values[0][0].tensors} == {0, 1}
 
 
+def test_threaded_mode_inference_meets_on_the_gpus_only(monkeypatch):
+    """bf16 shards in one process: the planner swaps the row-parallel linears for the fused GEMM + all-reduce kernel, and a
+    forward pass without gradients never enters a host rendezvous (the reference waits at two host barriers per
+    collective, ``src/tensor_parallel/communications.py:34-52``)."""
+    sys.path.insert(0, REPO)
+    import copy
+
+    import tensor_parallel_b200 as tp
+    from tensor_parallel_b200.models.llama import LlamaConfig, LlamaForCausalLM
+    from tensor_parallel_b200.parallel import collectives
+
+    torch.manual_seed(2)
+    cfg = LlamaConfig(vocab_size=512, hidden_size=256, intermediate_size=688, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2)
+    full = LlamaForCausalLM(cfg).to(device="cuda:0", dtype=torch.bfloat16).eval()
+    ids = torch.randint(0, 512, (2, 24))
+    with torch.no_grad():
+        want = full(input_ids=ids.cuda()).logits.float().cpu()
+    wrapped = tp.tensor_parallel(copy.deepcopy(full), ["cuda:0", "cuda:1"])
+    assert wrapped.fused_sites > 0, "the planner left the row-parallel linears of the single-process mode un-fused"
+    with torch.no_grad():
+        wrapped(input_ids=ids)  # shapes are compared on the host once
+    entered = []
+    original = collectives.Rendezvous.exchange
+    monkeypatch.setattr(collectives.Rendezvous, "exchange", lambda self, rank, value: (entered.append(rank), original(self, rank, value))[1])
+    with torch.no_grad():
+        got = wrapped(input_ids=ids).logits.float().cpu()
+    assert not entered, f"{len(entered)} host rendezvous during an inference forward"
+    torch.testing.assert_close(got, want, atol=0.1, rtol=0.05)
+    for comm in wrapped._device_backend.comms:
+        torch.cuda.synchronize(comm.device)
+        comm.check_status()
+        comm.check_guards()
+
+
 def test_threaded_mode_serving_engine():
     """Single process, two GPUs: generate() runs one kernel-level engine per rank (fused GEMM + all-reduce over the shared
     symmetric heaps), all driven by the calling thread."""
