@@ -9,12 +9,14 @@
 //                              lies in memory) into a TMEM output tile; QK of tile j + 1 is issued BEFORE the wait for the
 //                              probabilities of tile j, so the tensor core works on the next scores while the softmax
 //                              warps are busy
-//   warps 2-5: softmax       - thread r owns query row r (= TMEM lane r): pass 1 reads the scores from TMEM, applies
-//                              scale / bias / masks, writes them back and takes the row maximum; then the previous tile's
-//                              P V product is folded into the fp32 output registers (o = o * alpha + O_tile: the running
-//                              output never lives in TMEM, so nothing there is ever rescaled); pass 2 exponentiates,
-//                              sums, and stores the bf16 probabilities into shared memory in the 128-byte-swizzled K-major
-//                              layout the tensor core reads.
+//   warps 2-9: softmax       - two threads per query row (= TMEM lane), one per half of the tile's 128 keys and of the
+//                              head dimension, so that every SM scheduler has two softmax warps to hide TMEM and MUFU
+//                              latency with.  Pass 1 reads the scores from TMEM, applies scale / bias / masks (tiles that
+//                              need them write the result back) and takes the row maximum, which the two halves exchange
+//                              through shared memory; then the previous tile's P V product is folded into the fp32 output
+//                              registers (o = o * alpha + O_tile: the running output never lives in TMEM, so nothing there
+//                              is ever rescaled); pass 2 exponentiates, sums, and stores the bf16 probabilities into
+//                              shared memory in the 128-byte-swizzled K-major layout the tensor core reads.
 //
 // TMEM: scores 2 x 128 columns, output tile head_dim columns (512 allocated).  Shared memory at head_dim 128:
 // Q 32 KB + 2 x (K 32 KB + V 32 KB) + P 32 KB = 192 KB.  Every mbarrier wait is bounded; on expiry the CTA records a
@@ -38,8 +40,33 @@ typedef __nv_bfloat16 bf16;
 
 constexpr int FA_M = 128;        // queries per CTA
 constexpr int FA_N = 128;        // keys per tile
-constexpr int FA_THREADS = 192;  // producer warp, MMA warp, four softmax warps
+constexpr int FA_SOFTMAX_WARPS = 8;
+constexpr int FA_THREADS = 64 + 32 * FA_SOFTMAX_WARPS;  // producer warp, MMA warp, eight softmax warps
 constexpr int FA_BLOCK_BYTES = 128 * 128;  // one [128 rows][64 elements] swizzled block
+
+__device__ __forceinline__ float ex2_approx(float x) {  // 2^x on the special-function unit; 2^-inf = 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// Two fp32 lanes per instruction (fma.rn.f32x2 / add.f32x2): the softmax warps are bound by instruction issue.
+__device__ __forceinline__ void ffma2(float& d0, float& d1, float a0, float a1, float b0, float b1, float c0, float c1) {
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d0), "=f"(d1)
+      : "f"(a0), "f"(a1), "f"(b0), "f"(b1), "f"(c0), "f"(c1));
+}
+__device__ __forceinline__ void fadd2(float& d0, float& d1, float a0, float a1, float b0, float b1) {
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "add.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d0), "=f"(d1)
+      : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
 
 struct FaParams {
   int sq, sk, q_heads, kv_heads, causal;
@@ -80,6 +107,7 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
   uint64_t* o_full = bars + 8;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
   volatile uint32_t* abort_flag = tmem_slot + 1;
+  float* row_stat = reinterpret_cast<float*>(tmem_slot + 2);  // [2 sets][2 halves][128 rows]: row maxima, at the end row sums
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qblk = gridDim.x - 1 - blockIdx.x;  // heavy (late) causal tiles first
@@ -101,7 +129,7 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
       mbar_init(&kv_empty[s], 1);
       mbar_init(&s_full[s], 1);
     }
-    mbar_init(p_full, 4);  // one arrival per softmax warp
+    mbar_init(p_full, FA_SOFTMAX_WARPS);  // one arrival per softmax warp
     mbar_init(o_full, 1);
     *abort_flag = 0;
     fence_mbar_init();
@@ -185,59 +213,64 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
     }
   } else {
     // ---------------- softmax warps ----------------
+    constexpr int HN = FA_N / 2;   // keys per thread and tile
+    constexpr int HD = D / 2;      // output columns per thread
     const int quarter = warp & 3;  // TMEM lane quarter this warp may access
+    const int half = (warp - 2) >> 2;
     const int row = quarter * 32 + lane;
     const int qi = q0 + row;
     const uint32_t t_lane = tmem_base + (uint32_t(quarter * 32) << 16);
-    float o_reg[D];
+    float o_reg[HD];
 #pragma unroll
-    for (int i = 0; i < D; ++i) o_reg[i] = 0.f;
+    for (int i = 0; i < HD; ++i) o_reg[i] = 0.f;
     float m_run = -INFINITY, l_run = 0.f, alpha_prev = 1.f;
     const float* bias_f = static_cast<const float*>(p.bias);
     const bf16* bias_h = static_cast<const bf16*>(p.bias);
     const long long bias_row = p.bias_kind ? (b * p.bias_sb + h * p.bias_sh + (long long)min(qi, p.sq - 1) * p.bias_sq) : 0;
     bool alive = true;
 
-    auto fold_output = [&](float alpha) {  // o = o * alpha + O_tile
+    // o = o * alpha + O_tile (this thread's half of the head dimension), two columns per instruction
+    auto fold_output = [&](float alpha) {
 #pragma unroll
-      for (int c = 0; c < D; c += 32) {
-        uint32_t r[32];
-        tmem_ld_x32(t_lane + O_COL0 + c, r);
+      for (int c = 0; c < HD; c += 32) {
+        uint32_t t[32];
+        tmem_ld_x32(t_lane + O_COL0 + half * HD + c, t);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) o_reg[c + i] = o_reg[c + i] * alpha + __uint_as_float(r[i]);
+        for (int i = 0; i < 32; i += 2)
+          ffma2(o_reg[c + i], o_reg[c + i + 1], o_reg[c + i], o_reg[c + i + 1], alpha, alpha, __uint_as_float(t[i]), __uint_as_float(t[i + 1]));
       }
     };
+    // The two threads of a row meet at a barrier of their own two warps.  Every softmax thread takes part in every such
+    // barrier, whatever happened before: a thread that gave up keeps arriving (with neutral values), so that nobody is
+    // left waiting.
+    auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory"); };
 
     for (int j = 0; j < n_tiles; ++j) {
-      if (*abort_flag || !mbar_wait(&s_full[j & 1], (j >> 1) & 1)) {
+      if (alive && (*abort_flag || !mbar_wait(&s_full[j & 1], (j >> 1) & 1))) {
         if (!*abort_flag) give_up(STATUS_TIMEOUT_MBAR);
         alive = false;
-        break;
       }
       tc_fence_after();
-      const uint32_t s_addr = t_lane + (j & 1) * S_COLS;
-      const int key0 = j * FA_N;
-      // only tiles that touch the diagonal, the end of the keys or a bias need per-element work in pass 1
-      const bool plain = !p.bias_kind && key0 + FA_N <= p.sk && (!p.causal || key0 + FA_N - 1 <= q0 + shift);
-      // ---- pass 1: final scores (log2 units) back into TMEM, row maximum ----
-      float m_new = m_run;
-#pragma unroll 1
-      for (int c = 0; c < FA_N; c += 32) {
-        uint32_t r[32];
-        tmem_ld_x32(s_addr + c, r);
+      const uint32_t s_addr = t_lane + (j & 1) * S_COLS + half * HN;
+      const int key0 = j * FA_N + half * HN;
+      // only tiles that touch the diagonal, the end of the keys or a bias need per-element work
+      const bool plain = !p.bias_kind && j * FA_N + FA_N <= p.sk && (!p.causal || j * FA_N + FA_N - 1 <= q0 + shift);
+      // ---- pass 1: this half's scores come out of TMEM once and stay in registers; row maximum ----
+      uint32_t r[HN];
+      float m_half = -INFINITY;
+      if (alive) {
+#pragma unroll
+        for (int c = 0; c < HN; c += 32) tmem_ld_x32(s_addr + c, *reinterpret_cast<uint32_t(*)[32]>(r + c));
         tmem_ld_wait();
         if (plain) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float sv = __uint_as_float(r[i]) * p.scale_log2e;
-            r[i] = __float_as_uint(sv);
-            m_new = fmaxf(m_new, sv);
-          }
+          for (int i = 0; i < HN; i += 2) m_half = fmax3(m_half, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+          m_half *= p.scale_log2e;  // (the scale is positive: the maximum commutes with it)
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int key = key0 + c + i;
+          for (int i = 0; i < HN; ++i) {
+            const int key = key0 + i;
             const bool dead = key >= p.sk || (p.causal && key > qi + shift);
             float sv = dead ? -INFINITY : __uint_as_float(r[i]) * p.scale_log2e;
             if (p.bias_kind && !dead) {
@@ -246,53 +279,53 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
               sv += bv * 1.4426950408889634f;
             }
             r[i] = __float_as_uint(sv);
-            m_new = fmaxf(m_new, sv);
+            m_half = fmaxf(m_half, sv);
           }
         }
-        tmem_st_x32(s_addr + c, r);
       }
-      tmem_st_wait();
+      float* stat = row_stat + (j & 1) * 2 * FA_M;  // (two sets, so that one barrier per tile is enough)
+      stat[half * FA_M + row] = m_half;
+      pair_sync();
+      const float m_new = fmax3(m_run, m_half, stat[(half ^ 1) * FA_M + row]);
       const float base = m_new == -INFINITY ? 0.f : m_new;
-      const float alpha = m_run == -INFINITY ? 0.f : exp2f(m_run - base);
+      const float alpha = m_run == -INFINITY ? 0.f : ex2_approx(m_run - base);
       // ---- fold the previous tile's P V into the output registers (also: P(j - 1) has been consumed) ----
-      if (j > 0) {
+      if (alive && j > 0) {
         if (!mbar_wait(o_full, (j - 1) & 1)) {
           give_up(STATUS_TIMEOUT_MBAR);
           alive = false;
-          break;
+        } else {
+          tc_fence_after();
+          fold_output(alpha_prev);
         }
-        tc_fence_after();
-        fold_output(alpha_prev);
       }
       // ---- pass 2: probabilities -> shared memory (K-major, 128-byte swizzle: chunk c of row r sits at c ^ (r & 7)) ----
-      float row_sum = 0.f;
-      uint8_t* p_row = p_s + row * 128;
-#pragma unroll 1
-      for (int c = 0; c < FA_N; c += 32) {
-        uint32_t r[32];
-        tmem_ld_x32(s_addr + c, r);
-        tmem_ld_wait();
-        uint32_t packed[16];
+      if (alive) {
+        float sum0 = 0.f, sum1 = 0.f;
+        uint8_t* p_row = p_s + half * FA_BLOCK_BYTES + row * 128;  // this half's 64 keys are one swizzled block
+        const float mul = plain ? p.scale_log2e : 1.f;
+        const float nbase = -base;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float p0 = exp2f(__uint_as_float(r[2 * i]) - base), p1 = exp2f(__uint_as_float(r[2 * i + 1]) - base);
-          row_sum += p0 + p1;
-          packed[i] = pack_bf16x2(p0, p1);
-        }
+        for (int c = 0; c < HN; c += 8) {  // one 16-byte chunk of eight keys
+          uint32_t packed[4];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int chunk = (c >> 3) + q;  // 16-byte chunk (8 keys) within the 128-key row: block chunk / 8, position chunk % 8
-          uint8_t* dst = p_row + (chunk >> 3) * FA_BLOCK_BYTES + (((chunk & 7) ^ (row & 7)) << 4);
-          *reinterpret_cast<uint4*>(dst) = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+          for (int i = 0; i < 4; ++i) {
+            float t0, t1;
+            ffma2(t0, t1, __uint_as_float(r[c + 2 * i]), __uint_as_float(r[c + 2 * i + 1]), mul, mul, nbase, nbase);
+            const float p0 = ex2_approx(t0), p1 = ex2_approx(t1);
+            fadd2(sum0, sum1, sum0, sum1, p0, p1);
+            packed[i] = pack_bf16x2(p0, p1);
+          }
+          *reinterpret_cast<uint4*>(p_row + ((((c >> 3)) ^ (row & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
         }
+        l_run = l_run * alpha + (sum0 + sum1);
       }
-      l_run = l_run * alpha + row_sum;
       m_run = m_new;
       alpha_prev = alpha;
       tc_fence_before();
       fence_proxy_async_smem();  // the probabilities must be visible to the tensor core's shared-memory reads
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
+      if (lane == 0 && alive) mbar_arrive(p_full);
     }
     if (alive && n_tiles > 0) {
       if (mbar_wait(o_full, (n_tiles - 1) & 1)) {
@@ -303,12 +336,17 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
         alive = false;
       }
     }
+    // the two halves of a row add up their sums
+    float* stat = row_stat + (n_tiles & 1) * 2 * FA_M;
+    stat[half * FA_M + row] = l_run;
+    pair_sync();
+    l_run += stat[(half ^ 1) * FA_M + row];
     if (alive && qi < p.sq) {
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      bf16* orow = p.out + b * p.o_sb + (long long)qi * p.o_ss + (long long)h * p.o_sh;
+      bf16* orow = p.out + b * p.o_sb + (long long)qi * p.o_ss + (long long)h * p.o_sh + half * HD;
       if ((reinterpret_cast<uintptr_t>(orow) & 15) == 0) {
 #pragma unroll
-        for (int c = 0; c < D; c += 8) {
+        for (int c = 0; c < HD; c += 8) {
           uint4 v;
           v.x = pack_bf16x2(o_reg[c] * inv, o_reg[c + 1] * inv);
           v.y = pack_bf16x2(o_reg[c + 2] * inv, o_reg[c + 3] * inv);
@@ -318,10 +356,10 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
         }
       } else {
 #pragma unroll
-        for (int c = 0; c < D; c += 2)
+        for (int c = 0; c < HD; c += 2)
           *reinterpret_cast<uint32_t*>(orow + c) = pack_bf16x2(o_reg[c] * inv, o_reg[c + 1] * inv);
       }
-      if (p.lse)
+      if (p.lse && half == 0)
         p.lse[((long long)b * p.q_heads + h) * p.sq + qi] = l_run > 0.f ? (m_run * 0.6931471805599453f + logf(l_run)) : -INFINITY;
     }
   }
@@ -368,7 +406,7 @@ static int fa_tmap(CUtensorMap* map, const void* ptr, int head_dim, long long se
 
 template <int D>
 static int fa_launch(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FaParams& p, dim3 grid, cudaStream_t stream) {
-  constexpr size_t smem = size_t(D / 64) * FA_BLOCK_BYTES * 5 + 2 * FA_BLOCK_BYTES + 1024 + 128;
+  constexpr size_t smem = size_t(D / 64) * FA_BLOCK_BYTES * 5 + 2 * FA_BLOCK_BYTES + 1024 + 128 + 4 * FA_M * sizeof(float);
   static std::atomic<bool> configured[64];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return TPB_ERR_CUDA;

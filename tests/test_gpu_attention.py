@@ -64,7 +64,7 @@ def test_prefill_attention_additive_bias(kind):
     out = OF.attention(q, k, v, causal, bias=bias)
     ref = OF.attention_ref(q.float(), k.float(), v.float(), causal, bias=bias.float())
     torch.testing.assert_close(out.float(), ref, atol=2e-2, rtol=2e-2)
-    assert not nat.attention_supported(q.requires_grad_(), k, v, bias)  # training with a bias stays on the PyTorch path
+    assert nat.attention_supported(q.requires_grad_(), k, v, bias)  # training with a bias runs on the native kernels too
 
 
 def test_prefill_attention_reads_cache_layout():
