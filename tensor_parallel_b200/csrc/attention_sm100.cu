@@ -27,6 +27,7 @@
 #include <math.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <atomic>
@@ -66,6 +67,25 @@ __device__ __forceinline__ void fadd2(float& d0, float& d1, float a0, float a1, 
       "add.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
       : "=f"(d0), "=f"(d1)
       : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
+
+// 2^x on the FMA pipe for a pair of values (the special-function unit, at 16 results per clock and SM, is what bounds the
+// softmax of a 128 x 128 tile: as long as the tensor core needs for its two products).  x = n + f with n = round(x) taken
+// from the low mantissa bits of x + 1.5 * 2^23, a cubic for 2^f on [-0.5, 0.5] (relative error 7.5e-5, far below the bf16
+// rounding of the probabilities), n added into the exponent field.  x is clamped at -126: a masked score becomes 2^-126.
+__device__ __forceinline__ void ex2_poly2(float& x0, float& x1) {
+  constexpr float MAGIC = 12582912.f;
+  x0 = fmaxf(x0, -126.f);
+  x1 = fmaxf(x1, -126.f);
+  float t0, t1, n0, n1, f0, f1, p0, p1;
+  fadd2(t0, t1, x0, x1, MAGIC, MAGIC);
+  fadd2(n0, n1, t0, t1, -MAGIC, -MAGIC);
+  ffma2(f0, f1, n0, n1, -1.f, -1.f, x0, x1);
+  ffma2(p0, p1, f0, f1, 0.0551716685f, 0.0551716685f, 0.2426111251f, 0.2426111251f);
+  ffma2(p0, p1, p0, p1, f0, f1, 0.6932609677f, 0.6932609677f);
+  ffma2(p0, p1, p0, p1, f0, f1, 0.9999280572f, 0.9999280572f);
+  x0 = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
+  x1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
 }
 
 struct FaParams {
@@ -370,6 +390,354 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
   if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// Two query tiles per CTA, ping-pong: while the softmax warps of one tile work, the tensor core multiplies for the other.
+//
+//   warp 0     : TMA producer  - Q (two tiles of 128 queries) once, then K and V tiles into two 2-deep rings
+//   warp 1     : MMA issuer    - per tile t: S_t = Q_t K(j)^T; wait for P_t(j); O_t += P_t(j) V(j); S_t = Q_t K(j + 1)^T ...
+//                                The probabilities are the A operand read from TENSOR MEMORY (they overwrite the first 64
+//                                columns of their own scores), V is the MN-major B operand as it lies in memory, and O_t
+//                                accumulates in tensor memory over all key tiles.
+//   warps 2-3  : idle (they give their registers to the softmax warps)
+//   warps 4-7  : softmax of tile 0, warps 8-11: softmax of tile 1 - thread r owns query row r: scores out of TMEM once
+//                (128 registers), row maximum, exponentials, bf16 probabilities back into TMEM.  The running maximum is
+//                LAZY: the accumulated output is rescaled (TMEM load, multiply, store) only when the maximum rose by more
+//                than 2^8 since the last rescale, which after the first tiles of a row is rare; the stale maximum cancels
+//                in O / l and in the log-sum-exp.
+//
+// TMEM (512 columns): S_0 | S_1 | O_0 | O_1, 128 columns each.  Shared memory at head_dim 128: Q 64 KB + K 64 KB + V 64 KB.
+// Ordering: MMAs of one thread execute in issue order, so QK_t(j + 1), issued after PV_t(j), may overwrite the columns
+// PV_t(j) reads; s_full_t(j) (a commit after QK_t(j)) therefore also says that PV_t(j - 1) is complete, which is what a
+// rescale of O_t needs.  Every mbarrier wait is bounded; on expiry the CTA records a status code and drains.
+constexpr int FA2_M = 256;
+constexpr int FA2_THREADS = 384;
+constexpr float FA2_RESCALE_LOG2 = 8.f;
+
+template <int D, int POLY>  // POLY of every 4 pairs of exponentials run on the FMA pipe
+__global__ void __launch_bounds__(FA2_THREADS, 1)
+attn_fwd_pingpong_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                         const __grid_constant__ CUtensorMap tmap_v, const FaParams p) {
+  constexpr int DB = D / 64;
+  constexpr uint32_t T_BYTES = DB * FA_BLOCK_BYTES;  // one 128-row tile of Q, K or V
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr uint32_t O_COL0 = 256;
+  constexpr uint32_t IDESC_QK = make_idesc_bf16(FA_M, FA_N, false, false);
+  constexpr uint32_t IDESC_PV = make_idesc_bf16(FA_M, D, false, true);
+
+  extern __shared__ uint8_t fa_smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(fa_smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* q_s = smem;                 // [2 tiles]
+  uint8_t* k_s = q_s + 2 * T_BYTES;    // [2 stages]
+  uint8_t* v_s = k_s + 2 * T_BYTES;    // [2 stages]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + 2 * T_BYTES);
+  uint64_t* q_full = bars;
+  uint64_t* k_full = bars + 1;    // [2]
+  uint64_t* k_empty = bars + 3;   // [2]
+  uint64_t* v_full = bars + 5;    // [2]
+  uint64_t* v_empty = bars + 7;   // [2]
+  uint64_t* s_full = bars + 9;    // [2 tiles]
+  uint64_t* p_full = bars + 11;   // [2 tiles]
+  uint64_t* o_full = bars + 13;   // [2 tiles]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qblk = gridDim.x - 1 - blockIdx.x;  // heavy (late) causal tiles first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int kvh = h / (p.q_heads / p.kv_heads);
+  const int q0 = qblk * FA2_M;
+  const int shift = p.sk - p.sq;  // query i may see keys j <= i + shift when causal
+  int n_tiles[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    int kv_end = p.sk;
+    if (p.causal) kv_end = min(p.sk, q0 + t * FA_M + FA_M + shift);
+    n_tiles[t] = (q0 + t * FA_M < p.sq && kv_end > 0) ? (kv_end + FA_N - 1) / FA_N : 0;
+  }
+  const int n_max = max(n_tiles[0], n_tiles[1]);
+
+  if (threadIdx.x == 0) {
+    prefetch_tmap(&tmap_q);
+    prefetch_tmap(&tmap_k);
+    prefetch_tmap(&tmap_v);
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
+      mbar_init(&s_full[s], 1);
+      mbar_init(&p_full[s], 4);  // one arrival per softmax warp of the tile
+      mbar_init(&o_full[s], 1);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  auto give_up = [&](uint32_t code) {
+    atomicMax(p.status, code);
+    *abort_flag = 1;
+  };
+
+  if (warp < 4) {
+    setmaxnreg_dec<56>();
+    if (warp == 0) {
+      // ---------------- TMA producer ----------------
+      if (elect_one() && n_max > 0) {
+        mbar_expect_tx(q_full, 2 * T_BYTES);
+#pragma unroll
+        for (int t = 0; t < 2; ++t)
+#pragma unroll
+          for (int d = 0; d < DB; ++d) tma_load_4d(q_s + t * T_BYTES + d * FA_BLOCK_BYTES, &tmap_q, q_full, d * 64, q0 + t * FA_M, h, b);
+        for (int j = 0; j < n_max && !*abort_flag; ++j) {
+          const int s = j & 1;
+          const uint32_t par = ((j >> 1) & 1) ^ 1;
+          if (!mbar_wait(&k_empty[s], par)) { give_up(STATUS_TIMEOUT_MBAR); break; }
+          mbar_expect_tx(&k_full[s], T_BYTES);
+#pragma unroll
+          for (int d = 0; d < DB; ++d) tma_load_4d(k_s + s * T_BYTES + d * FA_BLOCK_BYTES, &tmap_k, &k_full[s], d * 64, j * FA_N, kvh, b);
+          if (!mbar_wait(&v_empty[s], par)) { give_up(STATUS_TIMEOUT_MBAR); break; }
+          mbar_expect_tx(&v_full[s], T_BYTES);
+#pragma unroll
+          for (int d = 0; d < DB; ++d) tma_load_4d(v_s + s * T_BYTES + d * FA_BLOCK_BYTES, &tmap_v, &v_full[s], d * 64, j * FA_N, kvh, b);
+        }
+      }
+    } else if (warp == 1) {
+      // ---------------- MMA issuer ----------------
+      if (elect_one() && n_max > 0) {
+        const uint32_t q_addr = smem_u32(q_s);
+        auto issue_qk = [&](int t, int j) {  // S_t = Q_t K(j)^T
+          const uint32_t k_addr = smem_u32(k_s + (j & 1) * T_BYTES);
+          const uint32_t d_tmem = tmem_base + t * FA_N;
+#pragma unroll
+          for (int d = 0; d < DB; ++d) {
+#pragma unroll
+            for (int kk = 0; kk < 64 / 16; ++kk) {
+              const uint64_t adesc = make_desc_kmajor_sw128(q_addr + t * T_BYTES + d * FA_BLOCK_BYTES + kk * 32);
+              const uint64_t bdesc = make_desc_kmajor_sw128(k_addr + d * FA_BLOCK_BYTES + kk * 32);
+              umma_bf16(d_tmem, adesc, bdesc, IDESC_QK, (d | kk) ? 1u : 0u);
+            }
+          }
+          umma_commit(&s_full[t]);
+        };
+        auto issue_pv = [&](int t, int j) {  // O_t (+)= P_t(j) V(j): P from tensor memory, V tile [128 keys][D] MN-major
+          const uint32_t v_addr = smem_u32(v_s + (j & 1) * T_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < FA_N / 16; ++kk) {
+            const uint64_t bdesc = make_desc_mnmajor_sw128(v_addr + kk * 16 * 128, FA_BLOCK_BYTES);
+            umma_bf16_tmem_a(tmem_base + O_COL0 + t * FA_N, tmem_base + t * FA_N + kk * 8, bdesc, IDESC_PV, (j | kk) ? 1u : 0u);
+          }
+        };
+        bool ok = mbar_wait(q_full, 0) && mbar_wait(&k_full[0], 0);
+        if (!ok) give_up(STATUS_TIMEOUT_MBAR);
+        if (ok) {
+          tc_fence_after();
+#pragma unroll
+          for (int t = 0; t < 2; ++t)
+            if (n_tiles[t] > 0) issue_qk(t, 0);
+          umma_commit(&k_empty[0]);
+        }
+        for (int j = 0; ok && j < n_max && !*abort_flag; ++j) {
+          const bool next = j + 1 < n_max;
+          if (next && !mbar_wait(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1)) { give_up(STATUS_TIMEOUT_MBAR); break; }
+          if (!mbar_wait(&v_full[j & 1], (j >> 1) & 1)) { give_up(STATUS_TIMEOUT_MBAR); break; }
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            if (ok && j < n_tiles[t]) {
+              if (!mbar_wait(&p_full[t], j & 1)) {
+                give_up(STATUS_TIMEOUT_MBAR);
+                ok = false;
+              } else {
+                tc_fence_after();
+                issue_pv(t, j);
+                if (j == n_tiles[t] - 1)
+                  umma_commit(&o_full[t]);
+                else
+                  issue_qk(t, j + 1);
+              }
+            }
+          }
+          if (!ok) break;
+          umma_commit(&v_empty[j & 1]);          // V(j) may be overwritten once these MMAs retire
+          if (next) umma_commit(&k_empty[(j + 1) & 1]);  // and K(j + 1)
+        }
+      }
+    }
+  } else {
+    // ---------------- softmax warps ----------------
+    setmaxnreg_inc<224>();
+    const int t = (warp - 4) >> 2;
+    const int quarter = warp & 3;  // TMEM lane quarter this warp may access
+    const int row = quarter * 32 + lane;
+    const int qi = q0 + t * FA_M + row;
+    const int my_tiles = n_tiles[t];
+    const uint32_t s_addr = tmem_base + (uint32_t(quarter * 32) << 16) + t * FA_N;  // scores, and in their first 64 columns P
+    const uint32_t o_addr = tmem_base + (uint32_t(quarter * 32) << 16) + O_COL0 + t * FA_N;
+    float m_run = -INFINITY, l_run = 0.f;
+    const float* bias_f = static_cast<const float*>(p.bias);
+    const bf16* bias_h = static_cast<const bf16*>(p.bias);
+    const long long bias_row = p.bias_kind ? (b * p.bias_sb + h * p.bias_sh + (long long)min(qi, p.sq - 1) * p.bias_sq) : 0;
+    bool alive = true;
+
+    for (int j = 0; j < my_tiles; ++j) {
+      if (*abort_flag || !mbar_wait(&s_full[t], j & 1)) {
+        if (!*abort_flag) give_up(STATUS_TIMEOUT_MBAR);
+        alive = false;
+        break;
+      }
+      tc_fence_after();
+      const int key0 = j * FA_N;
+      // only tiles that touch the diagonal, the end of the keys or a bias need per-element work
+      const bool plain = !p.bias_kind && key0 + FA_N <= p.sk && (!p.causal || key0 + FA_N - 1 <= q0 + t * FA_M + shift);
+      uint32_t r[FA_N];
+#pragma unroll
+      for (int c = 0; c < FA_N; c += 32) tmem_ld_x32(s_addr + c, *reinterpret_cast<uint32_t(*)[32]>(r + c));
+      tmem_ld_wait();
+      float m_tile;
+      if (!p.bias_kind) {
+        if (!plain) {  // keys [0, visible) of this tile count, the others become -inf
+          const int visible = min(p.sk, p.causal ? qi + shift + 1 : p.sk) - key0;
+#pragma unroll
+          for (int i = 0; i < FA_N; ++i)
+            if (i >= visible) r[i] = 0xff800000u;
+        }
+        float m0 = -INFINITY, m1 = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < FA_N; i += 4) {
+          m0 = fmax3(m0, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+          m1 = fmax3(m1, __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+        }
+        m_tile = fmaxf(m0, m1) * p.scale_log2e;  // (the scale is positive: the maximum commutes with it)
+      } else {
+        m_tile = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < FA_N; ++i) {
+          const int key = key0 + i;
+          const bool dead = key >= p.sk || (p.causal && key > qi + shift);
+          float sv = dead ? -INFINITY : __uint_as_float(r[i]) * p.scale_log2e;
+          if (!dead) {
+            const long long bi = bias_row + (long long)key * p.bias_sk;
+            const float bv = p.bias_kind == 1 ? __ldg(bias_f + bi) : __bfloat162float(bias_h[bi]);
+            sv += bv * 1.4426950408889634f;
+          }
+          r[i] = __float_as_uint(sv);
+          m_tile = fmaxf(m_tile, sv);
+        }
+      }
+      // ---- lazy running maximum; rescale the accumulated output only after a large rise ----
+      float factor = 1.f;
+      bool rescale = false;
+      if (m_run == -INFINITY) {
+        m_run = m_tile;  // nothing accumulated for this row yet
+      } else if (m_tile > m_run + FA2_RESCALE_LOG2) {
+        factor = ex2_approx(m_run - m_tile);
+        m_run = m_tile;
+        rescale = true;
+      }
+      if (j > 0 && __any_sync(0xffffffffu, rescale)) {
+#pragma unroll
+        for (int c = 0; c < D; c += 32) {
+          uint32_t o[32];
+          tmem_ld_x32(o_addr + c, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+          tmem_st_x32(o_addr + c, o);
+        }
+      }
+      l_run *= factor;
+      // ---- probabilities (bf16 pairs, key 2c and 2c + 1 in column c of this row) over the scores' first 64 columns ----
+      const float mul = p.bias_kind ? 1.f : p.scale_log2e;
+      const float nbase = m_run == -INFINITY ? 0.f : -m_run;
+      float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+      for (int c = 0; c < FA_N / 2; c += 32) {
+        uint32_t packed[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float t0, t1;
+          ffma2(t0, t1, __uint_as_float(r[2 * (c + i)]), __uint_as_float(r[2 * (c + i) + 1]), mul, mul, nbase, nbase);
+          float p0, p1;
+          if ((i & 3) < POLY) {
+            ex2_poly2(t0, t1);
+            p0 = t0;
+            p1 = t1;
+          } else {
+            p0 = ex2_approx(t0);
+            p1 = ex2_approx(t1);
+          }
+          fadd2(sum0, sum1, sum0, sum1, p0, p1);
+          packed[i] = pack_bf16x2(p0, p1);
+        }
+        tmem_st_x32(s_addr + c, packed);
+      }
+      l_run += sum0 + sum1;
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[t]);
+    }
+    // ---- epilogue: O_t / l -> global memory ----
+    if (alive && my_tiles > 0) {
+      if (mbar_wait(&o_full[t], 0)) {
+        tc_fence_after();
+      } else {
+        give_up(STATUS_TIMEOUT_MBAR);
+        alive = false;
+      }
+    }
+    if (alive && q0 + t * FA_M < p.sq) {  // (warp-uniform: the TMEM loads below are warp-wide)
+      if (m_run == -INFINITY) l_run = 0.f;  // no visible key at all (the cubic turns a masked score into 2^-126, not 0)
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      bf16* orow = p.out + b * p.o_sb + (long long)min(qi, p.sq - 1) * p.o_ss + (long long)h * p.o_sh;
+      const bool vec = (reinterpret_cast<uintptr_t>(orow) & 15) == 0;
+#pragma unroll
+      for (int c = 0; c < D; c += 32) {
+        uint32_t o[32];
+        if (my_tiles > 0) {
+          tmem_ld_x32(o_addr + c, o);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = 0u;
+        }
+        if (qi < p.sq) {
+          if (vec) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              uint4 v;
+              v.x = pack_bf16x2(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+              v.y = pack_bf16x2(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+              v.z = pack_bf16x2(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
+              v.w = pack_bf16x2(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
+              *reinterpret_cast<uint4*>(orow + c + i) = v;
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; i += 2)
+              *reinterpret_cast<uint32_t*>(orow + c + i) = pack_bf16x2(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+          }
+        }
+      }
+      if (p.lse && qi < p.sq)
+        p.lse[((long long)b * p.q_heads + h) * p.sq + qi] = l_run > 0.f ? (m_run * 0.6931471805599453f + logf(l_run)) : -INFINITY;
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -418,6 +786,20 @@ static int fa_launch(const CUtensorMap& tq, const CUtensorMap& tk, const CUtenso
   return cudaGetLastError() == cudaSuccess ? TPB_OK : TPB_ERR_CUDA;
 }
 
+template <int D, int POLY>
+static int fa2_launch(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FaParams& p, dim3 grid, cudaStream_t stream) {
+  constexpr size_t smem = size_t(D / 64) * FA_BLOCK_BYTES * 6 + 1024 + 256;
+  static std::atomic<bool> configured[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return TPB_ERR_CUDA;
+  if (!configured[dev].load(std::memory_order_acquire)) {
+    if (cudaFuncSetAttribute(attn_fwd_pingpong_kernel<D, POLY>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return TPB_ERR_CUDA;
+    configured[dev].store(true, std::memory_order_release);
+  }
+  attn_fwd_pingpong_kernel<D, POLY><<<grid, FA2_THREADS, smem, stream>>>(tq, tk, tv, p);
+  return cudaGetLastError() == cudaSuccess ? TPB_OK : TPB_ERR_CUDA;
+}
+
 }  // namespace tpb
 
 using namespace tpb;
@@ -463,7 +845,26 @@ extern "C" int tpb_attn_prefill_sm100(const void* q, const void* k, const void* 
   p.bias_kind = !bias ? 0 : (bias_dtype == 1 ? 1 : 2);
   p.bias_sb = bias_sb; p.bias_sh = bias_sh; p.bias_sq = bias_sq; p.bias_sk = bias_sk;
   p.status = static_cast<uint32_t*>(status);
-  dim3 grid((sq + FA_M - 1) / FA_M, q_heads, batch);
   cudaStream_t s = static_cast<cudaStream_t>(stream_);
+  static const bool one_tile = getenv("TPB_ATTN_ONE_TILE") != nullptr;  // (A/B switch: the kernel with one query tile per CTA)
+  if (!one_tile && sq > FA_M) {
+    dim3 grid((sq + FA2_M - 1) / FA2_M, q_heads, batch);
+    static const int poly = getenv("TPB_ATTN_POLY") ? atoi(getenv("TPB_ATTN_POLY")) : 1;
+    if (head_dim == 128) {
+      switch (poly) {
+        case 0: return fa2_launch<128, 0>(tq, tk, tv, p, grid, s);
+        case 2: return fa2_launch<128, 2>(tq, tk, tv, p, grid, s);
+        case 3: return fa2_launch<128, 3>(tq, tk, tv, p, grid, s);
+        default: return fa2_launch<128, 1>(tq, tk, tv, p, grid, s);
+      }
+    }
+    switch (poly) {
+      case 0: return fa2_launch<64, 0>(tq, tk, tv, p, grid, s);
+      case 2: return fa2_launch<64, 2>(tq, tk, tv, p, grid, s);
+      case 3: return fa2_launch<64, 3>(tq, tk, tv, p, grid, s);
+      default: return fa2_launch<64, 1>(tq, tk, tv, p, grid, s);
+    }
+  }
+  dim3 grid((sq + FA_M - 1) / FA_M, q_heads, batch);
   return head_dim == 128 ? fa_launch<128>(tq, tk, tv, p, grid, s) : fa_launch<64>(tq, tk, tv, p, grid, s);
 }
