@@ -347,6 +347,17 @@ using namespace tpb;
 // bias (may be null): the additive score bias the forward pass was given, dtype bias_dtype (0 bf16, 1 fp32), element strides
 // over (batch, head, query, key) with 0 broadcasting.  dbias (may be null): fp32 buffer addressed with the same strides,
 // zero-initialised by the caller; receives the gradient of the bias (added with atomics where the bias broadcasts).
+// delta[b, h, i] = sum_d out[b, i, h, d] * dout[b, i, h, d] (fp32, [batch][heads][sq]); strides in elements.
+extern "C" int tpb_attn_bwd_delta(const void* out, const void* dout, float* delta, int batch, int sq, int heads, int head_dim,
+                                  long long o_sb, long long o_ss, long long o_sh, long long do_sb, long long do_ss, long long do_sh,
+                                  void* stream_) {
+  if (!out || !dout || !delta || batch <= 0 || sq <= 0 || heads <= 0 || head_dim <= 0) return TPB_ERR_ARG;
+  const long long rows = (long long)batch * heads * sq;
+  attn_bwd_delta_kernel<<<int((rows + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream_)>>>(
+      (const bf16*)out, (const bf16*)dout, delta, sq, heads, head_dim, o_sb, o_ss, o_sh, do_sb, do_ss, do_sh, rows);
+  return cudaGetLastError() == cudaSuccess ? TPB_OK : TPB_ERR_CUDA;
+}
+
 extern "C" int tpb_attn_backward_bias(const void* q, const void* k, const void* v, const void* out, const void* dout,
                                       const float* lse, float* delta, void* dq, void* dk, void* dv, int batch, int sq, int sk,
                                       int q_heads, int kv_heads, int head_dim, long long q_sb, long long q_ss, long long q_sh,

@@ -115,6 +115,11 @@ BWD_CASES = [
     (2, 77, 77, 4, 4, 64, False),     # bidirectional
     (1, 64, 300, 4, 1, 128, True),    # cached prefix, MQA
     (1, 37, 133, 2, 2, 64, False),    # cross attention
+    (1, 384, 384, 4, 2, 128, True),   # several resident tiles and streamed steps, GQA
+    (2, 300, 300, 2, 2, 64, True),    # ragged ends on both sides
+    (1, 256, 512, 2, 1, 128, True),   # cached prefix over several tiles, MQA
+    (1, 130, 260, 2, 2, 128, False),  # ragged cross attention
+    (1, 512, 512, 2, 2, 128, False),
 ]
 
 
