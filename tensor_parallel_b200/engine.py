@@ -66,7 +66,8 @@ def _cat_bias(parts, sizes, device) -> Optional[torch.Tensor]:
 
 class DecoderEngine:
     def __init__(self, shard, comm=None, max_batch: int = 8, max_seq: int = 2560, use_graph: bool = True, embed_table=None,
-                 process_group=None, replicate_embedding: bool = True, spec: Optional[engine_spec.DecoderSpec] = None):
+                 process_group=None, replicate_embedding: bool = True, spec: Optional[engine_spec.DecoderSpec] = None,
+                 pipeline_prefill: Optional[bool] = None):
         spec = spec if spec is not None else engine_spec.describe(shard, max_seq)
         if spec is None:
             raise ValueError("no serving description for this model (see tensor_parallel_b200.engine_spec)")
@@ -79,6 +80,10 @@ class DecoderEngine:
         self.theta, self.head_dim, self.hidden = spec.rope_theta, spec.head_dim, spec.hidden
         self.max_batch, self.max_seq = max_batch, max_seq
         self.use_graph = use_graph and not os.environ.get("TPB_NO_GRAPH")
+        # two half-batches in flight during prefill, the all-reduce of one under the GEMMs of the other (one process per
+        # GPU only: a single thread that drives every rank launches the ranks' kernels one after the other)
+        self.pipeline_prefill = (use_graph if pipeline_prefill is None else pipeline_prefill) and os.environ.get("TPB_PREFILL_PIPELINE", "1") != "0"
+        self._side_stream: Optional[torch.cuda.Stream] = None
         self.device = dev = spec.embed.device
         self._versions = tuple(t._version for t in spec.parameters())
         D, H = self.head_dim, self.hidden
@@ -373,13 +378,108 @@ class DecoderEngine:
         q_rot = torch.empty(tokens, self.nq, D, **bf)
         cat = torch.empty(tokens, self.cat.shape[1], **bf)
         act_buf = None if self.parallel else torch.empty(tokens, self.ff, **bf)
-        for i in range(len(self.layers)):
-            self._layer(i, x, n, qkv, q_rot, cat, act_buf, batch, seq, decode=False)
+        if self._can_pipeline(batch, seq):
+            self._prefill_pipelined(x, n, qkv, q_rot, cat, act_buf, batch, seq)
+        else:
+            for i in range(len(self.layers)):
+                self._layer(i, x, n, qkv, q_rot, cat, act_buf, batch, seq, decode=False)
         last = x.view(batch, seq, self.hidden)[:, -1].contiguous()
         logits_local = torch.empty(batch, self.vocab_local, **bf)
         logits = self._head(last, logits_local, batch)
         self.pos.fill_(base + seq)
         return logits.float()
+
+    def _can_pipeline(self, batch: int, seq: int) -> bool:
+        if not self.pipeline_prefill or self.world == 1 or batch < 2 or batch * seq < 1024:
+            return False
+        region = -(-((batch + 1) // 2 * seq * self.hidden * 2) // 1024) * 1024
+        return 2 * region <= self.comm.staging_in.numel()
+
+    def _prefill_pipelined(self, x, n, qkv, q_rot, cat, act_buf, batch: int, seq: int):
+        """All layers of a prefill with the batch cut in two halves that take turns: while the row-parallel output of
+        one half is summed over the ranks (stand-alone all-reduce kernel on a side stream, in place in its own part of
+        the staging buffers), the tensor cores work on the other half.  Collectives run one at a time and in the same
+        order on every rank (half 0, half 1, half 0, ...).  The sum is added to the residual stream by the norm kernel
+        that opens the next stage (``x += sum; n = norm(x)`` in one pass)."""
+        comm, dev, D = self.comm, self.device, self.head_dim
+        main = torch.cuda.current_stream(dev)
+        if self._side_stream is None:
+            self._side_stream = torch.cuda.Stream(dev)
+        side = self._side_stream
+        cut = (batch + 1) // 2
+        halves = ((0, cut), (cut, batch))
+        region = -(-(cut * seq * self.hidden * 2) // 1024) * 1024
+        nq_w, nk_w = self.nq * D, self.nkv * D
+        pending = [None, None]  # per half: (event, summed rows in the staging-out buffer, bias of that projection)
+
+        def rows(t, h):
+            return None if t is None else t[halves[h][0] * seq : halves[h][1] * seq]
+
+        def staged(h):
+            count = (halves[h][1] - halves[h][0]) * seq
+            return comm.staging_in[h * region : h * region + count * self.hidden * 2].view(torch.bfloat16).view(count, self.hidden)
+
+        def reduce_async(h, bias):
+            ready = torch.cuda.Event()
+            ready.record(main)
+            side.wait_event(ready)
+            with torch.cuda.stream(side):
+                out = comm.all_reduce_staged(h * region, staged(h).shape)
+                done = torch.cuda.Event()
+                done.record(side)
+            pending[h] = (done, out, bias)
+
+        def open_stage(h):
+            """Residual stream of half ``h`` brought up to date, and its normalised rows."""
+            xh, nh = rows(x, h), rows(n, h)
+            if pending[h] is None:
+                native.norm_forward(xh, None, None, self.eps, self.mode - 1, out=nh)
+                return xh, nh
+            done, red, bias = pending[h]
+            pending[h] = None
+            main.wait_event(done)
+            if bias is None:
+                native.norm_forward(xh, None, None, self.eps, self.mode - 1, residual=red, sum_out=xh, out=nh)
+            else:
+                xh.add_(red).add_(bias * self.world)
+                native.norm_forward(xh, None, None, self.eps, self.mode - 1, out=nh)
+            return xh, nh
+
+        for i, L in enumerate(self.layers):
+            for h, (b0, b1) in enumerate(halves):
+                xh, nh = open_stage(h)
+                qkv_h, cat_h = rows(qkv, h), rows(cat, h)
+                native.gemm_nt(nh, L["wqkv"], bias=L["bqkv"], out=qkv_h)
+                q2, k2, v2 = qkv_h[:, :nq_w], qkv_h[:, nq_w : nq_w + nk_w], qkv_h[:, nq_w + nk_w :]
+                q_rot_h = rows(q_rot, h)
+                native.qkv_rope_append(q2, k2, v2, q_rot_h, self.kcache[i][b0:b1], self.vcache[i][b0:b1], self.pos, b1 - b0, seq,
+                                       self.spec.rotary_dim, self.theta, interleaved=self.spec.rope_interleaved)
+                total = self._prefill_base + seq
+                attn = cat_h[:, :nq_w]
+                native.attention_forward(q_rot_h.view(b1 - b0, seq, self.nq, D), self.kcache[i][b0:b1, :, :total].transpose(1, 2),
+                                         self.vcache[i][b0:b1, :, :total].transpose(1, 2), True, None,
+                                         out=attn.unflatten(0, (b1 - b0, seq)).unflatten(2, (self.nq, D)))
+                if self.parallel:
+                    native.gemm_nt(nh, L["w1"], bias=L["b1"], act=self.act, out=cat_h[:, nq_w:])
+                    native.gemm_nt(cat_h, L["wcat"], out=staged(h))
+                    reduce_async(h, L["bcat"])
+                else:
+                    native.gemm_nt(attn, L["wo"], out=staged(h))
+                    reduce_async(h, L["bo"])
+            if not self.parallel:
+                for h in range(2):
+                    xh, nh = open_stage(h)
+                    act_h = rows(act_buf, h)
+                    native.gemm_nt(nh, L["w1"], bias=L["b1"], act=self.act, out=act_h)
+                    native.gemm_nt(act_h, L["wd"], out=staged(h))
+                    reduce_async(h, L["bd"])
+        for h in range(2):
+            done, red, bias = pending[h]
+            main.wait_event(done)
+            xh = rows(x, h)
+            xh.add_(red)
+            if bias is not None:
+                xh.add_(bias * self.world)
 
     # -- decode -----------------------------------------------------------------------------------
 

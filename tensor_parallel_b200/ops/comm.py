@@ -138,7 +138,7 @@ class RankComm:
             self.local[off : off + GUARD_BYTES].fill_(GUARD_PATTERN)
         self._call = 0
         self._ctxs = [self._make_ctx(0), self._make_ctx(1)]
-        self._ptr_arrays: Dict[str, ctypes.Array] = {}
+        self._ptr_arrays: Dict = {}
         for name, off in (("in", layout.off_staging_in), ("out", layout.off_staging_out), ("sig", layout.off_signals)):
             arr = (c_void_p * MAX_WORLD)()
             for r in range(world):
@@ -234,14 +234,37 @@ class RankComm:
 
     # -- stand-alone collectives on the staging buffers -------------------------------------------
 
-    def _collective(self, kind: int, dtype: torch.dtype, n: int, force_algo: int = -1):
+    def _collective(self, kind: int, dtype: torch.dtype, n: int, force_algo: int = -1, offset: int = 0):
+        """``offset`` (bytes, the same on every rank) moves the operation to a later part of the staging buffers."""
         code = 0 if dtype == torch.bfloat16 else 1
-        mc_in = self.mc_base + self.layout.off_staging_in if self.mc_base else 0
-        mc_out = self.mc_base + self.layout.off_staging_out if self.mc_base else 0
-        check(LIB.tpb_collective(kind, code, self.world, self.rank, self._ptr_arrays["in"], self._ptr_arrays["out"],
+        mc_in = self.mc_base + self.layout.off_staging_in + offset if self.mc_base else 0
+        mc_out = self.mc_base + self.layout.off_staging_out + offset if self.mc_base else 0
+        ins, outs = self._ptr_arrays["in"], self._ptr_arrays["out"]
+        if offset:
+            key = ("off", offset)
+            if key not in self._ptr_arrays:
+                pair = ((c_void_p * MAX_WORLD)(), (c_void_p * MAX_WORLD)())
+                for r in range(self.world):
+                    pair[0][r] = self.base[r] + self.layout.off_staging_in + offset
+                    pair[1][r] = self.base[r] + self.layout.off_staging_out + offset
+                self._ptr_arrays[key] = pair
+            ins, outs = self._ptr_arrays[key]
+        check(LIB.tpb_collective(kind, code, self.world, self.rank, ins, outs,
                                  self._ptr_arrays["sig"], c_void_p(self.epochs.data_ptr()), c_void_p(self.status.data_ptr()), n,
                                  force_algo, self.wait_seconds, c_void_p(mc_in), c_void_p(mc_out), native._stream()), "tpb_collective")
         native.launch_count += 1
+
+    def all_reduce_staged(self, offset: int, shape, dtype=torch.bfloat16) -> torch.Tensor:
+        """Sum over ranks of the tensor that already lies in the staging-in buffer at byte ``offset`` (a multiple of
+        1024, the same on every rank); returns the view of the staging-out buffer that holds the result.  Launches on
+        the current stream: callers that overlap the reduction with other work (``engine.py``: prefill) call it under a
+        side stream, one collective at a time and in the same order on every rank."""
+        n = int(torch.Size(shape).numel())
+        size = 2 if dtype == torch.bfloat16 else 4
+        if offset % 1024 or (n * size) % 16 or offset + n * size > self.staging_in.numel():
+            raise ValueError("staged all-reduce: misaligned or outside the staging buffers")
+        self._collective(0, dtype, n, offset=offset)
+        return self.staging_out[offset : offset + n * size].view(dtype).view(shape)
 
     def _capacity(self, dtype: torch.dtype, in_copies: int, out_copies: int) -> int:
         """Largest element count (a multiple of 16 bytes) whose ``in_copies`` / ``out_copies`` fit the staging buffers."""

@@ -1,7 +1,7 @@
 """The ``-DTPB_BOUNDS`` build of the native library: kernels check their store indices against the extents the host
 passed and report ``STATUS_BAD_ARG`` instead of touching memory outside them (nothing traps, nothing faults).  The
 variant is loaded in a child process through ``TPB_LIB_PATH``; it is built by ``__graft_entry__.build()`` (or here, if
-absent and nvcc is present)."""
+absent or older than the sources, and nvcc is present)."""
 import os
 import subprocess
 import sys
@@ -55,7 +55,9 @@ print("bounds ok")
 
 def test_checked_build_reports_instead_of_writing_out_of_bounds():
     lib = os.path.join(REPO, "tensor_parallel_b200", "lib", "libtpb200_bounds.so")
-    if not os.path.exists(lib):
+    csrc = os.path.join(REPO, "tensor_parallel_b200", "csrc")
+    newest = max(os.path.getmtime(os.path.join(csrc, f)) for f in os.listdir(csrc))
+    if not os.path.exists(lib) or os.path.getmtime(lib) < newest:  # absent, or older than the sources it was built from
         sys.path.insert(0, REPO)
         from tensor_parallel_b200 import build
 

@@ -211,6 +211,13 @@ def _model_worker(rank, world, out_dir):
     assert tp2._engine.world == world and tp2._engine.graph is not None
     agree = (got_tokens == want_tokens).float().mean().item()
     assert agree > 0.9, agree  # bf16 summation order differs between 1 and 2 ranks; near-ties may flip
+    # a prompt large enough for the two-half prefill pipeline (all-reduce of one half under the GEMMs of the other)
+    long_prompt = torch.randint(0, 512, (5, 288), device=dev)
+    dist.broadcast(long_prompt, 0)
+    want_long = single.prefill(long_prompt.cpu(), max_new_tokens=4)
+    got_long = tp2.prefill(long_prompt.cpu(), max_new_tokens=4)
+    assert tp2._engine._side_stream is not None, "the pipelined prefill did not run"
+    torch.testing.assert_close(got_long, want_long, atol=0.1, rtol=0.05)
     torch.cuda.synchronize()
     tp2._engine.comm.check_status()
     dist.barrier()
