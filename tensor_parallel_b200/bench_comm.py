@@ -84,18 +84,29 @@ def main():
         out.append(kw)
 
     # stand-alone all-reduce: device kernel vs NCCL
-    for nbytes in (64 << 10, 1 << 20, 16 << 20, 128 << 20):
+    for nbytes in (8 << 10, 64 << 10, 256 << 10, 1 << 20, 16 << 20, 128 << 20):
         n = nbytes // 2
         x = torch.randn(n, device=dev, dtype=torch.bfloat16)
         src = rc.staging_view("in", (n,), torch.bfloat16)
         src.copy_(x)
         t_dev = timed(lambda i: rc.all_reduce(src))
+        t_one = timed(lambda i: rc.all_reduce(src, force_algo=0)) if nbytes <= (1 << 20) else None
         t_peer = timed(lambda i: rc.all_reduce(src, force_algo=1))
         t_nvls = timed(lambda i: rc.all_reduce(src, force_algo=4)) if rc.mc_base else None
         y = x.clone()
         t_nccl = timed(lambda i: dist.all_reduce(y))
+        # below 1 MiB the eager numbers above are bound by the host (one Python call per collective on either side):
+        # the same launches replayed from a CUDA graph show the device time
+        g_dev = g_bar = g_nccl = None
+        if nbytes <= (1 << 20):
+            g_dev = graph_timed(lambda i: rc.all_reduce(src))
+            g_bar = graph_timed(lambda i: rc.all_reduce(src, force_algo=0))
+            try:
+                g_nccl = graph_timed(lambda i: dist.all_reduce(y))
+            except Exception:  # noqa: BLE001 - a NCCL build that cannot be captured: leave the column empty
+                g_nccl = None
         bus = 2 * (world - 1) / world * nbytes
-        report(case="all_reduce", bytes=nbytes, world=world, device_us=t_dev, peer_two_shot_us=t_peer, nvls_two_shot_us=t_nvls,
+        report(case="all_reduce", bytes=nbytes, world=world, graph_device_us=g_dev, graph_barrier_one_shot_us=g_bar, graph_nccl_us=g_nccl, device_us=t_dev, barrier_one_shot_us=t_one, peer_two_shot_us=t_peer, nvls_two_shot_us=t_nvls,
                nccl_us=t_nccl, device_busbw_gbs=bus / t_dev / 1e3, nccl_busbw_gbs=bus / t_nccl / 1e3,
                link_roofline_us=nbytes / (LINK_GBS * 1e3))
 

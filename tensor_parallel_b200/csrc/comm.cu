@@ -13,7 +13,8 @@
 // pushes / reads"), matched by block index across ranks.
 //
 // Collectives (bf16 or fp32 payload, fp32 accumulation, fixed summation order -> identical bits on all ranks):
-//   all-reduce   one-shot : every rank reads all peers' inputs and reduces everything locally
+//   all-reduce   flagged   : up to 256 KB; data and flag travel in the same 16-byte word, no barrier and no fence
+//                one-shot : every rank reads all peers' inputs and reduces everything locally
 //                two-shot : rank r reduces slice r from all peers and pushes it to every rank's output
 //   all-gather            : rank r pushes its slice to offset r of every rank's output
 //   reduce-scatter        : rank r reduces slice r from all peers into its local output
@@ -35,18 +36,21 @@ namespace tpb {
 
 constexpr int COMM_MAX_BLOCKS = TPB_COMM_MAX_BLOCKS;
 constexpr int COMM_THREADS = 512;
+constexpr int LL_BLOCKS = 64;                                  // block b always owns words i with (i / COMM_THREADS) % LL_BLOCKS == b
+constexpr long long LL_MAX_WORDS = TPB_COMM_LL_MAX_WORDS;      // 8 payload bytes per word
 
 struct CommParams {
   int world, rank;
   const void* in[TPB_MAX_WORLD];   // every rank's input buffer
   void* out[TPB_MAX_WORLD];        // every rank's output buffer
   uint32_t* sig[TPB_MAX_WORLD];    // every rank's signal array: [2][COMM_MAX_BLOCKS][TPB_MAX_WORLD]
-  uint32_t* epochs;                // local: [COMM_MAX_BLOCKS]
+  uint32_t* epochs;                // local: [2][COMM_MAX_BLOCKS] (barrier epochs | epochs of the flagged-word all-reduce)
   uint32_t* status;                // local status word
   long long n;                     // elements (all-reduce: total; all-gather / reduce-scatter: per-rank slice)
   uint64_t wait_ns;
   const void* mc_in;               // multicast view of the input buffers (null: no NVLS)
   void* mc_out;                    // multicast view of the output buffers
+  uint4* ll[TPB_MAX_WORLD];        // every rank's flagged-word area: [2 parities][world][LL_MAX_WORDS] 16-byte words
 };
 
 __device__ __forceinline__ bool block_barrier(const CommParams& p, int phase, uint32_t epoch) {
@@ -201,6 +205,58 @@ __global__ void __launch_bounds__(COMM_THREADS) collective_kernel(const CommPara
   block_barrier(p, 1, epoch);
 }
 
+// Small all-reduce without barriers or fences: every 8 payload bytes travel as one 16-byte word {lo, epoch, hi, epoch}
+// stored to every rank's flagged-word area (st.relaxed.sys.v4: the four fields of a word arrive together), and every rank
+// sums the words of all ranks as they turn up, in rank order (identical bits everywhere).  Two parities alternate: a rank
+// that writes epoch e + 2 has finished epoch e + 1, for which it needed every peer's words of e + 1, which a peer sends only
+// after it has finished reading epoch e.  The input is read locally, so it may lie anywhere.  A word is always owned by
+// the same block index, whatever the size of the call, and a block keeps its own epoch (in device memory, so that a
+// captured graph can be replayed): a word left behind by an earlier call can never carry the epoch a later one waits for.
+template <typename T>
+__global__ void __launch_bounds__(COMM_THREADS) ll_allreduce_kernel(const CommParams p, const uint2* __restrict__ in, uint2* __restrict__ out,
+                                                                     long long words) {
+  const uint32_t epoch = p.epochs[COMM_MAX_BLOCKS + blockIdx.x] + 1;
+  __syncthreads();
+  if (threadIdx.x == 0) p.epochs[COMM_MAX_BLOCKS + blockIdx.x] = epoch;
+  const long long parity_off = (long long)(epoch & 1) * p.world * LL_MAX_WORDS;
+  const long long stride = (long long)LL_BLOCKS * COMM_THREADS;
+  for (long long i = blockIdx.x * (long long)COMM_THREADS + threadIdx.x; i < words; i += stride) {
+    const uint2 d = in[i];
+#pragma unroll
+    for (int r = 0; r < TPB_MAX_WORLD; ++r)
+      if (r < p.world) st_relaxed_sys_v4(p.ll[r] + parity_off + p.rank * LL_MAX_WORDS + i, d.x, epoch, d.y, epoch);
+  }
+  const uint4* mine = p.ll[p.rank] + parity_off;
+  const uint64_t t0 = globaltimer_ns();
+  bool ok = true;
+  for (long long i = blockIdx.x * (long long)COMM_THREADS + threadIdx.x; ok && i < words; i += stride) {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int r = 0; r < TPB_MAX_WORLD; ++r) {
+      if (r < p.world && ok) {
+        uint4 w = ld_relaxed_sys_v4(mine + r * LL_MAX_WORDS + i);
+        uint32_t spins = 0;
+        while (w.y != epoch || w.w != epoch) {
+          if ((++spins & 63u) == 0 && globaltimer_ns() - t0 > p.wait_ns) {
+            atomicMax(p.status, STATUS_TIMEOUT_FLAG);
+            ok = false;
+            break;
+          }
+          w = ld_relaxed_sys_v4(mine + r * LL_MAX_WORDS + i);
+        }
+        if (sizeof(T) == 2) {
+          acc[0] += __uint_as_float(w.x << 16); acc[1] += __uint_as_float(w.x & 0xFFFF0000u);
+          acc[2] += __uint_as_float(w.z << 16); acc[3] += __uint_as_float(w.z & 0xFFFF0000u);
+        } else {
+          acc[0] += __uint_as_float(w.x); acc[1] += __uint_as_float(w.z);
+        }
+      }
+    }
+    if (ok) out[i] = sizeof(T) == 2 ? make_uint2(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]))
+                                    : make_uint2(__float_as_uint(acc[0]), __float_as_uint(acc[1]));
+  }
+}
+
 __global__ void wait_flag_test_kernel(const uint32_t* flag, uint32_t target, uint32_t* status, uint64_t wait_ns) {
   if (!wait_flag_ge(flag, target, wait_ns)) atomicMax(status, STATUS_TIMEOUT_FLAG);
 }
@@ -254,9 +310,12 @@ extern "C" int tpb_last_cuda_error(char* buf, int len) {
 // and n * sizeof(T) a multiple of 16.
 // mc_in / mc_out: multicast views of the input / output buffers (null: plain peer loads and stores).  With them, all-reduces
 // above 512 KiB, all-gathers and reduce-scatters go through the NVSwitch (force_algo 4 / 1 picks the two-shot variant by hand).
+// ll: every rank's flagged-word area (null: none).  With it, all-reduces of up to 8 * TPB_COMM_LL_MAX_WORDS bytes (force_algo 7:
+// by hand) take the barrier-free path; `local_in` (optional) is then read instead of in[rank] and may lie outside the heap.
 extern "C" int tpb_collective(int kind, int dtype, int world, int rank, void* const* in, void* const* out,
                               void* const* sig, void* epochs, void* status, long long n, int force_algo,
-                              double wait_seconds, const void* mc_in, void* mc_out, void* stream_) {
+                              double wait_seconds, const void* mc_in, void* mc_out, void* const* ll, const void* local_in,
+                              void* stream_) {
   if (world < 1 || world > TPB_MAX_WORLD || rank < 0 || rank >= world || !in || !out || !sig || !epochs || !status || n <= 0)
     return TPB_ERR_ARG;
   const int per_packet = dtype == 0 ? 8 : 4;
@@ -279,7 +338,21 @@ extern "C" int tpb_collective(int kind, int dtype, int world, int rank, void* co
   // through the switch from 4 ranks on: at 2 ranks the peer two-shot moves the same bytes with less latency
   // (128 MiB: 234 us against 377 us with multimem, NCCL 280 us; measured on B200)
   const bool nvls_auto = nvls && world >= 4;
-  if (kind == 0) mode = force_algo >= 0 ? force_algo : (bytes <= 512 * 1024 ? 0 : (nvls_auto ? 4 : 1));
+  const bool ll_ok = ll && world > 1 && bytes <= 8 * LL_MAX_WORDS;
+  if (kind == 0) mode = force_algo >= 0 ? force_algo : (ll_ok ? 7 : (bytes <= 512 * 1024 ? 0 : (nvls_auto ? 4 : 1)));
+  if (mode == 7) {
+    if (kind != 0 || !ll_ok) return TPB_ERR_ARG;
+    for (int r = 0; r < world; ++r) p.ll[r] = static_cast<uint4*>(ll[r]);
+    const long long words = bytes / 8;
+    const int ll_blocks = int(words + COMM_THREADS - 1) / COMM_THREADS > LL_BLOCKS ? LL_BLOCKS : int((words + COMM_THREADS - 1) / COMM_THREADS);
+    const uint2* src = static_cast<const uint2*>(local_in ? local_in : in[rank]);
+    if (reinterpret_cast<uintptr_t>(src) & 7) return TPB_ERR_ALIGN;
+    if (dtype == 0)
+      ll_allreduce_kernel<__nv_bfloat16><<<ll_blocks, COMM_THREADS, 0, s>>>(p, src, static_cast<uint2*>(out[rank]), words);
+    else
+      ll_allreduce_kernel<float><<<ll_blocks, COMM_THREADS, 0, s>>>(p, src, static_cast<uint2*>(out[rank]), words);
+    return cudaGetLastError() == cudaSuccess ? TPB_OK : TPB_ERR_CUDA;
+  }
   if (kind == 2 && nvls_auto && force_algo != 2) mode = 5;
   if (kind == 3 && nvls_auto && force_algo != 3) mode = 6;
   if (mode >= 4 && !nvls) return TPB_ERR_ARG;
@@ -315,6 +388,8 @@ extern "C" int tpb_comm_preload(void) {
   LOAD(__nv_bfloat16, 4); LOAD(__nv_bfloat16, 5); LOAD(__nv_bfloat16, 6);
   LOAD(float, 0); LOAD(float, 1); LOAD(float, 2); LOAD(float, 3); LOAD(float, 4); LOAD(float, 5); LOAD(float, 6);
 #undef LOAD
+  if (e == cudaSuccess) e = cudaFuncGetAttributes(&attr, ll_allreduce_kernel<__nv_bfloat16>);
+  if (e == cudaSuccess) e = cudaFuncGetAttributes(&attr, ll_allreduce_kernel<float>);
   return e == cudaSuccess ? TPB_OK : TPB_ERR_CUDA;
 }
 

@@ -21,6 +21,7 @@ enum {
 
 #define TPB_MAX_WORLD 8
 #define TPB_COMM_MAX_BLOCKS 160  // largest grid of a stand-alone collective = rows of its signal arrays (one CTA per SM and more)
+#define TPB_COMM_LL_MAX_WORDS 32768  // 16-byte words (8 payload bytes each) per rank and parity in the flagged-word area
 
 typedef struct {
   int swapped;  // 1: weight rows fill the 128 tensor-core rows (few tokens), 0: tokens do

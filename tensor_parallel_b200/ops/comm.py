@@ -23,6 +23,7 @@ from __future__ import annotations
 
 import atexit
 import ctypes
+import math
 import logging
 import os
 import socket
@@ -43,6 +44,8 @@ MAX_WORLD = 8
 COMM_MAX_BLOCKS = 160  # = TPB_COMM_MAX_BLOCKS of csrc/tpb_api.h
 SIGNAL_BYTES = 2 * COMM_MAX_BLOCKS * MAX_WORLD * 4
 MAX_TILES = native.MAX_TILES
+LL_MAX_WORDS = 32768  # = TPB_COMM_LL_MAX_WORDS of csrc/tpb_api.h: 16-byte words per rank and parity of the barrier-free all-reduce
+LL_AREA_BYTES = 2 * MAX_WORLD * LL_MAX_WORDS * 16
 
 LIB.tpb_malloc.argtypes = [ctypes.POINTER(c_void_p), ctypes.c_size_t]
 LIB.tpb_free.argtypes = [c_void_p]
@@ -51,7 +54,8 @@ LIB.tpb_ipc_get_handle.argtypes = [c_void_p, c_void_p]
 LIB.tpb_ipc_open_handle.argtypes = [c_void_p, ctypes.POINTER(c_void_p)]
 LIB.tpb_ipc_close_handle.argtypes = [c_void_p]
 LIB.tpb_collective.argtypes = [c_int, c_int, c_int, c_int, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p),
-                               ctypes.POINTER(c_void_p), c_void_p, c_void_p, c_ll, c_int, ctypes.c_double, c_void_p, c_void_p, c_void_p]
+                               ctypes.POINTER(c_void_p), c_void_p, c_void_p, c_ll, c_int, ctypes.c_double, c_void_p, c_void_p,
+                               ctypes.POINTER(c_void_p), c_void_p, c_void_p]
 _ull, _size_t = ctypes.c_ulonglong, ctypes.c_size_t
 LIB.tpb_symm_support.argtypes = [c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int)]
 LIB.tpb_symm_round_size.argtypes = [c_int, c_int, _size_t, ctypes.POINTER(_size_t)]
@@ -112,8 +116,9 @@ class HeapLayout:
         self.off_staging_in = self.off_slots + 2 * self.region_slot_bytes + g
         self.off_staging_out = self.off_staging_in + _align(staging_bytes) + g
         self.off_gather = self.off_staging_out + _align(staging_bytes) + g  # two gathered-operand buffers
-        self.total = self.off_gather + 2 * _align(gather_bytes) + g
-        self.guards = [self.off_slots - g, self.off_staging_in - g, self.off_staging_out - g, self.off_gather - g, self.total - g]
+        self.off_ll = self.off_gather + 2 * _align(gather_bytes) + g        # flagged words of the small all-reduce
+        self.total = self.off_ll + LL_AREA_BYTES + g
+        self.guards = [self.off_slots - g, self.off_staging_in - g, self.off_staging_out - g, self.off_gather - g, self.off_ll - g, self.total - g]
 
 
 class RankComm:
@@ -126,7 +131,7 @@ class RankComm:
         self.mc_base = mc_base  # multicast (NVLS) view of all ranks' regions, same offsets; 0: none
         self.heap = heap        # owner of the mappings (None: cudaMalloc'ed region, freed with the process)
         with torch.cuda.device(device):
-            self.epochs = torch.zeros(COMM_MAX_BLOCKS, dtype=torch.int32, device=device)
+            self.epochs = torch.zeros(2 * COMM_MAX_BLOCKS, dtype=torch.int32, device=device)  # barrier epochs | flagged-word epochs
             self.expected = torch.zeros(2 * MAX_TILES, dtype=torch.int32, device=device)
             self.split_counters = torch.zeros(2 * MAX_TILES, dtype=torch.int32, device=device)
             self.ll_epochs = torch.zeros(2 * MAX_TILES, dtype=torch.int32, device=device)
@@ -139,7 +144,9 @@ class RankComm:
         self._call = 0
         self._ctxs = [self._make_ctx(0), self._make_ctx(1)]
         self._ptr_arrays: Dict = {}
-        for name, off in (("in", layout.off_staging_in), ("out", layout.off_staging_out), ("sig", layout.off_signals)):
+        self._views: Dict = {}
+        self._c_epochs, self._c_status = c_void_p(self.epochs.data_ptr()), c_void_p(self.status.data_ptr())
+        for name, off in (("in", layout.off_staging_in), ("out", layout.off_staging_out), ("sig", layout.off_signals), ("ll", layout.off_ll)):
             arr = (c_void_p * MAX_WORLD)()
             for r in range(world):
                 arr[r] = self.base[r] + off
@@ -234,8 +241,9 @@ class RankComm:
 
     # -- stand-alone collectives on the staging buffers -------------------------------------------
 
-    def _collective(self, kind: int, dtype: torch.dtype, n: int, force_algo: int = -1, offset: int = 0):
-        """``offset`` (bytes, the same on every rank) moves the operation to a later part of the staging buffers."""
+    def _collective(self, kind: int, dtype: torch.dtype, n: int, force_algo: int = -1, offset: int = 0, local_in: int = 0):
+        """``offset`` (bytes, the same on every rank) moves the operation to a later part of the staging buffers;
+        ``local_in``: address the barrier-free small all-reduce reads its input from instead of the staging buffer."""
         code = 0 if dtype == torch.bfloat16 else 1
         mc_in = self.mc_base + self.layout.off_staging_in + offset if self.mc_base else 0
         mc_out = self.mc_base + self.layout.off_staging_out + offset if self.mc_base else 0
@@ -250,8 +258,9 @@ class RankComm:
                 self._ptr_arrays[key] = pair
             ins, outs = self._ptr_arrays[key]
         check(LIB.tpb_collective(kind, code, self.world, self.rank, ins, outs,
-                                 self._ptr_arrays["sig"], c_void_p(self.epochs.data_ptr()), c_void_p(self.status.data_ptr()), n,
-                                 force_algo, self.wait_seconds, c_void_p(mc_in), c_void_p(mc_out), native._stream()), "tpb_collective")
+                                 self._ptr_arrays["sig"], self._c_epochs, self._c_status, n,
+                                 force_algo, self.wait_seconds, mc_in, mc_out, self._ptr_arrays["ll"], local_in,
+                                 native._stream()), "tpb_collective")
         native.launch_count += 1
 
     def all_reduce_staged(self, offset: int, shape, dtype=torch.bfloat16) -> torch.Tensor:
@@ -274,10 +283,16 @@ class RankComm:
 
     def staging_view(self, which: str, shape, dtype) -> torch.Tensor:
         buf = self.staging_in if which == "in" else self.staging_out
-        nbytes = int(torch.Size(shape).numel()) * torch.empty((), dtype=dtype).element_size()
-        if nbytes > buf.numel():
-            raise ValueError(f"collective payload of {nbytes} bytes exceeds the staging buffer ({buf.numel()} bytes)")
-        return buf[:nbytes].view(dtype).view(shape)
+        key = (which, buf.data_ptr(), buf.numel(), tuple(shape), dtype)
+        view = self._views.get(key)  # (a collective of a few microseconds should not spend more than that on view objects)
+        if view is None:
+            nbytes = math.prod(shape) * (2 if dtype == torch.bfloat16 else torch.empty((), dtype=dtype).element_size())
+            if nbytes > buf.numel():
+                raise ValueError(f"collective payload of {nbytes} bytes exceeds the staging buffer ({buf.numel()} bytes)")
+            if len(self._views) > 256:
+                self._views.clear()
+            view = self._views[key] = buf[:nbytes].view(dtype).view(tuple(shape))
+        return view
 
     @traced("tpb.all_reduce")
     def all_reduce(self, x: torch.Tensor, force_algo: int = -1) -> torch.Tensor:
@@ -292,6 +307,12 @@ class RankComm:
             for s in range(0, n, cap):
                 out[s : s + cap].copy_(self.all_reduce(flat[s : s + cap], force_algo))
             return out.view(x.shape)
+        size = 2 if dtype == torch.bfloat16 else 4
+        if (force_algo in (-1, 7) and self.world > 1 and n_pad * size <= 8 * LL_MAX_WORDS and n_pad == n and x.dtype == dtype
+                and x.is_contiguous() and x.data_ptr() % 8 == 0):
+            # small: the barrier-free kernel reads its input where it lies (no copy into the heap)
+            self._collective(0, dtype, n_pad, force_algo, local_in=x.data_ptr())
+            return self.staging_view("out", x.shape, dtype)
         src = self.staging_view("in", (n_pad,), dtype)
         if x.data_ptr() != src.data_ptr():
             src[:n].copy_(x.reshape(-1))

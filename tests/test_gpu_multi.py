@@ -80,6 +80,16 @@ def _collectives_worker(rank, world, out_dir):
                 got = rc.all_reduce(x, force_algo=algo).clone()
             tol = dict(atol=3e-2, rtol=3e-2) if dtype == torch.bfloat16 else dict(atol=1e-5, rtol=1e-5)
             torch.testing.assert_close(got.float(), want, **tol)
+        # the barrier-free small all-reduce (algorithm 7; chosen by size up to 256 KB): sizes in changing order, so that a
+        # word is reused by calls of different extent, and more calls than there are parities
+        limit = 8 * C.LL_MAX_WORDS // x.element_size()
+        for n in (8, 4096, 65536, 8, limit, 1000 * 8, 4096, limit):
+            x = torch.randn(n, device=dev, dtype=dtype)
+            want = x.float().clone()
+            dist.all_reduce(want)
+            got = rc.all_reduce(x, force_algo=7 if n % 2 else -1).clone()
+            tol = dict(atol=3e-2, rtol=3e-2) if dtype == torch.bfloat16 else dict(atol=1e-5, rtol=1e-5)
+            torch.testing.assert_close(got.float(), want, **tol)
         x = torch.randn(3, 1000, device=dev, dtype=dtype)
         parts = [torch.empty_like(x) for _ in range(world)]
         dist.all_gather(parts, x)
