@@ -29,6 +29,8 @@
 #include <stdint.h>
 #include <string.h>
 
+#include <atomic>
+
 #include "ptx_sm100.cuh"
 #include "tpb_api.h"
 
@@ -305,21 +307,47 @@ extern "C" int tpb_last_cuda_error(char* buf, int len) {
   return TPB_OK;
 }
 
+// A CTA can only join an SM whose shared-memory / L1 split suits its kernel, and an SM changes the split only when it is
+// idle.  The GEMM and attention kernels run with the largest shared-memory carve-out; the collectives (which bypass L1
+// anyway: system-scope and multimem accesses) ask for the same one, so that their CTAs can be resident BESIDE a GEMM's
+// instead of waiting for the SMs to drain - which is what lets the prefill pipeline hide an all-reduce under a GEMM.
+static int comm_configure() {
+  static std::atomic<bool> configured[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return TPB_ERR_CUDA;
+  if (configured[dev].load(std::memory_order_acquire)) return TPB_OK;
+  cudaError_t e = cudaSuccess;
+#define CARVE(K) if (e == cudaSuccess) e = cudaFuncSetAttribute(K, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared)
+#define CARVE_ALL(T) CARVE((collective_kernel<T, 0>)); CARVE((collective_kernel<T, 1>)); CARVE((collective_kernel<T, 2>)); \
+                     CARVE((collective_kernel<T, 3>)); CARVE((collective_kernel<T, 4>)); CARVE((collective_kernel<T, 5>)); \
+                     CARVE((collective_kernel<T, 6>)); CARVE((ll_allreduce_kernel<T>))
+  CARVE_ALL(__nv_bfloat16);
+  CARVE_ALL(float);
+#undef CARVE_ALL
+#undef CARVE
+  if (e != cudaSuccess) return TPB_ERR_CUDA;
+  configured[dev].store(true, std::memory_order_release);
+  return TPB_OK;
+}
+
 // kind: 0 all-reduce (algorithm chosen by size), 2 all-gather, 3 reduce-scatter.  dtype: 0 bf16, 1 fp32.
 // `n` = total elements for all-reduce, per-rank slice elements otherwise.  Buffers must be 16-byte aligned
 // and n * sizeof(T) a multiple of 16.
 // mc_in / mc_out: multicast views of the input / output buffers (null: plain peer loads and stores).  With them, all-reduces
 // above 512 KiB, all-gathers and reduce-scatters go through the NVSwitch (force_algo 4 / 1 picks the two-shot variant by hand).
+// block_threads: 0 (512) or 128 / 256: a collective that should run BESIDE another kernel (a GEMM that holds 48 K registers of
+// every SM) must fit into what that kernel leaves free; 256 threads of at most 64 registers do.
 // ll: every rank's flagged-word area (null: none).  With it, all-reduces of up to 8 * TPB_COMM_LL_MAX_WORDS bytes (force_algo 7:
 // by hand) take the barrier-free path; `local_in` (optional) is then read instead of in[rank] and may lie outside the heap.
 extern "C" int tpb_collective(int kind, int dtype, int world, int rank, void* const* in, void* const* out,
                               void* const* sig, void* epochs, void* status, long long n, int force_algo,
                               double wait_seconds, const void* mc_in, void* mc_out, void* const* ll, const void* local_in,
-                              void* stream_) {
+                              int block_threads, void* stream_) {
   if (world < 1 || world > TPB_MAX_WORLD || rank < 0 || rank >= world || !in || !out || !sig || !epochs || !status || n <= 0)
     return TPB_ERR_ARG;
   const int per_packet = dtype == 0 ? 8 : 4;
   if (n % per_packet) return TPB_ERR_ALIGN;
+  if (comm_configure() != TPB_OK) return TPB_ERR_CUDA;
   CommParams p;
   memset(&p, 0, sizeof(p));
   p.world = world;
@@ -358,10 +386,11 @@ extern "C" int tpb_collective(int kind, int dtype, int world, int rank, void* co
   if (mode >= 4 && !nvls) return TPB_ERR_ARG;
   const long long packets = n / per_packet;
   long long work = (mode == 1 || mode == 4) ? (packets + world - 1) / world : packets;
-  int blocks = int((work + COMM_THREADS - 1) / COMM_THREADS);
+  const int threads = (block_threads == 128 || block_threads == 256) ? block_threads : COMM_THREADS;
+  int blocks = int((work + threads - 1) / threads);
   if (blocks < 1) blocks = 1;
   if (blocks > COMM_MAX_BLOCKS) blocks = COMM_MAX_BLOCKS;
-#define RUN(T, M) collective_kernel<T, M><<<blocks, COMM_THREADS, 0, s>>>(p)
+#define RUN(T, M) collective_kernel<T, M><<<blocks, threads, 0, s>>>(p)
   if (dtype == 0) {
     switch (mode) { case 0: RUN(__nv_bfloat16, 0); break; case 1: RUN(__nv_bfloat16, 1); break;
                     case 2: RUN(__nv_bfloat16, 2); break; case 3: RUN(__nv_bfloat16, 3); break;

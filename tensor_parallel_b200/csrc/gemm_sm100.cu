@@ -240,8 +240,11 @@ struct WorkIter {
 // accumulate into the same TMEM columns serialise on the accumulator; at N = 16 / 32 one instruction is
 // far shorter than that dependent latency, so the k-steps are dealt round-robin to NACC accumulators that
 // the epilogue adds up.  (At N >= 64 one accumulator keeps the tensor pipe busy.)
+// Register budget: the many-token instantiations (BN >= 128) are compiled as if two CTAs had to share an SM (at most 168
+// registers per thread, although shared memory admits one CTA only): that leaves every SM sub-partition room for the
+// warps of a small-footprint collective kernel, which is how the prefill pipeline runs an all-reduce BESIDE a GEMM.
 template <int BN, int KBOX, int NACC>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(NUM_THREADS, BN >= 128 ? 2 : 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                          const GemmParams p) {
   constexpr uint32_t A_BYTES = BM * BK * 2;

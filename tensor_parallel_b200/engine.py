@@ -424,7 +424,7 @@ class DecoderEngine:
             ready.record(main)
             side.wait_event(ready)
             with torch.cuda.stream(side):
-                out = comm.all_reduce_staged(h * region, staged(h).shape)
+                out = comm.all_reduce_staged(h * region, staged(h).shape, block_threads=256)  # fits beside a GEMM's CTAs
                 done = torch.cuda.Event()
                 done.record(side)
             pending[h] = (done, out, bias)

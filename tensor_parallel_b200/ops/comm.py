@@ -55,7 +55,7 @@ LIB.tpb_ipc_open_handle.argtypes = [c_void_p, ctypes.POINTER(c_void_p)]
 LIB.tpb_ipc_close_handle.argtypes = [c_void_p]
 LIB.tpb_collective.argtypes = [c_int, c_int, c_int, c_int, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p),
                                ctypes.POINTER(c_void_p), c_void_p, c_void_p, c_ll, c_int, ctypes.c_double, c_void_p, c_void_p,
-                               ctypes.POINTER(c_void_p), c_void_p, c_void_p]
+                               ctypes.POINTER(c_void_p), c_void_p, c_int, c_void_p]
 _ull, _size_t = ctypes.c_ulonglong, ctypes.c_size_t
 LIB.tpb_symm_support.argtypes = [c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int)]
 LIB.tpb_symm_round_size.argtypes = [c_int, c_int, _size_t, ctypes.POINTER(_size_t)]
@@ -241,7 +241,8 @@ class RankComm:
 
     # -- stand-alone collectives on the staging buffers -------------------------------------------
 
-    def _collective(self, kind: int, dtype: torch.dtype, n: int, force_algo: int = -1, offset: int = 0, local_in: int = 0):
+    def _collective(self, kind: int, dtype: torch.dtype, n: int, force_algo: int = -1, offset: int = 0, local_in: int = 0,
+                    block_threads: int = 0):
         """``offset`` (bytes, the same on every rank) moves the operation to a later part of the staging buffers;
         ``local_in``: address the barrier-free small all-reduce reads its input from instead of the staging buffer."""
         code = 0 if dtype == torch.bfloat16 else 1
@@ -260,19 +261,20 @@ class RankComm:
         check(LIB.tpb_collective(kind, code, self.world, self.rank, ins, outs,
                                  self._ptr_arrays["sig"], self._c_epochs, self._c_status, n,
                                  force_algo, self.wait_seconds, mc_in, mc_out, self._ptr_arrays["ll"], local_in,
-                                 native._stream()), "tpb_collective")
+                                 block_threads, native._stream()), "tpb_collective")
         native.launch_count += 1
 
-    def all_reduce_staged(self, offset: int, shape, dtype=torch.bfloat16) -> torch.Tensor:
+    def all_reduce_staged(self, offset: int, shape, dtype=torch.bfloat16, block_threads: int = 0) -> torch.Tensor:
         """Sum over ranks of the tensor that already lies in the staging-in buffer at byte ``offset`` (a multiple of
         1024, the same on every rank); returns the view of the staging-out buffer that holds the result.  Launches on
         the current stream: callers that overlap the reduction with other work (``engine.py``: prefill) call it under a
-        side stream, one collective at a time and in the same order on every rank."""
+        side stream, one collective at a time and in the same order on every rank; ``block_threads=256`` keeps the
+        kernel's CTAs small enough to be resident beside the CTAs of a GEMM."""
         n = int(torch.Size(shape).numel())
         size = 2 if dtype == torch.bfloat16 else 4
         if offset % 1024 or (n * size) % 16 or offset + n * size > self.staging_in.numel():
             raise ValueError("staged all-reduce: misaligned or outside the staging buffers")
-        self._collective(0, dtype, n, offset=offset)
+        self._collective(0, dtype, n, offset=offset, block_threads=block_threads)
         return self.staging_out[offset : offset + n * size].view(dtype).view(shape)
 
     def _capacity(self, dtype: torch.dtype, in_copies: int, out_copies: int) -> int:
