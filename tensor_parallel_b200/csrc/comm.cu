@@ -141,7 +141,7 @@ __device__ __forceinline__ uint4 reduce_packet(const CommParams& p, long long pa
 
 // mode: 0 all-reduce one-shot, 1 all-reduce two-shot, 2 all-gather, 3 reduce-scatter; 4, 5, 6 = 1, 2, 3 through the multicast view
 template <typename T, int MODE>
-__global__ void __launch_bounds__(COMM_THREADS) collective_kernel(const CommParams p) {
+__global__ void __launch_bounds__(COMM_THREADS, 3) collective_kernel(const CommParams p) {
   const uint32_t epoch = p.epochs[blockIdx.x] + 1;
   __syncthreads();
   if (threadIdx.x == 0) p.epochs[blockIdx.x] = epoch;
