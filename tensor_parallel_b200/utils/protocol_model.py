@@ -15,6 +15,8 @@ What is modelled, word for word:
 
 The two halves are enough because a rank can run at most one call ahead of a peer: its call ``i + 1`` cannot complete
 before that peer has pushed its own call ``i + 1``, which the peer does only after it has finished reading call ``i``.
+
+The same module models the barrier-free small all-reduce of ``csrc/comm.cu`` (``SmallAllReduceRank``).
 """
 from __future__ import annotations
 
@@ -133,6 +135,101 @@ def run_ranks(world: int, calls: Sequence[Tuple[int, int]], tile_keyed: bool = T
     if failures:
         raise failures[0]
     return [max(errors[r][c] for r in range(world)) for c in range(len(calls))]
+
+
+# ---------------------------------------------------------------------------------------------------
+# barrier-free small all-reduce (``ll_allreduce_kernel`` in csrc/comm.cu)
+# ---------------------------------------------------------------------------------------------------
+
+SMALL_BLOCKS = 4    # the kernel's LL_BLOCKS (64 there): block b owns the words i with (i // SMALL_THREADS) % SMALL_BLOCKS == b
+SMALL_THREADS = 8   # the kernel's COMM_THREADS (512 there)
+
+
+class SmallAllReduceHeap:
+    """``mem[dest][parity][src]`` maps a word index to ``(value, flag)`` (the kernel's word carries the flag twice)."""
+
+    def __init__(self, world: int, parities: int = 2):
+        self.world, self.parities = world, parities
+        self.mem = [[[dict() for _ in range(world)] for _ in range(parities)] for _ in range(world)]
+
+
+class SmallAllReduceRank:
+    """One rank of the small all-reduce: per-block epochs that only grow, ``parities`` alternating areas (2 in the
+    kernel; 1 shows why one is not enough), no barrier: a word is accepted when its flag equals the block's epoch."""
+
+    def __init__(self, heap: SmallAllReduceHeap, rank: int, jitter: float = 0.0, seed: int = 0):
+        self.heap, self.rank = heap, rank
+        self.epochs = [0] * SMALL_BLOCKS
+        self.rng = random.Random(seed * 104729 + rank)
+        self.jitter = jitter
+
+    def _pause(self):
+        if self.jitter:
+            time.sleep(self.rng.random() * self.jitter)
+
+    def all_reduce(self, values: Sequence[float], timeout: float = 2.0, read_delay: float = 0.0) -> List[float]:
+        words, world = len(values), self.heap.world
+        blocks = min(SMALL_BLOCKS, -(-words // SMALL_THREADS))
+        out = [0.0] * words
+        order = list(range(blocks))
+        self.rng.shuffle(order)  # blocks of one launch run in any order
+        owned = {b: [i for i in range(words) if (i // SMALL_THREADS) % SMALL_BLOCKS == b] for b in order}
+        flags = {}
+        for b in order:  # every block first sends all its words ...
+            self.epochs[b] += 1
+            flags[b] = self.epochs[b]
+            par = flags[b] % self.heap.parities
+            for i in owned[b]:
+                for dest in range(world):
+                    self.heap.mem[dest][par][self.rank][i] = (values[i], flags[b])
+                self._pause()
+        if read_delay:
+            time.sleep(read_delay)
+        deadline = time.monotonic() + timeout
+        for b in order:  # ... then sums what arrives, in rank order
+            par = flags[b] % self.heap.parities
+            for i in owned[b]:
+                acc = 0.0
+                for src in range(world):
+                    while True:
+                        w = self.heap.mem[self.rank][par][src].get(i)
+                        if w is not None and w[1] == flags[b]:
+                            break
+                        if time.monotonic() > deadline:
+                            raise TimeoutError(f"rank {self.rank}: word {i} of rank {src} never showed flag {flags[b]} (found {w})")
+                        time.sleep(0)
+                    acc += w[0]
+                out[i] = acc
+        return out
+
+
+def run_small_all_reduce(world: int, sizes: Sequence[int], parities: int = 2, jitter: float = 0.0, seed: int = 0,
+                         read_delay: Dict[Tuple[int, int], float] = None, timeout: float = 2.0):
+    """``sizes`` = words per call.  Rank ``k`` contributes ``(k + 1) * (call + 1 + i / 1024)``; returns the largest absolute
+    error per call.  ``read_delay[(rank, call)]``: seconds that rank waits between its sends and its reads."""
+    heap = SmallAllReduceHeap(world, parities)
+    errors: List[List[float]] = [[] for _ in range(world)]
+    failures: List[BaseException] = []
+
+    def body(rank):
+        me = SmallAllReduceRank(heap, rank, jitter, seed)
+        try:
+            for c, words in enumerate(sizes):
+                vals = [(rank + 1) * (c + 1 + i / 1024.0) for i in range(words)]
+                got = me.all_reduce(vals, timeout=timeout, read_delay=(read_delay or {}).get((rank, c), 0.0))
+                scale = sum(r + 1 for r in range(world))
+                errors[rank].append(max(abs(got[i] - scale * (c + 1 + i / 1024.0)) for i in range(words)))
+        except BaseException as e:
+            failures.append(e)
+
+    threads = [threading.Thread(target=body, args=(r,)) for r in range(world)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    if failures:
+        raise failures[0]
+    return [max(errors[r][c] for r in range(world)) for c in range(len(sizes))]
 
 
 # ---------------------------------------------------------------------------------------------------

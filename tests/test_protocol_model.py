@@ -37,6 +37,27 @@ def test_shape_dependent_addresses_would_accept_stale_words():
     assert max(errs) < 1e-9, errs   # ... the tile-keyed order waits for the straggler and gets it right
 
 
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_small_all_reduce_is_exact_for_changing_sizes(world):
+    """Sizes in changing order (a word is reused by calls of different extent; blocks that only large calls use keep
+    lower epochs) and more calls than parities, under random thread schedules."""
+    sizes = [3, 32, 100, 3, 8, 100, 17, 64, 100, 3]
+    for seed in range(2):
+        errs = pm.run_small_all_reduce(world, sizes, jitter=1e-4, seed=seed)
+        assert max(errs) < 1e-9, errs
+
+
+def test_small_all_reduce_needs_both_parities():
+    """A rank that is slow to READ call 0 while its peer races ahead: with two alternating areas the peer's words of call
+    1 land beside those of call 0, and the peer cannot start call 2 before the slow rank has sent call 1 (after its
+    reads); with a single area the words of call 1 overwrite what the slow rank still has to read."""
+    slow = {(1, 0): 0.3}
+    errs = pm.run_small_all_reduce(2, [16, 16, 16], parities=2, read_delay=slow)
+    assert max(errs) < 1e-9, errs
+    with pytest.raises(TimeoutError):
+        pm.run_small_all_reduce(2, [16, 16, 16], parities=1, read_delay=slow, timeout=1.0)
+
+
 def test_nvtx_ranges_nest_and_are_free_when_off():
     calls = []
 
