@@ -1357,9 +1357,10 @@ static int gemm_impl(const void* x, const void* w, void* out, const void* bias, 
     p.split_counters = static_cast<uint32_t*>(rc->split_counters);
     p.slot_stride = rc->slot_stride;
     p.status = static_cast<uint32_t*>(rc->status);
-    // default: up to 4 ranks.  At 8 ranks the arrival-counter protocol measured faster (15.8 vs 17.6 us for the o_proj
-    // shard of a Llama-2-7B layer): a thread then polls 8 x tokens flagged words, which costs more than one fence.
-    const bool ll_wanted = g_disable_ll < 0 || (g_disable_ll == 0 && rc->world <= 4);
+    // default: flagged words at every rank count for up to 16 tokens (with bf16 words, 8 ranks, 8 tokens, replayed from
+    // a CUDA graph: 13.3 vs 16.1 us for the o_proj shard of a Llama-2-7B layer, 15.7 vs 20.8 us for down_proj); beyond
+    // 16 tokens at more than 4 ranks a thread polls many words per row and the arrival counters stay the default.
+    const bool ll_wanted = g_disable_ll < 0 || (g_disable_ll == 0 && (rc->world <= 4 || tokens <= 16));
     if (rc->world > 1 && plan->swapped && act != 5 && rc->ll_epochs && ll_wanted && rc->max_slots >= LL_FIRST_SLOT + 2 * rc->world &&
         rc->world + plan->k_splits <= LL_FIRST_SLOT && size_t(plan->tiles) * LL_TILE_WORDS <= rc->slot_stride / 2) {
       p.ll = 1;
