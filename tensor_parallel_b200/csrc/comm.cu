@@ -214,7 +214,8 @@ __global__ void __launch_bounds__(COMM_THREADS, 3) collective_kernel(const CommP
 // after it has finished reading epoch e.  The input is read locally, so it may lie anywhere.  A word is always owned by
 // the same block index, whatever the size of the call, and a block keeps its own epoch (in device memory, so that a
 // captured graph can be replayed): a word left behind by an earlier call can never carry the epoch a later one waits for.
-template <typename T>
+// GATHER: the same exchange without the sum - rank r's words land at out[r * words + i] (a small all-gather).
+template <typename T, bool GATHER = false>
 __global__ void __launch_bounds__(COMM_THREADS) ll_allreduce_kernel(const CommParams p, const uint2* __restrict__ in, uint2* __restrict__ out,
                                                                      long long words) {
   const uint32_t epoch = p.epochs[COMM_MAX_BLOCKS + blockIdx.x] + 1;
@@ -246,7 +247,9 @@ __global__ void __launch_bounds__(COMM_THREADS) ll_allreduce_kernel(const CommPa
           }
           w = ld_relaxed_sys_v4(mine + r * LL_MAX_WORDS + i);
         }
-        if (sizeof(T) == 2) {
+        if (GATHER) {
+          if (ok) out[r * words + i] = make_uint2(w.x, w.z);
+        } else if (sizeof(T) == 2) {
           acc[0] += __uint_as_float(w.x << 16); acc[1] += __uint_as_float(w.x & 0xFFFF0000u);
           acc[2] += __uint_as_float(w.z << 16); acc[3] += __uint_as_float(w.z & 0xFFFF0000u);
         } else {
@@ -254,7 +257,7 @@ __global__ void __launch_bounds__(COMM_THREADS) ll_allreduce_kernel(const CommPa
         }
       }
     }
-    if (ok) out[i] = sizeof(T) == 2 ? make_uint2(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]))
+    if (ok && !GATHER) out[i] = sizeof(T) == 2 ? make_uint2(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]))
                                     : make_uint2(__float_as_uint(acc[0]), __float_as_uint(acc[1]));
   }
 }
@@ -320,7 +323,7 @@ static int comm_configure() {
 #define CARVE(K) if (e == cudaSuccess) e = cudaFuncSetAttribute(K, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared)
 #define CARVE_ALL(T) CARVE((collective_kernel<T, 0>)); CARVE((collective_kernel<T, 1>)); CARVE((collective_kernel<T, 2>)); \
                      CARVE((collective_kernel<T, 3>)); CARVE((collective_kernel<T, 4>)); CARVE((collective_kernel<T, 5>)); \
-                     CARVE((collective_kernel<T, 6>)); CARVE((ll_allreduce_kernel<T>))
+                     CARVE((collective_kernel<T, 6>)); CARVE((ll_allreduce_kernel<T, false>)); CARVE((ll_allreduce_kernel<T, true>))
   CARVE_ALL(__nv_bfloat16);
   CARVE_ALL(float);
 #undef CARVE_ALL
@@ -368,6 +371,17 @@ extern "C" int tpb_collective(int kind, int dtype, int world, int rank, void* co
   const bool nvls_auto = nvls && world >= 4;
   const bool ll_ok = ll && world > 1 && bytes <= 8 * LL_MAX_WORDS;
   if (kind == 0) mode = force_algo >= 0 ? force_algo : (ll_ok ? 7 : (bytes <= 512 * 1024 ? 0 : (nvls_auto ? 4 : 1)));
+  if (kind == 2 && ll_ok && (force_algo < 0 || force_algo == 8)) mode = 8;  // small all-gather: the same words, not summed
+  if (mode == 8) {
+    if (kind != 2 || !ll_ok) return TPB_ERR_ARG;
+    for (int r = 0; r < world; ++r) p.ll[r] = static_cast<uint4*>(ll[r]);
+    const long long words = bytes / 8;
+    const int ll_blocks = int(words + COMM_THREADS - 1) / COMM_THREADS > LL_BLOCKS ? LL_BLOCKS : int((words + COMM_THREADS - 1) / COMM_THREADS);
+    const uint2* src = static_cast<const uint2*>(local_in ? local_in : in[rank]);
+    if (reinterpret_cast<uintptr_t>(src) & 7) return TPB_ERR_ALIGN;
+    ll_allreduce_kernel<float, true><<<ll_blocks, COMM_THREADS, 0, s>>>(p, src, static_cast<uint2*>(out[rank]), words);  // (bytes are bytes)
+    return cudaGetLastError() == cudaSuccess ? TPB_OK : TPB_ERR_CUDA;
+  }
   if (mode == 7) {
     if (kind != 0 || !ll_ok) return TPB_ERR_ARG;
     for (int r = 0; r < world; ++r) p.ll[r] = static_cast<uint4*>(ll[r]);
@@ -381,7 +395,7 @@ extern "C" int tpb_collective(int kind, int dtype, int world, int rank, void* co
       ll_allreduce_kernel<float><<<ll_blocks, COMM_THREADS, 0, s>>>(p, src, static_cast<uint2*>(out[rank]), words);
     return cudaGetLastError() == cudaSuccess ? TPB_OK : TPB_ERR_CUDA;
   }
-  if (kind == 2 && nvls_auto && force_algo != 2) mode = 5;
+  if (kind == 2 && nvls_auto && force_algo != 2) mode = 5;  // (a small one takes the flagged-word path below instead)
   if (kind == 3 && nvls_auto && force_algo != 3) mode = 6;
   if (mode >= 4 && !nvls) return TPB_ERR_ARG;
   const long long packets = n / per_packet;
@@ -419,6 +433,7 @@ extern "C" int tpb_comm_preload(void) {
 #undef LOAD
   if (e == cudaSuccess) e = cudaFuncGetAttributes(&attr, ll_allreduce_kernel<__nv_bfloat16>);
   if (e == cudaSuccess) e = cudaFuncGetAttributes(&attr, ll_allreduce_kernel<float>);
+  if (e == cudaSuccess) e = cudaFuncGetAttributes(&attr, ll_allreduce_kernel<float, true>);
   return e == cudaSuccess ? TPB_OK : TPB_ERR_CUDA;
 }
 
