@@ -385,6 +385,9 @@ attn_decode_fused_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k,
   const int bh = blockIdx.x;
   const int b = bh / kv_heads, kvh = bh % kv_heads;
   const int split = blockIdx.y;
+  // several groups of G query heads of the same KV head may share a launch (grid z): each has its own arrival counter
+  g_offset += blockIdx.z * G;
+  counters += (size_t)blockIdx.z * gridDim.x;
   const int pos = pos_ptr[0];
   const int len = min(pos + 1, max_seq);
   const int chunk = (len + splits - 1) / splits;
@@ -910,14 +913,15 @@ extern "C" int tpb_rope_table(void* table, int positions, int rotary_dim, float 
 // One launch per decode step and layer: RoPE(q, k) + cache append + attention over [0, pos] + split combine.
 // q / k / v: rows of the projection output for ONE new token per sequence ([batch, heads * head_dim], row pitches
 // q_ld / k_ld / v_ld); pos_ptr[0] = position of the new token = number of tokens already cached.
-// part_o / part_ml as for tpb_attn_decode; counters: uint32 [batch * kv_heads], zeroed once by the caller.
+// part_o / part_ml as for tpb_attn_decode; counters: uint32 [counter_elems] >= batch * kv_heads, zeroed once by the caller;
+// with batch * q_heads of them every group of query heads of a KV head fits into ONE launch (GQA / MQA with large groups).
 // rope_table: optional output of tpb_rope_table covering every position < max_seq (null: angles are computed in place).
 // out: [batch][q_heads * head_dim] with a row pitch of out_ld elements (<= 0: dense).
 extern "C" int tpb_attn_decode_fused(const void* q, const void* k, const void* v, void* kcache, void* vcache, void* out,
                                      float* part_o, float* part_ml, void* counters, const int* pos_ptr, int batch, int q_heads,
                                      int kv_heads, int head_dim, int max_seq, int splits, float scale, int rotary_dim, float theta,
                                      int interleaved, long long q_ld, long long k_ld, long long v_ld, const void* rope_table,
-                                     long long out_ld, void* stream_) {
+                                     long long out_ld, int counter_elems, void* stream_) {
   if (!q || !k || !v || !kcache || !vcache || !out || !pos_ptr || batch <= 0 || splits < 1 || q_heads % kv_heads) return TPB_ERR_ARG;
   if (splits > 1 && (!part_o || !part_ml || !counters)) return TPB_ERR_ARG;
   if (head_dim != 64 && head_dim != 128) return TPB_ERR_SIZE;
@@ -927,13 +931,16 @@ extern "C" int tpb_attn_decode_fused(const void* q, const void* k, const void* v
   const int g_total = q_heads / kv_heads;
   const float sl2 = scale * 1.4426950408889634f;
   const float l2t = log2f(theta);
-  dim3 grid(batch * kv_heads, splits);
   int done = 0, launches = 0;
   while (done < g_total) {
     const int left = g_total - done;
     const int gmax = head_dim == 128 ? 4 : 8;
     int gnow = 1;
     while (gnow * 2 <= left && gnow * 2 <= gmax) gnow *= 2;
+    // equal groups share one launch (grid z) when the caller's counter array has a counter for each of them
+    int reps = left / gnow;
+    if (splits > 1 && (long long)batch * kv_heads * reps > counter_elems) reps = 1;
+    dim3 grid(batch * kv_heads, splits, reps);
 #define DECF(D, G)                                                                                                           \
   if (!dec_smem_ready<attn_decode_fused_kernel<D, G>>(dec_ring_bytes<D>())) return TPB_ERR_CUDA;                               \
   launch_kernel(attn_decode_fused_kernel<D, G>, grid, dim3(DEC_THREADS), dec_ring_bytes<D>(), s, (const bf16*)q, (const bf16*)k, (const bf16*)v, \
@@ -945,7 +952,7 @@ extern "C" int tpb_attn_decode_fused(const void* q, const void* k, const void* v
       if (gnow == 1) { DECF(64, 1); } else if (gnow == 2) { DECF(64, 2); } else if (gnow == 4) { DECF(64, 4); } else { DECF(64, 8); }
     }
 #undef DECF
-    done += gnow;
+    done += gnow * reps;
     ++launches;
   }
   g_last_launches = launches;

@@ -196,10 +196,12 @@ class DecoderEngine:
         self.next_ids = torch.zeros(B, dtype=torch.int64, device=dev)
         self.rope_angles = native.rope_table(max_seq, spec.rotary_dim, self.theta, dev) if spec.rotary_dim else None
         # split the key range only when (batch x kv heads) alone cannot occupy the SMs
-        self.splits = 1 if B * self.nkv >= 128 else max(1, min(8, math.ceil(256 / (B * self.nkv))))
+        # (a KV head's query heads run in groups of up to 4 (head_dim 128) or 8 (64) per CTA, all groups in one launch)
+        ctas = B * self.nkv * math.ceil(self.nq / self.nkv / (4 if D == 128 else 8))
+        self.splits = 1 if ctas >= 128 else max(1, min(8, math.ceil(256 / ctas)))
         self.attn_ws = (torch.empty(B * self.nq * self.splits * D, dtype=torch.float32, device=dev),
                         torch.empty(B * self.nq * self.splits * 2, dtype=torch.float32, device=dev),
-                        torch.zeros(B * self.nkv, dtype=torch.int32, device=dev))
+                        torch.zeros(B * self.nq, dtype=torch.int32, device=dev))  # one arrival counter per group of query heads
         self.status_host = torch.zeros(4, dtype=torch.int32).pin_memory()
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.graph_batch = 0

@@ -667,7 +667,7 @@ def attn_decode(q, kcache, vcache, len_ptr, len_add, scale=None, splits=1, works
     return out
 
 
-LIB.tpb_attn_decode_fused.argtypes = [c_void_p] * 10 + [c_int] * 6 + [c_float, c_int, c_float, c_int, c_ll, c_ll, c_ll, c_void_p, c_ll, c_void_p]
+LIB.tpb_attn_decode_fused.argtypes = [c_void_p] * 10 + [c_int] * 6 + [c_float, c_int, c_float, c_int, c_ll, c_ll, c_ll, c_void_p, c_ll, c_int, c_void_p]
 LIB.tpb_rope_table.argtypes = [c_void_p, c_int, c_int, c_float, c_void_p]
 
 
@@ -685,7 +685,8 @@ def attn_decode_fused(q, k, v, kcache, vcache, pos_ptr, rotary_dim, theta, inter
                       workspace=None, out=None, rope_angles=None):
     """One decode step of attention in a single launch: rotate q / k of the new token (``q/k/v``: 2-D row views of the
     projection output), append k, v to the cache at ``pos_ptr[0]``, attend over ``[0, pos]`` and merge the key splits.
-    ``workspace = (part_o, part_ml, counters)`` with ``counters`` an int32 tensor ``[batch * kv_heads]`` zeroed once."""
+    ``workspace = (part_o, part_ml, counters)`` with ``counters`` an int32 tensor of at least ``batch * kv_heads`` elements
+    zeroed once (``batch * q_heads``: all query-head groups of a KV head share one launch)."""
     global launch_count
     d = kcache.shape[3]
     b, hq, hkv, smax = q.shape[0], q.shape[1] // d, kcache.shape[1], kcache.shape[2]
@@ -695,13 +696,13 @@ def attn_decode_fused(q, k, v, kcache, vcache, pos_ptr, rotary_dim, theta, inter
         if workspace is None:
             workspace = (torch.empty(b * hq * splits * d, dtype=torch.float32, device=q.device),
                          torch.empty(b * hq * splits * 2, dtype=torch.float32, device=q.device),
-                         torch.zeros(b * hkv, dtype=torch.int32, device=q.device))
+                         torch.zeros(b * hq, dtype=torch.int32, device=q.device))
         part_o, part_ml, counters = workspace
     scale = 1.0 / math.sqrt(d) if scale is None else scale
     check(LIB.tpb_attn_decode_fused(_ptr(q), _ptr(k), _ptr(v), _ptr(kcache), _ptr(vcache), _ptr(out), _ptr(part_o), _ptr(part_ml),
                                     _ptr(counters), _ptr(pos_ptr), b, hq, hkv, d, smax, splits, scale, rotary_dim, theta,
                                     int(interleaved), q.stride(0), k.stride(0), v.stride(0), _ptr(rope_angles),
-                                    out.stride(0) if out.stride(0) != hq * d else 0, _stream()),
+                                    out.stride(0) if out.stride(0) != hq * d else 0, 0 if counters is None else counters.numel(), _stream()),
           "tpb_attn_decode_fused")
     launch_count += LIB.tpb_last_launches()
     return out

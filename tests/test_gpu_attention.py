@@ -162,7 +162,7 @@ def test_rope_append_variants(interleaved, rotary_dim):
     assert kc[:, :, :base].abs().sum().item() == 0 and kc[:, :, base + s :].abs().sum().item() == 0
 
 
-@pytest.mark.parametrize("hq,hkv,d", [(8, 8, 128), (8, 2, 128), (16, 1, 64), (6, 2, 64)])
+@pytest.mark.parametrize("hq,hkv,d", [(8, 8, 128), (8, 2, 128), (16, 1, 64), (6, 2, 64), (8, 1, 128), (24, 1, 64)])
 @pytest.mark.parametrize("splits,angle_table", [(1, False), (4, False), (4, True)])
 def test_fused_decode_step_matches_separate_kernels(hq, hkv, d, splits, angle_table):
     """rope + append + attention + split merge in one launch vs the three stand-alone kernels, two steps in a row."""
@@ -185,8 +185,12 @@ def test_fused_decode_step_matches_separate_kernels(hq, hkv, d, splits, angle_ta
         want = nat.attn_decode(q_out, kc, vc, pos, 1, splits=splits)
         if ws is None and splits > 1:
             ws = (torch.empty(b * hq * splits * d, device="cuda"), torch.empty(b * hq * splits * 2, device="cuda"),
-                  torch.zeros(b * hkv, dtype=torch.int32, device="cuda"))
+                  # one counter per KV head: a launch per group of query heads; one per query head: the groups share a launch
+                  torch.zeros(b * (hq if angle_table else hkv), dtype=torch.int32, device="cuda"))
+        before = nat.launch_count
         got = nat.attn_decode_fused(q2, k2, v2, kc2, vc2, pos, d, 10000.0, splits=splits, workspace=ws, rope_angles=angles)
+        if angle_table and (hq // hkv) in (8, 16) and (hq // hkv) > (4 if d == 128 else 8) - 1 and (hq // hkv) % (4 if d == 128 else 8) == 0:
+            assert nat.launch_count - before == 1, "equal groups of query heads should share one launch"
         torch.testing.assert_close(got.float(), want.float(), atol=1e-2, rtol=1e-2)
         torch.testing.assert_close(kc2, kc)
         torch.testing.assert_close(vc2, vc)
