@@ -88,6 +88,7 @@ struct GemmParams {
   // 8-byte word {value, epoch}; the receiver spins on the word itself, so no fence and no arrival counter is needed
   int ll;
   uint32_t* ll_epochs;            // local: [tiles] epoch of the previous flagged call (device-resident: graph replays advance it)
+  float* mc_slots;                // NVLink multicast alias of every rank's slot area (null: one peer store per rank instead)
   // fused all-gather of the token-side operand (ag_world > 1): every rank owns a column slice [rows, ag_cols] of x;
   // the kernel first pushes its slice into every rank's gathered buffer, then consumes k-blocks slice by slice
   // (own slice first) as the peers' pushes arrive
@@ -763,6 +764,18 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       const size_t ll_row = size_t(tile) * LL_TILE_WORDS + size_t(row);  // this thread's word of token quad 0; quad q is 128 q words on
       auto push_ll = [&](int n0, const float (&v)[16]) {
         if (!chunk_valid(n0)) return;
+        if (p.mc_slots) {
+          // one multimem.st per word reaches this rank's slot in EVERY rank's workspace (the NVSwitch replicates it); each
+          // 8-byte half of a word carries its own copy of the flag, so nothing depends on the 16 bytes landing together
+          uint4* dst = reinterpret_cast<uint4*>(p.mc_slots + size_t(LL_FIRST_SLOT + 2 * p.rank) * p.slot_stride) + ll_row + size_t(n0 >> 2) * BM;
+          if (!TPB_IN_BOUNDS(ll_row + size_t((n0 >> 2) + 3) * BM < (p.slot_stride >> 1), p.status)) return;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            if (n0 + 4 * q >= p.n_extent) break;
+            multimem_st(dst + q * BM, make_uint4(pack_bf16x2(v[4 * q], v[4 * q + 1]), ll_flag, pack_bf16x2(v[4 * q + 2], v[4 * q + 3]), ll_flag));
+          }
+          return;
+        }
 #pragma unroll 1  // (rolled: small code, see read_acc)
         for (int d = 0; d < p.world; ++d) {
           uint4* dst = reinterpret_cast<uint4*>(p.slots[d] + size_t(LL_FIRST_SLOT + 2 * p.rank) * p.slot_stride) + ll_row + size_t(n0 >> 2) * BM;
@@ -1365,6 +1378,7 @@ static int gemm_impl(const void* x, const void* w, void* out, const void* bias, 
         rc->world + plan->k_splits <= LL_FIRST_SLOT && size_t(plan->tiles) * LL_TILE_WORDS <= rc->slot_stride / 2) {
       p.ll = 1;
       p.ll_epochs = static_cast<uint32_t*>(rc->ll_epochs);
+      p.mc_slots = static_cast<float*>(rc->mc_slots);
     }
   } else {
     if (!rc || !rc->status) return TPB_ERR_ARG;

@@ -50,6 +50,8 @@ typedef struct {
   int max_slots, max_tiles;
   void* ll_epochs;                // local uint32 [max_tiles], zero-initialised: epochs of the flagged-word exchange that small
                                   // cross-rank sums use (needs max_slots >= 32 + 2 * world); null selects arrival counters
+  void* mc_slots;                 // NVLink multicast alias of slots[*] (the same offsets reach every rank's workspace): the flagged
+                                  // words are then pushed with one multimem.st instead of one store per rank; null: peer stores
 } tpb_reduce_ctx_t;
 
 // Operands of the fused all-gather + GEMM (see tpb_gemm_allgather_bf16).

@@ -168,6 +168,11 @@ class RankComm:
         ctx.split_counters = self.split_counters.data_ptr() + region * MAX_TILES * 4
         ctx.status = self.status.data_ptr()
         ctx.ll_epochs = self.ll_epochs.data_ptr() + region * MAX_TILES * 4
+        # TPB_FUSED_MULTICAST=1: the flagged words of the fused GEMM + all-reduce go out through the multicast mapping (one
+        # multimem.st instead of one store per rank).  Off by default: at 4 ranks it measured slower than the peer stores
+        # (o_proj 13.8 vs 13.0 us, down_proj 18.3 vs 17.6 us, replayed from a CUDA graph); not measured at 8 ranks.
+        if self.mc_base and self.world >= 4 and os.environ.get("TPB_FUSED_MULTICAST", "0") == "1":
+            ctx.mc_slots = self.mc_base + self.layout.off_slots + region * self.layout.region_slot_bytes
         ctx.slot_stride = self.layout.slot_stride
         ctx.max_slots, ctx.max_tiles = self.layout.max_slots, MAX_TILES
         return ctx

@@ -45,7 +45,7 @@ class GemmPlan(ctypes.Structure):
 class ReduceCtx(ctypes.Structure):
     _fields_ = [("world", c_int), ("rank", c_int), ("slots", c_void_p * 8), ("arrivals", c_void_p * 8),
                 ("expected", c_void_p), ("split_counters", c_void_p), ("status", c_void_p), ("slot_stride", c_size_t), ("max_slots", c_int),
-                ("max_tiles", c_int), ("ll_epochs", c_void_p)]
+                ("max_tiles", c_int), ("ll_epochs", c_void_p), ("mc_slots", c_void_p)]
 
 
 class GemmOpts(ctypes.Structure):
