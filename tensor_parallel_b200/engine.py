@@ -220,7 +220,40 @@ class DecoderEngine:
     def stale(self) -> bool:
         """True when a tensor the serving layout was derived from has been written to since (an optimizer step, a
         ``load_state_dict``, a merged adapter): the engine must be rebuilt."""
+        if self._versions is None:  # the source weights were released: nothing left to watch
+            return False
         return tuple(t._version for t in self.spec.parameters()) != self._versions
+
+    def _own_tensors(self):
+        seen = [self.embed, self.embed_local, self.pos_embed, self.pos_local, self.lm_head, self.head_bias, self.head_rowsum]
+        for entry in self.layers:
+            seen.extend(entry.values())
+        return [t for t in seen if isinstance(t, torch.Tensor)]
+
+    @torch.no_grad()
+    def release_source_weights(self, shard) -> int:
+        """Serving only: frees every parameter of ``shard`` on this device whose values the engine holds in its own
+        layout (q / k / v behind the fused, norm-folded ``wqkv``; gate / up behind the interleaved ``w1``; the head behind
+        its folded copy ...) - about two thirds of a Llama shard.  Parameters the engine reads in place (row-parallel
+        output projections, the embedding table) stay.  Returns the bytes freed.  Afterwards the module can no longer run
+        ``forward()``, be trained or be saved, and the engine stops watching for weight updates."""
+        kept = {t.untyped_storage().data_ptr() for t in self._own_tensors()}
+        freed, seen = 0, set()
+        for param in engine_spec.unwrap(shard).parameters():
+            storage = param.untyped_storage()
+            if param.device != self.device or storage.data_ptr() in kept or storage.data_ptr() in seen:
+                continue
+            seen.add(storage.data_ptr())
+            freed += storage.nbytes()
+        # the description holds views of the same storages: drop them first, then the parameters' own references
+        self.spec.layers = []
+        self.spec.head_w = self.spec.final_ln_w = self.spec.final_ln_b = None
+        self._versions = None
+        for param in engine_spec.unwrap(shard).parameters():
+            if param.device == self.device and param.untyped_storage().data_ptr() in seen:
+                param.data = torch.empty(0, dtype=param.dtype, device=param.device)
+        torch.cuda.empty_cache()
+        return freed
 
     def _status_tensor(self):
         return self.comm.status if self.comm is not None else native.device_state(self.device).status

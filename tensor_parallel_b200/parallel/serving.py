@@ -44,6 +44,9 @@ class ServingMixin:
         fits = eng is not None and eng.max_batch >= max_batch and eng.max_seq >= max_seq
         if fits:
             return eng
+        if eng is not None and any(e._versions is None for e in getattr(eng, "engines", [eng])):
+            raise RuntimeError("the training-layout weights were released (release_training_weights): the engine cannot be "
+                               f"rebuilt for max_batch={max_batch}, max_seq={max_seq}; it serves up to {eng.max_batch} x {eng.max_seq}")
         if eng is not None:
             max_batch, max_seq = max(max_batch, eng.max_batch), max(max_seq, eng.max_seq)
         spec = engine_spec.describe(shard, max_seq)
@@ -72,6 +75,18 @@ class ServingMixin:
         self._engine = DecoderEngine(shard, comm if world > 1 else None, max_batch=max_batch, max_seq=max_seq, spec=spec,
                                      process_group=getattr(self, "process_group", None))
         return self._engine
+
+    def release_training_weights(self) -> int:
+        """Serving only: once the kernel-level engine exists, frees the parameters it holds in its own layout (see
+        ``DecoderEngine.release_source_weights``); returns the bytes freed on this process's devices.  The model then
+        serves through ``generate`` / ``prefill`` / ``decode_step`` only."""
+        eng = self._engine
+        if eng is None:
+            raise RuntimeError("build the engine first (serving_engine(), prefill() or generate())")
+        if getattr(self, "sharding_manager", None) is not None:
+            raise RuntimeError("a model created with sharded=True keeps training state in its parameters; nothing was released")
+        engines = getattr(eng, "engines", [eng])
+        return sum(e.release_source_weights(shard) for e, shard in zip(engines, self.module_shards))
 
     @torch.no_grad()
     def generate(self, input_ids: Optional[torch.Tensor] = None, max_new_tokens: int = 20, **kwargs):

@@ -185,3 +185,30 @@ def test_engine_is_rebuilt_after_a_weight_update():
     second = wrapped.prefill(ids, max_new_tokens=4)
     assert wrapped._engine is not engine
     assert (first - second).abs().max().item() > 1e-3
+
+
+def test_release_training_weights_keeps_serving_and_frees_memory():
+    """After ``release_training_weights()`` the engine answers exactly as before from its own layout, the parameters it
+    copied are gone from the device, the ones it reads in place are still there, and a rebuild is refused."""
+    import gc
+
+    _, model = _models(2)
+    wrapped = tp.tensor_parallel(model, ["cuda:0"])
+    ids = torch.randint(0, 1024, (2, 40), generator=torch.Generator().manual_seed(4))
+    before_logits = wrapped.prefill(ids, max_new_tokens=8).clone()
+    before_tokens = wrapped.generate(ids, max_new_tokens=6).clone()
+    gc.collect()
+    torch.cuda.synchronize()
+    allocated = torch.cuda.memory_allocated()
+    freed = wrapped.release_training_weights()
+    shard = wrapped.module_shards[0]
+    layer = shard.model.layers[0]
+    total = sum(p.numel() * 2 for p in _models(2)[1].parameters())
+    assert freed > 0.5 * total, (freed, total)                       # q / k / v, gate / up, norms, head
+    assert allocated - torch.cuda.memory_allocated() >= 0.9 * freed  # really returned to the allocator
+    assert layer.self_attn.q_proj.weight.numel() == 0 and layer.mlp.gate_proj.weight.numel() == 0
+    assert layer.self_attn.o_proj.weight.numel() > 0 and layer.mlp.down_proj.weight.numel() > 0  # read in place by the engine
+    torch.testing.assert_close(wrapped.prefill(ids, max_new_tokens=8), before_logits, atol=0, rtol=0)
+    assert torch.equal(wrapped.generate(ids, max_new_tokens=6), before_tokens)
+    with pytest.raises(RuntimeError, match="released"):
+        wrapped.serving_engine(max_batch=64, max_seq=8192)
