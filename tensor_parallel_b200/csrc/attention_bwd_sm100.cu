@@ -1,12 +1,14 @@
-// Attention backward for sm_100a on tcgen05 tensor cores (no score bias; calls with a bias use the kernels in
-// attention_bwd.cu).
+// Attention backward for sm_100a on tcgen05 tensor cores, with an optional additive score bias (scores = S * scale + bias;
+// d(bias) = P * (dP - delta), summed over whatever dimensions the bias broadcasts over, is added into an fp32 buffer by the
+// dQ launch, which visits every (query, key) pair exactly once).
 //
 //   P  = exp(S * scale - lse)          S  = Q K^T
 //   dV = P^T dO                        dP = dO V^T
 //   dS = P * (dP - delta) * scale      delta[i] = sum_d out[i, d] * dout[i, d]
 //   dQ = dS K                          dK = dS^T Q
 //
-// Two launches of ONE kernel template, both free of atomics and therefore deterministic.  A CTA keeps 128 "resident"
+// Two launches of ONE kernel template, both free of atomics and therefore deterministic (the optional bias gradient is the
+// exception: fp32 atomic adds).  A CTA keeps 128 "resident"
 // rows (the TMEM lanes) and streams the other sequence through in steps of 64 rows (TMEM columns):
 //
 //   dK / dV (DKV = true) : resident = 128 keys of one KV head (K and V tiles), streamed = queries (Q and dO, over all
@@ -58,10 +60,15 @@ struct BwParams {
   long long o0_sb, o0_ss, o0_sh;
   bf16* out1;          // dV (DKV)
   long long o1_sb, o1_ss, o1_sh;
+  const void* bias;    // additive score bias in natural-log units over (batch, head, query, key), element strides, 0 broadcasts
+  int bias_kind;       // 0 none, 1 fp32, 2 bf16
+  long long b_sb, b_sh, b_sq, b_sk;
+  float* dbias;        // fp32, the bias' own strides, zero-initialised by the caller; written by the dQ launch only (or null)
+  float inv_scale;
   uint32_t* status;
 };
 
-template <int D, bool DKV>
+template <int D, bool DKV, bool BIAS>  // BIAS: the score-bias code exists only in the instantiations that need it
 __global__ void __launch_bounds__(BW_THREADS, 1)
 attn_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_r1, const __grid_constant__ CUtensorMap tmap_r2,
                         const __grid_constant__ CUtensorMap tmap_t1, const __grid_constant__ CUtensorMap tmap_t2, const BwParams p) {
@@ -299,6 +306,13 @@ attn_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_r1, const __gri
         hi = min(HC, min(p.sk, p.causal ? ri + shift + 1 : p.sk) - col0);  // key <= query + shift
       }
       const bool masked = lo > 0 || hi < HC;
+      // score bias: element (query, key) = (col0 + c, ri) for dK / dV and (ri, col0 + c) for dQ
+      const float* bias_f = static_cast<const float*>(p.bias);
+      const bf16* bias_h = static_cast<const bf16*>(p.bias);
+      const int b_head = DKV ? head + g : head;
+      const long long bias_base = BIAS ? (long long)b * p.b_sb + (long long)b_head * p.b_sh + (long long)ri * (DKV ? p.b_sk : p.b_sq) : 0;
+      const long long bias_step = DKV ? p.b_sq : p.b_sk;  // per column
+      const int col_limit = DKV ? p.sq : p.sk, row_limit = DKV ? p.sk : p.sq;
       uint32_t pp[HC / 2], ds[HC / 2];
 #pragma unroll
       for (int c = 0; c < HC; c += 2) {
@@ -313,6 +327,16 @@ attn_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_r1, const __gri
         }
         float x0, x1, p0, p1, g0, g1;
         ffma2(x0, x1, __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]), p.scale_log2e, p.scale_log2e, -l0, -l1);
+        long long bi0 = 0, bi1 = 0;
+        if (BIAS) {
+          bi0 = bias_base + (long long)(col0 + c) * bias_step;
+          bi1 = bi0 + bias_step;
+          const bool in0 = ri < row_limit && col0 + c < col_limit, in1 = ri < row_limit && col0 + c + 1 < col_limit;
+          const float b0 = !in0 ? 0.f : (p.bias_kind == 1 ? __ldg(bias_f + bi0) : __bfloat162float(bias_h[bi0]));
+          const float b1 = !in1 ? 0.f : (p.bias_kind == 1 ? __ldg(bias_f + bi1) : __bfloat162float(bias_h[bi1]));
+          x0 += b0 * 1.4426950408889634f;
+          x1 += b1 * 1.4426950408889634f;
+        }
         p0 = ex2_approx(x0);
         p1 = ex2_approx(x1);
         if (masked) {
@@ -321,6 +345,10 @@ attn_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_r1, const __gri
         }
         ffma2(g0, g1, __uint_as_float(dv[c]), __uint_as_float(dv[c + 1]), p.scale, p.scale, -d0, -d1);  // (dP - delta) * scale
         ffma2(g0, g1, g0, g1, p0, p1, 0.f, 0.f);
+        if (BIAS && !DKV && p.dbias) {  // d(bias) = P (dP - delta) = dS / scale; pairs that are masked or out of range contribute nothing
+          if (p0 != 0.f && ri < row_limit && col0 + c < col_limit) atomicAdd(p.dbias + bi0, g0 * p.inv_scale);
+          if (p1 != 0.f && ri < row_limit && col0 + c + 1 < col_limit) atomicAdd(p.dbias + bi1, g1 * p.inv_scale);
+        }
         if (DKV) pp[c >> 1] = pack_bf16x2(p0, p1);
         ds[c >> 1] = pack_bf16x2(g0, g1);
       }
@@ -388,7 +416,7 @@ attn_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_r1, const __gri
   if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
-template <int D, bool DKV>
+template <int D, bool DKV, bool BIAS>
 static int bw_launch(const CUtensorMap& r1, const CUtensorMap& r2, const CUtensorMap& t1, const CUtensorMap& t2, const BwParams& p, dim3 grid,
                      cudaStream_t stream) {
   constexpr size_t smem = size_t(D / 64) * (2 * FA_BLOCK_BYTES + 2 * BW_STAGES * BW_T_BLOCK_BYTES) + 2 * BW_STAGES * BW_T * sizeof(float) + 1024 + 256;
@@ -396,11 +424,11 @@ static int bw_launch(const CUtensorMap& r1, const CUtensorMap& r2, const CUtenso
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return TPB_ERR_CUDA;
   if (!configured[dev].load(std::memory_order_acquire)) {
-    if (cudaFuncSetAttribute(attn_bwd_tcgen05_kernel<D, DKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess)
+    if (cudaFuncSetAttribute(attn_bwd_tcgen05_kernel<D, DKV, BIAS>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess)
       return TPB_ERR_CUDA;
     configured[dev].store(true, std::memory_order_release);
   }
-  attn_bwd_tcgen05_kernel<D, DKV><<<grid, BW_THREADS, smem, stream>>>(r1, r2, t1, t2, p);
+  attn_bwd_tcgen05_kernel<D, DKV, BIAS><<<grid, BW_THREADS, smem, stream>>>(r1, r2, t1, t2, p);
   return cudaGetLastError() == cudaSuccess ? TPB_OK : TPB_ERR_CUDA;
 }
 
@@ -408,7 +436,8 @@ static int bw_launch(const CUtensorMap& r1, const CUtensorMap& r2, const CUtenso
 
 using namespace tpb;
 
-// Same contract as tpb_attn_backward (strides in elements, head_dim contiguous; `delta` is a [batch][q_heads][sq] fp32
+// Same contract as tpb_attn_backward_bias (strides in elements, head_dim contiguous; bias strides of 0 broadcast; dbias is fp32 with
+// the bias' strides, zero-initialised; `delta` is a [batch][q_heads][sq] fp32
 // scratch buffer this call fills) plus: every stride of q / k / v / dout must be a multiple of 8 elements and their bases
 // 16-byte aligned (TMA); `status` is a device word that receives a non-zero code if a wait inside a kernel ran out of time.
 extern "C" int tpb_attn_backward_sm100(const void* q, const void* k, const void* v, const void* out, const void* dout, const float* lse,
@@ -417,11 +446,13 @@ extern "C" int tpb_attn_backward_sm100(const void* q, const void* k, const void*
                                        long long k_sh, long long v_sb, long long v_ss, long long v_sh, long long o_sb, long long o_ss,
                                        long long o_sh, long long do_sb, long long do_ss, long long do_sh, long long dq_sb, long long dq_ss,
                                        long long dq_sh, long long dk_sb, long long dk_ss, long long dk_sh, int causal, float scale,
-                                       void* status, void* stream_) {
+                                       const void* bias, int bias_dtype, long long bias_sb, long long bias_sh, long long bias_sq,
+                                       long long bias_sk, float* dbias, void* status, void* stream_) {
   if (!q || !k || !v || !out || !dout || !lse || !delta || !dq || !dk || !dv || !status || batch <= 0 || sq <= 0 || sk <= 0 || q_heads <= 0 ||
       kv_heads <= 0 || q_heads % kv_heads)
     return TPB_ERR_ARG;
   if (head_dim != 64 && head_dim != 128) return TPB_ERR_SIZE;
+  if ((bias && bias_dtype != 0 && bias_dtype != 1) || (dbias && !bias) || (bias && !(scale > 0.f))) return TPB_ERR_ARG;
   const long long strides[] = {q_ss, k_ss, v_ss, do_ss, q_heads > 1 ? q_sh : 0, q_heads > 1 ? do_sh : 0, kv_heads > 1 ? k_sh : 0,
                                kv_heads > 1 ? v_sh : 0, batch > 1 ? q_sb : 0, batch > 1 ? k_sb : 0, batch > 1 ? v_sb : 0, batch > 1 ? do_sb : 0};
   for (long long s : strides)
@@ -450,14 +481,26 @@ extern "C" int tpb_attn_backward_sm100(const void* q, const void* k, const void*
   p.lse = lse;
   p.delta = delta;
   p.status = static_cast<uint32_t*>(status);
+  p.bias = bias;
+  p.bias_kind = !bias ? 0 : (bias_dtype == 1 ? 1 : 2);
+  p.b_sb = bias_sb; p.b_sh = bias_sh; p.b_sq = bias_sq; p.b_sk = bias_sk;
+  p.dbias = nullptr;  // (the dK / dV launch leaves it alone)
+  p.inv_scale = scale > 0.f ? 1.f / scale : 0.f;
   // dK / dV: the dk strides serve dv too (the existing contract)
   p.out0 = static_cast<bf16*>(dk); p.o0_sb = dk_sb; p.o0_ss = dk_ss; p.o0_sh = dk_sh;
   p.out1 = static_cast<bf16*>(dv); p.o1_sb = dk_sb; p.o1_ss = dk_ss; p.o1_sh = dk_sh;
   dim3 grid_kv((sk + BW_R - 1) / BW_R, kv_heads, batch);
-  rc = head_dim == 128 ? bw_launch<128, true>(k128, v128, q64, do64, p, grid_kv, s) : bw_launch<64, true>(k128, v128, q64, do64, p, grid_kv, s);
+  const bool with_bias = bias != nullptr;
+  if (head_dim == 128)
+    rc = with_bias ? bw_launch<128, true, true>(k128, v128, q64, do64, p, grid_kv, s) : bw_launch<128, true, false>(k128, v128, q64, do64, p, grid_kv, s);
+  else
+    rc = with_bias ? bw_launch<64, true, true>(k128, v128, q64, do64, p, grid_kv, s) : bw_launch<64, true, false>(k128, v128, q64, do64, p, grid_kv, s);
   if (rc != TPB_OK) return rc;
   p.out0 = static_cast<bf16*>(dq); p.o0_sb = dq_sb; p.o0_ss = dq_ss; p.o0_sh = dq_sh;
   p.out1 = nullptr;
+  p.dbias = dbias;
   dim3 grid_q((sq + BW_R - 1) / BW_R, q_heads, batch);
-  return head_dim == 128 ? bw_launch<128, false>(q128, do128, k64, v64, p, grid_q, s) : bw_launch<64, false>(q128, do128, k64, v64, p, grid_q, s);
+  if (head_dim == 128)
+    return with_bias ? bw_launch<128, false, true>(q128, do128, k64, v64, p, grid_q, s) : bw_launch<128, false, false>(q128, do128, k64, v64, p, grid_q, s);
+  return with_bias ? bw_launch<64, false, true>(q128, do128, k64, v64, p, grid_q, s) : bw_launch<64, false, false>(q128, do128, k64, v64, p, grid_q, s);
 }

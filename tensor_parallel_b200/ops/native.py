@@ -568,7 +568,7 @@ def attention_forward(q, k, v, causal, scale, want_lse=False, bias=None, out=Non
 
 LIB.tpb_attn_backward.argtypes = [c_void_p] * 10 + [c_int] * 6 + [c_ll] * 21 + [c_int, c_float, c_void_p]
 LIB.tpb_attn_backward_bias.argtypes = [c_void_p] * 10 + [c_int] * 6 + [c_ll] * 21 + [c_int, c_float, c_void_p, c_int] + [c_ll] * 4 + [c_void_p, c_void_p]
-LIB.tpb_attn_backward_sm100.argtypes = [c_void_p] * 10 + [c_int] * 6 + [c_ll] * 21 + [c_int, c_float, c_void_p, c_void_p]
+LIB.tpb_attn_backward_sm100.argtypes = [c_void_p] * 10 + [c_int] * 6 + [c_ll] * 21 + [c_int, c_float, c_void_p, c_int] + [c_ll] * 4 + [c_void_p, c_void_p, c_void_p]
 
 
 def _bias_view(bias):
@@ -589,17 +589,6 @@ def attention_backward(q, k, v, out, dout, lse, causal, scale, bias=None, want_d
     dv = torch.empty(b, sk, hkv, d, dtype=q.dtype, device=q.device)
     delta = torch.empty(b, hq, sq, dtype=torch.float32, device=q.device)
     scale = 1.0 / math.sqrt(d) if scale is None else scale
-    if bias is None and not _LEGACY_ATTENTION:  # tcgen05 kernels (two launches of one template) + the delta kernel
-        status = device_state(q.device).status
-        check(LIB.tpb_attn_backward_sm100(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(dout), _ptr(lse), _ptr(delta), _ptr(dq), _ptr(dk), _ptr(dv),
-                                          b, sq, sk, hq, hkv, d,
-                                          q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
-                                          v.stride(0), v.stride(1), v.stride(2), out.stride(0), out.stride(1), out.stride(2),
-                                          dout.stride(0), dout.stride(1), dout.stride(2), dq.stride(0), dq.stride(1), dq.stride(2),
-                                          dk.stride(0), dk.stride(1), dk.stride(2), int(causal), scale, _ptr(status), _stream()),
-              "tpb_attn_backward_sm100")
-        launch_count += 3
-        return dq, dk, dv
     bias4, bstr, dbias = None, [0, 0, 0, 0], None
     if bias is not None:
         bias4, bstr = _bias_view(bias)
@@ -609,13 +598,28 @@ def attention_backward(q, k, v, out, dout, lse, causal, scale, bias=None, want_d
             if dstr != bstr:  # a non-contiguous bias view: keep one addressing for both
                 bias4 = bias4.contiguous()
                 bstr = dstr
+    bias_is_fp32 = 1 if (bias4 is not None and bias4.dtype == torch.float32) else 0
+    if not _LEGACY_ATTENTION:  # tcgen05 kernels (two launches of one template) + the delta kernel
+        status = device_state(q.device).status
+        check(LIB.tpb_attn_backward_sm100(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(dout), _ptr(lse), _ptr(delta), _ptr(dq), _ptr(dk), _ptr(dv),
+                                          b, sq, sk, hq, hkv, d,
+                                          q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
+                                          v.stride(0), v.stride(1), v.stride(2), out.stride(0), out.stride(1), out.stride(2),
+                                          dout.stride(0), dout.stride(1), dout.stride(2), dq.stride(0), dq.stride(1), dq.stride(2),
+                                          dk.stride(0), dk.stride(1), dk.stride(2), int(causal), scale, _ptr(bias4), bias_is_fp32,
+                                          bstr[0], bstr[1], bstr[2], bstr[3], _ptr(dbias), _ptr(status), _stream()),
+              "tpb_attn_backward_sm100")
+        launch_count += 3
+        if want_dbias:
+            return dq, dk, dv, dbias.reshape(bias.shape)
+        return dq, dk, dv
     check(LIB.tpb_attn_backward_bias(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(dout), _ptr(lse), _ptr(delta), _ptr(dq), _ptr(dk), _ptr(dv),
                                      b, sq, sk, hq, hkv, d,
                                      q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
                                      v.stride(0), v.stride(1), v.stride(2), out.stride(0), out.stride(1), out.stride(2),
                                      dout.stride(0), dout.stride(1), dout.stride(2), dq.stride(0), dq.stride(1), dq.stride(2),
                                      dk.stride(0), dk.stride(1), dk.stride(2), int(causal), scale, _ptr(bias4),
-                                     1 if (bias4 is not None and bias4.dtype == torch.float32) else 0, bstr[0], bstr[1], bstr[2], bstr[3],
+                                     bias_is_fp32, bstr[0], bstr[1], bstr[2], bstr[3],
                                      _ptr(dbias), _stream()), "tpb_attn_backward")
     launch_count += 3
     if want_dbias:
